@@ -1,0 +1,420 @@
+"""Host-side mirror of the reference's operator interface for the trie-walk hot path.
+
+Everything here forwards to the C ABI in ``libagpt_b200.so``; torch supplies device
+memory and streams only.  Names follow the reference: a *trie* (radix, with edges), its
+*char positions*, a *walker plan* over the char tree, the per-subtree *KV store*, and the
+legacy ``cuda_batched_varlen_attention*`` kernels.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+import os
+
+import numpy as np
+
+from ._lib import AgptError, PlanInfo, TrieInfo, check, lib
+
+KV_F32, KV_BF16 = 0, 1
+
+
+def _np_i32(a):
+    return np.ascontiguousarray(a, dtype=np.int32)
+
+
+def _vp(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _view(ptr, n, dtype):
+    if n == 0:
+        return np.zeros(0, dtype=dtype)
+    return np.ctypeslib.as_array(ptr, shape=(int(n),))
+
+
+# ----------------------------------------------------------------------------------------
+# synthetic workloads
+# ----------------------------------------------------------------------------------------
+def synth_markov_corpus(n: int, vocab: int, order: int, seed: int = 0) -> np.ndarray:
+    out = np.zeros(n, np.int32)
+    check(lib().agpt_b200_synth_markov_corpus(n, vocab, order, seed, _vp(out)), "synth_markov_corpus")
+    return out
+
+
+def synth_tree(max_nodes: int, max_depth: int = 64, root_children: int = 65, p_stop: float = 0.35,
+               max_children: int = 65, level_cap: int = 75_000, seed: int = 0) -> np.ndarray:
+    """Parent array (breadth-first ids, -1 under the root) of the attention microbenchmark tree."""
+    out = np.zeros(max_nodes, np.int32)
+    n = check(lib().agpt_b200_synth_tree(max_nodes, max_depth, root_children, p_stop, max_children, level_cap,
+                                         seed, _vp(out)), "synth_tree")
+    return out[:n].copy()
+
+
+# ----------------------------------------------------------------------------------------
+# radix trie
+# ----------------------------------------------------------------------------------------
+class RadixTrie:
+    """Radix trie with the reference's node numbering, counts, edge mass and char positions."""
+
+    def __init__(self, handle):
+        self._h = handle
+        info = TrieInfo()
+        check(lib().agpt_b200_trie_info(handle, C.byref(info)), "trie_info")
+        R = info.radix_count
+        self.radix_count, self.n_depth_files = R, info.n_depth_files
+        self.total_edge_chars = int(info.total_edge_chars)
+        self.leveled_nodes = int(info.leveled_nodes)
+        for name in ("parent", "first_char_depth", "edge_len", "edge_mass", "endpoint_depth", "subtree_key",
+                     "edge_start"):
+            setattr(self, name, _view(getattr(info, name), R, np.int32))
+        self.edge_off = _view(info.edge_off, R + 1, np.int64)
+        self.edge_tok = _view(info.edge_tok, self.total_edge_chars, np.int32)
+        self.cnt_off = _view(info.cnt_off, R + 1, np.int64)
+        self.cnt_tok = _view(info.cnt_tok, info.total_counts, np.int32)
+        self.cnt_val = _view(info.cnt_val, info.total_counts, np.int32)
+
+    @classmethod
+    def build(cls, corpus, max_depth: int, subtree_level: int = 1, prune_min_mass: int = 1,
+              prune_min_depth: int = 4) -> "RadixTrie":
+        c = _np_i32(corpus)
+        h = C.c_void_p()
+        check(lib().agpt_b200_trie_build(_vp(c), c.size, max_depth, subtree_level, prune_min_mass, prune_min_depth,
+                                         C.byref(h)), "trie_build")
+        return cls(h)
+
+    @classmethod
+    def load_dir(cls, path: str) -> "RadixTrie":
+        h = C.c_void_p()
+        check(lib().agpt_b200_trie_load_dir(path.encode(), C.byref(h)), "trie_load_dir")
+        return cls(h)
+
+    def save_dir(self, path: str, corpus_tokens: int, vocab: int, corpus_hash: int,
+                 tag: str = "char.sorted_unique.v1", per_subtree: bool = False):
+        os.makedirs(path, exist_ok=True)
+        if per_subtree:
+            os.makedirs(os.path.join(path, "subtrees"), exist_ok=True)
+        check(lib().agpt_b200_trie_save_dir(self._h, path.encode(), int(per_subtree), corpus_tokens, vocab,
+                                            corpus_hash, tag.encode()), "trie_save_dir")
+
+    def char_tree(self):
+        """(parent, token, depth, radix_of_char) per char position, trainer numbering."""
+        n = self.total_edge_chars
+        out = [np.zeros(n, np.int32) for _ in range(4)]
+        check(lib().agpt_b200_trie_char_tree(self._h, *[_vp(a) for a in out]), "trie_char_tree")
+        return tuple(out)
+
+    def close(self):
+        if self._h is not None:
+            lib().agpt_b200_trie_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def token_hash(tokens) -> int:
+    t = _np_i32(tokens)
+    return int(lib().agpt_b200_token_hash(_vp(t), t.size))
+
+
+# ----------------------------------------------------------------------------------------
+# walker plan
+# ----------------------------------------------------------------------------------------
+class WalkerPlan:
+    """Depth-first layout of a tree plus the tile index the attention kernels walk."""
+
+    def __init__(self, parent, tile_m: int = 64, device: int = -1):
+        par = _np_i32(parent)
+        h = C.c_void_p()
+        check(lib().agpt_b200_plan_create(_vp(par), par.size, tile_m, device, C.byref(h)), "plan_create")
+        self._h = h
+        info = PlanInfo()
+        check(lib().agpt_b200_plan_info(h, C.byref(info)), "plan_info")
+        self.info = info
+        n = int(info.n)
+        self.n, self.tile_m, self.n_tiles = n, info.tile_m, int(info.n_tiles)
+        self.max_depth, self.sum_depth = info.max_depth, int(info.sum_depth)
+        self.sum_group_prefix, self.n_groups = int(info.sum_group_prefix), int(info.n_groups)
+        self.chain_rows = int(info.chain_rows)
+        self.dfs_to_node = _view(info.dfs_to_node, n, np.int32)
+        self.node_to_dfs = _view(info.node_to_dfs, n, np.int32)
+        self.parent_dfs = _view(info.parent_dfs, n, np.int32)
+        self.depth = _view(info.depth, n, np.int32)
+        self.sub_end = _view(info.sub_end, n, np.int32)
+        self.device = info.device
+
+    def workspace_bytes(self, d_model: int) -> int:
+        return check(lib().agpt_b200_attn_bwd_workspace_bytes(self._h, d_model), "attn_bwd_workspace_bytes")
+
+    def units(self, level: int = 1):
+        """Root-child (level 1) or bigram (level 2) units as depth-first [begin, end) ranges."""
+        cnt = check(lib().agpt_b200_plan_units(self._h, level, 0, None, None), "plan_units")
+        b = np.zeros(cnt, np.int64)
+        e = np.zeros(cnt, np.int64)
+        check(lib().agpt_b200_plan_units(self._h, level, cnt, _vp(b), _vp(e)), "plan_units")
+        return b, e
+
+    def algorithmic_bytes(self, d_model: int, n_heads: int, kv_bytes: int = 4):
+        """Bytes of the sibling-group-shared traffic model for one forward+backward of one layer:
+        each sibling group reads its parent's ancestor chain once per direction and every per-node
+        tensor is read or written once."""
+        D, H, b, N = d_model, n_heads, kv_bytes, self.n
+        fwd = self.sum_group_prefix * 2 * D * b + N * (D * 4 + 2 * D * b + D * 4 + H * 4)
+        bwd = self.sum_group_prefix * 2 * D * b + N * (3 * D * 4 + 2 * H * 4 + 2 * D * b + D * 4 + 2 * D * 4)
+        return fwd, bwd
+
+    def close(self):
+        if self._h is not None:
+            lib().agpt_b200_plan_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def partition_lpt(unit_weight, n_ranks: int) -> np.ndarray:
+    w = np.ascontiguousarray(unit_weight, dtype=np.int64)
+    out = np.zeros(w.size, np.int32)
+    check(lib().agpt_b200_partition_lpt(_vp(w), w.size, n_ranks, _vp(out)), "partition_lpt")
+    return out
+
+
+def shard_tree(parent, rank: int, n_ranks: int, level: int = 2):
+    """Nodes of `rank`'s share of a tree partitioned by root-child (level 1) or bigram (level 2)
+    subtree, longest-processing-time balanced on unit size.  Returns (local_parent, node_ids,
+    is_context): the sub-forest's parent array, the original ids of its nodes, and a mask of
+    context-only rows (a depth-1 ancestor kept so its descendants' chains stay complete while the
+    node itself is trained by another rank)."""
+    parent = _np_i32(parent)
+    plan = WalkerPlan(parent, 64, -1)
+    ub, ue = plan.units(level)
+    owner = partition_lpt(ue - ub, n_ranks)
+    mine = np.zeros(plan.n, bool)
+    for b, e, o in zip(ub, ue, owner):
+        if o == rank:
+            mine[b:e] = True
+    ctx = np.zeros(plan.n, bool)
+    if level == 2:
+        # depth-1 ancestors of owned depth>=2 rows ride along as context
+        pos = np.nonzero(mine)[0]
+        if pos.size:
+            d1 = pos.copy()
+            # walk up to depth 1 using subtree intervals: depth-1 ancestor = last depth-1 start <= pos
+            starts = np.nonzero(plan.depth == 1)[0]
+            d1 = starts[np.searchsorted(starts, pos, side="right") - 1]
+            need = np.unique(d1)
+            ctx[need[~mine[need]]] = True
+    keep = mine | ctx
+    pos = np.nonzero(keep)[0]
+    remap = np.full(plan.n, -1, np.int64)
+    remap[pos] = np.arange(pos.size)
+    pp = plan.parent_dfs[pos]
+    local_parent = np.where(pp < 0, -1, remap[np.maximum(pp, 0)]).astype(np.int32)
+    node_ids = plan.dfs_to_node[pos].copy()
+    return local_parent, node_ids, ctx[pos].copy()
+
+
+# ----------------------------------------------------------------------------------------
+# device entry points (torch tensors on the plan's device)
+# ----------------------------------------------------------------------------------------
+def _stream():
+    import torch
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dp(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _chk_f32(t, name):
+    import torch
+    if t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous():
+        raise AgptError(f"{name} must be a contiguous float32 CUDA tensor")
+
+
+def gather_rows(src, index):
+    import torch
+    _chk_f32(src, "src")
+    out = torch.empty((index.numel(), src.shape[1]), dtype=torch.float32, device=src.device)
+    check(lib().agpt_b200_gather_rows(_dp(src), _dp(index), _dp(out), index.numel(), src.shape[1], _stream()),
+          "gather_rows")
+    return out
+
+
+def rope_table(max_seq: int, head_dim: int, base: float = 10000.0):
+    """cos/sin tables [max_seq, head_dim] in float32 arithmetic, pair-duplicated like the reference's
+    build_rope_cache (theta = pos / base^(2i/dim) with float32 pow, cos, sin)."""
+    half = head_dim // 2
+    i = np.arange(half, dtype=np.float32)
+    expo = (np.float32(2.0) * i) / np.float32(head_dim)
+    denom = np.power(np.float32(base), expo, dtype=np.float32)
+    theta = (np.arange(max_seq, dtype=np.float32)[:, None] / denom[None, :]).astype(np.float32)
+    c = np.repeat(np.cos(theta, dtype=np.float32), 2, axis=1)
+    s = np.repeat(np.sin(theta, dtype=np.float32), 2, axis=1)
+    return np.ascontiguousarray(c), np.ascontiguousarray(s)
+
+
+def rope_(x, pos, cos, sin, n_heads: int, inverse: bool = False):
+    """Rotate x [n, n_heads*head_dim] in place by per-row positions."""
+    _chk_f32(x, "x")
+    hd = x.shape[1] // n_heads
+    check(lib().agpt_b200_rope(_dp(x), _dp(pos), _dp(cos), _dp(sin), x.shape[0], n_heads, hd, int(inverse), _stream()),
+          "rope")
+    return x
+
+
+def kv_store_write_bf16(src):
+    import torch
+    _chk_f32(src, "src")
+    out = torch.empty(src.shape, dtype=torch.bfloat16, device=src.device)
+    check(lib().agpt_b200_kv_store_write_bf16(_dp(src), _dp(out), src.shape[0], src.shape[1], _stream()),
+          "kv_store_write_bf16")
+    return out
+
+
+def _kv_dtype(k):
+    import torch
+    if k.dtype == torch.float32:
+        return KV_F32
+    if k.dtype == torch.bfloat16:
+        return KV_BF16
+    raise AgptError("KV store must be float32 or bfloat16")
+
+
+def attn_forward(plan: WalkerPlan, q, k, v, n_heads: int, scale: float | None = None, out=None, lse=None):
+    import torch
+    _chk_f32(q, "q")
+    n, D = q.shape
+    hd = D // n_heads
+    scale = 1.0 / math.sqrt(hd) if scale is None else scale
+    out = torch.empty_like(q) if out is None else out
+    lse = torch.empty((n, n_heads), dtype=torch.float32, device=q.device) if lse is None else lse
+    check(lib().agpt_b200_attn_fwd(plan._h, _dp(q), _dp(k), _dp(v), _kv_dtype(k), _dp(out), _dp(lse), n_heads, hd,
+                                   scale, _stream()), "attn_fwd")
+    return out, lse
+
+
+def attn_backward(plan: WalkerPlan, q, k, v, out, lse, dout, n_heads: int, scale: float | None = None,
+                  workspace=None, dq=None, dk=None, dv=None):
+    import torch
+    _chk_f32(q, "q")
+    _chk_f32(dout, "dout")
+    n, D = q.shape
+    hd = D // n_heads
+    scale = 1.0 / math.sqrt(hd) if scale is None else scale
+    if workspace is None:
+        workspace = torch.empty(plan.workspace_bytes(D), dtype=torch.uint8, device=q.device)
+    dq = torch.empty_like(q) if dq is None else dq
+    dk = torch.empty_like(q) if dk is None else dk
+    dv = torch.empty_like(q) if dv is None else dv
+    check(lib().agpt_b200_attn_bwd(plan._h, _dp(q), _dp(k), _dp(v), _kv_dtype(k), _dp(out), _dp(lse), _dp(dout),
+                                   _dp(dq), _dp(dk), _dp(dv), _dp(workspace), workspace.numel(), n_heads, hd, scale,
+                                   _stream()), "attn_bwd")
+    return dq, dk, dv
+
+
+def attn_fwd_bwd_host(plan: WalkerPlan, q, k, v, dout, n_heads: int, kv_dtype: int = KV_F32, scale=None,
+                      outs=None):
+    """Host-buffer step: numpy float32 arrays in and out."""
+    n, D = q.shape
+    hd = D // n_heads
+    scale = 1.0 / math.sqrt(hd) if scale is None else scale
+    if outs is None:
+        outs = [np.empty((n, D), np.float32), np.empty((n, n_heads), np.float32)] + \
+               [np.empty((n, D), np.float32) for _ in range(3)]
+    o, lse, dq, dk, dv = outs
+    check(lib().agpt_b200_attn_fwd_bwd_host(plan._h, _vp(q), _vp(k), _vp(v), _vp(dout), _vp(o), _vp(lse), _vp(dq),
+                                            _vp(dk), _vp(dv), kv_dtype, n_heads, hd, scale), "attn_fwd_bwd_host")
+    return o, lse, dq, dk, dv
+
+
+def loss_per_query(logits, query_to_node, query_offsets, radix_ids, token_ids, counts_offset, counts_tok,
+                   counts_val, mass_weights=None, entropy_lambda: float = 0.0, intermediate_weight: float = 1.0,
+                   ce_only: bool = False):
+    import torch
+    _chk_f32(logits, "logits")
+    T, V = logits.shape
+    g = torch.empty_like(logits)
+    loss = torch.empty(T, dtype=torch.float32, device=logits.device)
+    check(lib().agpt_b200_loss_per_query(_dp(logits), _dp(query_to_node), _dp(query_offsets), _dp(radix_ids),
+                                         _dp(token_ids), _dp(counts_offset), _dp(counts_tok), _dp(counts_val),
+                                         _dp(mass_weights), _dp(g), _dp(loss), T, V, entropy_lambda,
+                                         intermediate_weight, int(ce_only), _stream()), "loss_per_query")
+    return loss, g
+
+
+def loss_per_node(logits, node_ids, counts_offset, counts_tok, counts_val):
+    import torch
+    _chk_f32(logits, "logits")
+    N, V = logits.shape
+    g = torch.empty_like(logits)
+    loss = torch.empty(N, dtype=torch.float32, device=logits.device)
+    check(lib().agpt_b200_loss_per_node(_dp(logits), _dp(node_ids), _dp(counts_offset), _dp(counts_tok),
+                                        _dp(counts_val), _dp(g), _dp(loss), N, V, _stream()), "loss_per_node")
+    return loss, g
+
+
+def mass_weights(edge_mass, edge_len, mode: str = "linear") -> np.ndarray:
+    """Per-query mass weights of one chunk: f(edge_mass) / mean over the chunk's queries
+    (float32 arithmetic with a float64 running total, like the reference's host loop)."""
+    em = np.asarray(edge_mass, dtype=np.float32)
+    el = np.asarray(edge_len, dtype=np.int64)
+    if mode == "log":
+        w = np.log(np.float32(1.0) + em, dtype=np.float32)
+    elif mode == "sqrt":
+        w = np.sqrt(em, dtype=np.float32)
+    elif mode == "linear":
+        w = em
+    else:
+        w = np.ones_like(em)
+    tq = int(el.sum())
+    mean = np.float32((w.astype(np.float64) * el).sum() / tq) if tq > 0 else np.float32(1.0)
+    if mean <= 0:
+        mean = np.float32(1.0)
+    return np.repeat((w / mean).astype(np.float32), el)
+
+
+# legacy kernel boundary -------------------------------------------------------------------
+def legacy_attention(q, k, v, kv_offsets, kv_lengths, n_heads, head_dim, max_len, scale, query_to_node=None,
+                     query_offsets=None):
+    import torch
+    T = q.numel() // (n_heads * head_dim)
+    out = torch.empty(T * n_heads * head_dim, dtype=torch.float32, device=q.device)
+    w = torch.empty(T * n_heads * max_len, dtype=torch.float32, device=q.device)
+    if query_to_node is None:
+        lib().cuda_batched_varlen_attention(_dp(q), _dp(k), _dp(v), _dp(kv_offsets), _dp(kv_lengths), _dp(out), _dp(w),
+                                            T, n_heads, head_dim, max_len, scale)
+    else:
+        lib().cuda_batched_varlen_attention_L_queries(_dp(q), _dp(k), _dp(v), _dp(query_to_node), _dp(query_offsets),
+                                                      _dp(kv_offsets), _dp(kv_lengths), _dp(out), _dp(w), T, n_heads,
+                                                      head_dim, max_len, scale)
+    lib().cuda_sync()
+    return out, w
+
+
+def legacy_attention_backward(q, k, v, w, d_out, kv_offsets, kv_lengths, n_heads, head_dim, max_len, scale,
+                              query_to_node=None, query_offsets=None):
+    import torch
+    T = q.numel() // (n_heads * head_dim)
+    dq = torch.empty_like(q)
+    if query_to_node is None:
+        dk = torch.empty_like(k)
+        dv = torch.empty_like(v)
+        lib().cuda_batched_varlen_attention_backward(_dp(q), _dp(k), _dp(v), _dp(w), _dp(d_out), _dp(kv_offsets),
+                                                     _dp(kv_lengths), _dp(dq), _dp(dk), _dp(dv), T, n_heads, head_dim,
+                                                     max_len, scale)
+    else:
+        dk = torch.zeros_like(k)
+        dv = torch.zeros_like(v)
+        lib().cuda_batched_varlen_attention_L_queries_backward(_dp(q), _dp(k), _dp(v), _dp(w), _dp(d_out),
+                                                               _dp(query_to_node), _dp(query_offsets), _dp(kv_offsets),
+                                                               _dp(kv_lengths), _dp(dq), _dp(dk), _dp(dv), T, n_heads,
+                                                               head_dim, max_len, scale)
+    lib().cuda_sync()
+    return dq, dk, dv

@@ -1,0 +1,38 @@
+// Shared between the host walker code and the CUDA translation unit of libagpt_b200.
+#pragma once
+#include <cstdint>
+#include <vector>
+
+#define AGPT_REDUCE_SEG 128   // tiles summed by one warp of the dK/dV reduction before a second pass
+
+int agpt_set_error(int code, const char *fmt, ...);
+
+// Walker plan: a tree laid out in depth-first pre-order.  Position i's subtree is the
+// interval [i, sub_end[i]); a is an ancestor-or-self of i iff a <= i < sub_end[a].  Queries
+// are processed in tiles of tile_m consecutive positions; a tile's keys are the ancestor
+// chain of its first position (chain_ids, root side first, chain_off per tile) plus the
+// tile's own rows.
+struct agpt_plan {
+    int64_t n = 0;
+    int32_t tile_m = 64;
+    int64_t n_tiles = 0;
+    int32_t max_depth = 0;
+    int64_t sum_depth = 0, sum_group_prefix = 0, n_groups = 0, n_reduce_nodes = 0, n_multi_items = 0;
+    std::vector<int32_t> dfs_to_node, node_to_dfs, parent_dfs, depth, sub_end;
+    std::vector<int64_t> chain_off;
+    std::vector<int32_t> chain_ids;
+    // dK/dV reduction work list: item = (node, inclusive tile range); slot >= 0 when the node's range
+    // is cut into several items whose sums meet in a second pass
+    std::vector<int32_t> item_node, item_t0, item_t1, item_slot;
+    std::vector<int32_t> multi_node, multi_count;
+    std::vector<int64_t> multi_first;
+    // device copies (owned)
+    int device = -1;
+    int32_t *d_depth = nullptr, *d_sub_end = nullptr, *d_chain_ids = nullptr;
+    int64_t *d_chain_off = nullptr, *d_multi_first = nullptr;
+    int32_t *d_item_node = nullptr, *d_item_t0 = nullptr, *d_item_t1 = nullptr, *d_item_slot = nullptr;
+    int32_t *d_multi_node = nullptr, *d_multi_count = nullptr;
+    ~agpt_plan();
+};
+
+int agpt_plan_upload(agpt_plan *p, int device);

@@ -1,0 +1,998 @@
+// CUDA side of libagpt_b200 (sm_100a): trie-scoped attention forward/backward over a
+// depth-first KV store, the deterministic dK/dV reduction, the per-query loss, RoPE, and the
+// legacy packed-prefix kernels.
+//
+// Layout.  Activations are row-major [n, H*hd] in the plan's depth-first order, so a node's
+// subtree is a contiguous row interval and the keys a tile of M consecutive queries can attend
+// are exactly: the ancestor chain of the tile's first query (shared by the whole tile, listed in
+// chain_ids) plus the tile's own rows.  Key a is attended by query i iff a <= i < sub_end[a].
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+
+#include "../../include/agpt_b200.h"
+#include "internal.h"
+
+#define CUDA_TRY(x)                                                                              \
+    do {                                                                                         \
+        cudaError_t e_ = (x);                                                                    \
+        if (e_ != cudaSuccess) return agpt_set_error(AGPT_E_CUDA, "%s: %s", #x, cudaGetErrorString(e_)); \
+    } while (0)
+
+static inline int launch_status(const char *what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return agpt_set_error(AGPT_E_CUDA, "%s launch: %s", what, cudaGetErrorString(e));
+    return AGPT_OK;
+}
+
+// --------------------------------------------------------------------------------------
+// plan: device copies
+// --------------------------------------------------------------------------------------
+template <typename T>
+static int upload(T **dst, const std::vector<T> &src) {
+    size_t bytes = (src.size() ? src.size() : 1) * sizeof(T);
+    CUDA_TRY(cudaMalloc((void **)dst, bytes));
+    if (!src.empty()) CUDA_TRY(cudaMemcpy(*dst, src.data(), src.size() * sizeof(T), cudaMemcpyHostToDevice));
+    return AGPT_OK;
+}
+
+int agpt_plan_upload(agpt_plan *p, int device) {
+    CUDA_TRY(cudaSetDevice(device));
+    p->device = device;
+    int rc;
+    if ((rc = upload(&p->d_depth, p->depth))) return rc;
+    if ((rc = upload(&p->d_sub_end, p->sub_end))) return rc;
+    if ((rc = upload(&p->d_chain_ids, p->chain_ids))) return rc;
+    if ((rc = upload(&p->d_chain_off, p->chain_off))) return rc;
+    if ((rc = upload(&p->d_item_node, p->item_node))) return rc;
+    if ((rc = upload(&p->d_item_t0, p->item_t0))) return rc;
+    if ((rc = upload(&p->d_item_t1, p->item_t1))) return rc;
+    if ((rc = upload(&p->d_item_slot, p->item_slot))) return rc;
+    if ((rc = upload(&p->d_multi_node, p->multi_node))) return rc;
+    if ((rc = upload(&p->d_multi_count, p->multi_count))) return rc;
+    if ((rc = upload(&p->d_multi_first, p->multi_first))) return rc;
+    return AGPT_OK;
+}
+
+agpt_plan::~agpt_plan() {
+    if (device >= 0) {
+        int cur = -1;
+        cudaGetDevice(&cur);
+        cudaSetDevice(device);
+        cudaFree(d_depth); cudaFree(d_sub_end); cudaFree(d_chain_ids); cudaFree(d_chain_off);
+        cudaFree(d_item_node); cudaFree(d_item_t0); cudaFree(d_item_t1); cudaFree(d_item_slot);
+        cudaFree(d_multi_node); cudaFree(d_multi_count); cudaFree(d_multi_first);
+        if (cur >= 0) cudaSetDevice(cur);
+    }
+}
+
+extern "C" void agpt_b200_plan_destroy(agpt_plan *p) { delete p; }
+
+// --------------------------------------------------------------------------------------
+// small helpers
+// --------------------------------------------------------------------------------------
+#define KC 32            // keys staged per chunk
+#define LOG2E 1.4426950408889634f
+#define LN2 0.6931471805599453f
+
+__device__ __forceinline__ float4 ld4(const float *p) { return __ldg(reinterpret_cast<const float4 *>(p)); }
+__device__ __forceinline__ float4 ld4(const __nv_bfloat16 *p) {
+    uint2 raw = __ldg(reinterpret_cast<const uint2 *>(p));
+    float4 r;
+    r.x = __uint_as_float(raw.x << 16); r.y = __uint_as_float(raw.x & 0xffff0000u);
+    r.z = __uint_as_float(raw.y << 16); r.w = __uint_as_float(raw.y & 0xffff0000u);
+    return r;
+}
+
+// Stage the id, subtree end and K/V rows of keys [kc, kc+cnt) of a tile into shared memory.
+template <int HD, int NT, typename KVT>
+__device__ __forceinline__ void stage_keys(const KVT *__restrict__ K, const KVT *__restrict__ V,
+                                           const int32_t *__restrict__ sub_end, const int32_t *__restrict__ chain,
+                                           int p, int i0, int kc, int cnt, int D, int hoff, int *s_kid, int *s_kend,
+                                           float (*sK)[HD + 4], float (*sV)[HD + 4]) {
+    const int tid = threadIdx.x;
+    if (tid < KC) {
+        int kk = kc + tid, kid = -1, kend = 0;
+        if (tid < cnt) { kid = kk < p ? chain[kk] : i0 + (kk - p); kend = sub_end[kid]; }
+        s_kid[tid] = kid; s_kend[tid] = kend;
+    }
+    __syncthreads();
+    constexpr int C4 = HD / 4;
+    for (int idx = tid; idx < cnt * C4; idx += NT) {
+        int r = idx / C4, c = idx % C4;
+        int64_t base = (int64_t)s_kid[r] * D + hoff + c * 4;
+        *reinterpret_cast<float4 *>(&sK[r][c * 4]) = ld4(K + base);
+        *reinterpret_cast<float4 *>(&sV[r][c * 4]) = ld4(V + base);
+    }
+    __syncthreads();
+}
+
+// --------------------------------------------------------------------------------------
+// forward: one thread per (query, head); keys broadcast from shared memory
+// --------------------------------------------------------------------------------------
+template <int HD, int M, typename KVT>
+__global__ void __launch_bounds__(M) attn_fwd_kernel(const float *__restrict__ Q, const KVT *__restrict__ K,
+                                                     const KVT *__restrict__ V, float *__restrict__ O,
+                                                     float *__restrict__ LSE, const int32_t *__restrict__ sub_end,
+                                                     const int64_t *__restrict__ chain_off,
+                                                     const int32_t *__restrict__ chain_ids, int n, int H, float scale) {
+    __shared__ __align__(16) float sK[KC][HD + 4];
+    __shared__ __align__(16) float sV[KC][HD + 4];
+    __shared__ int s_kid[KC], s_kend[KC];
+    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int D = H * HD, hoff = h * HD;
+    const int i0 = t * M, i = i0 + tid;
+    const bool active = i < n;
+    const int64_t coff = chain_off[t];
+    const int p = (int)(chain_off[t + 1] - coff);
+    const int nkeys = p + min(M, n - i0);
+    const int32_t *chain = chain_ids + coff;
+
+    float q[HD], acc[HD];
+    const float qs = scale * LOG2E;
+#pragma unroll
+    for (int c = 0; c < HD / 4; c++) {
+        float4 x = active ? ld4(Q + (int64_t)i * D + hoff + c * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        q[4 * c] = x.x * qs; q[4 * c + 1] = x.y * qs; q[4 * c + 2] = x.z * qs; q[4 * c + 3] = x.w * qs;
+        acc[4 * c] = acc[4 * c + 1] = acc[4 * c + 2] = acc[4 * c + 3] = 0.f;
+    }
+    float m = -INFINITY, l = 0.f;
+
+    for (int kc = 0; kc < nkeys; kc += KC) {
+        const int cnt = min(KC, nkeys - kc);
+        __syncthreads();
+        stage_keys<HD, M, KVT>(K, V, sub_end, chain, p, i0, kc, cnt, D, hoff, s_kid, s_kend, sK, sV);
+        for (int j0 = 0; j0 < cnt; j0 += 4) {
+            bool vld[4];
+            bool anyv = false;
+#pragma unroll
+            for (int jj = 0; jj < 4; jj++) {
+                int j = j0 + jj;
+                vld[jj] = active && j < cnt && s_kid[j] <= i && i < s_kend[j];
+                anyv |= vld[jj];
+            }
+            if (!__any_sync(0xffffffffu, anyv)) continue;
+            float s[4];
+#pragma unroll
+            for (int jj = 0; jj < 4; jj++) {
+                int j = min(j0 + jj, cnt - 1);
+                float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+                for (int c = 0; c < HD / 4; c++) {
+                    float4 kk = *reinterpret_cast<const float4 *>(&sK[j][c * 4]);
+                    d0 = fmaf(q[4 * c], kk.x, d0); d1 = fmaf(q[4 * c + 1], kk.y, d1);
+                    d0 = fmaf(q[4 * c + 2], kk.z, d0); d1 = fmaf(q[4 * c + 3], kk.w, d1);
+                }
+                s[jj] = vld[jj] ? d0 + d1 : -INFINITY;
+            }
+            float mx = fmaxf(fmaxf(s[0], s[1]), fmaxf(s[2], s[3]));
+            float mn = fmaxf(m, mx);
+            float mu = mn == -INFINITY ? 0.f : mn;
+            float corr = exp2f(m - mu);
+            m = mn;
+            l *= corr;
+#pragma unroll
+            for (int d = 0; d < HD; d++) acc[d] *= corr;
+#pragma unroll
+            for (int jj = 0; jj < 4; jj++) {
+                int j = min(j0 + jj, cnt - 1);
+                float w = exp2f(s[jj] - mu);
+                l += w;
+#pragma unroll
+                for (int c = 0; c < HD / 4; c++) {
+                    float4 vv = *reinterpret_cast<const float4 *>(&sV[j][c * 4]);
+                    acc[4 * c] = fmaf(w, vv.x, acc[4 * c]); acc[4 * c + 1] = fmaf(w, vv.y, acc[4 * c + 1]);
+                    acc[4 * c + 2] = fmaf(w, vv.z, acc[4 * c + 2]); acc[4 * c + 3] = fmaf(w, vv.w, acc[4 * c + 3]);
+                }
+            }
+        }
+    }
+    if (active) {
+        float inv = 1.0f / l;
+#pragma unroll
+        for (int c = 0; c < HD / 4; c++)
+            *reinterpret_cast<float4 *>(O + (int64_t)i * D + hoff + c * 4) =
+                make_float4(acc[4 * c] * inv, acc[4 * c + 1] * inv, acc[4 * c + 2] * inv, acc[4 * c + 3] * inv);
+        LSE[(int64_t)i * H + h] = (m + log2f(l)) * LN2;
+    }
+}
+
+// --------------------------------------------------------------------------------------
+// backward.  Per chunk of KC keys:
+//   phase 1 (thread = query): w = exp(s - lse), ds = w (dO.v - delta) scale, dq += ds k; w and ds go
+//                             to shared memory;
+//   phase 2 (lane = key, warp = slice of head_dim): dK_key += sum_i ds[i] q_i, dV_key += sum_i w[i] dO_i
+//                             over the tile's queries in index order.
+// Rows of chain keys are written to the partial buffers (one row per (tile, chain slot)); rows of the
+// tile's own keys go straight to dK/dV.  No atomics anywhere.
+// --------------------------------------------------------------------------------------
+template <int HD, int M>
+struct BwdSmem {
+    float sK[KC][HD + 4];
+    float sV[KC][HD + 4];
+    float sQ[M][HD];
+    float sG[M][HD];
+    float sW[M][KC + 1];
+    float sS[M][KC + 1];
+    int s_kid[KC], s_kend[KC];
+};
+
+template <int HD, int M, typename KVT>
+__global__ void __launch_bounds__(M) attn_bwd_kernel(const float *__restrict__ Q, const KVT *__restrict__ K,
+                                                     const KVT *__restrict__ V, const float *__restrict__ O,
+                                                     const float *__restrict__ LSE, const float *__restrict__ dO,
+                                                     float *__restrict__ dQ, float *__restrict__ dK,
+                                                     float *__restrict__ dV, float *__restrict__ Pk,
+                                                     float *__restrict__ Pv, const int32_t *__restrict__ sub_end,
+                                                     const int64_t *__restrict__ chain_off,
+                                                     const int32_t *__restrict__ chain_ids, int n, int H, float scale) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    BwdSmem<HD, M> &S = *reinterpret_cast<BwdSmem<HD, M> *>(smem_raw);
+    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int D = H * HD, hoff = h * HD;
+    const int i0 = t * M, i = i0 + tid;
+    const bool active = i < n;
+    const int nt = min(M, n - i0);
+    const int64_t coff = chain_off[t];
+    const int p = (int)(chain_off[t + 1] - coff);
+    const int nkeys = p + nt;
+    const int32_t *chain = chain_ids + coff;
+
+    float q[HD], g[HD], dq[HD];
+    float delta = 0.f;
+#pragma unroll
+    for (int c = 0; c < HD / 4; c++) {
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f), y = x, o = x;
+        if (active) {
+            x = ld4(Q + (int64_t)i * D + hoff + c * 4);
+            y = ld4(dO + (int64_t)i * D + hoff + c * 4);
+            o = ld4(O + (int64_t)i * D + hoff + c * 4);
+        }
+        q[4 * c] = x.x; q[4 * c + 1] = x.y; q[4 * c + 2] = x.z; q[4 * c + 3] = x.w;
+        g[4 * c] = y.x; g[4 * c + 1] = y.y; g[4 * c + 2] = y.z; g[4 * c + 3] = y.w;
+        delta = fmaf(y.x, o.x, delta); delta = fmaf(y.y, o.y, delta);
+        delta = fmaf(y.z, o.z, delta); delta = fmaf(y.w, o.w, delta);
+        dq[4 * c] = dq[4 * c + 1] = dq[4 * c + 2] = dq[4 * c + 3] = 0.f;
+        *reinterpret_cast<float4 *>(&S.sQ[tid][c * 4]) = x;
+        *reinterpret_cast<float4 *>(&S.sG[tid][c * 4]) = y;
+    }
+    const float qs = scale * LOG2E;
+    const float lse2 = active ? LSE[(int64_t)i * H + h] * LOG2E : 0.f;
+
+    constexpr int NW = M / 32;          // warps = slices of head_dim in phase 2
+    constexpr int SL = HD / NW;         // columns per slice
+    const int lane = tid & 31, slice0 = (tid >> 5) * SL;
+
+    for (int kc = 0; kc < nkeys; kc += KC) {
+        const int cnt = min(KC, nkeys - kc);
+        __syncthreads();
+        stage_keys<HD, M, KVT>(K, V, sub_end, chain, p, i0, kc, cnt, D, hoff, S.s_kid, S.s_kend, S.sK, S.sV);
+        // ---- phase 1 ----
+        for (int j = 0; j < cnt; j++) {
+            const bool vld = active && S.s_kid[j] <= i && i < S.s_kend[j];
+            if (!__any_sync(0xffffffffu, vld)) {
+                S.sW[tid][j] = 0.f; S.sS[tid][j] = 0.f;
+                continue;
+            }
+            float d0 = 0.f, d1 = 0.f, e0 = 0.f, e1 = 0.f;
+#pragma unroll
+            for (int c = 0; c < HD / 4; c++) {
+                float4 kk = *reinterpret_cast<const float4 *>(&S.sK[j][c * 4]);
+                float4 vv = *reinterpret_cast<const float4 *>(&S.sV[j][c * 4]);
+                d0 = fmaf(q[4 * c], kk.x, d0); d1 = fmaf(q[4 * c + 1], kk.y, d1);
+                d0 = fmaf(q[4 * c + 2], kk.z, d0); d1 = fmaf(q[4 * c + 3], kk.w, d1);
+                e0 = fmaf(g[4 * c], vv.x, e0); e1 = fmaf(g[4 * c + 1], vv.y, e1);
+                e0 = fmaf(g[4 * c + 2], vv.z, e0); e1 = fmaf(g[4 * c + 3], vv.w, e1);
+            }
+            float w = vld ? exp2f((d0 + d1) * qs - lse2) : 0.f;
+            float ds = w * ((e0 + e1) - delta) * scale;
+            S.sW[tid][j] = w; S.sS[tid][j] = ds;
+#pragma unroll
+            for (int c = 0; c < HD / 4; c++) {
+                float4 kk = *reinterpret_cast<const float4 *>(&S.sK[j][c * 4]);
+                dq[4 * c] = fmaf(ds, kk.x, dq[4 * c]); dq[4 * c + 1] = fmaf(ds, kk.y, dq[4 * c + 1]);
+                dq[4 * c + 2] = fmaf(ds, kk.z, dq[4 * c + 2]); dq[4 * c + 3] = fmaf(ds, kk.w, dq[4 * c + 3]);
+            }
+        }
+        __syncthreads();
+        // ---- phase 2 ----
+        if (lane < cnt) {
+            float ak[SL], av[SL];
+#pragma unroll
+            for (int c = 0; c < SL; c++) { ak[c] = 0.f; av[c] = 0.f; }
+            const int kk_idx = kc + lane;
+            // a tile key (index kk_idx - p inside the tile) is attended only by queries at or after it
+            const int first_q = max(0, kc - p);
+            for (int qi = first_q; qi < nt; qi++) {
+                float w = S.sW[qi][lane], ds = S.sS[qi][lane];
+                if (w == 0.f) continue;
+#pragma unroll
+                for (int c = 0; c < SL / 4; c++) {
+                    float4 qq = *reinterpret_cast<const float4 *>(&S.sQ[qi][slice0 + c * 4]);
+                    float4 gg = *reinterpret_cast<const float4 *>(&S.sG[qi][slice0 + c * 4]);
+                    ak[4 * c] = fmaf(ds, qq.x, ak[4 * c]); ak[4 * c + 1] = fmaf(ds, qq.y, ak[4 * c + 1]);
+                    ak[4 * c + 2] = fmaf(ds, qq.z, ak[4 * c + 2]); ak[4 * c + 3] = fmaf(ds, qq.w, ak[4 * c + 3]);
+                    av[4 * c] = fmaf(w, gg.x, av[4 * c]); av[4 * c + 1] = fmaf(w, gg.y, av[4 * c + 1]);
+                    av[4 * c + 2] = fmaf(w, gg.z, av[4 * c + 2]); av[4 * c + 3] = fmaf(w, gg.w, av[4 * c + 3]);
+                }
+            }
+            float *ok, *ov;
+            if (kk_idx < p) {
+                ok = Pk + (coff + kk_idx) * D + hoff + slice0;
+                ov = Pv + (coff + kk_idx) * D + hoff + slice0;
+            } else {
+                ok = dK + (int64_t)(i0 + kk_idx - p) * D + hoff + slice0;
+                ov = dV + (int64_t)(i0 + kk_idx - p) * D + hoff + slice0;
+            }
+#pragma unroll
+            for (int c = 0; c < SL / 4; c++) {
+                *reinterpret_cast<float4 *>(ok + c * 4) = make_float4(ak[4 * c], ak[4 * c + 1], ak[4 * c + 2], ak[4 * c + 3]);
+                *reinterpret_cast<float4 *>(ov + c * 4) = make_float4(av[4 * c], av[4 * c + 1], av[4 * c + 2], av[4 * c + 3]);
+            }
+        }
+    }
+    if (active) {
+#pragma unroll
+        for (int c = 0; c < HD / 4; c++)
+            *reinterpret_cast<float4 *>(dQ + (int64_t)i * D + hoff + c * 4) =
+                make_float4(dq[4 * c], dq[4 * c + 1], dq[4 * c + 2], dq[4 * c + 3]);
+    }
+}
+
+// dK/dV reduction, pass 1: one warp per work item = (node, tile range).  The node's row in tile t's
+// partial block is chain_off[t] + depth - 1.  Tiles are summed in increasing order.
+__global__ void reduce_items_kernel(const float *__restrict__ Pk, const float *__restrict__ Pv, float *__restrict__ dK,
+                                    float *__restrict__ dV, float *__restrict__ segk, float *__restrict__ segv,
+                                    const int64_t *__restrict__ chain_off, const int32_t *__restrict__ depth,
+                                    const int32_t *__restrict__ item_node, const int32_t *__restrict__ item_t0,
+                                    const int32_t *__restrict__ item_t1, const int32_t *__restrict__ item_slot,
+                                    int64_t n_items, int D) {
+    int64_t it = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (it >= n_items) return;
+    const int lane = threadIdx.x & 31;
+    const int a = item_node[it], t0 = item_t0[it], t1 = item_t1[it], slot = item_slot[it];
+    const int row = depth[a] - 1;
+    for (int c = lane * 4; c < D; c += 128) {
+        float4 sk = make_float4(0.f, 0.f, 0.f, 0.f), sv = sk;
+#pragma unroll 4
+        for (int t = t0; t <= t1; t++) {
+            int64_t r = (chain_off[t] + row) * D + c;
+            float4 a4 = __ldcs(reinterpret_cast<const float4 *>(Pk + r));
+            float4 b4 = __ldcs(reinterpret_cast<const float4 *>(Pv + r));
+            sk.x += a4.x; sk.y += a4.y; sk.z += a4.z; sk.w += a4.w;
+            sv.x += b4.x; sv.y += b4.y; sv.z += b4.z; sv.w += b4.w;
+        }
+        if (slot < 0) {
+            float4 *pk = reinterpret_cast<float4 *>(dK + (int64_t)a * D + c), *pv = reinterpret_cast<float4 *>(dV + (int64_t)a * D + c);
+            float4 x = *pk, y = *pv;
+            *pk = make_float4(x.x + sk.x, x.y + sk.y, x.z + sk.z, x.w + sk.w);
+            *pv = make_float4(y.x + sv.x, y.y + sv.y, y.z + sv.z, y.w + sv.w);
+        } else {
+            *reinterpret_cast<float4 *>(segk + (int64_t)slot * D + c) = sk;
+            *reinterpret_cast<float4 *>(segv + (int64_t)slot * D + c) = sv;
+        }
+    }
+}
+
+// pass 2: nodes whose range was cut into several items; their segment sums are added in item order.
+__global__ void reduce_multi_kernel(const float *__restrict__ segk, const float *__restrict__ segv, float *__restrict__ dK,
+                                    float *__restrict__ dV, const int32_t *__restrict__ multi_node,
+                                    const int32_t *__restrict__ multi_count, const int64_t *__restrict__ multi_first,
+                                    const int32_t *__restrict__ item_slot, int64_t n_multi, int D) {
+    int64_t mi = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (mi >= n_multi) return;
+    const int lane = threadIdx.x & 31;
+    const int a = multi_node[mi], cnt = multi_count[mi];
+    const int slot0 = item_slot[multi_first[mi]];     // slots of one node are consecutive
+    for (int c = lane * 4; c < D; c += 128) {
+        float4 sk = make_float4(0.f, 0.f, 0.f, 0.f), sv = sk;
+        for (int s = 0; s < cnt; s++) {
+            float4 a4 = *reinterpret_cast<const float4 *>(segk + (int64_t)(slot0 + s) * D + c);
+            float4 b4 = *reinterpret_cast<const float4 *>(segv + (int64_t)(slot0 + s) * D + c);
+            sk.x += a4.x; sk.y += a4.y; sk.z += a4.z; sk.w += a4.w;
+            sv.x += b4.x; sv.y += b4.y; sv.z += b4.z; sv.w += b4.w;
+        }
+        float4 *pk = reinterpret_cast<float4 *>(dK + (int64_t)a * D + c), *pv = reinterpret_cast<float4 *>(dV + (int64_t)a * D + c);
+        float4 x = *pk, y = *pv;
+        *pk = make_float4(x.x + sk.x, x.y + sk.y, x.z + sk.z, x.w + sk.w);
+        *pv = make_float4(y.x + sv.x, y.y + sv.y, y.z + sv.z, y.w + sv.w);
+    }
+}
+
+// --------------------------------------------------------------------------------------
+// native launchers
+// --------------------------------------------------------------------------------------
+static int check_common(const agpt_plan *p, int n_heads, int head_dim, const char *who) {
+    if (!p) return agpt_set_error(AGPT_E_ARG, "%s: null plan", who);
+    if (p->device < 0) return agpt_set_error(AGPT_E_ARG, "%s: plan has no device index (create it with device >= 0)", who);
+    if (n_heads < 1 || n_heads > 65535) return agpt_set_error(AGPT_E_ARG, "%s: n_heads out of range", who);
+    if (head_dim != 16 && head_dim != 32 && head_dim != 64)
+        return agpt_set_error(AGPT_E_ARG, "%s: head_dim %d unsupported (16, 32 or 64)", who, head_dim);
+    return AGPT_OK;
+}
+
+template <int HD, int M, typename KVT>
+static int launch_fwd(const agpt_plan *p, const float *q, const void *k, const void *v, float *out, float *lse, int H,
+                      float scale, cudaStream_t st) {
+    dim3 grid((unsigned)p->n_tiles, (unsigned)H);
+    attn_fwd_kernel<HD, M, KVT><<<grid, M, 0, st>>>(q, (const KVT *)k, (const KVT *)v, out, lse, p->d_sub_end,
+                                                    p->d_chain_off, p->d_chain_ids, (int)p->n, H, scale);
+    return launch_status("attn_fwd");
+}
+
+template <int HD, int M, typename KVT>
+static int launch_bwd(const agpt_plan *p, const float *q, const void *k, const void *v, const float *o, const float *lse,
+                      const float *dout, float *dq, float *dk, float *dv, float *pk, float *pv, int H, float scale,
+                      cudaStream_t st) {
+    dim3 grid((unsigned)p->n_tiles, (unsigned)H);
+    size_t smem = sizeof(BwdSmem<HD, M>);
+    CUDA_TRY(cudaFuncSetAttribute(attn_bwd_kernel<HD, M, KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attn_bwd_kernel<HD, M, KVT><<<grid, M, smem, st>>>(q, (const KVT *)k, (const KVT *)v, o, lse, dout, dq, dk, dv, pk, pv,
+                                                       p->d_sub_end, p->d_chain_off, p->d_chain_ids, (int)p->n, H, scale);
+    return launch_status("attn_bwd");
+}
+
+#define DISPATCH_HD_M_KV(FN, ...)                                                                  \
+    do {                                                                                           \
+        const bool bf = kv_dtype == AGPT_KV_BF16;                                                  \
+        const int m_ = p->tile_m;                                                                  \
+        if (head_dim == 16 && m_ == 32) return bf ? FN<16, 32, __nv_bfloat16>(__VA_ARGS__) : FN<16, 32, float>(__VA_ARGS__);   \
+        if (head_dim == 16 && m_ == 64) return bf ? FN<16, 64, __nv_bfloat16>(__VA_ARGS__) : FN<16, 64, float>(__VA_ARGS__);   \
+        if (head_dim == 16 && m_ == 128) return bf ? FN<16, 128, __nv_bfloat16>(__VA_ARGS__) : FN<16, 128, float>(__VA_ARGS__); \
+        if (head_dim == 32 && m_ == 32) return bf ? FN<32, 32, __nv_bfloat16>(__VA_ARGS__) : FN<32, 32, float>(__VA_ARGS__);   \
+        if (head_dim == 32 && m_ == 64) return bf ? FN<32, 64, __nv_bfloat16>(__VA_ARGS__) : FN<32, 64, float>(__VA_ARGS__);   \
+        if (head_dim == 32 && m_ == 128) return bf ? FN<32, 128, __nv_bfloat16>(__VA_ARGS__) : FN<32, 128, float>(__VA_ARGS__); \
+        if (head_dim == 64 && m_ == 32) return bf ? FN<64, 32, __nv_bfloat16>(__VA_ARGS__) : FN<64, 32, float>(__VA_ARGS__);   \
+        if (head_dim == 64 && m_ == 64) return bf ? FN<64, 64, __nv_bfloat16>(__VA_ARGS__) : FN<64, 64, float>(__VA_ARGS__);   \
+        if (head_dim == 64 && m_ == 128) return bf ? FN<64, 128, __nv_bfloat16>(__VA_ARGS__) : FN<64, 128, float>(__VA_ARGS__); \
+        return agpt_set_error(AGPT_E_ARG, "unsupported head_dim/tile combination");               \
+    } while (0)
+
+static int fwd_dispatch(const agpt_plan *p, const float *q, const void *k, const void *v, int kv_dtype, float *out,
+                        float *lse, int H, int head_dim, float scale, cudaStream_t st) {
+    DISPATCH_HD_M_KV(launch_fwd, p, q, k, v, out, lse, H, scale, st);
+}
+
+static int bwd_dispatch(const agpt_plan *p, const float *q, const void *k, const void *v, int kv_dtype, const float *o,
+                        const float *lse, const float *dout, float *dq, float *dk, float *dv, float *pk, float *pv, int H,
+                        int head_dim, float scale, cudaStream_t st) {
+    DISPATCH_HD_M_KV(launch_bwd, p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st);
+}
+
+extern "C" int agpt_b200_attn_fwd(const agpt_plan *p, const float *d_q, const void *d_k, const void *d_v, int kv_dtype,
+                                  float *d_out, float *d_lse, int n_heads, int head_dim, float scale, void *stream) {
+    int rc = check_common(p, n_heads, head_dim, "attn_fwd");
+    if (rc) return rc;
+    if (!d_q || !d_k || !d_v || !d_out || !d_lse) return agpt_set_error(AGPT_E_ARG, "attn_fwd: null buffer");
+    if (kv_dtype != AGPT_KV_F32 && kv_dtype != AGPT_KV_BF16) return agpt_set_error(AGPT_E_ARG, "attn_fwd: bad kv_dtype");
+    return fwd_dispatch(p, d_q, d_k, d_v, kv_dtype, d_out, d_lse, n_heads, head_dim, scale, (cudaStream_t)stream);
+}
+
+static int run_reduce(const agpt_plan *p, float *pk, float *pv, float *segk, float *segv, float *dk, float *dv, int D,
+                      cudaStream_t st) {
+    int64_t n_items = (int64_t)p->item_node.size();
+    if (n_items > 0) {
+        const int wpb = 8;
+        reduce_items_kernel<<<(unsigned)((n_items + wpb - 1) / wpb), wpb * 32, 0, st>>>(
+            pk, pv, dk, dv, segk, segv, p->d_chain_off, p->d_depth, p->d_item_node, p->d_item_t0, p->d_item_t1,
+            p->d_item_slot, n_items, D);
+        int rc = launch_status("reduce_items");
+        if (rc) return rc;
+    }
+    int64_t n_multi = (int64_t)p->multi_node.size();
+    if (n_multi > 0) {
+        const int wpb = 4;
+        reduce_multi_kernel<<<(unsigned)((n_multi + wpb - 1) / wpb), wpb * 32, 0, st>>>(
+            segk, segv, dk, dv, p->d_multi_node, p->d_multi_count, p->d_multi_first, p->d_item_slot, n_multi, D);
+        int rc = launch_status("reduce_multi");
+        if (rc) return rc;
+    }
+    return AGPT_OK;
+}
+
+extern "C" int agpt_b200_attn_bwd(const agpt_plan *p, const float *d_q, const void *d_k, const void *d_v, int kv_dtype,
+                                  const float *d_out, const float *d_lse, const float *d_dout, float *d_dq, float *d_dk,
+                                  float *d_dv, void *d_workspace, int64_t workspace_bytes, int n_heads, int head_dim,
+                                  float scale, void *stream) {
+    int rc = check_common(p, n_heads, head_dim, "attn_bwd");
+    if (rc) return rc;
+    if (!d_q || !d_k || !d_v || !d_out || !d_lse || !d_dout || !d_dq || !d_dk || !d_dv || !d_workspace)
+        return agpt_set_error(AGPT_E_ARG, "attn_bwd: null buffer");
+    if (kv_dtype != AGPT_KV_F32 && kv_dtype != AGPT_KV_BF16) return agpt_set_error(AGPT_E_ARG, "attn_bwd: bad kv_dtype");
+    const int D = n_heads * head_dim;
+    int64_t need = agpt_b200_attn_bwd_workspace_bytes(p, D);
+    if (workspace_bytes < need)
+        return agpt_set_error(AGPT_E_ARG, "attn_bwd: workspace %lld bytes < required %lld", (long long)workspace_bytes, (long long)need);
+    const int64_t rows = (int64_t)p->chain_ids.size();
+    float *pk = (float *)d_workspace, *pv = pk + rows * D, *segk = pv + rows * D, *segv = segk + p->n_multi_items * D;
+    rc = bwd_dispatch(p, d_q, d_k, d_v, kv_dtype, d_out, d_lse, d_dout, d_dq, d_dk, d_dv, pk, pv, n_heads, head_dim, scale,
+                      (cudaStream_t)stream);
+    if (rc) return rc;
+    return run_reduce(p, pk, pv, segk, segv, d_dk, d_dv, D, (cudaStream_t)stream);
+}
+
+// --------------------------------------------------------------------------------------
+// row gather, RoPE, bf16 store write
+// --------------------------------------------------------------------------------------
+__global__ void gather_rows_kernel(const float *__restrict__ src, const int32_t *__restrict__ index, float *__restrict__ dst,
+                                   int64_t n, int cols4) {
+    int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n * cols4) return;
+    int64_t r = idx / cols4;
+    int c = (int)(idx % cols4);
+    reinterpret_cast<float4 *>(dst)[idx] = __ldg(reinterpret_cast<const float4 *>(src) + (int64_t)index[r] * cols4 + c);
+}
+
+extern "C" int agpt_b200_gather_rows(const float *d_src, const int32_t *d_index, float *d_dst, int64_t n, int cols, void *stream) {
+    if (!d_src || !d_index || !d_dst || n < 0 || cols <= 0 || cols % 4) return agpt_set_error(AGPT_E_ARG, "gather_rows: bad argument (cols must be a multiple of 4)");
+    if (n == 0) return AGPT_OK;
+    int64_t total = n * (cols / 4);
+    gather_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(d_src, d_index, d_dst, n, cols / 4);
+    return launch_status("gather_rows");
+}
+
+__global__ void rope_kernel(float *__restrict__ x, const int32_t *__restrict__ pos, const float *__restrict__ cosv,
+                            const float *__restrict__ sinv, int64_t n, int H, int hd, int inverse) {
+    const int half = hd / 2;
+    int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n * H * half) return;
+    int64_t row = idx / (H * half);
+    int rem = (int)(idx % (H * half));
+    int h = rem / half, i = rem % half;
+    int ps = pos[row];
+    float c = cosv[ps * hd + 2 * i], s = sinv[ps * hd + 2 * i];
+    float2 *px = reinterpret_cast<float2 *>(x + row * (int64_t)(H * hd) + h * hd + 2 * i);
+    float2 v = *px;
+    if (!inverse) *px = make_float2(v.x * c - v.y * s, v.x * s + v.y * c);
+    else *px = make_float2(v.x * c + v.y * s, -v.x * s + v.y * c);
+}
+
+extern "C" int agpt_b200_rope(float *d_x, const int32_t *d_pos, const float *d_cos, const float *d_sin, int64_t n, int n_heads,
+                              int head_dim, int inverse, void *stream) {
+    if (!d_x || !d_pos || !d_cos || !d_sin || n < 0 || n_heads < 1 || head_dim < 2 || head_dim % 2)
+        return agpt_set_error(AGPT_E_ARG, "rope: bad argument");
+    if (n == 0) return AGPT_OK;
+    int64_t total = n * n_heads * (head_dim / 2);
+    rope_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(d_x, d_pos, d_cos, d_sin, n, n_heads, head_dim, inverse);
+    return launch_status("rope");
+}
+
+__global__ void store_bf16_kernel(const float *__restrict__ src, __nv_bfloat16 *__restrict__ dst, int64_t total4) {
+    int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total4) return;
+    float4 v = __ldg(reinterpret_cast<const float4 *>(src) + idx);
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 o;
+    o.x = *reinterpret_cast<uint32_t *>(&a); o.y = *reinterpret_cast<uint32_t *>(&b);
+    reinterpret_cast<uint2 *>(dst)[idx] = o;
+}
+
+extern "C" int agpt_b200_kv_store_write_bf16(const float *d_src, void *d_store, int64_t n, int cols, void *stream) {
+    if (!d_src || !d_store || n < 0 || cols <= 0 || cols % 4) return agpt_set_error(AGPT_E_ARG, "kv_store_write_bf16: bad argument");
+    if (n == 0) return AGPT_OK;
+    int64_t total4 = n * (cols / 4);
+    store_bf16_kernel<<<(unsigned)((total4 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(d_src, (__nv_bfloat16 *)d_store, total4);
+    return launch_status("kv_store_write_bf16");
+}
+
+// --------------------------------------------------------------------------------------
+// loss: one warp per query row
+// --------------------------------------------------------------------------------------
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ int warp_sum_i(int v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// mode 0: per-query (radix); mode 1: per-node (leveled, node_ids index the counts)
+__global__ void loss_kernel(const float *__restrict__ logits, const int32_t *__restrict__ query_to_node,
+                            const int32_t *__restrict__ query_offsets, const int32_t *__restrict__ ids,
+                            const int32_t *__restrict__ token_ids, const int32_t *__restrict__ counts_offset,
+                            const int32_t *__restrict__ counts_tok, const int32_t *__restrict__ counts_val,
+                            const float *__restrict__ mass_weights, float *__restrict__ d_logits, float *__restrict__ loss_out,
+                            int64_t T_q, int V, float entropy_lambda, float intermediate_weight, int ce_only, int mode) {
+    int64_t qi = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (qi >= T_q) return;
+    const int lane = threadIdx.x & 31;
+    const float *in = logits + qi * V;
+    float *g = d_logits + qi * V;
+    float mx = -3.402823466e+38f;
+    for (int j = lane; j < V; j += 32) mx = fmaxf(mx, in[j]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int j = lane; j < V; j += 32) sum += expf(in[j] - mx);
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+
+    bool endpoint_path;
+    int cid = 0;
+    if (mode == 1) { endpoint_path = true; cid = ids[qi]; }
+    else {
+        int n_idx = query_to_node[qi];
+        bool is_endpoint = (qi + 1) == query_offsets[n_idx + 1];
+        bool ce_as_intermediate = ce_only && is_endpoint && (qi + 1 < T_q);
+        endpoint_path = is_endpoint && !ce_as_intermediate;
+        if (endpoint_path) cid = ids[n_idx];
+    }
+    float weight = 1.0f, loss = 0.f;
+    if (endpoint_path) {
+        const int start = counts_offset[cid], end = counts_offset[cid + 1];
+        if (start == end) {
+            // no observed continuation: zero loss; the row keeps the plain probabilities
+            for (int j = lane; j < V; j += 32) g[j] = expf(in[j] - mx) * inv;
+            if (lane == 0) loss_out[qi] = 0.f;
+            return;
+        }
+        int total = 0;
+        for (int e = start + lane; e < end; e += 32) total += counts_val[e];
+        total = warp_sum_i(total);
+        const float total_f = (float)total;
+        if (mode == 0) {
+            if (entropy_lambda > 0.0f && (end - start) > 1) {
+                float Hh = 0.f;
+                for (int e = start + lane; e < end; e += 32) {
+                    float qe = counts_val[e] / total_f;
+                    if (qe > 0.f) Hh -= qe * logf(qe);
+                }
+                Hh = warp_sum(Hh);
+                weight = 1.0f + entropy_lambda * (Hh / logf((float)V));
+            }
+            if (mass_weights) weight *= mass_weights[qi];
+        }
+        for (int j = lane; j < V; j += 32) g[j] = expf(in[j] - mx) * inv * weight;
+        __syncwarp();
+        for (int e = start + lane; e < end; e += 32) {
+            int tok = counts_tok[e];
+            float tgt = counts_val[e] / total_f;
+            float pr = expf(in[tok] - mx) * inv;
+            loss -= tgt * logf(pr + 1e-10f);
+            g[tok] = (pr - tgt) * weight;      // tokens of one node are distinct
+        }
+        loss = warp_sum(loss) * weight;
+    } else {
+        const int target = token_ids[qi + 1];
+        weight = intermediate_weight;
+        if (mass_weights) weight *= mass_weights[qi];
+        for (int j = lane; j < V; j += 32) {
+            float pr = expf(in[j] - mx) * inv;
+            g[j] = (j == target ? pr - 1.0f : pr) * weight;
+        }
+        float pr = expf(in[target] - mx) * inv;
+        loss = -logf(pr + 1e-10f) * weight;
+    }
+    if (lane == 0) loss_out[qi] = loss;
+}
+
+extern "C" int agpt_b200_loss_per_query(const float *d_logits, const int32_t *d_query_to_node, const int32_t *d_query_offsets,
+                                        const int32_t *d_radix_ids, const int32_t *d_token_ids, const int32_t *d_counts_offset,
+                                        const int32_t *d_counts_tok, const int32_t *d_counts_val, const float *d_mass_weights,
+                                        float *d_dlogits, float *d_loss, int64_t T_q, int V, float entropy_lambda,
+                                        float intermediate_weight, int ce_only, void *stream) {
+    if (!d_logits || !d_query_to_node || !d_query_offsets || !d_radix_ids || !d_token_ids || !d_counts_offset || !d_counts_tok ||
+        !d_counts_val || !d_dlogits || !d_loss || T_q < 0 || V < 1)
+        return agpt_set_error(AGPT_E_ARG, "loss_per_query: bad argument");
+    if (T_q == 0) return AGPT_OK;
+    const int wpb = 8;
+    loss_kernel<<<(unsigned)((T_q + wpb - 1) / wpb), wpb * 32, 0, (cudaStream_t)stream>>>(
+        d_logits, d_query_to_node, d_query_offsets, d_radix_ids, d_token_ids, d_counts_offset, d_counts_tok, d_counts_val,
+        d_mass_weights, d_dlogits, d_loss, T_q, V, entropy_lambda, intermediate_weight, ce_only, 0);
+    return launch_status("loss_per_query");
+}
+
+extern "C" int agpt_b200_loss_per_node(const float *d_logits, const int32_t *d_node_ids, const int32_t *d_counts_offset,
+                                       const int32_t *d_counts_tok, const int32_t *d_counts_val, float *d_dlogits, float *d_loss,
+                                       int64_t N, int V, void *stream) {
+    if (!d_logits || !d_node_ids || !d_counts_offset || !d_counts_tok || !d_counts_val || !d_dlogits || !d_loss || N < 0 || V < 1)
+        return agpt_set_error(AGPT_E_ARG, "loss_per_node: bad argument");
+    if (N == 0) return AGPT_OK;
+    const int wpb = 8;
+    loss_kernel<<<(unsigned)((N + wpb - 1) / wpb), wpb * 32, 0, (cudaStream_t)stream>>>(
+        d_logits, nullptr, nullptr, d_node_ids, nullptr, d_counts_offset, d_counts_tok, d_counts_val, nullptr, d_dlogits, d_loss,
+        N, V, 0.f, 1.f, 0, 1);
+    return launch_status("loss_per_node");
+}
+
+// --------------------------------------------------------------------------------------
+// legacy packed-prefix kernels: one warp per (query, head), lanes over packed rows
+// --------------------------------------------------------------------------------------
+__device__ __forceinline__ void packed_query_span(const int *query_to_node, const int *query_offsets, const int *kv_offsets,
+                                                  const int *kv_lengths, int t, int &node, int &len, int64_t &off) {
+    node = query_to_node ? query_to_node[t] : t;
+    len = query_to_node ? kv_lengths[node] - (query_offsets[node + 1] - t) + 1 : kv_lengths[node];
+    off = kv_offsets[node];
+}
+
+template <int HD>
+__global__ void packed_fwd_kernel(const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
+                                  const int *__restrict__ query_to_node, const int *__restrict__ query_offsets,
+                                  const int *__restrict__ kv_offsets, const int *__restrict__ kv_lengths,
+                                  float *__restrict__ out, float *__restrict__ weights, int T_q, int H, int max_len, float scale) {
+    int64_t wid = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (wid >= (int64_t)T_q * H) return;
+    const int lane = threadIdx.x & 31;
+    const int t = (int)(wid / H), h = (int)(wid % H);
+    int node, len;
+    int64_t off;
+    packed_query_span(query_to_node, query_offsets, kv_offsets, kv_lengths, t, node, len, off);
+    float qv[HD];
+#pragma unroll
+    for (int c = 0; c < HD / 4; c++) {
+        float4 x = ld4(q + ((int64_t)t * H + h) * HD + c * 4);
+        qv[4 * c] = x.x; qv[4 * c + 1] = x.y; qv[4 * c + 2] = x.z; qv[4 * c + 3] = x.w;
+    }
+    float *wr = weights + ((int64_t)t * H + h) * max_len;
+    float mx = -INFINITY;
+    for (int p = lane; p < len; p += 32) {
+        const float *kr = k + ((off + p) * H + h) * HD;
+        float d = 0.f;
+#pragma unroll
+        for (int c = 0; c < HD / 4; c++) {
+            float4 kk = ld4(kr + c * 4);
+            d = fmaf(qv[4 * c], kk.x, d); d = fmaf(qv[4 * c + 1], kk.y, d);
+            d = fmaf(qv[4 * c + 2], kk.z, d); d = fmaf(qv[4 * c + 3], kk.w, d);
+        }
+        d *= scale;
+        wr[p] = d;
+        mx = fmaxf(mx, d);
+    }
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int p = lane; p < len; p += 32) { float e = expf(wr[p] - mx); wr[p] = e; sum += e; }
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+    float acc[HD];
+#pragma unroll
+    for (int d = 0; d < HD; d++) acc[d] = 0.f;
+    for (int p = lane; p < max_len; p += 32) {
+        if (p >= len) { wr[p] = 0.f; continue; }
+        float w = wr[p] * inv;
+        wr[p] = w;
+        const float *vr = v + ((off + p) * H + h) * HD;
+#pragma unroll
+        for (int c = 0; c < HD / 4; c++) {
+            float4 vv = ld4(vr + c * 4);
+            acc[4 * c] = fmaf(w, vv.x, acc[4 * c]); acc[4 * c + 1] = fmaf(w, vv.y, acc[4 * c + 1]);
+            acc[4 * c + 2] = fmaf(w, vv.z, acc[4 * c + 2]); acc[4 * c + 3] = fmaf(w, vv.w, acc[4 * c + 3]);
+        }
+    }
+#pragma unroll
+    for (int d = 0; d < HD; d++) acc[d] = warp_sum(acc[d]);
+    if (lane == 0) {
+        float *o = out + ((int64_t)t * H + h) * HD;
+#pragma unroll
+        for (int c = 0; c < HD / 4; c++) *reinterpret_cast<float4 *>(o + c * 4) = make_float4(acc[4 * c], acc[4 * c + 1], acc[4 * c + 2], acc[4 * c + 3]);
+    }
+}
+
+// One warp per (node, head); the node's queries are visited in order and lane p%32 owns packed row p, so
+// every dk_full/dv_full element is accumulated by one lane in a fixed order.
+template <int HD>
+__global__ void packed_bwd_kernel(const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
+                                  const float *__restrict__ weights, const float *__restrict__ d_out,
+                                  const int *__restrict__ query_offsets, const int *__restrict__ kv_offsets,
+                                  const int *__restrict__ kv_lengths, float *__restrict__ dq, float *__restrict__ dk_full,
+                                  float *__restrict__ dv_full, int n_nodes, int H, int max_len, float scale, int accumulate) {
+    int64_t wid = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (wid >= (int64_t)n_nodes * H) return;
+    const int lane = threadIdx.x & 31;
+    const int node = (int)(wid / H), h = (int)(wid % H);
+    const int q0 = query_offsets ? query_offsets[node] : node;
+    const int q1 = query_offsets ? query_offsets[node + 1] : node + 1;
+    const int klen = kv_lengths[node];
+    const int64_t off = kv_offsets[node];
+    for (int t = q0; t < q1; t++) {
+        const int len = klen - (q1 - t) + 1;
+        float qv[HD], gv[HD], dqa[HD];
+#pragma unroll
+        for (int c = 0; c < HD / 4; c++) {
+            float4 x = ld4(q + ((int64_t)t * H + h) * HD + c * 4), y = ld4(d_out + ((int64_t)t * H + h) * HD + c * 4);
+            qv[4 * c] = x.x; qv[4 * c + 1] = x.y; qv[4 * c + 2] = x.z; qv[4 * c + 3] = x.w;
+            gv[4 * c] = y.x; gv[4 * c + 1] = y.y; gv[4 * c + 2] = y.z; gv[4 * c + 3] = y.w;
+            dqa[4 * c] = dqa[4 * c + 1] = dqa[4 * c + 2] = dqa[4 * c + 3] = 0.f;
+        }
+        const float *wr = weights + ((int64_t)t * H + h) * max_len;
+        float dot = 0.f;
+        for (int p = lane; p < len; p += 32) {
+            const float *vr = v + ((off + p) * H + h) * HD;
+            float d = 0.f;
+#pragma unroll
+            for (int c = 0; c < HD / 4; c++) {
+                float4 vv = ld4(vr + c * 4);
+                d = fmaf(gv[4 * c], vv.x, d); d = fmaf(gv[4 * c + 1], vv.y, d);
+                d = fmaf(gv[4 * c + 2], vv.z, d); d = fmaf(gv[4 * c + 3], vv.w, d);
+            }
+            dot = fmaf(d, wr[p], dot);
+        }
+        dot = warp_sum(dot);
+        for (int p = lane; p < len; p += 32) {
+            const float *kr = k + ((off + p) * H + h) * HD;
+            const float *vr = v + ((off + p) * H + h) * HD;
+            float *dkr = dk_full + ((off + p) * H + h) * HD, *dvr = dv_full + ((off + p) * H + h) * HD;
+            const float w = wr[p];
+            float d = 0.f;
+#pragma unroll
+            for (int c = 0; c < HD / 4; c++) {
+                float4 vv = ld4(vr + c * 4);
+                d = fmaf(gv[4 * c], vv.x, d); d = fmaf(gv[4 * c + 1], vv.y, d);
+                d = fmaf(gv[4 * c + 2], vv.z, d); d = fmaf(gv[4 * c + 3], vv.w, d);
+            }
+            const float ds = w * (d - dot) * scale;
+            const bool add = accumulate || t > q0;
+#pragma unroll
+            for (int c = 0; c < HD / 4; c++) {
+                float4 kk = ld4(kr + c * 4);
+                dqa[4 * c] = fmaf(ds, kk.x, dqa[4 * c]); dqa[4 * c + 1] = fmaf(ds, kk.y, dqa[4 * c + 1]);
+                dqa[4 * c + 2] = fmaf(ds, kk.z, dqa[4 * c + 2]); dqa[4 * c + 3] = fmaf(ds, kk.w, dqa[4 * c + 3]);
+                float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+                if (add) { a = *reinterpret_cast<float4 *>(dkr + c * 4); b = *reinterpret_cast<float4 *>(dvr + c * 4); }
+                a.x = fmaf(ds, qv[4 * c], a.x); a.y = fmaf(ds, qv[4 * c + 1], a.y); a.z = fmaf(ds, qv[4 * c + 2], a.z); a.w = fmaf(ds, qv[4 * c + 3], a.w);
+                b.x = fmaf(w, gv[4 * c], b.x); b.y = fmaf(w, gv[4 * c + 1], b.y); b.z = fmaf(w, gv[4 * c + 2], b.z); b.w = fmaf(w, gv[4 * c + 3], b.w);
+                *reinterpret_cast<float4 *>(dkr + c * 4) = a;
+                *reinterpret_cast<float4 *>(dvr + c * 4) = b;
+            }
+        }
+#pragma unroll
+        for (int d = 0; d < HD; d++) dqa[d] = warp_sum(dqa[d]);
+        if (lane == 0) {
+            float *o = dq + ((int64_t)t * H + h) * HD;
+#pragma unroll
+            for (int c = 0; c < HD / 4; c++) *reinterpret_cast<float4 *>(o + c * 4) = make_float4(dqa[4 * c], dqa[4 * c + 1], dqa[4 * c + 2], dqa[4 * c + 3]);
+        }
+        __syncwarp();
+    }
+}
+
+static void legacy_fwd(const float *q, const float *k, const float *v, const int *q2n, const int *qoff, const int *kvo,
+                       const int *kvl, float *out, float *w, int T_q, int H, int hd, int max_len, float scale) {
+    if (T_q <= 0) return;
+    const int wpb = 4;
+    unsigned blocks = (unsigned)(((int64_t)T_q * H + wpb - 1) / wpb);
+    switch (hd) {
+        case 16: packed_fwd_kernel<16><<<blocks, wpb * 32>>>(q, k, v, q2n, qoff, kvo, kvl, out, w, T_q, H, max_len, scale); break;
+        case 32: packed_fwd_kernel<32><<<blocks, wpb * 32>>>(q, k, v, q2n, qoff, kvo, kvl, out, w, T_q, H, max_len, scale); break;
+        case 64: packed_fwd_kernel<64><<<blocks, wpb * 32>>>(q, k, v, q2n, qoff, kvo, kvl, out, w, T_q, H, max_len, scale); break;
+        default: agpt_set_error(AGPT_E_ARG, "legacy attention: head_dim %d unsupported (16, 32 or 64)", hd); return;
+    }
+    launch_status("legacy attention forward");
+}
+
+static void legacy_bwd(const float *q, const float *k, const float *v, const float *w, const float *d_out, const int *qoff,
+                       const int *kvo, const int *kvl, float *dq, float *dk, float *dv, int n_nodes, int H, int hd, int max_len,
+                       float scale, int accumulate) {
+    if (n_nodes <= 0) return;
+    const int wpb = 4;
+    unsigned blocks = (unsigned)(((int64_t)n_nodes * H + wpb - 1) / wpb);
+    switch (hd) {
+        case 16: packed_bwd_kernel<16><<<blocks, wpb * 32>>>(q, k, v, w, d_out, qoff, kvo, kvl, dq, dk, dv, n_nodes, H, max_len, scale, accumulate); break;
+        case 32: packed_bwd_kernel<32><<<blocks, wpb * 32>>>(q, k, v, w, d_out, qoff, kvo, kvl, dq, dk, dv, n_nodes, H, max_len, scale, accumulate); break;
+        case 64: packed_bwd_kernel<64><<<blocks, wpb * 32>>>(q, k, v, w, d_out, qoff, kvo, kvl, dq, dk, dv, n_nodes, H, max_len, scale, accumulate); break;
+        default: agpt_set_error(AGPT_E_ARG, "legacy attention backward: head_dim %d unsupported (16, 32 or 64)", hd); return;
+    }
+    launch_status("legacy attention backward");
+}
+
+extern "C" void cuda_batched_varlen_attention(const float *q, const float *k, const float *v, const int *kv_offsets,
+                                              const int *kv_lengths, float *output, float *weights_out, int n_nodes, int n_heads,
+                                              int head_dim, int max_len, float scale) {
+    legacy_fwd(q, k, v, nullptr, nullptr, kv_offsets, kv_lengths, output, weights_out, n_nodes, n_heads, head_dim, max_len, scale);
+}
+
+extern "C" void cuda_batched_varlen_attention_backward(const float *q, const float *k, const float *v, const float *w,
+                                                       const float *d_out, const int *kv_offsets, const int *kv_lengths, float *dq,
+                                                       float *dk_full, float *dv_full, int n_nodes, int n_heads, int head_dim,
+                                                       int max_len, float scale) {
+    legacy_bwd(q, k, v, w, d_out, nullptr, kv_offsets, kv_lengths, dq, dk_full, dv_full, n_nodes, n_heads, head_dim, max_len, scale, 0);
+}
+
+extern "C" void cuda_batched_varlen_attention_L_queries(const float *q, const float *k, const float *v, const int *query_to_node,
+                                                        const int *query_offsets, const int *kv_offsets, const int *kv_lengths,
+                                                        float *output, float *weights_out, int T_q, int n_heads, int head_dim,
+                                                        int max_kv_len, float scale) {
+    legacy_fwd(q, k, v, query_to_node, query_offsets, kv_offsets, kv_lengths, output, weights_out, T_q, n_heads, head_dim, max_kv_len, scale);
+}
+
+// The node count is not an argument of the reference signature; it is query_to_node[T_q - 1] + 1.
+extern "C" void cuda_batched_varlen_attention_L_queries_backward(const float *q, const float *k, const float *v, const float *w,
+                                                                 const float *d_out, const int *query_to_node,
+                                                                 const int *query_offsets, const int *kv_offsets,
+                                                                 const int *kv_lengths, float *dq, float *dk_full, float *dv_full,
+                                                                 int T_q, int n_heads, int head_dim, int max_kv_len, float scale) {
+    if (T_q <= 0) return;
+    int last = 0;
+    if (cudaMemcpy(&last, query_to_node + (T_q - 1), sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) {
+        agpt_set_error(AGPT_E_CUDA, "L_queries_backward: cannot read query_to_node");
+        return;
+    }
+    legacy_bwd(q, k, v, w, d_out, query_offsets, kv_offsets, kv_lengths, dq, dk_full, dv_full, last + 1, n_heads, head_dim, max_kv_len, scale, 1);
+}
+
+__global__ void copy_kernel(const float4 *__restrict__ src, float4 *__restrict__ dst, int64_t n4) {
+    int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < n4) dst[idx] = src[idx];
+}
+__global__ void copy_tail_kernel(const float *__restrict__ src, float *__restrict__ dst, int64_t from, int64_t n) {
+    int64_t idx = from + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < n) dst[idx] = src[idx];
+}
+
+// [n*H, hd] and [n, H*hd] are the same bytes: a plain copy.
+extern "C" void cuda_unpack_batched_attn_output(const float *packed_output, float *unpacked_output, int n_nodes, int n_heads, int head_dim) {
+    int64_t total = (int64_t)n_nodes * n_heads * head_dim;
+    if (total <= 0 || packed_output == unpacked_output) return;
+    bool aligned = (((uintptr_t)packed_output | (uintptr_t)unpacked_output) & 15) == 0;
+    int64_t n4 = aligned ? total / 4 : 0;
+    if (n4) copy_kernel<<<(unsigned)((n4 + 255) / 256), 256>>>((const float4 *)packed_output, (float4 *)unpacked_output, n4);
+    if (n4 * 4 < total) copy_tail_kernel<<<(unsigned)((total - n4 * 4 + 255) / 256), 256>>>(packed_output, unpacked_output, n4 * 4, total);
+    launch_status("unpack");
+}
+
+extern "C" void cuda_sync(void) {
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) agpt_set_error(AGPT_E_CUDA, "cuda_sync: %s", cudaGetErrorString(e));
+}
+
+// --------------------------------------------------------------------------------------
+// host-buffer step
+// --------------------------------------------------------------------------------------
+extern "C" int agpt_b200_attn_fwd_bwd_host(const agpt_plan *p, const float *h_q, const float *h_k, const float *h_v,
+                                           const float *h_dout, float *h_out, float *h_lse, float *h_dq, float *h_dk, float *h_dv,
+                                           int kv_dtype, int n_heads, int head_dim, float scale) {
+    int rc = check_common(p, n_heads, head_dim, "attn_fwd_bwd_host");
+    if (rc) return rc;
+    if (!h_q || !h_k || !h_v || !h_dout || !h_out || !h_lse || !h_dq || !h_dk || !h_dv)
+        return agpt_set_error(AGPT_E_ARG, "attn_fwd_bwd_host: null buffer");
+    CUDA_TRY(cudaSetDevice(p->device));
+    const int D = n_heads * head_dim;
+    const size_t rowb = (size_t)p->n * D * sizeof(float);
+    const int64_t wsb = agpt_b200_attn_bwd_workspace_bytes(p, D);
+    float *d[9] = {nullptr};   // q k v dout out dq dk dv lse
+    void *kb = nullptr, *vb = nullptr, *ws = nullptr;
+    cudaStream_t st = nullptr;
+    auto cleanup = [&]() {
+        for (float *x : d) cudaFree(x);
+        cudaFree(kb); cudaFree(vb); cudaFree(ws);
+        if (st) cudaStreamDestroy(st);
+    };
+#define TRY_OR_CLEAN(x)                                                                                      \
+    do {                                                                                                     \
+        cudaError_t e_ = (x);                                                                                \
+        if (e_ != cudaSuccess) { cleanup(); return agpt_set_error(AGPT_E_CUDA, "%s: %s", #x, cudaGetErrorString(e_)); } \
+    } while (0)
+    TRY_OR_CLEAN(cudaStreamCreate(&st));
+    for (int j = 0; j < 8; j++) TRY_OR_CLEAN(cudaMalloc((void **)&d[j], rowb));
+    TRY_OR_CLEAN(cudaMalloc((void **)&d[8], (size_t)p->n * n_heads * sizeof(float)));
+    TRY_OR_CLEAN(cudaMalloc(&ws, (size_t)wsb));
+    TRY_OR_CLEAN(cudaMemcpyAsync(d[0], h_q, rowb, cudaMemcpyHostToDevice, st));
+    TRY_OR_CLEAN(cudaMemcpyAsync(d[1], h_k, rowb, cudaMemcpyHostToDevice, st));
+    TRY_OR_CLEAN(cudaMemcpyAsync(d[2], h_v, rowb, cudaMemcpyHostToDevice, st));
+    TRY_OR_CLEAN(cudaMemcpyAsync(d[3], h_dout, rowb, cudaMemcpyHostToDevice, st));
+    const void *kk = d[1], *vv = d[2];
+    if (kv_dtype == AGPT_KV_BF16) {
+        TRY_OR_CLEAN(cudaMalloc(&kb, rowb / 2));
+        TRY_OR_CLEAN(cudaMalloc(&vb, rowb / 2));
+        if ((rc = agpt_b200_kv_store_write_bf16(d[1], kb, p->n, D, st)) || (rc = agpt_b200_kv_store_write_bf16(d[2], vb, p->n, D, st))) { cleanup(); return rc; }
+        kk = kb; vv = vb;
+    }
+    if ((rc = agpt_b200_attn_fwd(p, d[0], kk, vv, kv_dtype, d[4], d[8], n_heads, head_dim, scale, st))) { cleanup(); return rc; }
+    if ((rc = agpt_b200_attn_bwd(p, d[0], kk, vv, kv_dtype, d[4], d[8], d[3], d[5], d[6], d[7], ws, wsb, n_heads, head_dim, scale, st))) { cleanup(); return rc; }
+    TRY_OR_CLEAN(cudaMemcpyAsync(h_out, d[4], rowb, cudaMemcpyDeviceToHost, st));
+    TRY_OR_CLEAN(cudaMemcpyAsync(h_lse, d[8], (size_t)p->n * n_heads * sizeof(float), cudaMemcpyDeviceToHost, st));
+    TRY_OR_CLEAN(cudaMemcpyAsync(h_dq, d[5], rowb, cudaMemcpyDeviceToHost, st));
+    TRY_OR_CLEAN(cudaMemcpyAsync(h_dk, d[6], rowb, cudaMemcpyDeviceToHost, st));
+    TRY_OR_CLEAN(cudaMemcpyAsync(h_dv, d[7], rowb, cudaMemcpyDeviceToHost, st));
+    TRY_OR_CLEAN(cudaStreamSynchronize(st));
+    cleanup();
+    return AGPT_OK;
+}

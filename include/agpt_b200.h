@@ -1,0 +1,247 @@
+/*
+ * agpt_b200.h — C ABI of libagpt_b200.so: the trie-walk attention hot path of AGPT
+ * (forward, backward, mass-weighted next-token loss, per-subtree KV store and walker
+ * index) written for NVIDIA B200 (sm_100a).
+ *
+ * Two groups of entry points:
+ *
+ *  1. The legacy kernel boundary: the symbols the reference's Crystal `lib
+ *     LibCUDAKernels` binding and its C++ trainer link against, with identical names,
+ *     argument order and packed-prefix buffer layout.  Citations are to files of the
+ *     reference project.
+ *  2. The native tree-indexed boundary (`agpt_b200_*`): the same maths addressed through
+ *     a walker plan (depth-first node order, subtree intervals, per-tile ancestor chains)
+ *     instead of materialised per-node prefixes.
+ *
+ * Conventions: all pointers named `d_*` or documented as device pointers are CUDA device
+ * memory owned by the caller; the library never retains them.  `int` status returns are
+ * 0 on success and a negative AGPT_E_* code otherwise; agpt_b200_last_error() gives the
+ * message of the calling thread's last failure.  No function traps or aborts.
+ */
+#ifndef AGPT_B200_H
+#define AGPT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AGPT_OK 0
+#define AGPT_E_ARG (-1)      /* bad argument (null pointer, unsupported head_dim, ...) */
+#define AGPT_E_CUDA (-2)     /* a CUDA runtime call or kernel launch failed */
+#define AGPT_E_IO (-3)       /* file could not be read or written, or has a bad magic */
+#define AGPT_E_LIMIT (-4)    /* size beyond a documented maximum */
+#define AGPT_E_NOMEM (-5)
+
+#define AGPT_KV_F32 0
+#define AGPT_KV_BF16 1
+
+const char *agpt_b200_last_error(void);
+const char *agpt_b200_version(void);
+
+/* ======================================================================== */
+/* 1. Legacy kernel boundary                                                */
+/* ======================================================================== */
+
+/* Replaces cuda_batched_varlen_attention (declared src/cuda/agpt_train.cu:73-77; called
+ * src/agpt/batched_depth_forward.cr:767-771 and src/cuda/agpt_train.cu:2805-2809).
+ * q_packed [n_nodes*n_heads, head_dim]; k/v_packed [(kv_offsets[i]+pos)*n_heads+h]*head_dim;
+ * output [n_nodes*n_heads, head_dim]; weights_out [(i*n_heads+h)*max_len + pos]. */
+void cuda_batched_varlen_attention(const float *q_packed, const float *k_packed, const float *v_packed,
+                                   const int *kv_offsets, const int *kv_lengths, float *output,
+                                   float *weights_out, int n_nodes, int n_heads, int head_dim, int max_len,
+                                   float scale);
+
+/* Replaces cuda_batched_varlen_attention_backward (declared src/cuda/agpt_train.cu:78-83;
+ * called src/agpt/batched_depth_backward.cr:471-476, src/cuda/agpt_train.cu:2997-3002).
+ * dq [n_nodes*n_heads, head_dim]; dk_full/dv_full in the packed-prefix layout, fully written. */
+void cuda_batched_varlen_attention_backward(const float *q_packed, const float *k_packed,
+                                            const float *v_packed, const float *attn_weights,
+                                            const float *d_out, const int *kv_offsets, const int *kv_lengths,
+                                            float *dq, float *dk_full, float *dv_full, int n_nodes,
+                                            int n_heads, int head_dim, int max_len, float scale);
+
+/* Replaces cuda_unpack_batched_attn_output (declared src/cuda/agpt_train.cu:84-86; called
+ * src/agpt/batched_depth_forward.cr:776-778): [n*H, hd] -> [n, H*hd]. */
+void cuda_unpack_batched_attn_output(const float *packed_output, float *unpacked_output, int n_nodes,
+                                     int n_heads, int head_dim);
+
+/* Replaces cuda_batched_varlen_attention_L_queries (declared src/cuda/agpt_train.cu:3120-3125;
+ * called :4740-4744): query t of radix node query_to_node[t] attends the node's ancestors plus its
+ * own edge rows 0..j, i.e. the first kv_lengths[node] - (query_offsets[node+1] - t) + 1 packed rows. */
+void cuda_batched_varlen_attention_L_queries(const float *q_packed, const float *k_packed,
+                                             const float *v_packed, const int *query_to_node,
+                                             const int *query_offsets, const int *kv_offsets,
+                                             const int *kv_lengths, float *output, float *weights_out,
+                                             int T_q, int n_heads, int head_dim, int max_kv_len, float scale);
+
+/* Replaces cuda_batched_varlen_attention_L_queries_backward (declared
+ * src/cuda/agpt_train.cu:3126-3132; called :4988-4992).  dk_full/dv_full are accumulated into and
+ * must be zeroed by the caller (:4983-4984); the accumulation order is fixed (no atomics). */
+void cuda_batched_varlen_attention_L_queries_backward(const float *q_packed, const float *k_packed,
+                                                      const float *v_packed, const float *attn_weights,
+                                                      const float *d_out, const int *query_to_node,
+                                                      const int *query_offsets, const int *kv_offsets,
+                                                      const int *kv_lengths, float *dq, float *dk_full,
+                                                      float *dv_full, int T_q, int n_heads, int head_dim,
+                                                      int max_kv_len, float scale);
+
+/* Replaces cuda_sync (declared src/cuda/agpt_train.cu:87; called
+ * src/agpt/batched_depth_forward.cr:772): cudaDeviceSynchronize. */
+void cuda_sync(void);
+
+/* ======================================================================== */
+/* 2. Native boundary                                                        */
+/* ======================================================================== */
+
+/* ---- synthetic workloads (seeded; stand-ins for the reference's corpora) ---- */
+
+/* Order-`order` Markov chain over `vocab` symbols with Zipf(1.1) unigram marginals. */
+int agpt_b200_synth_markov_corpus(int64_t n, int vocab, int order, uint64_t seed, int32_t *out);
+
+/* Level-capped random tree in breadth-first id order; parent_out[i] == -1 for the root's
+ * children.  Returns the node count (<= max_nodes) or a negative error. */
+int64_t agpt_b200_synth_tree(int64_t max_nodes, int max_depth, int root_children, double p_stop,
+                             int max_children, int64_t level_cap, uint64_t seed, int32_t *parent_out);
+
+/* ---- radix trie: build, on-disk directory format, char-position tree ---- */
+
+typedef struct agpt_trie agpt_trie;
+
+typedef struct {
+    int32_t radix_count;        /* including the virtual root, id 0 */
+    int32_t n_depth_files;      /* max endpoint depth + 1 */
+    int64_t total_edge_chars;   /* number of char positions (= attention queries per layer) */
+    int64_t total_counts;
+    int64_t leveled_nodes;      /* nodes of the depth-capped trie incl. root; 0 if loaded from disk */
+    const int32_t *parent, *first_char_depth, *edge_len, *edge_mass, *endpoint_depth, *subtree_key;
+    const int64_t *edge_off;    /* [radix_count+1] into edge_tok (emission order) */
+    const int32_t *edge_tok;
+    const int64_t *cnt_off;     /* [radix_count+1] */
+    const int32_t *cnt_tok, *cnt_val;
+    const int32_t *edge_start;  /* char position of the first edge char (file order) */
+} agpt_trie_info;
+
+/* Replaces StreamingLeveledBuilder#build + StreamingRadixBuilder#build
+ * (src/agpt/streaming_leveled_builder.cr:31, src/agpt/streaming_radix_builder.cr:103): same node
+ * numbering, counts, edge_mass, pruning rule and subtree keys. */
+int agpt_b200_trie_build(const int32_t *corpus, int64_t n, int max_depth, int subtree_level,
+                         int prune_min_mass, int prune_min_depth, agpt_trie **out);
+/* Replaces load_radix_trie (src/cuda/agpt_train.cu:772-946): reads meta.bin + radix_depth_NNN.bin. */
+int agpt_b200_trie_load_dir(const char *dir, agpt_trie **out);
+/* Writes meta.bin, radix_depth_NNN.bin and, when per_subtree != 0, subtrees/radix_subtree_KKKKKK.bin
+ * + manifest.bin, byte-identical to src/agpt/streaming_radix_builder.cr:245-343, :388-451. */
+int agpt_b200_trie_save_dir(const agpt_trie *t, const char *dir, int per_subtree, int32_t corpus_tokens,
+                            int32_t vocab, uint64_t corpus_hash, const char *tokenizer_tag);
+int agpt_b200_trie_info(const agpt_trie *t, agpt_trie_info *out);
+void agpt_b200_trie_free(agpt_trie *t);
+/* FNV-1a corpus hash (src/agpt/trie_corpus.cr:120-134). */
+uint64_t agpt_b200_token_hash(const int32_t *tokens, int64_t n);
+
+/* Char-position tree of a radix trie, in the trainer's char numbering
+ * (src/cuda/agpt_train.cu:832, :892-939): parent char (-1 under the root), token, absolute depth
+ * (1-based), owning radix id.  Each output array has total_edge_chars entries; any may be NULL. */
+int agpt_b200_trie_char_tree(const agpt_trie *t, int32_t *parent, int32_t *token, int32_t *depth,
+                             int32_t *radix_of_char);
+
+/* ---- walker plan: depth-first layout of a tree + tile index ---- */
+
+typedef struct agpt_plan agpt_plan;
+
+typedef struct {
+    int64_t n;                  /* nodes */
+    int32_t tile_m;             /* queries per tile */
+    int64_t n_tiles;
+    int64_t chain_rows;         /* sum over tiles of the first query's ancestor count */
+    int32_t max_depth;
+    int64_t sum_depth;          /* sum over nodes of depth (attended rows incl. self) */
+    int64_t sum_group_prefix;   /* sum over sibling groups of the shared prefix length */
+    int64_t n_groups;           /* sibling groups */
+    int64_t n_reduce_items, n_reduce_nodes;
+    const int32_t *dfs_to_node; /* host: node id at each depth-first position */
+    const int32_t *node_to_dfs; /* host */
+    const int32_t *parent_dfs;  /* host: parent position (-1 under the root) */
+    const int32_t *depth;       /* host: 1-based */
+    const int32_t *sub_end;     /* host: one past the last position of the node's subtree */
+    int device;                 /* CUDA device holding the index arrays, -1 = none */
+} agpt_plan_info;
+
+/* Replaces the ancestor index (src/agpt/batched_depth_forward.cr:351-359,
+ * src/cuda/agpt_train.cu:892-939, :1126-1198) and the walker's ordering
+ * (src/cuda/agpt_train.cu:3602-3736).  parent[i] is a node id or -1; any id order is accepted.
+ * With device >= 0 the index arrays are also allocated on that device (freed by plan_destroy). */
+int agpt_b200_plan_create(const int32_t *parent, int64_t n, int tile_m, int device, agpt_plan **out);
+int agpt_b200_plan_info(const agpt_plan *p, agpt_plan_info *out);
+void agpt_b200_plan_destroy(agpt_plan *p);
+/* Bytes of scratch attn_bwd needs for `d_model` columns. */
+int64_t agpt_b200_attn_bwd_workspace_bytes(const agpt_plan *p, int d_model);
+
+/* Root-child / bigram units of a plan as depth-first ranges (src/cuda/agpt_train.cu:3602-3623,
+ * src/agpt/streaming_radix_builder.cr:215-240).  level 1: one unit per depth-1 node; level 2: one
+ * per depth-2 node, the depth-1 node itself forming a unit of one.  Writes up to cap ranges into
+ * unit_begin/unit_end and returns the count. */
+int64_t agpt_b200_plan_units(const agpt_plan *p, int level, int64_t cap, int64_t *unit_begin,
+                             int64_t *unit_end);
+/* Longest-processing-time assignment of units to ranks; rank_of_unit[u] in [0, n_ranks). */
+int agpt_b200_partition_lpt(const int64_t *unit_weight, int64_t n_units, int n_ranks,
+                            int32_t *rank_of_unit);
+
+/* ---- device kernels (all asynchronous on `stream`, a cudaStream_t passed as void*) ---- */
+
+/* Row gather: dst[i, :] = src[index[i], :] (float32 rows of `cols`).  Used to bring
+ * id-ordered activations into depth-first order and back. */
+int agpt_b200_gather_rows(const float *d_src, const int32_t *d_index, float *d_dst, int64_t n, int cols,
+                          void *stream);
+
+/* Replaces rope_batched_kernel / rope_batched_inverse_kernel (src/cuda/agpt_train.cu:1305-1351):
+ * x [n, n_heads*head_dim] rotated in place, pair (2i, 2i+1) of each head by pos[row]. */
+int agpt_b200_rope(float *d_x, const int32_t *d_pos, const float *d_cos, const float *d_sin, int64_t n,
+                   int n_heads, int head_dim, int inverse, void *stream);
+
+/* Replaces kv_scatter_kernel_bf16 (src/cuda/agpt_train.cu:1537-1554) for a store laid out in
+ * depth-first order: d_store[i, :] = bf16(d_src[i, :]). */
+int agpt_b200_kv_store_write_bf16(const float *d_src, void *d_store_bf16, int64_t n, int cols, void *stream);
+
+/* Replaces kv_gather + cuda_batched_varlen_attention(_L_queries) (src/cuda/agpt_train.cu:4689-4749,
+ * src/agpt/batched_depth_forward.cr:836-971).  d_q, d_out [n, H*hd] float32 in depth-first order;
+ * d_k, d_v the KV store [n, H*hd] of kv_dtype; d_lse [n, H] = log sum exp of the scaled scores. */
+int agpt_b200_attn_fwd(const agpt_plan *p, const float *d_q, const void *d_k, const void *d_v, int kv_dtype,
+                       float *d_out, float *d_lse, int n_heads, int head_dim, float scale, void *stream);
+
+/* Replaces cuda_batched_varlen_attention(_L_queries)_backward + kv_scatter_add
+ * (src/cuda/agpt_train.cu:4982-5035, :1896-1935; src/agpt/batched_depth_backward.cr:605-695).
+ * d_dq, d_dk, d_dv [n, H*hd] float32 fully written; d_dk/d_dv hold, per node, the sum over the node
+ * itself and all its descendants, accumulated in a fixed order.  d_workspace: scratch of
+ * agpt_b200_attn_bwd_workspace_bytes(). */
+int agpt_b200_attn_bwd(const agpt_plan *p, const float *d_q, const void *d_k, const void *d_v, int kv_dtype,
+                       const float *d_out, const float *d_lse, const float *d_dout, float *d_dq, float *d_dk,
+                       float *d_dv, void *d_workspace, int64_t workspace_bytes, int n_heads, int head_dim,
+                       float scale, void *stream);
+
+/* Replaces agpt_loss_per_query_kernel (src/cuda/agpt_train.cu:2069-2216).  Same arguments. */
+int agpt_b200_loss_per_query(const float *d_logits, const int32_t *d_query_to_node,
+                             const int32_t *d_query_offsets, const int32_t *d_radix_ids,
+                             const int32_t *d_token_ids, const int32_t *d_counts_offset,
+                             const int32_t *d_counts_tok, const int32_t *d_counts_val,
+                             const float *d_mass_weights, float *d_dlogits, float *d_loss, int64_t T_q, int V,
+                             float entropy_lambda, float intermediate_weight, int ce_only, void *stream);
+
+/* Replaces agpt_loss_kernel (src/cuda/agpt_train.cu:1947-2044). */
+int agpt_b200_loss_per_node(const float *d_logits, const int32_t *d_node_ids, const int32_t *d_counts_offset,
+                            const int32_t *d_counts_tok, const int32_t *d_counts_val, float *d_dlogits,
+                            float *d_loss, int64_t N, int V, void *stream);
+
+/* Host-buffer convenience of the same step (what gpu_batched_attention /
+ * gpu_attention_backward_depth do around the kernels, src/agpt/batched_depth_forward.cr:745-823,
+ * src/agpt/batched_depth_backward.cr:453-500): uploads q, k, v, d_out from host memory, runs forward
+ * and backward, downloads out, lse, dq, dk, dv.  The device buffers are allocated per call. */
+int agpt_b200_attn_fwd_bwd_host(const agpt_plan *p, const float *h_q, const float *h_k, const float *h_v,
+                                const float *h_dout, float *h_out, float *h_lse, float *h_dq, float *h_dk,
+                                float *h_dv, int kv_dtype, int n_heads, int head_dim, float scale);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AGPT_B200_H */
