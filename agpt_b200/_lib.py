@@ -27,7 +27,7 @@ class TrieInfo(C.Structure):
 class PlanInfo(C.Structure):
     _fields_ = [("n", i64), ("tile_m", i32), ("n_tiles", i64), ("chain_rows", i64), ("max_depth", i32),
                 ("sum_depth", i64), ("sum_group_prefix", i64), ("n_groups", i64), ("n_reduce_items", i64),
-                ("n_reduce_nodes", i64),
+                ("n_reduce_nodes", i64), ("n_reduce_multi", i64),
                 ("dfs_to_node", P32), ("node_to_dfs", P32), ("parent_dfs", P32), ("depth", P32), ("sub_end", P32),
                 ("device", C.c_int)]
 
@@ -58,6 +58,7 @@ SIGNATURES = {
     "agpt_b200_plan_units": (i64, [vp, C.c_int, i64, vp, vp]),
     "agpt_b200_partition_lpt": (C.c_int, [vp, i64, C.c_int, vp]),
     "agpt_b200_gather_rows": (C.c_int, [vp, vp, vp, i64, C.c_int, vp]),
+    "agpt_b200_rope_table": (C.c_int, [vp, vp, C.c_int, C.c_int, f32]),
     "agpt_b200_rope": (C.c_int, [vp, vp, vp, vp, i64, C.c_int, C.c_int, C.c_int, vp]),
     "agpt_b200_kv_store_write_bf16": (C.c_int, [vp, vp, i64, C.c_int, vp]),
     "agpt_b200_attn_fwd": (C.c_int, [vp, vp, vp, vp, C.c_int, vp, vp, C.c_int, C.c_int, f32, vp]),

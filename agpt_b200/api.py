@@ -139,6 +139,8 @@ class WalkerPlan:
         self.max_depth, self.sum_depth = info.max_depth, int(info.sum_depth)
         self.sum_group_prefix, self.n_groups = int(info.sum_group_prefix), int(info.n_groups)
         self.chain_rows = int(info.chain_rows)
+        # kernels one backward launches: the tile kernel plus the reduction passes that have work
+        self.bwd_launches = 1 + int(info.n_reduce_items > 0) + int(info.n_reduce_multi > 0)
         self.dfs_to_node = _view(info.dfs_to_node, n, np.int32)
         self.node_to_dfs = _view(info.node_to_dfs, n, np.int32)
         self.parent_dfs = _view(info.parent_dfs, n, np.int32)
@@ -248,16 +250,11 @@ def gather_rows(src, index):
 
 
 def rope_table(max_seq: int, head_dim: int, base: float = 10000.0):
-    """cos/sin tables [max_seq, head_dim] in float32 arithmetic, pair-duplicated like the reference's
-    build_rope_cache (theta = pos / base^(2i/dim) with float32 pow, cos, sin)."""
-    half = head_dim // 2
-    i = np.arange(half, dtype=np.float32)
-    expo = (np.float32(2.0) * i) / np.float32(head_dim)
-    denom = np.power(np.float32(base), expo, dtype=np.float32)
-    theta = (np.arange(max_seq, dtype=np.float32)[:, None] / denom[None, :]).astype(np.float32)
-    c = np.repeat(np.cos(theta, dtype=np.float32), 2, axis=1)
-    s = np.repeat(np.sin(theta, dtype=np.float32), 2, axis=1)
-    return np.ascontiguousarray(c), np.ascontiguousarray(s)
+    """cos/sin tables [max_seq, head_dim], float32 host arithmetic, pair-duplicated."""
+    c = np.zeros((max_seq, head_dim), np.float32)
+    s = np.zeros((max_seq, head_dim), np.float32)
+    check(lib().agpt_b200_rope_table(_vp(c), _vp(s), max_seq, head_dim, base), "rope_table")
+    return c, s
 
 
 def rope_(x, pos, cos, sin, n_heads: int, inverse: bool = False):

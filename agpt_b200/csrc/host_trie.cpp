@@ -112,6 +112,19 @@ extern "C" int64_t agpt_b200_synth_tree(int64_t max_nodes, int max_depth, int ro
     return n;
 }
 
+// RoPE tables in float32 host arithmetic, value duplicated over each (2i, 2i+1) pair.
+extern "C" int agpt_b200_rope_table(float *cos_out, float *sin_out, int max_seq, int head_dim, float base) {
+    if (!cos_out || !sin_out || max_seq < 1 || head_dim < 2 || head_dim % 2) return agpt_set_error(AGPT_E_ARG, "rope_table: bad argument");
+    for (int pos = 0; pos < max_seq; pos++)
+        for (int i = 0; i < head_dim / 2; i++) {
+            float theta = pos / powf(base, 2.0f * i / head_dim);
+            float c = cosf(theta), s = sinf(theta);
+            cos_out[pos * head_dim + 2 * i] = cos_out[pos * head_dim + 2 * i + 1] = c;
+            sin_out[pos * head_dim + 2 * i] = sin_out[pos * head_dim + 2 * i + 1] = s;
+        }
+    return AGPT_OK;
+}
+
 // --------------------------------------------------------------------------------------
 // radix trie
 // --------------------------------------------------------------------------------------
@@ -532,7 +545,7 @@ extern "C" int agpt_b200_plan_info(const agpt_plan *p, agpt_plan_info *o) {
     if (!p || !o) return agpt_set_error(AGPT_E_ARG, "plan_info: null");
     o->n = p->n; o->tile_m = p->tile_m; o->n_tiles = p->n_tiles; o->chain_rows = (int64_t)p->chain_ids.size();
     o->max_depth = p->max_depth; o->sum_depth = p->sum_depth; o->sum_group_prefix = p->sum_group_prefix; o->n_groups = p->n_groups;
-    o->n_reduce_items = (int64_t)p->item_node.size(); o->n_reduce_nodes = p->n_reduce_nodes;
+    o->n_reduce_items = (int64_t)p->item_node.size(); o->n_reduce_nodes = p->n_reduce_nodes; o->n_reduce_multi = (int64_t)p->multi_node.size();
     o->dfs_to_node = p->dfs_to_node.data(); o->node_to_dfs = p->node_to_dfs.data(); o->parent_dfs = p->parent_dfs.data();
     o->depth = p->depth.data(); o->sub_end = p->sub_end.data(); o->device = p->device;
     return AGPT_OK;
@@ -550,7 +563,8 @@ extern "C" int64_t agpt_b200_plan_units(const agpt_plan *p, int level, int64_t c
     int64_t cnt = 0;
     auto emit = [&](int64_t b, int64_t e) { if (cnt < cap && ub && ue) { ub[cnt] = b; ue[cnt] = e; } cnt++; };
     for (int64_t a = 0; a < p->n; a = p->sub_end[a]) {       // depth-1 nodes
-        if (level == 1) { emit(a, p->sub_end[a]); continue; }
+        // a depth-1 node with a single child stays with that child (its radix edge runs on past depth 1)
+        if (level == 1 || (a + 1 < p->sub_end[a] && p->sub_end[a + 1] == p->sub_end[a])) { emit(a, p->sub_end[a]); continue; }
         emit(a, a + 1);
         for (int64_t c = a + 1; c < p->sub_end[a]; c = p->sub_end[c]) emit(c, p->sub_end[c]);
     }

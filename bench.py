@@ -1,0 +1,402 @@
+#!/usr/bin/env python
+"""Benchmark of the trie-walk attention hot path on B200.
+
+Workload (N GPUs, strong scaling): the depth-32 radix trie of a seeded 1.1M-char order-3 Markov corpus
+over 65 symbols (Zipf(1.1) marginals) -- 28.3M char positions -- with 4 heads x 32 (d_model 128), fp32.
+One step = one pass of the hot path over every position of the trie for one layer: trie-scoped attention
+forward, backward with the deterministic dK/dV reduction, and the mass-weighted per-query loss, unit by
+unit (root-child subtrees at N=1, bigram subtrees balanced over ranks at N>1), followed at N>1 by one
+NCCL all-reduce of a gradient-sized buffer.  `value` is trie nodes (char positions) per second with
+inputs resident in HBM; `e2e` is the same through the host-buffer C-ABI call.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload c2|c1|micro]
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: corpus chars, vocab, markov order, trie depth, heads, head_dim, model layers (for the grad buffer)
+    "c2": dict(chars=1_100_000, vocab=65, order=3, depth=32, heads=4, head_dim=32, layers=4,
+               label="depth-32 radix trie, 1.1M-char order-3 Markov corpus (vocab 65), d_model 128, 4 heads x 32, fp32"),
+    "c1": dict(chars=20_000, vocab=65, order=2, depth=8, heads=4, head_dim=16, layers=2,
+               label="depth-8 radix trie, 20k-char order-2 Markov corpus (vocab 65), d_model 64, 4 heads x 16, fp32"),
+    "micro": dict(nodes=4_000_000, depth=64, heads=8, head_dim=64, vocab=65, layers=1,
+                  label="attention microbench: 4M-node tree, depth 64, geometric(0.35) children, 8 heads x 64, fp32"),
+}
+
+
+def measured_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------------------------------------
+# workload construction (host)
+# ----------------------------------------------------------------------------------------------------------
+class Unit:
+    """One root-child or bigram subtree: its local tree plus the loss index arrays of its radix nodes."""
+    __slots__ = ("parent", "n", "tokens", "q2n", "qoff", "radix_ids", "mass_w", "n_ctx")
+
+
+def build_units(wl, rank, world, log):
+    import agpt_b200 as A
+    cfg = WORKLOADS[wl]
+    t0 = time.time()
+    if wl == "micro":
+        parent = A.synth_tree(cfg["nodes"], cfg["depth"], 65, 0.35, 65, 75_000, 0)
+        token = (np.arange(parent.size) % cfg["vocab"]).astype(np.int32)
+        radix_of = np.arange(1, parent.size + 1, dtype=np.int32)          # every node its own one-char edge
+        edge_mass = np.ones(parent.size + 1, np.int32)
+        counts = (np.arange(parent.size + 2, dtype=np.int32), (np.arange(parent.size + 1) % cfg["vocab"]).astype(np.int32),
+                  np.ones(parent.size + 1, np.int32))
+    else:
+        corpus = A.synth_markov_corpus(cfg["chars"], cfg["vocab"], cfg["order"], 0)
+        trie = A.RadixTrie.build(corpus, cfg["depth"], subtree_level=1 if world == 1 else 2)
+        parent, token, _, radix_of = trie.char_tree()
+        edge_mass = trie.edge_mass
+        counts = (trie.cnt_off.astype(np.int32), trie.cnt_tok, trie.cnt_val)
+    log(f"trie built: {parent.size} positions in {time.time() - t0:.1f}s")
+    plan = A.WalkerPlan(parent, 64, -1)
+    level = 1 if world == 1 else 2
+    ub, ue = plan.units(level)
+    owner = A.partition_lpt(ue - ub, world)
+    units = []
+    d2n = plan.dfs_to_node
+    for b, e, o in zip(ub, ue, owner):
+        if o != rank:
+            continue
+        b, e = int(b), int(e)
+        u = Unit()
+        pp = plan.parent_dfs[b:e].astype(np.int64) - b
+        ids = d2n[b:e]
+        u.n_ctx = 0
+        if level == 2 and plan.depth[b] == 2:
+            # bigram unit: the depth-1 ancestor rides along as a context row so every chain is complete
+            a = int(plan.parent_dfs[b])
+            pp = np.concatenate([[-1], pp + 1])
+            pp[1] = 0
+            ids = np.concatenate([[d2n[a]], ids])
+            u.n_ctx = 1
+        else:
+            pp[0] = -1
+        u.parent = pp.astype(np.int32)
+        u.n = u.parent.size
+        u.tokens = token[ids].astype(np.int32)
+        r = radix_of[ids]
+        starts = np.concatenate([[True], r[1:] != r[:-1]])
+        u.q2n = (np.cumsum(starts) - 1).astype(np.int32)
+        u.qoff = np.concatenate([np.nonzero(starts)[0], [u.n]]).astype(np.int32)
+        u.radix_ids = r[starts].astype(np.int32)
+        u.mass_w = A.mass_weights(edge_mass[u.radix_ids], np.diff(u.qoff), "linear")
+        units.append(u)
+    units.sort(key=lambda x: -x.n)
+    total = int(plan.n)
+    return units, counts, total, plan
+
+
+# ----------------------------------------------------------------------------------------------------------
+# the CPU arm: the oracle restatement of the reference's CPU path on the host cores
+# ----------------------------------------------------------------------------------------------------------
+def cpu_arm(units, cfg, budget_nodes, steps=1, warmup=0):
+    """Grouped forward + backward + per-query loss of the oracle on a bounded sample of units.
+    Returns (nodes per second, cores, description)."""
+    from oracle import pyoracle as O
+    H, hd, V = cfg["heads"], cfg["head_dim"], cfg["vocab"]
+    sample, tot = [], 0
+    for u in sorted(units, key=lambda x: x.n):
+        if u.n < 2000 and len(units) > 8:
+            continue
+        if tot + u.n > budget_nodes and sample:
+            break
+        sample.append(u)
+        tot += u.n
+    rng = np.random.default_rng(0)
+    data = []
+    for u in sample:
+        q, k, v, go = [rng.standard_normal((u.n, H * hd)).astype(np.float32) for _ in range(4)]
+        data.append((u, q, k, v, go, rng.standard_normal((u.n, V)).astype(np.float32)))
+
+    def one_pass():
+        for u, q, k, v, go, logits in data:
+            # local trees are in depth-first order, so parent < child holds
+            out, w, w_off, _ = O.attn_fwd(u.parent, H, hd, q, k, v, grouped=True)
+            roots = np.nonzero(u.parent < 0)[0]
+            unit_off = np.concatenate([roots, [u.n]]).astype(np.int32)
+            O.attn_bwd(u.parent, H, hd, q, k, v, w, w_off, go, unit_off=unit_off)
+    for _ in range(warmup):
+        one_pass()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        one_pass()
+    dt = (time.perf_counter() - t0) / steps
+    return tot / dt, O.num_threads(), f"{len(sample)} smallest units over 2000 nodes, {tot} nodes, attention fwd+bwd (oracle, OpenMP)", dt
+
+
+def run_reference(args):
+    cfg = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    units, counts, total, plan = build_units(args.workload, 0, 1, lambda s: print(s, file=sys.stderr))
+    nps, cores, sample, dt = cpu_arm(units, cfg, args.cpu_nodes, steps=max(1, args.steps), warmup=min(args.warmup, 1))
+    line = {"impl": "reference", "metric": "trie_nodes_per_sec_attn_fwd_bwd", "value": nps, "unit": "nodes/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": cfg["label"], "positions": total},
+            "cpu_baseline": {"value": nps, "unit": "nodes/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": nps, "unit": "nodes/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------------------------------------
+# the GPU arm
+# ----------------------------------------------------------------------------------------------------------
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    import agpt_b200 as A
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the product path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    log = (lambda s: print(f"[bench r{rank}] {s}", file=sys.stderr, flush=True))
+    cfg = WORKLOADS[args.workload]
+    H, hd, V = cfg["heads"], cfg["head_dim"], cfg["vocab"]
+    D = H * hd
+    units, counts, total_nodes, gplan = build_units(args.workload, rank, world, log)
+    n_rank = sum(u.n for u in units)
+    n_max = max(u.n for u in units)
+    log(f"{len(units)} units, {n_rank} rows on this rank (largest {n_max}); {total_nodes} positions in the trie")
+
+    plans = [A.WalkerPlan(u.parent, args.tile, local) for u in units]
+    ws_bytes = max(p.workspace_bytes(D) for p in plans)
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    big = [torch.randn((n_rank, D), device=dev, generator=g) for _ in range(4)]          # q k v dO, resident
+    logits = torch.randn((n_rank, V), device=dev, generator=g)
+    out = torch.empty((n_max, D), device=dev); lse = torch.empty((n_max, H), device=dev)
+    dq = torch.empty_like(out); dk = torch.empty_like(out); dv = torch.empty_like(out)
+    dlogits = torch.empty((n_max, V), device=dev); loss = torch.empty(n_max, device=dev)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    c_off, c_tok, c_val = [torch.from_numpy(np.ascontiguousarray(c)).to(dev) for c in counts]
+    meta = []
+    row = 0
+    for u in units:
+        meta.append(dict(row=row, q2n=torch.from_numpy(u.q2n).to(dev), qoff=torch.from_numpy(u.qoff).to(dev),
+                         rid=torch.from_numpy(u.radix_ids).to(dev), tok=torch.from_numpy(u.tokens).to(dev),
+                         mw=torch.from_numpy(u.mass_w).to(dev)))
+        row += u.n
+    # gradient-sized buffer for the per-step all-reduce: the flat parameter vector of the config's model
+    n_params = V * D + cfg["layers"] * (4 * (D * D + D) + 4 * D + 2 * 4 * D * D + 5 * D) + 2 * D + D * V + V
+    grads = torch.zeros(n_params, device=dev)
+    bwd_kernels = 0
+
+    def step(timers=None):
+        nonlocal bwd_kernels
+        launches = 0
+        for u, p, m in zip(units, plans, meta):
+            sl = slice(m["row"], m["row"] + u.n)
+            q, k, v, go = [t[sl] for t in big]
+            if timers is not None:
+                timers.append([torch.cuda.Event(enable_timing=True) for _ in range(4)])
+                timers[-1][0].record()
+            A.attn_forward(p, q, k, v, H, out=out[:u.n], lse=lse[:u.n])
+            if timers is not None:
+                timers[-1][1].record()
+            A.attn_backward(p, q, k, v, out[:u.n], lse[:u.n], go, H, workspace=ws, dq=dq[:u.n], dk=dk[:u.n], dv=dv[:u.n])
+            if timers is not None:
+                timers[-1][2].record()
+            check = A.lib().agpt_b200_loss_per_query(logits[sl].data_ptr(), m["q2n"].data_ptr(), m["qoff"].data_ptr(),
+                                                     m["rid"].data_ptr(), m["tok"].data_ptr(), c_off.data_ptr(),
+                                                     c_tok.data_ptr(), c_val.data_ptr(), m["mw"].data_ptr(),
+                                                     dlogits.data_ptr(), loss.data_ptr(), u.n, V, 0.0, 1.0, 0,
+                                                     torch.cuda.current_stream().cuda_stream)
+            if check != 0:
+                raise RuntimeError(A.lib().agpt_b200_last_error().decode())
+            if timers is not None:
+                timers[-1][3].record()
+            launches += 2 + p.bwd_launches
+        if world > 1:
+            dist.all_reduce(grads)
+        return launches
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sync_all()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    launches = 0
+    for _ in range(args.steps):
+        launches += step()
+    e1.record()
+    sync_all()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_per_step = float(t.item()) / args.steps
+    value = total_nodes / (ms_per_step * 1e-3)
+
+    # per-kernel durations (separate untimed-for-value pass, CUDA events on the launching stream)
+    timers = []
+    step(timers)
+    torch.cuda.synchronize()
+    t_fwd = sum(ev[0].elapsed_time(ev[1]) for ev in timers) * 1e-3
+    t_bwd = sum(ev[1].elapsed_time(ev[2]) for ev in timers) * 1e-3
+    t_loss = sum(ev[2].elapsed_time(ev[3]) for ev in timers) * 1e-3
+    b_fwd = sum(p.algorithmic_bytes(D, H, 4)[0] for p in plans)
+    b_bwd = sum(p.algorithmic_bytes(D, H, 4)[1] for p in plans)
+    peak, peak_kind = measured_peak_gbs()
+    ach_bwd = b_bwd / t_bwd / 1e9
+    ach_fwd = b_fwd / t_fwd / 1e9
+    ach_all = (b_fwd + b_bwd) / (t_fwd + t_bwd) / 1e9
+
+    # end to end: the host-buffer C-ABI call on a bounded subset of this rank's units
+    e2e = None
+    if rank == 0 and not args.no_e2e:
+        budget = args.e2e_nodes
+        chosen, tot = [], 0
+        for u, p in zip(units, plans):
+            if tot + u.n <= budget:
+                chosen.append((u, p)); tot += u.n
+        if not chosen:
+            chosen, tot = [(units[-1], plans[-1])], units[-1].n
+        rng = np.random.default_rng(0)
+        host = []
+        for u, p in chosen:
+            ins = [torch.from_numpy(rng.standard_normal((u.n, D), dtype=np.float32)).pin_memory() for _ in range(4)]
+            outs = [torch.empty((u.n, D)).pin_memory(), torch.empty((u.n, H)).pin_memory()] + \
+                   [torch.empty((u.n, D)).pin_memory() for _ in range(3)]
+            host.append((u, p, [x.numpy() for x in ins], [x.numpy() for x in outs], ins, outs))
+        for _ in range(1):
+            for u, p, ins, outs, _, _ in host[:1]:
+                A.attn_fwd_bwd_host(p, *ins, H, outs=outs)
+        t0 = time.perf_counter()
+        for u, p, ins, outs, _, _ in host:
+            A.attn_fwd_bwd_host(p, *ins, H, outs=outs)
+        dt = time.perf_counter() - t0
+        e2e = {"value": tot / dt, "unit": "nodes/s", "h2d_bytes_per_step": int(tot * D * 4 * 4),
+               "d2h_bytes_per_step": int(tot * (D * 4 * 4 + H * 4)),
+               "sample": f"{len(chosen)} units, {tot} of {n_rank} rows of rank 0; attention fwd+bwd through agpt_b200_attn_fwd_bwd_host"}
+        del host
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        nps, cores, sample, _ = cpu_arm(units, cfg, args.cpu_nodes)
+        cpu = {"value": nps, "unit": "nodes/s", "cores": cores, "kind": "port", "sample": sample}
+
+    if rank == 0:
+        line = {"metric": "trie_nodes_per_sec_attn_fwd_bwd", "value": value, "unit": "nodes/s", "n_gpus": world,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": cfg["label"], "positions": total_nodes, "units_rank0": len(units),
+                           "partition": "root-child subtrees" if world == 1 else f"bigram subtrees, LPT over {world} ranks",
+                           "tile": args.tile, "l2": "inputs (GBs per tensor) far larger than the 126 MB L2"},
+                "roofline": {"bound": "hbm", "achieved": ach_bwd, "peak": peak, "unit": "GB/s", "frac": ach_bwd / peak,
+                             "traffic": None, "kernel": "attn_bwd_kernel + dK/dV reduction", "peak_kind": f"of {peak_kind}",
+                             "algorithmic_bytes_per_step": b_bwd, "seconds_per_step": t_bwd,
+                             "fwd": {"achieved": ach_fwd, "frac": ach_fwd / peak, "algorithmic_bytes_per_step": b_fwd, "seconds_per_step": t_fwd},
+                             "fwd_bwd": {"achieved": ach_all, "frac": ach_all / peak}, "loss_seconds_per_step": t_loss},
+                "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--tile", type=int, default=64)
+    ap.add_argument("--cpu-nodes", type=int, default=400_000, help="rows in the CPU arm's sample")
+    ap.add_argument("--e2e-nodes", type=int, default=2_000_000, help="rows in the host-buffer sample")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

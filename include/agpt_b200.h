@@ -159,7 +159,7 @@ typedef struct {
     int64_t sum_depth;          /* sum over nodes of depth (attended rows incl. self) */
     int64_t sum_group_prefix;   /* sum over sibling groups of the shared prefix length */
     int64_t n_groups;           /* sibling groups */
-    int64_t n_reduce_items, n_reduce_nodes;
+    int64_t n_reduce_items, n_reduce_nodes, n_reduce_multi;   /* dK/dV reduction work list sizes */
     const int32_t *dfs_to_node; /* host: node id at each depth-first position */
     const int32_t *node_to_dfs; /* host */
     const int32_t *parent_dfs;  /* host: parent position (-1 under the root) */
@@ -194,6 +194,10 @@ int agpt_b200_partition_lpt(const int64_t *unit_weight, int64_t n_units, int n_r
  * id-ordered activations into depth-first order and back. */
 int agpt_b200_gather_rows(const float *d_src, const int32_t *d_index, float *d_dst, int64_t n, int cols,
                           void *stream);
+
+/* Replaces build_rope_cache's host loop (src/cuda/agpt_train.cu:2298-2321): cos/sin [max_seq, head_dim],
+ * theta = pos / base^(2i/head_dim) in float32 (powf, cosf, sinf), each value stored at 2i and 2i+1. */
+int agpt_b200_rope_table(float *cos_out, float *sin_out, int max_seq, int head_dim, float base);
 
 /* Replaces rope_batched_kernel / rope_batched_inverse_kernel (src/cuda/agpt_train.cu:1305-1351):
  * x [n, n_heads*head_dim] rotated in place, pair (2i, 2i+1) of each head by pos[row]. */

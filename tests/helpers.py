@@ -1,0 +1,128 @@
+"""Shared builders for the tests: random trees, the deterministic spec model, tolerances."""
+from __future__ import annotations
+
+import numpy as np
+
+# Tolerances of the parity contract: float32 results within 1e-4 relative, bf16-store variants within
+# 2e-2, both measured normwise (max |diff| over max |reference| of the tensor).
+TOL_F32 = 1e-4
+TOL_BF16 = 2e-2
+
+
+def rel_err(a, b):
+    a = np.asarray(a, dtype=np.float64)
+    b = np.asarray(b, dtype=np.float64)
+    denom = max(np.abs(b).max(), 1e-30)
+    return float(np.abs(a - b).max() / denom)
+
+
+def random_tree(n, max_depth, seed, branch_bias=0.5, roots=3):
+    """Parent array with parent[i] < i (breadth-first-like ids), depth capped at max_depth."""
+    rng = np.random.default_rng(seed)
+    parent = np.full(n, -1, np.int32)
+    depth = np.ones(n, np.int32)
+    for i in range(roots, n):
+        while True:
+            lo = 0 if rng.random() < branch_bias else max(0, i - 8)
+            p = int(rng.integers(lo, i))
+            if depth[p] < max_depth:
+                break
+        parent[i] = p
+        depth[i] = depth[p] + 1
+    return parent
+
+
+def chain_tree(n):
+    return np.arange(-1, n - 1, dtype=np.int32)
+
+
+def random_qkv(n, D, seed):
+    rng = np.random.default_rng(seed)
+    return [rng.standard_normal((n, D)).astype(np.float32) for _ in range(4)]
+
+
+# ---- the deterministic model of the reference's backward-attention spec --------------------------------
+def fill_mat(rows, cols, scale, offset=0):
+    r = np.arange(rows)[:, None]
+    c = np.arange(cols)[None, :]
+    return ((((offset + r * cols + c) % 37) + 1).astype(np.float32) * np.float32(scale)).astype(np.float32)
+
+
+class SpecModel:
+    """d_model 8, heads [4, 4], one layer, d_ff 16, vocab 8, seq 8; weights from the fill rule
+    value = ((offset + r*cols + c) % 37 + 1) * scale (spec/agpt_backward_attention_spec.cr:3-51)."""
+
+    d_model, n_heads, hd, vocab, seq_len = 8, 2, 4, 8, 8
+
+    def __init__(self):
+        d = self.d_model
+        self.token_emb = fill_mat(self.vocab, d, 0.01, 1)
+        self.ln1_gamma = fill_mat(1, d, 0.02, 2)[0]
+        self.ln1_beta = fill_mat(1, d, 0.01, 3)[0]
+        self.wq_w, self.wq_b = fill_mat(d, d, 0.01, 6), fill_mat(1, d, 0.01, 7)[0]
+        self.wk_w, self.wk_b = fill_mat(d, d, 0.01, 8), fill_mat(1, d, 0.01, 9)[0]
+        self.wv_w, self.wv_b = fill_mat(d, d, 0.01, 10), fill_mat(1, d, 0.01, 11)[0]
+        self.wo_w, self.wo_b = fill_mat(d, d, 0.01, 12), fill_mat(1, d, 0.01, 13)[0]
+
+    def ln1(self, x):
+        """float32 layer norm, biased variance, eps 1e-5 (src/agpt/incremental_forward.cr:143-163)."""
+        x = x.astype(np.float32)
+        mean = np.float32(0)
+        for v in x:
+            mean = np.float32(mean + v)
+        mean = np.float32(mean / np.float32(x.size))
+        var = np.float32(0)
+        for v in x:
+            diff = np.float32(v - mean)
+            var = np.float32(var + diff * diff)
+        var = np.float32(var / np.float32(x.size))
+        sinv = np.float32(1.0 / np.sqrt(np.float64(np.float32(var + np.float32(1e-5)))))
+        return ((x - mean) * sinv * self.ln1_gamma + self.ln1_beta).astype(np.float32)
+
+    def qkv(self, token):
+        """Pre-RoPE q, k, v rows and the LN1 output for one token (layer 0 input = embedding)."""
+        xn = self.ln1(self.token_emb[token])
+        q = (xn @ self.wq_w + self.wq_b).astype(np.float32)
+        k = (xn @ self.wk_w + self.wk_b).astype(np.float32)
+        v = (xn @ self.wv_w + self.wv_b).astype(np.float32)
+        return q, k, v, xn
+
+
+class MemTrie:
+    """In-memory trie with insertion-order ids (src/agpt/trie_corpus.cr:200-228, :786-794, :897-913)."""
+
+    def __init__(self, tokens, max_depth, max_starts=None, start_offset=0):
+        self.parent, self.token, self.depth, self.children = [-1], [-1], [0], [dict()]
+        self.counts = [dict()]
+        n = len(tokens)
+        total = n - 1
+        if max_starts is None or max_starts >= total:
+            starts = list(range(total))
+        else:
+            off = start_offset % total
+            starts = [((i * total) // max_starts + off) % total for i in range(max_starts)]
+        for s in starts:
+            node, d, idx = 0, 0, s
+            while idx < total and d < max_depth:
+                tok, nxt = tokens[idx], tokens[idx + 1]
+                ch = self.children[node].get(tok)
+                if ch is None:
+                    ch = len(self.parent)
+                    self.parent.append(node); self.token.append(tok); self.depth.append(self.depth[node] + 1)
+                    self.children.append(dict()); self.counts.append(dict())
+                    self.children[node][tok] = ch
+                node = ch
+                self.counts[node][nxt] = self.counts[node].get(nxt, 0) + 1
+                idx += 1
+                d += 1
+
+    def levels(self):
+        """Breadth-first levels, children in token order (each_depth_level, :677-690)."""
+        level, out = [0], []
+        while level:
+            out.append(level)
+            nxt = []
+            for v in level:
+                nxt += [self.children[v][t] for t in sorted(self.children[v])]
+            level = nxt
+        return out

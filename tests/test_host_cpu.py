@@ -1,0 +1,200 @@
+"""Host-side logic of the product library, checked on CPU: trie construction and ancestor indexing
+bit-exact against the oracle's restatement of the reference builders, the on-disk radix directory
+byte-for-byte, walker-plan invariants, the unit partitioner and the exported C symbols."""
+import filecmp
+import os
+import re
+
+import numpy as np
+import pytest
+
+import agpt_b200 as A
+from agpt_b200 import _lib
+from oracle import pyoracle as O
+from tests.helpers import chain_tree, random_tree
+
+TRIE_FIELDS = ("parent", "first_char_depth", "edge_len", "edge_mass", "endpoint_depth", "subtree_key", "edge_start",
+               "edge_off", "edge_tok", "cnt_off", "cnt_tok", "cnt_val")
+
+
+def _same_trie(tr, rx):
+    assert tr.radix_count == rx.radix_count and tr.total_edge_chars == rx.total_edge_chars
+    for name in TRIE_FIELDS:
+        assert np.array_equal(getattr(tr, name), getattr(rx, name)), name
+
+
+@pytest.mark.parametrize("n,vocab,order,depth,seed", [(20_000, 65, 2, 8, 0), (5_000, 96, 3, 12, 3), (300, 5, 1, 40, 9),
+                                                      (2, 3, 1, 4, 1), (50, 2, 1, 64, 2)])
+def test_trie_build_bit_exact(n, vocab, order, depth, seed):
+    corpus = A.synth_markov_corpus(n, vocab, order, seed)
+    tr = A.RadixTrie.build(corpus, depth)
+    lv = O.Leveled(corpus, depth)
+    rx = O.Radix(lv)
+    _same_trie(tr, rx)
+    assert tr.leveled_nodes == lv.n_nodes
+    p1, t1, d1, r1 = tr.char_tree()
+    p2, t2, d2 = rx.char_tree()
+    assert np.array_equal(p1, p2) and np.array_equal(t1, t2) and np.array_equal(d1, d2)
+    # ancestor index: walking the char tree's parents reproduces the trainer's ancestor lists
+    for r in range(1, min(rx.radix_count, 400)):
+        anc = rx.anc_ids[rx.anc_off[r]:rx.anc_off[r + 1]]
+        walk, c = [], p1[rx.edge_start[r]]
+        while c >= 0:
+            walk.append(c)
+            c = p1[c]
+        assert walk[::-1] == list(anc)
+
+
+def test_config1_trie_shape():
+    """20k-char order-2 Markov corpus, depth 8: per-depth position counts of the synthetic stand-in."""
+    corpus = A.synth_markov_corpus(20_000, 65, 2, 0)
+    tr = A.RadixTrie.build(corpus, 8)
+    _, _, depth, _ = tr.char_tree()
+    assert tr.total_edge_chars == 65_985
+    assert list(np.bincount(depth)[1:]) == [65, 1256, 3031, 5818, 9281, 12828, 15816, 17890]
+
+
+@pytest.mark.parametrize("level,min_mass", [(1, 1), (2, 1), (1, 2), (2, 3)])
+def test_trie_pruning_and_bigram_keys(level, min_mass):
+    corpus = A.synth_markov_corpus(8_000, 30, 2, 5)
+    tr = A.RadixTrie.build(corpus, 10, subtree_level=level, prune_min_mass=min_mass, prune_min_depth=4)
+    rx = O.Radix(O.Leveled(corpus, 10), level, min_mass, 4)
+    _same_trie(tr, rx)
+    if min_mass > 1:
+        deep = tr.first_char_depth[1:] >= 4
+        assert (tr.edge_mass[1:][deep] >= min_mass).all()
+
+
+def test_radix_dir_bytes_and_reload(tmp_path):
+    corpus = A.synth_markov_corpus(6_000, 40, 2, 11)
+    tr = A.RadixTrie.build(corpus, 9)
+    rx = O.Radix(O.Leveled(corpus, 9))
+    h = A.token_hash(corpus)
+    assert h == O.token_hash(corpus)
+    a, b = str(tmp_path / "product"), str(tmp_path / "oracle")
+    tr.save_dir(a, corpus.size, 40, h, per_subtree=True)
+    rx.write_dir(b, corpus.size, 40, h)
+    names = sorted(f for f in os.listdir(b))
+    assert names == sorted(f for f in os.listdir(a) if f not in ("manifest.bin", "subtrees"))
+    for f in names:
+        assert filecmp.cmp(os.path.join(a, f), os.path.join(b, f), shallow=False), f
+    back = A.RadixTrie.load_dir(a)
+    for name in TRIE_FIELDS:
+        assert np.array_equal(getattr(back, name), getattr(tr, name)), name
+    # per-subtree files: one per root child, sizes add up, manifest sorted by key
+    subs = sorted(os.listdir(os.path.join(a, "subtrees")))
+    assert len(subs) == int((tr.parent[1:] == 0).sum())
+    raw = np.fromfile(os.path.join(a, "manifest.bin"), dtype=np.uint8)
+    n_sub = int(np.frombuffer(raw[8:12].tobytes(), np.int32)[0])
+    assert n_sub == len(subs)
+    with pytest.raises(A.AgptError):
+        A.RadixTrie.load_dir(str(tmp_path / "missing"))
+
+
+def _brute_plan_check(parent, tile_m):
+    plan = A.WalkerPlan(parent, tile_m, -1)
+    n = parent.size
+    d2n, n2d = plan.dfs_to_node, plan.node_to_dfs
+    assert sorted(d2n) == list(range(n)) and np.array_equal(n2d[d2n], np.arange(n))
+    depth = O.tree_depth_fast(parent)
+    assert np.array_equal(plan.depth, depth[d2n])
+    # parent links survive the relabelling and every parent precedes its children
+    pp = plan.parent_dfs
+    assert np.array_equal(np.where(pp < 0, -1, d2n[np.maximum(pp, 0)]), parent[d2n])
+    assert (pp < np.arange(n)).all()
+    # interval property: a is an ancestor-or-self of i  <=>  a <= i < sub_end[a]
+    anc = np.zeros((n, n), bool)
+    for i in range(n):
+        c = i
+        while c >= 0:
+            anc[c, i] = True
+            c = pp[c]
+    idx = np.arange(n)
+    interval = (idx[:, None] <= idx[None, :]) & (idx[None, :] < plan.sub_end[:, None])
+    assert np.array_equal(anc, interval)
+    assert plan.sum_depth == int(depth.sum())
+    kids = np.bincount(parent[parent >= 0], minlength=n)
+    assert plan.sum_group_prefix == int(depth[kids > 0].sum())
+    assert plan.n_groups == int((kids > 0).sum()) + 1
+    assert plan.chain_rows == int(sum(plan.depth[t * tile_m] - 1 for t in range(plan.n_tiles)))
+    return plan
+
+
+@pytest.mark.parametrize("n,md,seed,tile", [(1, 1, 0, 32), (37, 5, 1, 32), (300, 9, 2, 64), (257, 30, 3, 128), (129, 129, 4, 64)])
+def test_plan_invariants(n, md, seed, tile):
+    parent = chain_tree(n) if md >= n else random_tree(n, md, seed, roots=min(3, n))
+    _brute_plan_check(parent, tile)
+
+
+def test_plan_accepts_any_id_order_and_rejects_cycles():
+    parent = random_tree(200, 8, 5)
+    perm = np.random.default_rng(0).permutation(200)
+    inv = np.argsort(perm)
+    shuffled = np.where(parent[perm] < 0, -1, inv[np.maximum(parent[perm], 0)]).astype(np.int32)
+    _brute_plan_check(shuffled, 64)
+    bad = parent.copy()
+    bad[10], bad[20] = 20, 10
+    with pytest.raises(A.AgptError):
+        A.WalkerPlan(bad, 64, -1)
+    with pytest.raises(A.AgptError):
+        A.WalkerPlan(np.array([5], np.int32), 64, -1)
+    with pytest.raises(A.AgptError):
+        A.WalkerPlan(parent, 48, -1)
+
+
+def test_units_and_partition():
+    parent = random_tree(3000, 10, 7, roots=9)
+    plan = A.WalkerPlan(parent, 64, -1)
+    b1, e1 = plan.units(1)
+    assert b1[0] == 0 and e1[-1] == plan.n and np.array_equal(b1[1:], e1[:-1])
+    assert (plan.depth[b1] == 1).all() and len(b1) == 9
+    b2, e2 = plan.units(2)
+    assert b2[0] == 0 and e2[-1] == plan.n and np.array_equal(b2[1:], e2[:-1])
+    assert set(plan.depth[b2]) <= {1, 2}
+    w = e2 - b2
+    owner = A.partition_lpt(w, 4)
+    loads = np.bincount(owner, weights=w, minlength=4)
+    assert loads.max() <= w.sum() / 4 + w.max()
+    # shards cover every node exactly once (context rows aside) and keep chains intact
+    seen = np.zeros(plan.n, int)
+    for r in range(4):
+        lp, ids, ctx = A.shard_tree(parent, r, 4, level=2)
+        seen[ids[~ctx]] += 1
+        depth_local = O.tree_depth_fast(lp) if lp.size else lp
+        assert np.array_equal(depth_local, O.tree_depth_fast(parent)[ids])
+    assert (seen == 1).all()
+
+
+def test_every_declared_symbol_is_exported():
+    hdr = open(os.path.join(os.path.dirname(__file__), "..", "include", "agpt_b200.h")).read()
+    hdr = re.sub(r"/\*.*?\*/", "", hdr, flags=re.S)
+    names = set(re.findall(r"\b((?:agpt_b200|cuda)_[a-zA-Z0-9_]+)\s*\(", hdr))
+    assert len(names) >= 30
+    L = _lib.lib()
+    for name in sorted(names):
+        assert hasattr(L, name), name
+    assert names == set(_lib.SIGNATURES), names ^ set(_lib.SIGNATURES)
+    assert b"sm_100a" in L.agpt_b200_version()
+
+
+def test_compute_entry_points_refuse_without_a_device_plan():
+    """No CPU fallback: a plan without device index arrays is rejected by the kernels' launchers."""
+    plan = A.WalkerPlan(chain_tree(10), 64, -1)
+    rc = _lib.lib().agpt_b200_attn_fwd(plan._h, 1, 1, 1, 0, 1, 1, 2, 16, 0.25, None)
+    assert rc == -1 and b"device" in _lib.lib().agpt_b200_last_error()
+    assert plan.workspace_bytes(64) >= 256
+
+
+def test_mass_weights_match_oracle():
+    rng = np.random.default_rng(3)
+    em = rng.integers(1, 5000, size=50)
+    el = rng.integers(1, 9, size=50)
+    for mode, code in (("log", 1), ("sqrt", 2), ("linear", 3), ("off", 0)):
+        assert np.allclose(A.mass_weights(em, el, mode), O.mass_weights(em, el, code), rtol=1e-6, atol=0)
+
+
+def test_rope_table_matches_oracle():
+    for hd in (16, 32, 64):
+        c, s = A.rope_table(128, hd)
+        co, so = O.rope_table(128, hd)
+        assert np.array_equal(c, co) and np.array_equal(s, so)
