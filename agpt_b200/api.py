@@ -27,9 +27,10 @@ def _vp(a):
 
 
 def _view(ptr, n, dtype):
+    """Copy of a C array owned by a library handle (the copy outlives the handle)."""
     if n == 0:
         return np.zeros(0, dtype=dtype)
-    return np.ctypeslib.as_array(ptr, shape=(int(n),))
+    return np.ctypeslib.as_array(ptr, shape=(int(n),)).astype(dtype, copy=True)
 
 
 # ----------------------------------------------------------------------------------------

@@ -655,6 +655,7 @@ __global__ void loss_kernel(const float *__restrict__ logits, const int32_t *__r
         __syncwarp();
         for (int e = start + lane; e < end; e += 32) {
             int tok = counts_tok[e];
+            if ((unsigned)tok >= (unsigned)V) continue;      // a token outside the vocabulary is ignored, not written
             float tgt = counts_val[e] / total_f;
             float pr = expf(in[tok] - mx) * inv;
             loss -= tgt * logf(pr + 1e-10f);
@@ -662,7 +663,8 @@ __global__ void loss_kernel(const float *__restrict__ logits, const int32_t *__r
         }
         loss = warp_sum(loss) * weight;
     } else {
-        const int target = token_ids[qi + 1];
+        int target = token_ids[qi + 1];
+        if ((unsigned)target >= (unsigned)V) target = 0;      // never index outside the row
         weight = intermediate_weight;
         if (mass_weights) weight *= mass_weights[qi];
         for (int j = lane; j < V; j += 32) {

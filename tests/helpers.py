@@ -9,10 +9,12 @@ TOL_F32 = 1e-4
 TOL_BF16 = 2e-2
 
 
-def rel_err(a, b):
+def rel_err(a, b, floor=1e-2):
+    """max |a - b| over max |b|; the denominator is floored so that a reference tensor that is exactly
+    zero (a one-node tree has dq == 0) is compared absolutely at floor * tolerance."""
     a = np.asarray(a, dtype=np.float64)
     b = np.asarray(b, dtype=np.float64)
-    denom = max(np.abs(b).max(), 1e-30)
+    denom = max(np.abs(b).max(), floor)
     return float(np.abs(a - b).max() / denom)
 
 
