@@ -32,6 +32,11 @@ WORKLOADS = {
                label="depth-32 radix trie, 1.1M-char order-3 Markov corpus (vocab 65), d_model 128, 4 heads x 32, fp32"),
     "c1": dict(chars=20_000, vocab=65, order=2, depth=8, heads=4, head_dim=16, layers=2,
                label="depth-8 radix trie, 20k-char order-2 Markov corpus (vocab 65), d_model 64, 4 heads x 16, fp32"),
+    # reduced copies of the two above for profiler captures (inputs still larger than L2, a few GB on the device)
+    "c2s": dict(chars=50_000, vocab=65, order=3, depth=32, heads=4, head_dim=32, layers=4,
+                label="depth-32 radix trie, 50k-char order-3 Markov corpus (vocab 65), d_model 128, 4 heads x 32, fp32"),
+    "micro_s": dict(nodes=600_000, depth=64, heads=8, head_dim=64, vocab=65, layers=1,
+                    label="attention microbench, reduced: 600k-node tree, depth 64, 8 heads x 64, fp32"),
     "micro": dict(nodes=4_000_000, depth=64, heads=8, head_dim=64, vocab=65, layers=1,
                   label="attention microbench: 4M-node tree, depth 64, geometric(0.35) children, 8 heads x 64, fp32"),
 }
@@ -99,11 +104,11 @@ class Unit:
     __slots__ = ("parent", "n", "tokens", "q2n", "qoff", "radix_ids", "mass_w", "n_ctx")
 
 
-def build_units(wl, rank, world, log):
+def build_units(wl, rank, world, log, single_unit=False):
     import agpt_b200 as A
     cfg = WORKLOADS[wl]
     t0 = time.time()
-    if wl == "micro":
+    if wl.startswith("micro"):
         parent = A.synth_tree(cfg["nodes"], cfg["depth"], 65, 0.35, 65, 75_000, 0)
         token = (np.arange(parent.size) % cfg["vocab"]).astype(np.int32)
         radix_of = np.arange(1, parent.size + 1, dtype=np.int32)          # every node its own one-char edge
@@ -120,6 +125,8 @@ def build_units(wl, rank, world, log):
     plan = A.WalkerPlan(parent, 64, -1)
     level = 1 if world == 1 else 2
     ub, ue = plan.units(level)
+    if single_unit:       # the whole forest as one launch (profiling); its depth-1 nodes stay roots
+        ub, ue = np.array([0], np.int64), np.array([plan.n], np.int64)
     owner = A.partition_lpt(ue - ub, world)
     units = []
     d2n = plan.dfs_to_node
@@ -139,7 +146,7 @@ def build_units(wl, rank, world, log):
             ids = np.concatenate([[d2n[a]], ids])
             u.n_ctx = 1
         else:
-            pp[0] = -1
+            pp[plan.parent_dfs[b:e] < 0] = -1
         u.parent = pp.astype(np.int32)
         u.n = u.parent.size
         u.tokens = token[ids].astype(np.int32)
@@ -230,7 +237,7 @@ def run_gpu(args):
     cfg = WORKLOADS[args.workload]
     H, hd, V = cfg["heads"], cfg["head_dim"], cfg["vocab"]
     D = H * hd
-    units, counts, total_nodes, gplan = build_units(args.workload, rank, world, log)
+    units, counts, total_nodes, gplan = build_units(args.workload, rank, world, log, args.single_unit)
     n_rank = sum(u.n for u in units)
     n_max = max(u.n for u in units)
     log(f"{len(units)} units, {n_rank} rows on this rank (largest {n_max}); {total_nodes} positions in the trie")
@@ -292,7 +299,8 @@ def run_gpu(args):
             dist.barrier()
             torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
+    n_warm = args.warmup if args.profile else max(args.warmup, 3)
+    for _ in range(n_warm):
         step()
     sync_all()
     sampler = ClockSampler(local)
@@ -363,7 +371,7 @@ def run_gpu(args):
 
     if rank == 0:
         line = {"metric": "trie_nodes_per_sec_attn_fwd_bwd", "value": value, "unit": "nodes/s", "n_gpus": world,
-                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+                "steps": args.steps, "warmup": n_warm, "ms_per_step": ms_per_step, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": {"workload": cfg["label"], "positions": total_nodes, "units_rank0": len(units),
                            "partition": "root-child subtrees" if world == 1 else f"bigram subtrees, LPT over {world} ranks",
@@ -389,9 +397,13 @@ def main():
     ap.add_argument("--tile", type=int, default=64)
     ap.add_argument("--cpu-nodes", type=int, default=400_000, help="rows in the CPU arm's sample")
     ap.add_argument("--e2e-nodes", type=int, default=2_000_000, help="rows in the host-buffer sample")
+    ap.add_argument("--single-unit", action="store_true", help="one plan over the whole trie instead of per-subtree units")
+    ap.add_argument("--profile", action="store_true", help="profiler capture mode: warm-up as given, no e2e, no CPU arm")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
+    if args.profile:
+        args.no_e2e = args.no_cpu = True
     if args.impl == "reference":
         run_reference(args)
     else:
