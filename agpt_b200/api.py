@@ -317,6 +317,24 @@ def attn_backward(plan: WalkerPlan, q, k, v, out, lse, dout, n_heads: int, scale
     return dq, dk, dv
 
 
+def static_scratch_bytes() -> int:
+    return int(lib().agpt_b200_static_scratch_bytes())
+
+
+def attn_backward_static(plan: WalkerPlan, q, k, v, out, lse, dout, n_heads: int, dq, dk, dv, scale: float | None = None):
+    """attn_backward for callers that cannot allocate: the partial dK/dV rows go to the library's built-in
+    64 MiB device array, so no workspace is passed and the call allocates nothing (the three gradient
+    tensors are the caller's).  Plans needing more scratch than the array holds raise AgptError."""
+    _chk_f32(q, "q")
+    _chk_f32(dout, "dout")
+    n, D = q.shape
+    hd = D // n_heads
+    scale = 1.0 / math.sqrt(hd) if scale is None else scale
+    check(lib().agpt_b200_attn_bwd_static(plan._h, _dp(q), _dp(k), _dp(v), _kv_dtype(k), _dp(out), _dp(lse), _dp(dout),
+                                          _dp(dq), _dp(dk), _dp(dv), n_heads, hd, scale, _stream()), "attn_bwd_static")
+    return dq, dk, dv
+
+
 def attn_fwd_bwd_host(plan: WalkerPlan, q, k, v, dout, n_heads: int, kv_dtype: int = KV_F32, scale=None,
                       outs=None):
     """Host-buffer step: numpy float32 arrays in and out."""

@@ -998,3 +998,57 @@ extern "C" int agpt_b200_attn_fwd_bwd_host(const agpt_plan *p, const float *h_q,
     cleanup();
     return AGPT_OK;
 }
+
+// --------------------------------------------------------------------------------------
+// backward without any allocation: scratch in a fixed device array
+// --------------------------------------------------------------------------------------
+// Some callers of this library cannot obtain device memory at the point where they run the backward
+// pass: a host runtime that took the whole device at start-up and hands out slices of its own pool
+// (so cudaMalloc would fail or fragment what is left), or a step whose buffer set was fixed once and
+// must not grow.  For them the partial dK/dV rows live in this array instead of a caller workspace.
+// It is part of the module image, so every GPU that loads the library holds AGPT_STATIC_SCRATCH_BYTES
+// of it until the process exits.
+#define AGPT_STATIC_SCRATCH_BYTES (64ll << 20)
+static __device__ __align__(256) unsigned char g_static_scratch[AGPT_STATIC_SCRATCH_BYTES];
+
+#define AGPT_MAX_DEVICES 64
+static void *g_static_scratch_addr[AGPT_MAX_DEVICES];   // device address of the array, per device; nullptr = not looked up yet
+
+extern "C" int64_t agpt_b200_static_scratch_bytes(void) { return AGPT_STATIC_SCRATCH_BYTES; }
+
+extern "C" int agpt_b200_attn_bwd_static(const agpt_plan *p, const float *d_q, const void *d_k, const void *d_v, int kv_dtype,
+                                         const float *d_out, const float *d_lse, const float *d_dout, float *d_dq, float *d_dk,
+                                         float *d_dv, int n_heads, int head_dim, float scale, void *stream) {
+    int rc = check_common(p, n_heads, head_dim, "attn_bwd_static");
+    if (rc) return rc;
+    if (!d_q || !d_k || !d_v || !d_out || !d_lse || !d_dout || !d_dq || !d_dk || !d_dv)
+        return agpt_set_error(AGPT_E_ARG, "attn_bwd_static: null buffer");
+    if (kv_dtype != AGPT_KV_F32 && kv_dtype != AGPT_KV_BF16) return agpt_set_error(AGPT_E_ARG, "attn_bwd_static: bad kv_dtype");
+    const int D = n_heads * head_dim;
+    const int64_t need = agpt_b200_attn_bwd_workspace_bytes(p, D);
+    if (need > AGPT_STATIC_SCRATCH_BYTES)
+        return agpt_set_error(AGPT_E_LIMIT,
+                              "attn_bwd_static: this plan needs %lld bytes of scratch, the built-in array holds %lld; "
+                              "use agpt_b200_attn_bwd with a caller workspace or split the trie into smaller units",
+                              (long long)need, (long long)AGPT_STATIC_SCRATCH_BYTES);
+    int cur = -1;
+    CUDA_TRY(cudaGetDevice(&cur));
+    if (cur != p->device) return agpt_set_error(AGPT_E_ARG, "attn_bwd_static: current device %d is not the plan's device %d", cur, p->device);
+    if (cur < 0 || cur >= AGPT_MAX_DEVICES) return agpt_set_error(AGPT_E_LIMIT, "attn_bwd_static: device index %d beyond %d", cur, AGPT_MAX_DEVICES);
+    if (!g_static_scratch_addr[cur]) {
+        // In host code the array's name is only a handle; the address a kernel can use comes from the runtime,
+        // per device, with that device current.
+        void *addr = nullptr;
+        CUDA_TRY(cudaGetSymbolAddress(&addr, g_static_scratch));
+        if (!addr) return agpt_set_error(AGPT_E_CUDA, "attn_bwd_static: cudaGetSymbolAddress returned a null address");
+        g_static_scratch_addr[cur] = addr;
+    }
+    // Every partial row and every segment sum the reduction reads is written earlier in this same call, so nothing
+    // left in the array by a previous call is ever read and nothing needs clearing.
+    const int64_t rows = (int64_t)p->chain_ids.size();
+    float *pk = (float *)g_static_scratch_addr[cur], *pv = pk + rows * D, *segk = pv + rows * D, *segv = segk + p->n_multi_items * D;
+    rc = bwd_dispatch(p, d_q, d_k, d_v, kv_dtype, d_out, d_lse, d_dout, d_dq, d_dk, d_dv, pk, pv, n_heads, head_dim, scale,
+                      (cudaStream_t)stream);
+    if (rc) return rc;
+    return run_reduce(p, pk, pv, segk, segv, d_dk, d_dv, D, (cudaStream_t)stream);
+}

@@ -224,6 +224,24 @@ int agpt_b200_attn_bwd(const agpt_plan *p, const float *d_q, const void *d_k, co
                        float *d_dv, void *d_workspace, int64_t workspace_bytes, int n_heads, int head_dim,
                        float scale, void *stream);
 
+/* No counterpart in the reference.  agpt_b200_attn_bwd for callers that cannot allocate device memory
+ * when the backward runs -- a runtime that claimed the whole GPU at start-up and sub-allocates from its own
+ * pool, or a step whose set of buffers is frozen -- and therefore have no workspace to pass.  The partial
+ * dK/dV rows go to an array built into the library instead: agpt_b200_static_scratch_bytes() bytes
+ * (64 MiB), resident on every GPU that loads the library for as long as the process lives.  Same inputs,
+ * outputs and results as agpt_b200_attn_bwd.  A plan whose agpt_b200_attn_bwd_workspace_bytes() exceeds the
+ * array is refused with AGPT_E_LIMIT.  The call performs no cudaMalloc/cudaFree and calls no allocating
+ * routine.  The plan's device must be the current device.  The first call on each device looks up the
+ * array's device address (cudaGetSymbolAddress), so make that first call outside any stream capture.  All
+ * calls on one GPU share the array: two calls whose kernels may overlap (different streams, or different
+ * host threads) race on it -- keep them on one stream or serialise them.  Nothing in the array has to be
+ * cleared between calls: every element a call reads it has written first. */
+int agpt_b200_attn_bwd_static(const agpt_plan *p, const float *d_q, const void *d_k, const void *d_v,
+                              int kv_dtype, const float *d_out, const float *d_lse, const float *d_dout,
+                              float *d_dq, float *d_dk, float *d_dv, int n_heads, int head_dim, float scale,
+                              void *stream);
+int64_t agpt_b200_static_scratch_bytes(void);
+
 /* Replaces agpt_loss_per_query_kernel (src/cuda/agpt_train.cu:2069-2216).  Same arguments. */
 int agpt_b200_loss_per_query(const float *d_logits, const int32_t *d_query_to_node,
                              const int32_t *d_query_offsets, const int32_t *d_radix_ids,
