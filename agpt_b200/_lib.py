@@ -63,6 +63,7 @@ SIGNATURES = {
     "agpt_b200_kv_store_write_bf16": (C.c_int, [vp, vp, i64, C.c_int, vp]),
     "agpt_b200_attn_fwd": (C.c_int, [vp, vp, vp, vp, C.c_int, vp, vp, C.c_int, C.c_int, f32, vp]),
     "agpt_b200_attn_bwd": (C.c_int, [vp, vp, vp, vp, C.c_int, vp, vp, vp, vp, vp, vp, vp, i64, C.c_int, C.c_int, f32, vp]),
+    "agpt_b200_set_attn_impl": (C.c_int, [C.c_int]),
     "agpt_b200_attn_bwd_static": (C.c_int, [vp, vp, vp, vp, C.c_int, vp, vp, vp, vp, vp, vp, C.c_int, C.c_int, f32, vp]),
     "agpt_b200_static_scratch_bytes": (i64, []),
     "agpt_b200_loss_per_query": (C.c_int, [vp] * 11 + [i64, C.c_int, f32, f32, C.c_int, vp]),

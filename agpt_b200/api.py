@@ -317,6 +317,11 @@ def attn_backward(plan: WalkerPlan, q, k, v, out, lse, dout, n_heads: int, scale
     return dq, dk, dv
 
 
+def set_attn_impl(impl: int) -> None:
+    """1 = tensor-core kernels (default), 0 = FP32 FMA kernels."""
+    check(lib().agpt_b200_set_attn_impl(impl), "set_attn_impl")
+
+
 def static_scratch_bytes() -> int:
     return int(lib().agpt_b200_static_scratch_bytes())
 

@@ -11,6 +11,7 @@
 
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 
 #include "../../include/agpt_b200.h"
 #include "internal.h"
@@ -200,6 +201,189 @@ __global__ void __launch_bounds__(M) attn_fwd_kernel(const float *__restrict__ Q
 }
 
 // --------------------------------------------------------------------------------------
+// forward on the tensor cores: mma.sync m16n8k8 TF32 with error compensation.
+//
+// A tile of 64 depth-first-consecutive queries against (chain + tile) keys is a dense 64 x (p + 64)
+// problem with an interval mask, so QK^T and PV run as 16x8x8 MMAs: 4 warps x 16 query rows, key blocks of
+// 8.  float32 parity needs more than TF32's 10-bit mantissa, so every operand is split x = hi + lo
+// (hi = x rounded to TF32) and each product is hi*hi + lo*hi + hi*lo (the dropped lo*lo term is ~2^-22
+// relative).  A bf16 store is exact in TF32, so its lo part is absent and two MMAs suffice.  A warp skips
+// every 16x8 block in which none of its queries may attend any of the 8 keys.
+// --------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t tf32_round(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ void tf32_split(float x, uint32_t &hi, uint32_t &lo) {
+    hi = tf32_round(x);
+    lo = __float_as_uint(x - __uint_as_float(hi));
+}
+__device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Like stage_keys, for 128 threads, and rows beyond cnt are zero-filled (they enter MMAs with weight 0).
+template <int HD, typename KVT>
+__device__ __forceinline__ void stage_keys_mma(const KVT *__restrict__ K, const KVT *__restrict__ V,
+                                               const int32_t *__restrict__ sub_end, const int32_t *__restrict__ chain,
+                                               int p, int i0, int kc, int cnt, int D, int hoff, int *s_kid, int *s_kend,
+                                               float (*sK)[HD + 4], float (*sV)[HD + 4]) {
+    const int tid = threadIdx.x;
+    if (tid < KC) {
+        int kk = kc + tid, kid = -1, kend = 0;
+        if (tid < cnt) { kid = kk < p ? chain[kk] : i0 + (kk - p); kend = sub_end[kid]; }
+        s_kid[tid] = kid; s_kend[tid] = kend;
+    }
+    __syncthreads();
+    constexpr int C4 = HD / 4;
+    for (int idx = tid; idx < KC * C4; idx += 128) {
+        int r = idx / C4, c = idx % C4;
+        float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
+        if (r < cnt) {
+            int64_t base = (int64_t)s_kid[r] * D + hoff + c * 4;
+            kv = ld4(K + base); vv = ld4(V + base);
+        }
+        *reinterpret_cast<float4 *>(&sK[r][c * 4]) = kv;
+        *reinterpret_cast<float4 *>(&sV[r][c * 4]) = vv;
+    }
+    __syncthreads();
+}
+
+template <int HD, typename KVT>
+__global__ void __launch_bounds__(128) attn_fwd_mma_kernel(const float *__restrict__ Q, const KVT *__restrict__ K,
+                                                           const KVT *__restrict__ V, float *__restrict__ O,
+                                                           float *__restrict__ LSE, const int32_t *__restrict__ sub_end,
+                                                           const int64_t *__restrict__ chain_off,
+                                                           const int32_t *__restrict__ chain_ids, int n, int H, float scale) {
+    constexpr int M = 64, KS = HD / 8;
+    constexpr bool SPLIT_KV = sizeof(KVT) == 4;
+    __shared__ __align__(16) float sK[KC][HD + 4];
+    __shared__ __align__(16) float sV[KC][HD + 4];
+    __shared__ int s_kid[KC], s_kend[KC];
+    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, tig = lane & 3;
+    const int D = H * HD, hoff = h * HD;
+    const int i0 = t * M;
+    const int r0 = i0 + warp * 16 + g, r1 = r0 + 8;
+    const bool act0 = r0 < n, act1 = r1 < n;
+    const int64_t coff = chain_off[t];
+    const int p = (int)(chain_off[t + 1] - coff);
+    const int nkeys = p + min(M, n - i0);
+    const int32_t *chain = chain_ids + coff;
+    const float qs = scale * LOG2E;
+
+    uint32_t qh[KS][4], ql[KS][4];
+#pragma unroll
+    for (int ks = 0; ks < KS; ks++) {
+        const int d0 = hoff + ks * 8 + tig;
+        float x0 = act0 ? __ldg(Q + (int64_t)r0 * D + d0) * qs : 0.f;
+        float x1 = act1 ? __ldg(Q + (int64_t)r1 * D + d0) * qs : 0.f;
+        float x2 = act0 ? __ldg(Q + (int64_t)r0 * D + d0 + 4) * qs : 0.f;
+        float x3 = act1 ? __ldg(Q + (int64_t)r1 * D + d0 + 4) * qs : 0.f;
+        tf32_split(x0, qh[ks][0], ql[ks][0]); tf32_split(x1, qh[ks][1], ql[ks][1]);
+        tf32_split(x2, qh[ks][2], ql[ks][2]); tf32_split(x3, qh[ks][3], ql[ks][3]);
+    }
+    float o[KS][4];
+#pragma unroll
+    for (int db = 0; db < KS; db++) o[db][0] = o[db][1] = o[db][2] = o[db][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+    for (int kc = 0; kc < nkeys; kc += KC) {
+        const int cnt = min(KC, nkeys - kc);
+        __syncthreads();
+        stage_keys_mma<HD, KVT>(K, V, sub_end, chain, p, i0, kc, cnt, D, hoff, s_kid, s_kend, sK, sV);
+        float s[KC / 8][4];
+        unsigned live = 0;
+#pragma unroll
+        for (int nb = 0; nb < KC / 8; nb++) {
+            const int kA = nb * 8 + 2 * tig;
+            const int kidA = s_kid[kA], kendA = s_kend[kA], kidB = s_kid[kA + 1], kendB = s_kend[kA + 1];
+            const bool v0 = act0 && kidA <= r0 && r0 < kendA, v1 = act0 && kidB <= r0 && r0 < kendB;
+            const bool v2 = act1 && kidA <= r1 && r1 < kendA, v3 = act1 && kidB <= r1 && r1 < kendB;
+            s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = -INFINITY;
+            if (!__any_sync(0xffffffffu, v0 | v1 | v2 | v3)) continue;
+            live |= 1u << nb;
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int ks = 0; ks < KS; ks++) {
+                const float b0 = sK[nb * 8 + g][ks * 8 + tig], b1 = sK[nb * 8 + g][ks * 8 + tig + 4];
+                if (SPLIT_KV) {
+                    uint32_t h0, lo0, h1, lo1;
+                    tf32_split(b0, h0, lo0); tf32_split(b1, h1, lo1);
+                    mma_tf32(c, qh[ks], h0, h1); mma_tf32(c, ql[ks], h0, h1); mma_tf32(c, qh[ks], lo0, lo1);
+                } else {
+                    mma_tf32(c, qh[ks], __float_as_uint(b0), __float_as_uint(b1));
+                    mma_tf32(c, ql[ks], __float_as_uint(b0), __float_as_uint(b1));
+                }
+            }
+            if (v0) s[nb][0] = c[0];
+            if (v1) s[nb][1] = c[1];
+            if (v2) s[nb][2] = c[2];
+            if (v3) s[nb][3] = c[3];
+        }
+        if (live == 0) continue;                       // warp-uniform
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int nb = 0; nb < KC / 8; nb++) {
+            mx0 = fmaxf(mx0, fmaxf(s[nb][0], s[nb][1]));
+            mx1 = fmaxf(mx1, fmaxf(s[nb][2], s[nb][3]));
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const float mu0 = mn0 == -INFINITY ? 0.f : mn0, mu1 = mn1 == -INFINITY ? 0.f : mn1;
+        const float corr0 = exp2f(m0 - mu0), corr1 = exp2f(m1 - mu1);
+        m0 = mn0; m1 = mn1;
+        l0 *= corr0; l1 *= corr1;
+#pragma unroll
+        for (int db = 0; db < KS; db++) { o[db][0] *= corr0; o[db][1] *= corr0; o[db][2] *= corr1; o[db][3] *= corr1; }
+#pragma unroll
+        for (int nb = 0; nb < KC / 8; nb++) {
+            if (!(live & (1u << nb))) continue;
+            const float p0 = exp2f(s[nb][0] - mu0), p1 = exp2f(s[nb][1] - mu0);
+            const float p2 = exp2f(s[nb][2] - mu1), p3 = exp2f(s[nb][3] - mu1);
+            l0 += p0 + p1; l1 += p2 + p3;
+            // the C fragment of the scores is the A fragment of PV once key 2*tig sits in k-slot tig and key
+            // 2*tig+1 in k-slot tig+4; V is read with the same permutation
+            uint32_t ph[4], pl[4];
+            tf32_split(p0, ph[0], pl[0]); tf32_split(p2, ph[1], pl[1]);
+            tf32_split(p1, ph[2], pl[2]); tf32_split(p3, ph[3], pl[3]);
+#pragma unroll
+            for (int db = 0; db < KS; db++) {
+                const float b0 = sV[nb * 8 + 2 * tig][db * 8 + g], b1 = sV[nb * 8 + 2 * tig + 1][db * 8 + g];
+                if (SPLIT_KV) {
+                    uint32_t h0, lo0, h1, lo1;
+                    tf32_split(b0, h0, lo0); tf32_split(b1, h1, lo1);
+                    mma_tf32(o[db], ph, h0, h1); mma_tf32(o[db], pl, h0, h1); mma_tf32(o[db], ph, lo0, lo1);
+                } else {
+                    mma_tf32(o[db], ph, __float_as_uint(b0), __float_as_uint(b1));
+                    mma_tf32(o[db], pl, __float_as_uint(b0), __float_as_uint(b1));
+                }
+            }
+        }
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    if (act0) {
+        const float inv = 1.0f / l0;
+#pragma unroll
+        for (int db = 0; db < KS; db++)
+            *reinterpret_cast<float2 *>(O + (int64_t)r0 * D + hoff + db * 8 + 2 * tig) = make_float2(o[db][0] * inv, o[db][1] * inv);
+        if (tig == 0) LSE[(int64_t)r0 * H + h] = (m0 + log2f(l0)) * LN2;
+    }
+    if (act1) {
+        const float inv = 1.0f / l1;
+#pragma unroll
+        for (int db = 0; db < KS; db++)
+            *reinterpret_cast<float2 *>(O + (int64_t)r1 * D + hoff + db * 8 + 2 * tig) = make_float2(o[db][2] * inv, o[db][3] * inv);
+        if (tig == 0) LSE[(int64_t)r1 * H + h] = (m1 + log2f(l1)) * LN2;
+    }
+}
+
+// --------------------------------------------------------------------------------------
 // backward.  Per chunk of KC keys:
 //   phase 1 (thread = query): w = exp(s - lse), ds = w (dO.v - delta) scale, dq += ds k; w and ds go
 //                             to shared memory;
@@ -341,6 +525,218 @@ __global__ void __launch_bounds__(M) attn_bwd_kernel(const float *__restrict__ Q
     }
 }
 
+// --------------------------------------------------------------------------------------
+// backward on the tensor cores (same tiling and error compensation as attn_fwd_mma_kernel).
+// Per chunk of 32 keys:
+//   phase 1 (warp = 16 query rows): S = Q K^T, dP = dO V^T, P = exp2(S - lse), dS = P (dP - delta) scale,
+//            dQ += dS K; P and dS go to shared memory;
+//   phase 2 (warp = 16 keys x half of head_dim): dK = dS^T Q, dV = P^T dO, contracted over the tile's 64 queries
+//            in index order.
+// Output placement and the later reduction are those of attn_bwd_kernel.
+// --------------------------------------------------------------------------------------
+template <int HD>
+struct BwdMmaSmem {
+    float sK[KC][HD + 4];
+    float sV[KC][HD + 4];
+    float sQ[64][HD + 8];
+    float sG[64][HD + 8];
+    float sP[64][KC + 8];
+    float sS[64][KC + 8];
+    int s_kid[KC], s_kend[KC];
+    unsigned s_live[4];
+};
+
+template <int HD, typename KVT>
+__global__ void __launch_bounds__(128) attn_bwd_mma_kernel(const float *__restrict__ Q, const KVT *__restrict__ K,
+                                                           const KVT *__restrict__ V, const float *__restrict__ O,
+                                                           const float *__restrict__ LSE, const float *__restrict__ dO,
+                                                           float *__restrict__ dQ, float *__restrict__ dK,
+                                                           float *__restrict__ dV, float *__restrict__ Pk,
+                                                           float *__restrict__ Pv, const int32_t *__restrict__ sub_end,
+                                                           const int64_t *__restrict__ chain_off,
+                                                           const int32_t *__restrict__ chain_ids, int n, int H, float scale) {
+    constexpr int M = 64, KS = HD / 8;
+    constexpr bool SPLIT_KV = sizeof(KVT) == 4;
+    constexpr int NB2 = (KS + 1) / 2;          // head_dim blocks of 8 per warp in phase 2
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    BwdMmaSmem<HD> &S = *reinterpret_cast<BwdMmaSmem<HD> *>(smem_raw);
+    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, tig = lane & 3;
+    const int D = H * HD, hoff = h * HD;
+    const int i0 = t * M;
+    const int nt = min(M, n - i0);
+    const int q0 = warp * 16 + g, q1 = q0 + 8;            // tile-local query rows of this thread
+    const int r0 = i0 + q0, r1 = i0 + q1;
+    const bool act0 = r0 < n, act1 = r1 < n;
+    const int64_t coff = chain_off[t];
+    const int p = (int)(chain_off[t + 1] - coff);
+    const int nkeys = p + nt;
+    const int32_t *chain = chain_ids + coff;
+    const float qs = scale * LOG2E;
+
+    // the tile's Q and dO rows, zero beyond the last row
+    {
+        constexpr int C4 = HD / 4;
+        for (int idx = tid; idx < M * C4; idx += 128) {
+            int r = idx / C4, c = idx % C4;
+            float4 x = make_float4(0.f, 0.f, 0.f, 0.f), y = x;
+            if (r < nt) {
+                x = ld4(Q + (int64_t)(i0 + r) * D + hoff + c * 4);
+                y = ld4(dO + (int64_t)(i0 + r) * D + hoff + c * 4);
+            }
+            *reinterpret_cast<float4 *>(&S.sQ[r][c * 4]) = x;
+            *reinterpret_cast<float4 *>(&S.sG[r][c * 4]) = y;
+        }
+    }
+    __syncthreads();
+    uint32_t qh[KS][4], ql[KS][4], gh[KS][4], gl[KS][4];
+    float delta0 = 0.f, delta1 = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < KS; ks++) {
+        const int d0 = ks * 8 + tig;
+        const float x0 = S.sQ[q0][d0], x1 = S.sQ[q1][d0], x2 = S.sQ[q0][d0 + 4], x3 = S.sQ[q1][d0 + 4];
+        const float y0 = S.sG[q0][d0], y1 = S.sG[q1][d0], y2 = S.sG[q0][d0 + 4], y3 = S.sG[q1][d0 + 4];
+        tf32_split(x0 * qs, qh[ks][0], ql[ks][0]); tf32_split(x1 * qs, qh[ks][1], ql[ks][1]);
+        tf32_split(x2 * qs, qh[ks][2], ql[ks][2]); tf32_split(x3 * qs, qh[ks][3], ql[ks][3]);
+        tf32_split(y0, gh[ks][0], gl[ks][0]); tf32_split(y1, gh[ks][1], gl[ks][1]);
+        tf32_split(y2, gh[ks][2], gl[ks][2]); tf32_split(y3, gh[ks][3], gl[ks][3]);
+        if (act0) {
+            delta0 = fmaf(y0, __ldg(O + (int64_t)r0 * D + hoff + d0), delta0);
+            delta0 = fmaf(y2, __ldg(O + (int64_t)r0 * D + hoff + d0 + 4), delta0);
+        }
+        if (act1) {
+            delta1 = fmaf(y1, __ldg(O + (int64_t)r1 * D + hoff + d0), delta1);
+            delta1 = fmaf(y3, __ldg(O + (int64_t)r1 * D + hoff + d0 + 4), delta1);
+        }
+    }
+    delta0 += __shfl_xor_sync(0xffffffffu, delta0, 1); delta0 += __shfl_xor_sync(0xffffffffu, delta0, 2);
+    delta1 += __shfl_xor_sync(0xffffffffu, delta1, 1); delta1 += __shfl_xor_sync(0xffffffffu, delta1, 2);
+    const float lse0 = act0 ? LSE[(int64_t)r0 * H + h] * LOG2E : 0.f;
+    const float lse1 = act1 ? LSE[(int64_t)r1 * H + h] * LOG2E : 0.f;
+    float dq[KS][4];
+#pragma unroll
+    for (int db = 0; db < KS; db++) dq[db][0] = dq[db][1] = dq[db][2] = dq[db][3] = 0.f;
+
+    const int mb = warp & 1;                    // phase 2: 16-key block of the chunk
+    const int db0 = (warp >> 1) * NB2;          // phase 2: first head_dim block of this warp
+
+    for (int kc = 0; kc < nkeys; kc += KC) {
+        const int cnt = min(KC, nkeys - kc);
+        __syncthreads();
+        stage_keys_mma<HD, KVT>(K, V, sub_end, chain, p, i0, kc, cnt, D, hoff, S.s_kid, S.s_kend, S.sK, S.sV);
+        // ---- phase 1 ----
+        unsigned live = 0;
+#pragma unroll
+        for (int nb = 0; nb < KC / 8; nb++) {
+            const int kA = nb * 8 + 2 * tig;
+            const int kidA = S.s_kid[kA], kendA = S.s_kend[kA], kidB = S.s_kid[kA + 1], kendB = S.s_kend[kA + 1];
+            const bool v0 = act0 && kidA <= r0 && r0 < kendA, v1 = act0 && kidB <= r0 && r0 < kendB;
+            const bool v2 = act1 && kidA <= r1 && r1 < kendA, v3 = act1 && kidB <= r1 && r1 < kendB;
+            float pw[4] = {0.f, 0.f, 0.f, 0.f}, ds[4] = {0.f, 0.f, 0.f, 0.f};
+            if (__any_sync(0xffffffffu, v0 | v1 | v2 | v3)) {
+                live |= 1u << nb;
+                float c[4] = {0.f, 0.f, 0.f, 0.f}, e[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int ks = 0; ks < KS; ks++) {
+                    const float k0 = S.sK[nb * 8 + g][ks * 8 + tig], k1 = S.sK[nb * 8 + g][ks * 8 + tig + 4];
+                    const float w0 = S.sV[nb * 8 + g][ks * 8 + tig], w1 = S.sV[nb * 8 + g][ks * 8 + tig + 4];
+                    if (SPLIT_KV) {
+                        uint32_t h0, lo0, h1, lo1;
+                        tf32_split(k0, h0, lo0); tf32_split(k1, h1, lo1);
+                        mma_tf32(c, qh[ks], h0, h1); mma_tf32(c, ql[ks], h0, h1); mma_tf32(c, qh[ks], lo0, lo1);
+                        tf32_split(w0, h0, lo0); tf32_split(w1, h1, lo1);
+                        mma_tf32(e, gh[ks], h0, h1); mma_tf32(e, gl[ks], h0, h1); mma_tf32(e, gh[ks], lo0, lo1);
+                    } else {
+                        mma_tf32(c, qh[ks], __float_as_uint(k0), __float_as_uint(k1));
+                        mma_tf32(c, ql[ks], __float_as_uint(k0), __float_as_uint(k1));
+                        mma_tf32(e, gh[ks], __float_as_uint(w0), __float_as_uint(w1));
+                        mma_tf32(e, gl[ks], __float_as_uint(w0), __float_as_uint(w1));
+                    }
+                }
+                pw[0] = v0 ? exp2f(c[0] - lse0) : 0.f; pw[1] = v1 ? exp2f(c[1] - lse0) : 0.f;
+                pw[2] = v2 ? exp2f(c[2] - lse1) : 0.f; pw[3] = v3 ? exp2f(c[3] - lse1) : 0.f;
+                ds[0] = pw[0] * (e[0] - delta0) * scale; ds[1] = pw[1] * (e[1] - delta0) * scale;
+                ds[2] = pw[2] * (e[2] - delta1) * scale; ds[3] = pw[3] * (e[3] - delta1) * scale;
+                // dQ += dS K  (C fragment reused as A fragment: key 2*tig in k-slot tig, key 2*tig+1 in k-slot tig+4)
+                uint32_t ah[4], al[4];
+                tf32_split(ds[0], ah[0], al[0]); tf32_split(ds[2], ah[1], al[1]);
+                tf32_split(ds[1], ah[2], al[2]); tf32_split(ds[3], ah[3], al[3]);
+#pragma unroll
+                for (int db = 0; db < KS; db++) {
+                    const float b0 = S.sK[nb * 8 + 2 * tig][db * 8 + g], b1 = S.sK[nb * 8 + 2 * tig + 1][db * 8 + g];
+                    if (SPLIT_KV) {
+                        uint32_t h0, lo0, h1, lo1;
+                        tf32_split(b0, h0, lo0); tf32_split(b1, h1, lo1);
+                        mma_tf32(dq[db], ah, h0, h1); mma_tf32(dq[db], al, h0, h1); mma_tf32(dq[db], ah, lo0, lo1);
+                    } else {
+                        mma_tf32(dq[db], ah, __float_as_uint(b0), __float_as_uint(b1));
+                        mma_tf32(dq[db], al, __float_as_uint(b0), __float_as_uint(b1));
+                    }
+                }
+            }
+            *reinterpret_cast<float2 *>(&S.sP[q0][kA]) = make_float2(pw[0], pw[1]);
+            *reinterpret_cast<float2 *>(&S.sP[q1][kA]) = make_float2(pw[2], pw[3]);
+            *reinterpret_cast<float2 *>(&S.sS[q0][kA]) = make_float2(ds[0], ds[1]);
+            *reinterpret_cast<float2 *>(&S.sS[q1][kA]) = make_float2(ds[2], ds[3]);
+        }
+        if (lane == 0) S.s_live[warp] = live;
+        __syncthreads();
+        // ---- phase 2 ----
+        if (mb * 16 < cnt) {
+            float ak[NB2][4], av[NB2][4];
+#pragma unroll
+            for (int j = 0; j < NB2; j++) { ak[j][0] = ak[j][1] = ak[j][2] = ak[j][3] = 0.f; av[j][0] = av[j][1] = av[j][2] = av[j][3] = 0.f; }
+            // a key of the tile itself is attended only by queries at or after it
+            const int ks_first = max(0, kc + mb * 16 - p) / 8;
+            for (int ks = ks_first; ks < M / 8; ks++) {
+                if (!((S.s_live[ks >> 1] >> (2 * mb)) & 3u)) continue;       // the 16 queries x 16 keys are all masked
+                const int qa = ks * 8 + tig, kA = mb * 16 + g;
+                uint32_t sh[4], sl[4], ph[4], pl[4];
+                tf32_split(S.sS[qa][kA], sh[0], sl[0]); tf32_split(S.sS[qa][kA + 8], sh[1], sl[1]);
+                tf32_split(S.sS[qa + 4][kA], sh[2], sl[2]); tf32_split(S.sS[qa + 4][kA + 8], sh[3], sl[3]);
+                tf32_split(S.sP[qa][kA], ph[0], pl[0]); tf32_split(S.sP[qa][kA + 8], ph[1], pl[1]);
+                tf32_split(S.sP[qa + 4][kA], ph[2], pl[2]); tf32_split(S.sP[qa + 4][kA + 8], ph[3], pl[3]);
+#pragma unroll
+                for (int j = 0; j < NB2; j++) {
+                    const int dcol = (db0 + j) * 8 + g;
+                    if ((db0 + j) * 8 >= HD) continue;
+                    uint32_t h0, lo0, h1, lo1;
+                    tf32_split(S.sQ[qa][dcol], h0, lo0); tf32_split(S.sQ[qa + 4][dcol], h1, lo1);
+                    mma_tf32(ak[j], sh, h0, h1); mma_tf32(ak[j], sl, h0, h1); mma_tf32(ak[j], sh, lo0, lo1);
+                    tf32_split(S.sG[qa][dcol], h0, lo0); tf32_split(S.sG[qa + 4][dcol], h1, lo1);
+                    mma_tf32(av[j], ph, h0, h1); mma_tf32(av[j], pl, h0, h1); mma_tf32(av[j], ph, lo0, lo1);
+                }
+            }
+#pragma unroll
+            for (int half = 0; half < 2; half++) {
+                const int kl = mb * 16 + g + half * 8;       // key index inside the chunk
+                if (kl >= cnt) continue;
+                const int kk = kc + kl;
+                float *ok, *ov;
+                if (kk < p) { ok = Pk + (coff + kk) * D + hoff; ov = Pv + (coff + kk) * D + hoff; }
+                else { ok = dK + (int64_t)(i0 + kk - p) * D + hoff; ov = dV + (int64_t)(i0 + kk - p) * D + hoff; }
+#pragma unroll
+                for (int j = 0; j < NB2; j++) {
+                    if ((db0 + j) * 8 >= HD) continue;
+                    const int dcol = (db0 + j) * 8 + 2 * tig;
+                    *reinterpret_cast<float2 *>(ok + dcol) = make_float2(ak[j][2 * half], ak[j][2 * half + 1]);
+                    *reinterpret_cast<float2 *>(ov + dcol) = make_float2(av[j][2 * half], av[j][2 * half + 1]);
+                }
+            }
+        }
+    }
+    if (act0) {
+#pragma unroll
+        for (int db = 0; db < KS; db++)
+            *reinterpret_cast<float2 *>(dQ + (int64_t)r0 * D + hoff + db * 8 + 2 * tig) = make_float2(dq[db][0], dq[db][1]);
+    }
+    if (act1) {
+#pragma unroll
+        for (int db = 0; db < KS; db++)
+            *reinterpret_cast<float2 *>(dQ + (int64_t)r1 * D + hoff + db * 8 + 2 * tig) = make_float2(dq[db][2], dq[db][3]);
+    }
+}
+
 // dK/dV reduction, pass 1: one warp per work item = (node, tile range).  The node's row in tile t's
 // partial block is chain_off[t] + depth - 1.  Tiles are summed in increasing order.
 __global__ void reduce_items_kernel(const float *__restrict__ Pk, const float *__restrict__ Pv, float *__restrict__ dK,
@@ -450,14 +846,69 @@ static int launch_bwd(const agpt_plan *p, const float *q, const void *k, const v
         return agpt_set_error(AGPT_E_ARG, "unsupported head_dim/tile combination");               \
     } while (0)
 
+// Kernel family of the native attention entry points: 1 = tensor cores (mma.sync TF32, error-compensated; tiles
+// of 64), 0 = FP32 FMA.  Initialised from the environment variable AGPT_B200_ATTN_IMPL, default 1.
+static int g_attn_impl = -1;
+static int attn_impl() {
+    if (g_attn_impl < 0) {
+        const char *e = getenv("AGPT_B200_ATTN_IMPL");
+        g_attn_impl = (e && e[0] == '0') ? 0 : 1;
+    }
+    return g_attn_impl;
+}
+extern "C" int agpt_b200_set_attn_impl(int impl) {
+    if (impl != 0 && impl != 1) return agpt_set_error(AGPT_E_ARG, "set_attn_impl: 0 (FMA) or 1 (tensor cores)");
+    g_attn_impl = impl;
+    return AGPT_OK;
+}
+
+template <int HD, typename KVT>
+static int launch_fwd_mma(const agpt_plan *p, const float *q, const void *k, const void *v, float *out, float *lse, int H,
+                          float scale, cudaStream_t st) {
+    dim3 grid((unsigned)p->n_tiles, (unsigned)H);
+    attn_fwd_mma_kernel<HD, KVT><<<grid, 128, 0, st>>>(q, (const KVT *)k, (const KVT *)v, out, lse, p->d_sub_end,
+                                                       p->d_chain_off, p->d_chain_ids, (int)p->n, H, scale);
+    return launch_status("attn_fwd_mma");
+}
+
 static int fwd_dispatch(const agpt_plan *p, const float *q, const void *k, const void *v, int kv_dtype, float *out,
                         float *lse, int H, int head_dim, float scale, cudaStream_t st) {
+    if (attn_impl() == 1 && p->tile_m == 64) {
+        const bool bf = kv_dtype == AGPT_KV_BF16;
+        switch (head_dim) {
+            case 16: return bf ? launch_fwd_mma<16, __nv_bfloat16>(p, q, k, v, out, lse, H, scale, st) : launch_fwd_mma<16, float>(p, q, k, v, out, lse, H, scale, st);
+            case 32: return bf ? launch_fwd_mma<32, __nv_bfloat16>(p, q, k, v, out, lse, H, scale, st) : launch_fwd_mma<32, float>(p, q, k, v, out, lse, H, scale, st);
+            case 64: return bf ? launch_fwd_mma<64, __nv_bfloat16>(p, q, k, v, out, lse, H, scale, st) : launch_fwd_mma<64, float>(p, q, k, v, out, lse, H, scale, st);
+        }
+    }
     DISPATCH_HD_M_KV(launch_fwd, p, q, k, v, out, lse, H, scale, st);
+}
+
+template <int HD, typename KVT>
+static int launch_bwd_mma(const agpt_plan *p, const float *q, const void *k, const void *v, const float *o, const float *lse,
+                          const float *dout, float *dq, float *dk, float *dv, float *pk, float *pv, int H, float scale,
+                          cudaStream_t st) {
+    dim3 grid((unsigned)p->n_tiles, (unsigned)H);
+    size_t smem = sizeof(BwdMmaSmem<HD>);
+    CUDA_TRY(cudaFuncSetAttribute(attn_bwd_mma_kernel<HD, KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attn_bwd_mma_kernel<HD, KVT><<<grid, 128, smem, st>>>(q, (const KVT *)k, (const KVT *)v, o, lse, dout, dq, dk, dv, pk, pv,
+                                                          p->d_sub_end, p->d_chain_off, p->d_chain_ids, (int)p->n, H, scale);
+    return launch_status("attn_bwd_mma");
 }
 
 static int bwd_dispatch(const agpt_plan *p, const float *q, const void *k, const void *v, int kv_dtype, const float *o,
                         const float *lse, const float *dout, float *dq, float *dk, float *dv, float *pk, float *pv, int H,
                         int head_dim, float scale, cudaStream_t st) {
+    if (attn_impl() == 1 && p->tile_m == 64) {
+        const bool bf = kv_dtype == AGPT_KV_BF16;
+#define BWD_MMA_ARGS p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st
+        switch (head_dim) {
+            case 16: return bf ? launch_bwd_mma<16, __nv_bfloat16>(BWD_MMA_ARGS) : launch_bwd_mma<16, float>(BWD_MMA_ARGS);
+            case 32: return bf ? launch_bwd_mma<32, __nv_bfloat16>(BWD_MMA_ARGS) : launch_bwd_mma<32, float>(BWD_MMA_ARGS);
+            case 64: return bf ? launch_bwd_mma<64, __nv_bfloat16>(BWD_MMA_ARGS) : launch_bwd_mma<64, float>(BWD_MMA_ARGS);
+        }
+#undef BWD_MMA_ARGS
+    }
     DISPATCH_HD_M_KV(launch_bwd, p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st);
 }
 

@@ -104,7 +104,7 @@ class Unit:
     __slots__ = ("parent", "n", "tokens", "q2n", "qoff", "radix_ids", "mass_w", "n_ctx")
 
 
-def build_units(wl, rank, world, log, single_unit=False):
+def build_units(wl, rank, world, log, single_unit=False, group_rows=4_000_000):
     import agpt_b200 as A
     cfg = WORKLOADS[wl]
     t0 = time.time()
@@ -128,35 +128,57 @@ def build_units(wl, rank, world, log, single_unit=False):
     if single_unit:       # the whole forest as one launch (profiling); its depth-1 nodes stay roots
         ub, ue = np.array([0], np.int64), np.array([plan.n], np.int64)
     owner = A.partition_lpt(ue - ub, world)
-    units = []
+    # Each rank's units are packed, in depth-first order, into launch groups of at most `group_rows` rows: a
+    # group is one forest = one walker plan = one launch per kernel, and one loss chunk.
     d2n = plan.dfs_to_node
+    pieces, rows = [], 0      # (local parent, global ids, unit start flag) of the group being filled
+    units = []
+
+    def flush():
+        nonlocal pieces, rows
+        if not pieces:
+            return
+        u = Unit()
+        off, pars, idl, ustart = 0, [], [], []
+        for pp, ids in pieces:
+            pars.append(np.where(pp < 0, -1, pp + off))
+            idl.append(ids)
+            st = np.zeros(ids.size, bool); st[0] = True
+            ustart.append(st)
+            off += ids.size
+        u.parent = np.concatenate(pars).astype(np.int32)
+        ids = np.concatenate(idl)
+        u.n = u.parent.size
+        u.n_ctx = 0
+        u.tokens = token[ids].astype(np.int32)
+        r = radix_of[ids]
+        starts = np.concatenate([[True], r[1:] != r[:-1]]) | np.concatenate(ustart)
+        u.q2n = (np.cumsum(starts) - 1).astype(np.int32)
+        u.qoff = np.concatenate([np.nonzero(starts)[0], [u.n]]).astype(np.int32)
+        u.radix_ids = r[starts].astype(np.int32)
+        u.mass_w = A.mass_weights(edge_mass[u.radix_ids], np.diff(u.qoff), "linear")
+        units.append(u)
+        pieces, rows = [], 0
+
     for b, e, o in zip(ub, ue, owner):
         if o != rank:
             continue
         b, e = int(b), int(e)
-        u = Unit()
         pp = plan.parent_dfs[b:e].astype(np.int64) - b
         ids = d2n[b:e]
-        u.n_ctx = 0
         if level == 2 and plan.depth[b] == 2:
             # bigram unit: the depth-1 ancestor rides along as a context row so every chain is complete
             a = int(plan.parent_dfs[b])
             pp = np.concatenate([[-1], pp + 1])
             pp[1] = 0
             ids = np.concatenate([[d2n[a]], ids])
-            u.n_ctx = 1
         else:
             pp[plan.parent_dfs[b:e] < 0] = -1
-        u.parent = pp.astype(np.int32)
-        u.n = u.parent.size
-        u.tokens = token[ids].astype(np.int32)
-        r = radix_of[ids]
-        starts = np.concatenate([[True], r[1:] != r[:-1]])
-        u.q2n = (np.cumsum(starts) - 1).astype(np.int32)
-        u.qoff = np.concatenate([np.nonzero(starts)[0], [u.n]]).astype(np.int32)
-        u.radix_ids = r[starts].astype(np.int32)
-        u.mass_w = A.mass_weights(edge_mass[u.radix_ids], np.diff(u.qoff), "linear")
-        units.append(u)
+        if rows and rows + ids.size > group_rows:
+            flush()
+        pieces.append((pp, ids))
+        rows += ids.size
+    flush()
     units.sort(key=lambda x: -x.n)
     total = int(plan.n)
     return units, counts, total, plan
@@ -172,8 +194,6 @@ def cpu_arm(units, cfg, budget_nodes, steps=1, warmup=0):
     H, hd, V = cfg["heads"], cfg["head_dim"], cfg["vocab"]
     sample, tot = [], 0
     for u in sorted(units, key=lambda x: x.n):
-        if u.n < 2000 and len(units) > 8:
-            continue
         if tot + u.n > budget_nodes and sample:
             break
         sample.append(u)
@@ -197,7 +217,7 @@ def cpu_arm(units, cfg, budget_nodes, steps=1, warmup=0):
     for _ in range(steps):
         one_pass()
     dt = (time.perf_counter() - t0) / steps
-    return tot / dt, O.num_threads(), f"{len(sample)} smallest units over 2000 nodes, {tot} nodes, attention fwd+bwd (oracle, OpenMP)", dt
+    return tot / dt, O.num_threads(), f"{len(sample)} launch groups of the same trie, {tot} positions, attention fwd+bwd (oracle, OpenMP)", dt
 
 
 def run_reference(args):
@@ -205,7 +225,9 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    units, counts, total, plan = build_units(args.workload, 0, 1, lambda s: print(s, file=sys.stderr))
+    units, counts, total, plan = build_units(args.workload, 0, 1, lambda s: print(s, file=sys.stderr), group_rows=100_000)
+    from oracle import pyoracle as O
+    O.set_num_threads(os.cpu_count() or 1)      # torchrun pins OMP_NUM_THREADS=1; this arm may use every host core
     nps, cores, sample, dt = cpu_arm(units, cfg, args.cpu_nodes, steps=max(1, args.steps), warmup=min(args.warmup, 1))
     line = {"impl": "reference", "metric": "trie_nodes_per_sec_attn_fwd_bwd", "value": nps, "unit": "nodes/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
@@ -237,10 +259,10 @@ def run_gpu(args):
     cfg = WORKLOADS[args.workload]
     H, hd, V = cfg["heads"], cfg["head_dim"], cfg["vocab"]
     D = H * hd
-    units, counts, total_nodes, gplan = build_units(args.workload, rank, world, log, args.single_unit)
+    units, counts, total_nodes, gplan = build_units(args.workload, rank, world, log, args.single_unit, args.group_rows)
     n_rank = sum(u.n for u in units)
     n_max = max(u.n for u in units)
-    log(f"{len(units)} units, {n_rank} rows on this rank (largest {n_max}); {total_nodes} positions in the trie")
+    log(f"{len(units)} launch groups, {n_rank} rows on this rank (largest {n_max}); {total_nodes} positions in the trie")
 
     plans = [A.WalkerPlan(u.parent, args.tile, local) for u in units]
     ws_bytes = max(p.workspace_bytes(D) for p in plans)
@@ -361,19 +383,22 @@ def run_gpu(args):
         dt = time.perf_counter() - t0
         e2e = {"value": tot / dt, "unit": "nodes/s", "h2d_bytes_per_step": int(tot * D * 4 * 4),
                "d2h_bytes_per_step": int(tot * (D * 4 * 4 + H * 4)),
-               "sample": f"{len(chosen)} units, {tot} of {n_rank} rows of rank 0; attention fwd+bwd through agpt_b200_attn_fwd_bwd_host"}
+               "sample": f"{len(chosen)} launch groups, {tot} of {n_rank} rows of rank 0; attention fwd+bwd through agpt_b200_attn_fwd_bwd_host"}
         del host
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        nps, cores, sample, _ = cpu_arm(units, cfg, args.cpu_nodes)
+        from oracle import pyoracle as O
+        O.set_num_threads(os.cpu_count() or 1)
+        small, _, _, _ = build_units(args.workload, 0, 1, lambda s: None, group_rows=100_000)
+        nps, cores, sample, _ = cpu_arm(small, cfg, args.cpu_nodes)
         cpu = {"value": nps, "unit": "nodes/s", "cores": cores, "kind": "port", "sample": sample}
 
     if rank == 0:
         line = {"metric": "trie_nodes_per_sec_attn_fwd_bwd", "value": value, "unit": "nodes/s", "n_gpus": world,
                 "steps": args.steps, "warmup": n_warm, "ms_per_step": ms_per_step, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": cfg["label"], "positions": total_nodes, "units_rank0": len(units),
+                "config": {"workload": cfg["label"], "positions": total_nodes, "launch_groups_rank0": len(units), "group_rows": args.group_rows,
                            "partition": "root-child subtrees" if world == 1 else f"bigram subtrees, LPT over {world} ranks",
                            "tile": args.tile, "l2": "inputs (GBs per tensor) far larger than the 126 MB L2"},
                 "roofline": {"bound": "hbm", "achieved": ach_bwd, "peak": peak, "unit": "GB/s", "frac": ach_bwd / peak,
@@ -396,7 +421,8 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--tile", type=int, default=64)
     ap.add_argument("--cpu-nodes", type=int, default=400_000, help="rows in the CPU arm's sample")
-    ap.add_argument("--e2e-nodes", type=int, default=2_000_000, help="rows in the host-buffer sample")
+    ap.add_argument("--e2e-nodes", type=int, default=4_000_000, help="rows in the host-buffer sample")
+    ap.add_argument("--group-rows", type=int, default=4_000_000, help="rows per launch group (units are packed up to this)")
     ap.add_argument("--single-unit", action="store_true", help="one plan over the whole trie instead of per-subtree units")
     ap.add_argument("--profile", action="store_true", help="profiler capture mode: warm-up as given, no e2e, no CPU arm")
     ap.add_argument("--no-e2e", action="store_true")

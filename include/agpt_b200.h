@@ -224,6 +224,11 @@ int agpt_b200_attn_bwd(const agpt_plan *p, const float *d_q, const void *d_k, co
                        float *d_dv, void *d_workspace, int64_t workspace_bytes, int n_heads, int head_dim,
                        float scale, void *stream);
 
+/* Selects the kernel family behind agpt_b200_attn_fwd/_bwd: 1 = tensor cores (mma.sync TF32 with error
+ * compensation, tiles of 64; the default), 0 = FP32 FMA.  Both meet the same parity tolerances; the switch
+ * exists for A/B measurement.  Also read once from the environment variable AGPT_B200_ATTN_IMPL. */
+int agpt_b200_set_attn_impl(int impl);
+
 /* No counterpart in the reference.  agpt_b200_attn_bwd for callers that cannot allocate device memory
  * when the backward runs -- a runtime that claimed the whole GPU at start-up and sub-allocates from its own
  * pool, or a step whose set of buffers is frozen -- and therefore have no workspace to pass.  The partial

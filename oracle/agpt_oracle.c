@@ -884,6 +884,14 @@ ORC_API void orc_mass_weights(const int32_t *edge_mass, const int32_t *edge_len,
     free(nw);
 }
 
+ORC_API void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 ORC_API int orc_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

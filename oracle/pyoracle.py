@@ -364,5 +364,9 @@ def mass_weights(edge_mass, edge_len, mode):
     return out
 
 
+def set_num_threads(n: int) -> None:
+    lib().orc_set_num_threads(C.c_int(n))
+
+
 def num_threads() -> int:
     return int(lib().orc_num_threads())

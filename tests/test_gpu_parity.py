@@ -16,6 +16,14 @@ from tests.helpers import TOL_BF16, TOL_F32, chain_tree, random_qkv, random_tree
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True, params=[1, 0], ids=["tensor", "fma"])
+def attn_impl(request):
+    """Every test in this file runs against both kernel families of the native attention entry points."""
+    A.set_attn_impl(request.param)
+    yield request.param
+    A.set_attn_impl(1)
+
+
 def _dev(x, cuda):
     import torch
     return torch.from_numpy(np.ascontiguousarray(x)).to(cuda)
@@ -91,8 +99,11 @@ def test_deep_unary_chain_and_wide_star(cuda):
         q, k, v, go = random_qkv(n, H * hd, 77)
         ref = _oracle(parent, H, hd, q, k, v, go)
         _, (out, lse, dq, dk, dv) = _run_native(parent, H, hd, q, k, v, go, cuda, 64)
+        # without ancestors every softmax has one term, so dq and the ds part of dk are exactly zero in the
+        # oracle; those are compared absolutely (floor 1 = the O(1) scale of the inputs)
+        floor = 1.0 if (parent < 0).all() else 1e-2
         for got, want in zip((out, dq, dk, dv), ref[:4]):
-            assert rel_err(got, want) < TOL_F32
+            assert rel_err(got, want, floor) < TOL_F32
 
 
 def test_config1_trie_attention(cuda):
