@@ -516,6 +516,8 @@ extern "C" int agpt_b200_plan_create(const int32_t *parent, int64_t n, int tile_
         int32_t a = P->parent_dfs[t * tile_m];
         for (int64_t j = P->chain_off[t + 1] - 1; j >= P->chain_off[t]; j--) { P->chain_ids[j] = a; a = P->parent_dfs[a]; }
     }
+    P->chain_end.resize(P->chain_ids.size());
+    for (size_t j = 0; j < P->chain_ids.size(); j++) P->chain_end[j] = P->sub_end[P->chain_ids[j]];
     // reduction work list: node a receives one partial row from every tile that starts strictly inside
     // its subtree, i.e. tiles (a / M, (sub_end[a] - 1) / M]; long ranges are cut into segments
     const int64_t SEG = AGPT_REDUCE_SEG;

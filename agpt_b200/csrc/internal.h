@@ -20,7 +20,7 @@ struct agpt_plan {
     int64_t sum_depth = 0, sum_group_prefix = 0, n_groups = 0, n_reduce_nodes = 0, n_multi_items = 0;
     std::vector<int32_t> dfs_to_node, node_to_dfs, parent_dfs, depth, sub_end;
     std::vector<int64_t> chain_off;
-    std::vector<int32_t> chain_ids;
+    std::vector<int32_t> chain_ids, chain_end;   // chain_end[j] = sub_end[chain_ids[j]]
     // dK/dV reduction work list: item = (node, inclusive tile range); slot >= 0 when the node's range
     // is cut into several items whose sums meet in a second pass
     std::vector<int32_t> item_node, item_t0, item_t1, item_slot;
@@ -28,7 +28,7 @@ struct agpt_plan {
     std::vector<int64_t> multi_first;
     // device copies (owned)
     int device = -1;
-    int32_t *d_depth = nullptr, *d_sub_end = nullptr, *d_chain_ids = nullptr;
+    int32_t *d_depth = nullptr, *d_sub_end = nullptr, *d_chain_ids = nullptr, *d_chain_end = nullptr;
     int64_t *d_chain_off = nullptr, *d_multi_first = nullptr;
     int32_t *d_item_node = nullptr, *d_item_t0 = nullptr, *d_item_t1 = nullptr, *d_item_slot = nullptr;
     int32_t *d_multi_node = nullptr, *d_multi_count = nullptr;

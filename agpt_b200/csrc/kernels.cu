@@ -46,6 +46,7 @@ int agpt_plan_upload(agpt_plan *p, int device) {
     if ((rc = upload(&p->d_depth, p->depth))) return rc;
     if ((rc = upload(&p->d_sub_end, p->sub_end))) return rc;
     if ((rc = upload(&p->d_chain_ids, p->chain_ids))) return rc;
+    if ((rc = upload(&p->d_chain_end, p->chain_end))) return rc;
     if ((rc = upload(&p->d_chain_off, p->chain_off))) return rc;
     if ((rc = upload(&p->d_item_node, p->item_node))) return rc;
     if ((rc = upload(&p->d_item_t0, p->item_t0))) return rc;
@@ -62,7 +63,7 @@ agpt_plan::~agpt_plan() {
         int cur = -1;
         cudaGetDevice(&cur);
         cudaSetDevice(device);
-        cudaFree(d_depth); cudaFree(d_sub_end); cudaFree(d_chain_ids); cudaFree(d_chain_off);
+        cudaFree(d_depth); cudaFree(d_sub_end); cudaFree(d_chain_ids); cudaFree(d_chain_end); cudaFree(d_chain_off);
         cudaFree(d_item_node); cudaFree(d_item_t0); cudaFree(d_item_t1); cudaFree(d_item_slot);
         cudaFree(d_multi_node); cudaFree(d_multi_count); cudaFree(d_multi_first);
         if (cur >= 0) cudaSetDevice(cur);
@@ -225,31 +226,52 @@ __device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// Like stage_keys, for 128 threads, and rows beyond cnt are zero-filled (they enter MMAs with weight 0).
+#define MAXKEYS 512      // keys (chain + tile rows) a tile of the tensor-core kernels can hold metadata for
+
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src) {
+    unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// Id and subtree end of every key of the tile (chain first, then the tile's own rows): one round of
+// independent loads (chain_end is precomputed so that no load depends on another).  128 threads.
+__device__ __forceinline__ void load_key_meta(const int32_t *__restrict__ sub_end, const int32_t *__restrict__ chain,
+                                              const int32_t *__restrict__ chain_end, int p, int i0, int nkeys, int *s_kid,
+                                              int *s_kend) {
+    for (int j = threadIdx.x; j < nkeys; j += 128) {
+        int kid, kend;
+        if (j < p) { kid = __ldg(chain + j); kend = __ldg(chain_end + j); }
+        else { kid = i0 + (j - p); kend = __ldg(sub_end + kid); }
+        s_kid[j] = kid; s_kend[j] = kend;
+    }
+}
+
+// Start the copy of keys [kc, kc+cnt) into one shared-memory buffer.  float32 stores go through cp.async (the
+// copy overlaps the MMAs on the other buffer); a bf16 store is widened on the way in.  Rows beyond cnt are
+// zero-filled: they enter MMAs with weight 0.  128 threads; the caller commits/waits and synchronises.
 template <int HD, typename KVT>
-__device__ __forceinline__ void stage_keys_mma(const KVT *__restrict__ K, const KVT *__restrict__ V,
-                                               const int32_t *__restrict__ sub_end, const int32_t *__restrict__ chain,
-                                               int p, int i0, int kc, int cnt, int D, int hoff, int *s_kid, int *s_kend,
-                                               float (*sK)[HD + 4], float (*sV)[HD + 4]) {
-    const int tid = threadIdx.x;
-    if (tid < KC) {
-        int kk = kc + tid, kid = -1, kend = 0;
-        if (tid < cnt) { kid = kk < p ? chain[kk] : i0 + (kk - p); kend = sub_end[kid]; }
-        s_kid[tid] = kid; s_kend[tid] = kend;
-    }
-    __syncthreads();
+__device__ __forceinline__ void issue_chunk(const KVT *__restrict__ K, const KVT *__restrict__ V, const int *s_kid, int kc,
+                                            int cnt, int D, int hoff, float (*sK)[HD + 4], float (*sV)[HD + 4]) {
     constexpr int C4 = HD / 4;
-    for (int idx = tid; idx < KC * C4; idx += 128) {
-        int r = idx / C4, c = idx % C4;
-        float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
+    for (int idx = threadIdx.x; idx < KC * C4; idx += 128) {
+        const int r = idx / C4, c = idx % C4;
         if (r < cnt) {
-            int64_t base = (int64_t)s_kid[r] * D + hoff + c * 4;
-            kv = ld4(K + base); vv = ld4(V + base);
+            const int64_t base = (int64_t)s_kid[kc + r] * D + hoff + c * 4;
+            if (sizeof(KVT) == 4) {
+                cp_async16(&sK[r][c * 4], K + base);
+                cp_async16(&sV[r][c * 4], V + base);
+            } else {
+                *reinterpret_cast<float4 *>(&sK[r][c * 4]) = ld4(K + base);
+                *reinterpret_cast<float4 *>(&sV[r][c * 4]) = ld4(V + base);
+            }
+        } else {
+            *reinterpret_cast<float4 *>(&sK[r][c * 4]) = make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<float4 *>(&sV[r][c * 4]) = make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        *reinterpret_cast<float4 *>(&sK[r][c * 4]) = kv;
-        *reinterpret_cast<float4 *>(&sV[r][c * 4]) = vv;
     }
-    __syncthreads();
+    cp_async_commit();
 }
 
 template <int HD, typename KVT>
@@ -257,12 +279,14 @@ __global__ void __launch_bounds__(128) attn_fwd_mma_kernel(const float *__restri
                                                            const KVT *__restrict__ V, float *__restrict__ O,
                                                            float *__restrict__ LSE, const int32_t *__restrict__ sub_end,
                                                            const int64_t *__restrict__ chain_off,
-                                                           const int32_t *__restrict__ chain_ids, int n, int H, float scale) {
+                                                           const int32_t *__restrict__ chain_ids,
+                                                           const int32_t *__restrict__ chain_end_all, int n, int H,
+                                                           float scale) {
     constexpr int M = 64, KS = HD / 8;
     constexpr bool SPLIT_KV = sizeof(KVT) == 4;
-    __shared__ __align__(16) float sK[KC][HD + 4];
-    __shared__ __align__(16) float sV[KC][HD + 4];
-    __shared__ int s_kid[KC], s_kend[KC];
+    __shared__ __align__(16) float sKb[2][KC][HD + 4];
+    __shared__ __align__(16) float sVb[2][KC][HD + 4];
+    __shared__ int s_kid[MAXKEYS], s_kend[MAXKEYS];
     const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, tig = lane & 3;
     const int D = H * HD, hoff = h * HD;
@@ -274,6 +298,9 @@ __global__ void __launch_bounds__(128) attn_fwd_mma_kernel(const float *__restri
     const int nkeys = p + min(M, n - i0);
     const int32_t *chain = chain_ids + coff;
     const float qs = scale * LOG2E;
+    load_key_meta(sub_end, chain, chain_end_all + coff, p, i0, nkeys, s_kid, s_kend);
+    __syncthreads();
+    issue_chunk<HD, KVT>(K, V, s_kid, 0, min(KC, nkeys), D, hoff, sKb[0], sVb[0]);
 
     uint32_t qh[KS][4], ql[KS][4];
 #pragma unroll
@@ -292,15 +319,20 @@ __global__ void __launch_bounds__(128) attn_fwd_mma_kernel(const float *__restri
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
     for (int kc = 0; kc < nkeys; kc += KC) {
-        const int cnt = min(KC, nkeys - kc);
-        __syncthreads();
-        stage_keys_mma<HD, KVT>(K, V, sub_end, chain, p, i0, kc, cnt, D, hoff, s_kid, s_kend, sK, sV);
+        const int buf = (kc / KC) & 1;
+        float (*sK)[HD + 4] = sKb[buf];
+        float (*sV)[HD + 4] = sVb[buf];
+        cp_async_wait_all();
+        __syncthreads();                              // chunk kc has landed; the other buffer is free again
+        if (kc + KC < nkeys) issue_chunk<HD, KVT>(K, V, s_kid, kc + KC, min(KC, nkeys - kc - KC), D, hoff, sKb[buf ^ 1], sVb[buf ^ 1]);
         float s[KC / 8][4];
         unsigned live = 0;
 #pragma unroll
         for (int nb = 0; nb < KC / 8; nb++) {
             const int kA = nb * 8 + 2 * tig;
-            const int kidA = s_kid[kA], kendA = s_kend[kA], kidB = s_kid[kA + 1], kendB = s_kend[kA + 1];
+            const bool inA = kc + kA < nkeys, inB = kc + kA + 1 < nkeys;
+            const int kidA = inA ? s_kid[kc + kA] : 0, kendA = inA ? s_kend[kc + kA] : 0;
+            const int kidB = inB ? s_kid[kc + kA + 1] : 0, kendB = inB ? s_kend[kc + kA + 1] : 0;
             const bool v0 = act0 && kidA <= r0 && r0 < kendA, v1 = act0 && kidB <= r0 && r0 < kendB;
             const bool v2 = act1 && kidA <= r1 && r1 < kendA, v3 = act1 && kidB <= r1 && r1 < kendB;
             s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = -INFINITY;
@@ -536,13 +568,13 @@ __global__ void __launch_bounds__(M) attn_bwd_kernel(const float *__restrict__ Q
 // --------------------------------------------------------------------------------------
 template <int HD>
 struct BwdMmaSmem {
-    float sK[KC][HD + 4];
-    float sV[KC][HD + 4];
+    float sKb[2][KC][HD + 4];
+    float sVb[2][KC][HD + 4];
     float sQ[64][HD + 8];
     float sG[64][HD + 8];
     float sP[64][KC + 8];
     float sS[64][KC + 8];
-    int s_kid[KC], s_kend[KC];
+    int s_kid[MAXKEYS], s_kend[MAXKEYS];
     unsigned s_live[4];
 };
 
@@ -554,7 +586,9 @@ __global__ void __launch_bounds__(128) attn_bwd_mma_kernel(const float *__restri
                                                            float *__restrict__ dV, float *__restrict__ Pk,
                                                            float *__restrict__ Pv, const int32_t *__restrict__ sub_end,
                                                            const int64_t *__restrict__ chain_off,
-                                                           const int32_t *__restrict__ chain_ids, int n, int H, float scale) {
+                                                           const int32_t *__restrict__ chain_ids,
+                                                           const int32_t *__restrict__ chain_end_all, int n, int H,
+                                                           float scale) {
     constexpr int M = 64, KS = HD / 8;
     constexpr bool SPLIT_KV = sizeof(KVT) == 4;
     constexpr int NB2 = (KS + 1) / 2;          // head_dim blocks of 8 per warp in phase 2
@@ -574,6 +608,7 @@ __global__ void __launch_bounds__(128) attn_bwd_mma_kernel(const float *__restri
     const int32_t *chain = chain_ids + coff;
     const float qs = scale * LOG2E;
 
+    load_key_meta(sub_end, chain, chain_end_all + coff, p, i0, nkeys, S.s_kid, S.s_kend);
     // the tile's Q and dO rows, zero beyond the last row
     {
         constexpr int C4 = HD / 4;
@@ -589,6 +624,7 @@ __global__ void __launch_bounds__(128) attn_bwd_mma_kernel(const float *__restri
         }
     }
     __syncthreads();
+    issue_chunk<HD, KVT>(K, V, S.s_kid, 0, min(KC, nkeys), D, hoff, S.sKb[0], S.sVb[0]);
     uint32_t qh[KS][4], ql[KS][4], gh[KS][4], gl[KS][4];
     float delta0 = 0.f, delta1 = 0.f;
 #pragma unroll
@@ -622,14 +658,20 @@ __global__ void __launch_bounds__(128) attn_bwd_mma_kernel(const float *__restri
 
     for (int kc = 0; kc < nkeys; kc += KC) {
         const int cnt = min(KC, nkeys - kc);
-        __syncthreads();
-        stage_keys_mma<HD, KVT>(K, V, sub_end, chain, p, i0, kc, cnt, D, hoff, S.s_kid, S.s_kend, S.sK, S.sV);
+        const int buf = (kc / KC) & 1;
+        float (*sK)[HD + 4] = S.sKb[buf];
+        float (*sV)[HD + 4] = S.sVb[buf];
+        cp_async_wait_all();
+        __syncthreads();                              // chunk kc has landed; phase 2 of the previous chunk is over
+        if (kc + KC < nkeys) issue_chunk<HD, KVT>(K, V, S.s_kid, kc + KC, min(KC, nkeys - kc - KC), D, hoff, S.sKb[buf ^ 1], S.sVb[buf ^ 1]);
         // ---- phase 1 ----
         unsigned live = 0;
 #pragma unroll
         for (int nb = 0; nb < KC / 8; nb++) {
             const int kA = nb * 8 + 2 * tig;
-            const int kidA = S.s_kid[kA], kendA = S.s_kend[kA], kidB = S.s_kid[kA + 1], kendB = S.s_kend[kA + 1];
+            const bool inA = kc + kA < nkeys, inB = kc + kA + 1 < nkeys;
+            const int kidA = inA ? S.s_kid[kc + kA] : 0, kendA = inA ? S.s_kend[kc + kA] : 0;
+            const int kidB = inB ? S.s_kid[kc + kA + 1] : 0, kendB = inB ? S.s_kend[kc + kA + 1] : 0;
             const bool v0 = act0 && kidA <= r0 && r0 < kendA, v1 = act0 && kidB <= r0 && r0 < kendB;
             const bool v2 = act1 && kidA <= r1 && r1 < kendA, v3 = act1 && kidB <= r1 && r1 < kendB;
             float pw[4] = {0.f, 0.f, 0.f, 0.f}, ds[4] = {0.f, 0.f, 0.f, 0.f};
@@ -638,8 +680,8 @@ __global__ void __launch_bounds__(128) attn_bwd_mma_kernel(const float *__restri
                 float c[4] = {0.f, 0.f, 0.f, 0.f}, e[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int ks = 0; ks < KS; ks++) {
-                    const float k0 = S.sK[nb * 8 + g][ks * 8 + tig], k1 = S.sK[nb * 8 + g][ks * 8 + tig + 4];
-                    const float w0 = S.sV[nb * 8 + g][ks * 8 + tig], w1 = S.sV[nb * 8 + g][ks * 8 + tig + 4];
+                    const float k0 = sK[nb * 8 + g][ks * 8 + tig], k1 = sK[nb * 8 + g][ks * 8 + tig + 4];
+                    const float w0 = sV[nb * 8 + g][ks * 8 + tig], w1 = sV[nb * 8 + g][ks * 8 + tig + 4];
                     if (SPLIT_KV) {
                         uint32_t h0, lo0, h1, lo1;
                         tf32_split(k0, h0, lo0); tf32_split(k1, h1, lo1);
@@ -663,7 +705,7 @@ __global__ void __launch_bounds__(128) attn_bwd_mma_kernel(const float *__restri
                 tf32_split(ds[1], ah[2], al[2]); tf32_split(ds[3], ah[3], al[3]);
 #pragma unroll
                 for (int db = 0; db < KS; db++) {
-                    const float b0 = S.sK[nb * 8 + 2 * tig][db * 8 + g], b1 = S.sK[nb * 8 + 2 * tig + 1][db * 8 + g];
+                    const float b0 = sK[nb * 8 + 2 * tig][db * 8 + g], b1 = sK[nb * 8 + 2 * tig + 1][db * 8 + g];
                     if (SPLIT_KV) {
                         uint32_t h0, lo0, h1, lo1;
                         tf32_split(b0, h0, lo0); tf32_split(b1, h1, lo1);
@@ -867,13 +909,13 @@ static int launch_fwd_mma(const agpt_plan *p, const float *q, const void *k, con
                           float scale, cudaStream_t st) {
     dim3 grid((unsigned)p->n_tiles, (unsigned)H);
     attn_fwd_mma_kernel<HD, KVT><<<grid, 128, 0, st>>>(q, (const KVT *)k, (const KVT *)v, out, lse, p->d_sub_end,
-                                                       p->d_chain_off, p->d_chain_ids, (int)p->n, H, scale);
+                                                       p->d_chain_off, p->d_chain_ids, p->d_chain_end, (int)p->n, H, scale);
     return launch_status("attn_fwd_mma");
 }
 
 static int fwd_dispatch(const agpt_plan *p, const float *q, const void *k, const void *v, int kv_dtype, float *out,
                         float *lse, int H, int head_dim, float scale, cudaStream_t st) {
-    if (attn_impl() == 1 && p->tile_m == 64) {
+    if (attn_impl() == 1 && p->tile_m == 64 && p->max_depth + 64 <= MAXKEYS) {
         const bool bf = kv_dtype == AGPT_KV_BF16;
         switch (head_dim) {
             case 16: return bf ? launch_fwd_mma<16, __nv_bfloat16>(p, q, k, v, out, lse, H, scale, st) : launch_fwd_mma<16, float>(p, q, k, v, out, lse, H, scale, st);
@@ -892,14 +934,15 @@ static int launch_bwd_mma(const agpt_plan *p, const float *q, const void *k, con
     size_t smem = sizeof(BwdMmaSmem<HD>);
     CUDA_TRY(cudaFuncSetAttribute(attn_bwd_mma_kernel<HD, KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attn_bwd_mma_kernel<HD, KVT><<<grid, 128, smem, st>>>(q, (const KVT *)k, (const KVT *)v, o, lse, dout, dq, dk, dv, pk, pv,
-                                                          p->d_sub_end, p->d_chain_off, p->d_chain_ids, (int)p->n, H, scale);
+                                                          p->d_sub_end, p->d_chain_off, p->d_chain_ids, p->d_chain_end, (int)p->n, H,
+                                                          scale);
     return launch_status("attn_bwd_mma");
 }
 
 static int bwd_dispatch(const agpt_plan *p, const float *q, const void *k, const void *v, int kv_dtype, const float *o,
                         const float *lse, const float *dout, float *dq, float *dk, float *dv, float *pk, float *pv, int H,
                         int head_dim, float scale, cudaStream_t st) {
-    if (attn_impl() == 1 && p->tile_m == 64) {
+    if (attn_impl() == 1 && p->tile_m == 64 && p->max_depth + 64 <= MAXKEYS) {
         const bool bf = kv_dtype == AGPT_KV_BF16;
 #define BWD_MMA_ARGS p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st
         switch (head_dim) {
