@@ -664,62 +664,82 @@ __global__ void __launch_bounds__(128) attn_bwd_mma_kernel(const float *__restri
         cp_async_wait_all();
         __syncthreads();                              // chunk kc has landed; phase 2 of the previous chunk is over
         if (kc + KC < nkeys) issue_chunk<HD, KVT>(K, V, S.s_kid, kc + KC, min(KC, nkeys - kc - KC), D, hoff, S.sKb[buf ^ 1], S.sVb[buf ^ 1]);
-        // ---- phase 1 ----
+        // ---- phase 1 ----  (two key blocks at a time: four independent accumulator chains)
         unsigned live = 0;
 #pragma unroll
-        for (int nb = 0; nb < KC / 8; nb++) {
-            const int kA = nb * 8 + 2 * tig;
-            const bool inA = kc + kA < nkeys, inB = kc + kA + 1 < nkeys;
-            const int kidA = inA ? S.s_kid[kc + kA] : 0, kendA = inA ? S.s_kend[kc + kA] : 0;
-            const int kidB = inB ? S.s_kid[kc + kA + 1] : 0, kendB = inB ? S.s_kend[kc + kA + 1] : 0;
-            const bool v0 = act0 && kidA <= r0 && r0 < kendA, v1 = act0 && kidB <= r0 && r0 < kendB;
-            const bool v2 = act1 && kidA <= r1 && r1 < kendA, v3 = act1 && kidB <= r1 && r1 < kendB;
-            float pw[4] = {0.f, 0.f, 0.f, 0.f}, ds[4] = {0.f, 0.f, 0.f, 0.f};
-            if (__any_sync(0xffffffffu, v0 | v1 | v2 | v3)) {
-                live |= 1u << nb;
-                float c[4] = {0.f, 0.f, 0.f, 0.f}, e[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int nb2 = 0; nb2 < KC / 8; nb2 += 2) {
+            bool vv[2][4];
+            bool on[2];
+            float c[2][4], e[2][4];
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                const int kA = (nb2 + u) * 8 + 2 * tig;
+                const bool inA = kc + kA < nkeys, inB = kc + kA + 1 < nkeys;
+                const int kidA = inA ? S.s_kid[kc + kA] : 0, kendA = inA ? S.s_kend[kc + kA] : 0;
+                const int kidB = inB ? S.s_kid[kc + kA + 1] : 0, kendB = inB ? S.s_kend[kc + kA + 1] : 0;
+                vv[u][0] = act0 && kidA <= r0 && r0 < kendA; vv[u][1] = act0 && kidB <= r0 && r0 < kendB;
+                vv[u][2] = act1 && kidA <= r1 && r1 < kendA; vv[u][3] = act1 && kidB <= r1 && r1 < kendB;
+                on[u] = __any_sync(0xffffffffu, vv[u][0] | vv[u][1] | vv[u][2] | vv[u][3]);
+                if (on[u]) live |= 1u << (nb2 + u);
+                c[u][0] = c[u][1] = c[u][2] = c[u][3] = 0.f;
+                e[u][0] = e[u][1] = e[u][2] = e[u][3] = 0.f;
+            }
+            if (on[0] || on[1]) {
 #pragma unroll
                 for (int ks = 0; ks < KS; ks++) {
-                    const float k0 = sK[nb * 8 + g][ks * 8 + tig], k1 = sK[nb * 8 + g][ks * 8 + tig + 4];
-                    const float w0 = sV[nb * 8 + g][ks * 8 + tig], w1 = sV[nb * 8 + g][ks * 8 + tig + 4];
-                    if (SPLIT_KV) {
-                        uint32_t h0, lo0, h1, lo1;
-                        tf32_split(k0, h0, lo0); tf32_split(k1, h1, lo1);
-                        mma_tf32(c, qh[ks], h0, h1); mma_tf32(c, ql[ks], h0, h1); mma_tf32(c, qh[ks], lo0, lo1);
-                        tf32_split(w0, h0, lo0); tf32_split(w1, h1, lo1);
-                        mma_tf32(e, gh[ks], h0, h1); mma_tf32(e, gl[ks], h0, h1); mma_tf32(e, gh[ks], lo0, lo1);
-                    } else {
-                        mma_tf32(c, qh[ks], __float_as_uint(k0), __float_as_uint(k1));
-                        mma_tf32(c, ql[ks], __float_as_uint(k0), __float_as_uint(k1));
-                        mma_tf32(e, gh[ks], __float_as_uint(w0), __float_as_uint(w1));
-                        mma_tf32(e, gl[ks], __float_as_uint(w0), __float_as_uint(w1));
-                    }
-                }
-                pw[0] = v0 ? exp2f(c[0] - lse0) : 0.f; pw[1] = v1 ? exp2f(c[1] - lse0) : 0.f;
-                pw[2] = v2 ? exp2f(c[2] - lse1) : 0.f; pw[3] = v3 ? exp2f(c[3] - lse1) : 0.f;
-                ds[0] = pw[0] * (e[0] - delta0) * scale; ds[1] = pw[1] * (e[1] - delta0) * scale;
-                ds[2] = pw[2] * (e[2] - delta1) * scale; ds[3] = pw[3] * (e[3] - delta1) * scale;
-                // dQ += dS K  (C fragment reused as A fragment: key 2*tig in k-slot tig, key 2*tig+1 in k-slot tig+4)
-                uint32_t ah[4], al[4];
-                tf32_split(ds[0], ah[0], al[0]); tf32_split(ds[2], ah[1], al[1]);
-                tf32_split(ds[1], ah[2], al[2]); tf32_split(ds[3], ah[3], al[3]);
 #pragma unroll
-                for (int db = 0; db < KS; db++) {
-                    const float b0 = sK[nb * 8 + 2 * tig][db * 8 + g], b1 = sK[nb * 8 + 2 * tig + 1][db * 8 + g];
-                    if (SPLIT_KV) {
-                        uint32_t h0, lo0, h1, lo1;
-                        tf32_split(b0, h0, lo0); tf32_split(b1, h1, lo1);
-                        mma_tf32(dq[db], ah, h0, h1); mma_tf32(dq[db], al, h0, h1); mma_tf32(dq[db], ah, lo0, lo1);
-                    } else {
-                        mma_tf32(dq[db], ah, __float_as_uint(b0), __float_as_uint(b1));
-                        mma_tf32(dq[db], al, __float_as_uint(b0), __float_as_uint(b1));
+                    for (int u = 0; u < 2; u++) {
+                        if (!on[u]) continue;
+                        const int nb = nb2 + u;
+                        const float k0 = sK[nb * 8 + g][ks * 8 + tig], k1 = sK[nb * 8 + g][ks * 8 + tig + 4];
+                        const float w0 = sV[nb * 8 + g][ks * 8 + tig], w1 = sV[nb * 8 + g][ks * 8 + tig + 4];
+                        if (SPLIT_KV) {
+                            uint32_t h0, lo0, h1, lo1, x0, y0, x1, y1;
+                            tf32_split(k0, h0, lo0); tf32_split(k1, h1, lo1);
+                            tf32_split(w0, x0, y0); tf32_split(w1, x1, y1);
+                            mma_tf32(c[u], qh[ks], h0, h1); mma_tf32(e[u], gh[ks], x0, x1);
+                            mma_tf32(c[u], ql[ks], h0, h1); mma_tf32(e[u], gl[ks], x0, x1);
+                            mma_tf32(c[u], qh[ks], lo0, lo1); mma_tf32(e[u], gh[ks], y0, y1);
+                        } else {
+                            mma_tf32(c[u], qh[ks], __float_as_uint(k0), __float_as_uint(k1));
+                            mma_tf32(e[u], gh[ks], __float_as_uint(w0), __float_as_uint(w1));
+                            mma_tf32(c[u], ql[ks], __float_as_uint(k0), __float_as_uint(k1));
+                            mma_tf32(e[u], gl[ks], __float_as_uint(w0), __float_as_uint(w1));
+                        }
                     }
                 }
             }
-            *reinterpret_cast<float2 *>(&S.sP[q0][kA]) = make_float2(pw[0], pw[1]);
-            *reinterpret_cast<float2 *>(&S.sP[q1][kA]) = make_float2(pw[2], pw[3]);
-            *reinterpret_cast<float2 *>(&S.sS[q0][kA]) = make_float2(ds[0], ds[1]);
-            *reinterpret_cast<float2 *>(&S.sS[q1][kA]) = make_float2(ds[2], ds[3]);
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                const int nb = nb2 + u, kA = nb * 8 + 2 * tig;
+                float pw[4] = {0.f, 0.f, 0.f, 0.f}, ds[4] = {0.f, 0.f, 0.f, 0.f};
+                if (on[u]) {
+                    pw[0] = vv[u][0] ? exp2f(c[u][0] - lse0) : 0.f; pw[1] = vv[u][1] ? exp2f(c[u][1] - lse0) : 0.f;
+                    pw[2] = vv[u][2] ? exp2f(c[u][2] - lse1) : 0.f; pw[3] = vv[u][3] ? exp2f(c[u][3] - lse1) : 0.f;
+                    ds[0] = pw[0] * (e[u][0] - delta0) * scale; ds[1] = pw[1] * (e[u][1] - delta0) * scale;
+                    ds[2] = pw[2] * (e[u][2] - delta1) * scale; ds[3] = pw[3] * (e[u][3] - delta1) * scale;
+                    // dQ += dS K  (C fragment reused as A fragment: key 2*tig in k-slot tig, key 2*tig+1 in k-slot tig+4)
+                    uint32_t ah[4], al[4];
+                    tf32_split(ds[0], ah[0], al[0]); tf32_split(ds[2], ah[1], al[1]);
+                    tf32_split(ds[1], ah[2], al[2]); tf32_split(ds[3], ah[3], al[3]);
+#pragma unroll
+                    for (int db = 0; db < KS; db++) {
+                        const float b0 = sK[nb * 8 + 2 * tig][db * 8 + g], b1 = sK[nb * 8 + 2 * tig + 1][db * 8 + g];
+                        if (SPLIT_KV) {
+                            uint32_t h0, lo0, h1, lo1;
+                            tf32_split(b0, h0, lo0); tf32_split(b1, h1, lo1);
+                            mma_tf32(dq[db], ah, h0, h1); mma_tf32(dq[db], al, h0, h1); mma_tf32(dq[db], ah, lo0, lo1);
+                        } else {
+                            mma_tf32(dq[db], ah, __float_as_uint(b0), __float_as_uint(b1));
+                            mma_tf32(dq[db], al, __float_as_uint(b0), __float_as_uint(b1));
+                        }
+                    }
+                }
+                *reinterpret_cast<float2 *>(&S.sP[q0][kA]) = make_float2(pw[0], pw[1]);
+                *reinterpret_cast<float2 *>(&S.sP[q1][kA]) = make_float2(pw[2], pw[3]);
+                *reinterpret_cast<float2 *>(&S.sS[q0][kA]) = make_float2(ds[0], ds[1]);
+                *reinterpret_cast<float2 *>(&S.sS[q1][kA]) = make_float2(ds[2], ds[3]);
+            }
         }
         if (lane == 0) S.s_live[warp] = live;
         __syncthreads();
@@ -1090,25 +1110,33 @@ __device__ __forceinline__ int warp_sum_i(int v) {
     return v;
 }
 
-// mode 0: per-query (radix); mode 1: per-node (leveled, node_ids index the counts)
-__global__ void loss_kernel(const float *__restrict__ logits, const int32_t *__restrict__ query_to_node,
-                            const int32_t *__restrict__ query_offsets, const int32_t *__restrict__ ids,
-                            const int32_t *__restrict__ token_ids, const int32_t *__restrict__ counts_offset,
-                            const int32_t *__restrict__ counts_tok, const int32_t *__restrict__ counts_val,
-                            const float *__restrict__ mass_weights, float *__restrict__ d_logits, float *__restrict__ loss_out,
-                            int64_t T_q, int V, float entropy_lambda, float intermediate_weight, int ce_only, int mode) {
-    int64_t qi = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+// mode 0: per-query (radix); mode 1: per-node (leveled, node_ids index the counts).
+// One warp per row; the row lives in shared memory (lane l owns columns l, l+32, ...), so every logit is read
+// once, exponentiated once and every gradient element written once.
+#define LOSS_WPB 8
+__global__ void __launch_bounds__(LOSS_WPB * 32)
+loss_kernel(const float *__restrict__ logits, const int32_t *__restrict__ query_to_node,
+            const int32_t *__restrict__ query_offsets, const int32_t *__restrict__ ids,
+            const int32_t *__restrict__ token_ids, const int32_t *__restrict__ counts_offset,
+            const int32_t *__restrict__ counts_tok, const int32_t *__restrict__ counts_val,
+            const float *__restrict__ mass_weights, float *__restrict__ d_logits, float *__restrict__ loss_out,
+            int64_t T_q, int V, float entropy_lambda, float intermediate_weight, int ce_only, int mode) {
+    extern __shared__ float s_rows[];
+    int64_t qi = (int64_t)blockIdx.x * LOSS_WPB + (threadIdx.x >> 5);
     if (qi >= T_q) return;
     const int lane = threadIdx.x & 31;
+    float *row = s_rows + (threadIdx.x >> 5) * V;
     const float *in = logits + qi * V;
     float *g = d_logits + qi * V;
     float mx = -3.402823466e+38f;
-    for (int j = lane; j < V; j += 32) mx = fmaxf(mx, in[j]);
+    for (int j = lane; j < V; j += 32) { float x = __ldcs(in + j); row[j] = x; mx = fmaxf(mx, x); }
     mx = warp_max(mx);
     float sum = 0.f;
-    for (int j = lane; j < V; j += 32) sum += expf(in[j] - mx);
+    for (int j = lane; j < V; j += 32) { float e = expf(row[j] - mx); row[j] = e; sum += e; }
     sum = warp_sum(sum);
     const float inv = 1.0f / sum;
+    for (int j = lane; j < V; j += 32) row[j] *= inv;          // probabilities
+    __syncwarp();
 
     bool endpoint_path;
     int cid = 0;
@@ -1123,51 +1151,46 @@ __global__ void loss_kernel(const float *__restrict__ logits, const int32_t *__r
     float weight = 1.0f, loss = 0.f;
     if (endpoint_path) {
         const int start = counts_offset[cid], end = counts_offset[cid + 1];
-        if (start == end) {
-            // no observed continuation: zero loss; the row keeps the plain probabilities
-            for (int j = lane; j < V; j += 32) g[j] = expf(in[j] - mx) * inv;
-            if (lane == 0) loss_out[qi] = 0.f;
-            return;
-        }
-        int total = 0;
-        for (int e = start + lane; e < end; e += 32) total += counts_val[e];
-        total = warp_sum_i(total);
-        const float total_f = (float)total;
-        if (mode == 0) {
-            if (entropy_lambda > 0.0f && (end - start) > 1) {
-                float Hh = 0.f;
-                for (int e = start + lane; e < end; e += 32) {
-                    float qe = counts_val[e] / total_f;
-                    if (qe > 0.f) Hh -= qe * logf(qe);
+        if (start != end) {
+            int total = 0;
+            for (int e = start + lane; e < end; e += 32) total += counts_val[e];
+            total = warp_sum_i(total);
+            const float total_f = (float)total;
+            if (mode == 0) {
+                if (entropy_lambda > 0.0f && (end - start) > 1) {
+                    float Hh = 0.f;
+                    for (int e = start + lane; e < end; e += 32) {
+                        float qe = counts_val[e] / total_f;
+                        if (qe > 0.f) Hh -= qe * logf(qe);
+                    }
+                    Hh = warp_sum(Hh);
+                    weight = 1.0f + entropy_lambda * (Hh / logf((float)V));
                 }
-                Hh = warp_sum(Hh);
-                weight = 1.0f + entropy_lambda * (Hh / logf((float)V));
+                if (mass_weights) weight *= mass_weights[qi];
             }
-            if (mass_weights) weight *= mass_weights[qi];
+            for (int e = start + lane; e < end; e += 32) {
+                int tok = counts_tok[e];
+                if ((unsigned)tok >= (unsigned)V) continue;      // a token outside the vocabulary is ignored, not written
+                float tgt = counts_val[e] / total_f;
+                float pr = row[tok];
+                loss -= tgt * logf(pr + 1e-10f);
+                row[tok] = pr - tgt;                             // tokens of one node are distinct
+            }
+            loss = warp_sum(loss) * weight;
         }
-        for (int j = lane; j < V; j += 32) g[j] = expf(in[j] - mx) * inv * weight;
-        __syncwarp();
-        for (int e = start + lane; e < end; e += 32) {
-            int tok = counts_tok[e];
-            if ((unsigned)tok >= (unsigned)V) continue;      // a token outside the vocabulary is ignored, not written
-            float tgt = counts_val[e] / total_f;
-            float pr = expf(in[tok] - mx) * inv;
-            loss -= tgt * logf(pr + 1e-10f);
-            g[tok] = (pr - tgt) * weight;      // tokens of one node are distinct
-        }
-        loss = warp_sum(loss) * weight;
+        // else: no observed continuation -- zero loss, and the row keeps the plain probabilities
     } else {
         int target = token_ids[qi + 1];
-        if ((unsigned)target >= (unsigned)V) target = 0;      // never index outside the row
+        if ((unsigned)target >= (unsigned)V) target = 0;         // never index outside the row
         weight = intermediate_weight;
         if (mass_weights) weight *= mass_weights[qi];
-        for (int j = lane; j < V; j += 32) {
-            float pr = expf(in[j] - mx) * inv;
-            g[j] = (j == target ? pr - 1.0f : pr) * weight;
-        }
-        float pr = expf(in[target] - mx) * inv;
+        const float pr = row[target];
         loss = -logf(pr + 1e-10f) * weight;
+        __syncwarp();
+        if (lane == 0) row[target] = pr - 1.0f;
     }
+    __syncwarp();
+    for (int j = lane; j < V; j += 32) __stcs(g + j, row[j] * weight);
     if (lane == 0) loss_out[qi] = loss;
 }
 
@@ -1180,8 +1203,9 @@ extern "C" int agpt_b200_loss_per_query(const float *d_logits, const int32_t *d_
         !d_counts_val || !d_dlogits || !d_loss || T_q < 0 || V < 1)
         return agpt_set_error(AGPT_E_ARG, "loss_per_query: bad argument");
     if (T_q == 0) return AGPT_OK;
-    const int wpb = 8;
-    loss_kernel<<<(unsigned)((T_q + wpb - 1) / wpb), wpb * 32, 0, (cudaStream_t)stream>>>(
+    if (V > 1400) return agpt_set_error(AGPT_E_LIMIT, "loss_per_query: vocabulary %d beyond 1400", V);
+    const int wpb = LOSS_WPB;
+    loss_kernel<<<(unsigned)((T_q + wpb - 1) / wpb), wpb * 32, (size_t)wpb * V * sizeof(float), (cudaStream_t)stream>>>(
         d_logits, d_query_to_node, d_query_offsets, d_radix_ids, d_token_ids, d_counts_offset, d_counts_tok, d_counts_val,
         d_mass_weights, d_dlogits, d_loss, T_q, V, entropy_lambda, intermediate_weight, ce_only, 0);
     return launch_status("loss_per_query");
@@ -1193,8 +1217,9 @@ extern "C" int agpt_b200_loss_per_node(const float *d_logits, const int32_t *d_n
     if (!d_logits || !d_node_ids || !d_counts_offset || !d_counts_tok || !d_counts_val || !d_dlogits || !d_loss || N < 0 || V < 1)
         return agpt_set_error(AGPT_E_ARG, "loss_per_node: bad argument");
     if (N == 0) return AGPT_OK;
-    const int wpb = 8;
-    loss_kernel<<<(unsigned)((N + wpb - 1) / wpb), wpb * 32, 0, (cudaStream_t)stream>>>(
+    if (V > 1400) return agpt_set_error(AGPT_E_LIMIT, "loss_per_node: vocabulary %d beyond 1400", V);
+    const int wpb = LOSS_WPB;
+    loss_kernel<<<(unsigned)((N + wpb - 1) / wpb), wpb * 32, (size_t)wpb * V * sizeof(float), (cudaStream_t)stream>>>(
         d_logits, nullptr, nullptr, d_node_ids, nullptr, d_counts_offset, d_counts_tok, d_counts_val, nullptr, d_dlogits, d_loss,
         N, V, 0.f, 1.f, 0, 1);
     return launch_status("loss_per_node");
