@@ -32,6 +32,12 @@ struct agpt_plan {
     int64_t *d_chain_off = nullptr, *d_multi_first = nullptr;
     int32_t *d_item_node = nullptr, *d_item_t0 = nullptr, *d_item_t1 = nullptr, *d_item_slot = nullptr;
     int32_t *d_multi_node = nullptr, *d_multi_count = nullptr;
+    // host-buffer step (agpt_b200_attn_fwd_bwd_host): device arena, three streams (upload, compute, download) and
+    // per-chunk events; created at first use, kept for later calls, released with the plan
+    void *host_arena = nullptr;
+    size_t host_arena_bytes = 0;
+    void *host_streams[3] = {nullptr, nullptr, nullptr};
+    std::vector<void *> host_events;
     ~agpt_plan();
 };
 

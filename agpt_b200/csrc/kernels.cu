@@ -9,6 +9,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
@@ -66,6 +67,9 @@ agpt_plan::~agpt_plan() {
         cudaFree(d_depth); cudaFree(d_sub_end); cudaFree(d_chain_ids); cudaFree(d_chain_end); cudaFree(d_chain_off);
         cudaFree(d_item_node); cudaFree(d_item_t0); cudaFree(d_item_t1); cudaFree(d_item_slot);
         cudaFree(d_multi_node); cudaFree(d_multi_count); cudaFree(d_multi_first);
+        cudaFree(host_arena);
+        for (void *e : host_events) cudaEventDestroy((cudaEvent_t)e);
+        for (void *st : host_streams) if (st) cudaStreamDestroy((cudaStream_t)st);
         if (cur >= 0) cudaSetDevice(cur);
     }
 }
@@ -119,11 +123,11 @@ __global__ void __launch_bounds__(M) attn_fwd_kernel(const float *__restrict__ Q
                                                      const KVT *__restrict__ V, float *__restrict__ O,
                                                      float *__restrict__ LSE, const int32_t *__restrict__ sub_end,
                                                      const int64_t *__restrict__ chain_off,
-                                                     const int32_t *__restrict__ chain_ids, int n, int H, float scale) {
+                                                     const int32_t *__restrict__ chain_ids, int n, int H, float scale, int tile0) {
     __shared__ __align__(16) float sK[KC][HD + 4];
     __shared__ __align__(16) float sV[KC][HD + 4];
     __shared__ int s_kid[KC], s_kend[KC];
-    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int t = blockIdx.x + tile0, h = blockIdx.y, tid = threadIdx.x;
     const int D = H * HD, hoff = h * HD;
     const int i0 = t * M, i = i0 + tid;
     const bool active = i < n;
@@ -281,13 +285,13 @@ __global__ void __launch_bounds__(128) attn_fwd_mma_kernel(const float *__restri
                                                            const int64_t *__restrict__ chain_off,
                                                            const int32_t *__restrict__ chain_ids,
                                                            const int32_t *__restrict__ chain_end_all, int n, int H,
-                                                           float scale) {
+                                                           float scale, int tile0) {
     constexpr int M = 64, KS = HD / 8;
     constexpr bool SPLIT_KV = sizeof(KVT) == 4;
     __shared__ __align__(16) float sKb[2][KC][HD + 4];
     __shared__ __align__(16) float sVb[2][KC][HD + 4];
     __shared__ int s_kid[MAXKEYS], s_kend[MAXKEYS];
-    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int t = blockIdx.x + tile0, h = blockIdx.y, tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, tig = lane & 3;
     const int D = H * HD, hoff = h * HD;
     const int i0 = t * M;
@@ -443,10 +447,10 @@ __global__ void __launch_bounds__(M) attn_bwd_kernel(const float *__restrict__ Q
                                                      float *__restrict__ dV, float *__restrict__ Pk,
                                                      float *__restrict__ Pv, const int32_t *__restrict__ sub_end,
                                                      const int64_t *__restrict__ chain_off,
-                                                     const int32_t *__restrict__ chain_ids, int n, int H, float scale) {
+                                                     const int32_t *__restrict__ chain_ids, int n, int H, float scale, int tile0) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     BwdSmem<HD, M> &S = *reinterpret_cast<BwdSmem<HD, M> *>(smem_raw);
-    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int t = blockIdx.x + tile0, h = blockIdx.y, tid = threadIdx.x;
     const int D = H * HD, hoff = h * HD;
     const int i0 = t * M, i = i0 + tid;
     const bool active = i < n;
@@ -588,13 +592,13 @@ __global__ void __launch_bounds__(128) attn_bwd_mma_kernel(const float *__restri
                                                            const int64_t *__restrict__ chain_off,
                                                            const int32_t *__restrict__ chain_ids,
                                                            const int32_t *__restrict__ chain_end_all, int n, int H,
-                                                           float scale) {
+                                                           float scale, int tile0) {
     constexpr int M = 64, KS = HD / 8;
     constexpr bool SPLIT_KV = sizeof(KVT) == 4;
     constexpr int NB2 = (KS + 1) / 2;          // head_dim blocks of 8 per warp in phase 2
     extern __shared__ __align__(16) unsigned char smem_raw[];
     BwdMmaSmem<HD> &S = *reinterpret_cast<BwdMmaSmem<HD> *>(smem_raw);
-    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int t = blockIdx.x + tile0, h = blockIdx.y, tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, tig = lane & 3;
     const int D = H * HD, hoff = h * HD;
     const int i0 = t * M;
@@ -873,22 +877,22 @@ static int check_common(const agpt_plan *p, int n_heads, int head_dim, const cha
 
 template <int HD, int M, typename KVT>
 static int launch_fwd(const agpt_plan *p, const float *q, const void *k, const void *v, float *out, float *lse, int H,
-                      float scale, cudaStream_t st) {
-    dim3 grid((unsigned)p->n_tiles, (unsigned)H);
+                      float scale, cudaStream_t st, int tile0, int ntiles) {
+    dim3 grid((unsigned)ntiles, (unsigned)H);
     attn_fwd_kernel<HD, M, KVT><<<grid, M, 0, st>>>(q, (const KVT *)k, (const KVT *)v, out, lse, p->d_sub_end,
-                                                    p->d_chain_off, p->d_chain_ids, (int)p->n, H, scale);
+                                                    p->d_chain_off, p->d_chain_ids, (int)p->n, H, scale, tile0);
     return launch_status("attn_fwd");
 }
 
 template <int HD, int M, typename KVT>
 static int launch_bwd(const agpt_plan *p, const float *q, const void *k, const void *v, const float *o, const float *lse,
                       const float *dout, float *dq, float *dk, float *dv, float *pk, float *pv, int H, float scale,
-                      cudaStream_t st) {
-    dim3 grid((unsigned)p->n_tiles, (unsigned)H);
+                      cudaStream_t st, int tile0, int ntiles) {
+    dim3 grid((unsigned)ntiles, (unsigned)H);
     size_t smem = sizeof(BwdSmem<HD, M>);
     CUDA_TRY(cudaFuncSetAttribute(attn_bwd_kernel<HD, M, KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attn_bwd_kernel<HD, M, KVT><<<grid, M, smem, st>>>(q, (const KVT *)k, (const KVT *)v, o, lse, dout, dq, dk, dv, pk, pv,
-                                                       p->d_sub_end, p->d_chain_off, p->d_chain_ids, (int)p->n, H, scale);
+                                                       p->d_sub_end, p->d_chain_off, p->d_chain_ids, (int)p->n, H, scale, tile0);
     return launch_status("attn_bwd");
 }
 
@@ -926,45 +930,45 @@ extern "C" int agpt_b200_set_attn_impl(int impl) {
 
 template <int HD, typename KVT>
 static int launch_fwd_mma(const agpt_plan *p, const float *q, const void *k, const void *v, float *out, float *lse, int H,
-                          float scale, cudaStream_t st) {
-    dim3 grid((unsigned)p->n_tiles, (unsigned)H);
+                          float scale, cudaStream_t st, int tile0, int ntiles) {
+    dim3 grid((unsigned)ntiles, (unsigned)H);
     attn_fwd_mma_kernel<HD, KVT><<<grid, 128, 0, st>>>(q, (const KVT *)k, (const KVT *)v, out, lse, p->d_sub_end,
-                                                       p->d_chain_off, p->d_chain_ids, p->d_chain_end, (int)p->n, H, scale);
+                                                       p->d_chain_off, p->d_chain_ids, p->d_chain_end, (int)p->n, H, scale, tile0);
     return launch_status("attn_fwd_mma");
 }
 
 static int fwd_dispatch(const agpt_plan *p, const float *q, const void *k, const void *v, int kv_dtype, float *out,
-                        float *lse, int H, int head_dim, float scale, cudaStream_t st) {
+                        float *lse, int H, int head_dim, float scale, cudaStream_t st, int tile0, int ntiles) {
     if (attn_impl() == 1 && p->tile_m == 64 && p->max_depth + 64 <= MAXKEYS) {
         const bool bf = kv_dtype == AGPT_KV_BF16;
         switch (head_dim) {
-            case 16: return bf ? launch_fwd_mma<16, __nv_bfloat16>(p, q, k, v, out, lse, H, scale, st) : launch_fwd_mma<16, float>(p, q, k, v, out, lse, H, scale, st);
-            case 32: return bf ? launch_fwd_mma<32, __nv_bfloat16>(p, q, k, v, out, lse, H, scale, st) : launch_fwd_mma<32, float>(p, q, k, v, out, lse, H, scale, st);
-            case 64: return bf ? launch_fwd_mma<64, __nv_bfloat16>(p, q, k, v, out, lse, H, scale, st) : launch_fwd_mma<64, float>(p, q, k, v, out, lse, H, scale, st);
+            case 16: return bf ? launch_fwd_mma<16, __nv_bfloat16>(p, q, k, v, out, lse, H, scale, st, tile0, ntiles) : launch_fwd_mma<16, float>(p, q, k, v, out, lse, H, scale, st, tile0, ntiles);
+            case 32: return bf ? launch_fwd_mma<32, __nv_bfloat16>(p, q, k, v, out, lse, H, scale, st, tile0, ntiles) : launch_fwd_mma<32, float>(p, q, k, v, out, lse, H, scale, st, tile0, ntiles);
+            case 64: return bf ? launch_fwd_mma<64, __nv_bfloat16>(p, q, k, v, out, lse, H, scale, st, tile0, ntiles) : launch_fwd_mma<64, float>(p, q, k, v, out, lse, H, scale, st, tile0, ntiles);
         }
     }
-    DISPATCH_HD_M_KV(launch_fwd, p, q, k, v, out, lse, H, scale, st);
+    DISPATCH_HD_M_KV(launch_fwd, p, q, k, v, out, lse, H, scale, st, tile0, ntiles);
 }
 
 template <int HD, typename KVT>
 static int launch_bwd_mma(const agpt_plan *p, const float *q, const void *k, const void *v, const float *o, const float *lse,
                           const float *dout, float *dq, float *dk, float *dv, float *pk, float *pv, int H, float scale,
-                          cudaStream_t st) {
-    dim3 grid((unsigned)p->n_tiles, (unsigned)H);
+                          cudaStream_t st, int tile0, int ntiles) {
+    dim3 grid((unsigned)ntiles, (unsigned)H);
     size_t smem = sizeof(BwdMmaSmem<HD>);
     CUDA_TRY(cudaFuncSetAttribute(attn_bwd_mma_kernel<HD, KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attn_bwd_mma_kernel<HD, KVT><<<grid, 128, smem, st>>>(q, (const KVT *)k, (const KVT *)v, o, lse, dout, dq, dk, dv, pk, pv,
                                                           p->d_sub_end, p->d_chain_off, p->d_chain_ids, p->d_chain_end, (int)p->n, H,
-                                                          scale);
+                                                          scale, tile0);
     return launch_status("attn_bwd_mma");
 }
 
 static int bwd_dispatch(const agpt_plan *p, const float *q, const void *k, const void *v, int kv_dtype, const float *o,
                         const float *lse, const float *dout, float *dq, float *dk, float *dv, float *pk, float *pv, int H,
-                        int head_dim, float scale, cudaStream_t st) {
+                        int head_dim, float scale, cudaStream_t st, int tile0, int ntiles) {
     if (attn_impl() == 1 && p->tile_m == 64 && p->max_depth + 64 <= MAXKEYS) {
         const bool bf = kv_dtype == AGPT_KV_BF16;
-#define BWD_MMA_ARGS p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st
+#define BWD_MMA_ARGS p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles
         switch (head_dim) {
             case 16: return bf ? launch_bwd_mma<16, __nv_bfloat16>(BWD_MMA_ARGS) : launch_bwd_mma<16, float>(BWD_MMA_ARGS);
             case 32: return bf ? launch_bwd_mma<32, __nv_bfloat16>(BWD_MMA_ARGS) : launch_bwd_mma<32, float>(BWD_MMA_ARGS);
@@ -972,7 +976,7 @@ static int bwd_dispatch(const agpt_plan *p, const float *q, const void *k, const
         }
 #undef BWD_MMA_ARGS
     }
-    DISPATCH_HD_M_KV(launch_bwd, p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st);
+    DISPATCH_HD_M_KV(launch_bwd, p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles);
 }
 
 extern "C" int agpt_b200_attn_fwd(const agpt_plan *p, const float *d_q, const void *d_k, const void *d_v, int kv_dtype,
@@ -981,7 +985,7 @@ extern "C" int agpt_b200_attn_fwd(const agpt_plan *p, const float *d_q, const vo
     if (rc) return rc;
     if (!d_q || !d_k || !d_v || !d_out || !d_lse) return agpt_set_error(AGPT_E_ARG, "attn_fwd: null buffer");
     if (kv_dtype != AGPT_KV_F32 && kv_dtype != AGPT_KV_BF16) return agpt_set_error(AGPT_E_ARG, "attn_fwd: bad kv_dtype");
-    return fwd_dispatch(p, d_q, d_k, d_v, kv_dtype, d_out, d_lse, n_heads, head_dim, scale, (cudaStream_t)stream);
+    return fwd_dispatch(p, d_q, d_k, d_v, kv_dtype, d_out, d_lse, n_heads, head_dim, scale, (cudaStream_t)stream, 0, (int)p->n_tiles);
 }
 
 static int run_reduce(const agpt_plan *p, float *pk, float *pv, float *segk, float *segv, float *dk, float *dv, int D,
@@ -1022,7 +1026,7 @@ extern "C" int agpt_b200_attn_bwd(const agpt_plan *p, const float *d_q, const vo
     const int64_t rows = (int64_t)p->chain_ids.size();
     float *pk = (float *)d_workspace, *pv = pk + rows * D, *segk = pv + rows * D, *segv = segk + p->n_multi_items * D;
     rc = bwd_dispatch(p, d_q, d_k, d_v, kv_dtype, d_out, d_lse, d_dout, d_dq, d_dk, d_dv, pk, pv, n_heads, head_dim, scale,
-                      (cudaStream_t)stream);
+                      (cudaStream_t)stream, 0, (int)p->n_tiles);
     if (rc) return rc;
     return run_reduce(p, pk, pv, segk, segv, d_dk, d_dv, D, (cudaStream_t)stream);
 }
@@ -1465,56 +1469,90 @@ extern "C" void cuda_sync(void) {
 }
 
 // --------------------------------------------------------------------------------------
-// host-buffer step
+// host-buffer step: upload, forward, backward and download as a three-stream pipeline over row chunks.
+// Ancestors precede descendants in depth-first order, so once rows [0, e) are on the device every tile below e
+// can run forward and backward: chunk c+1 uploads while chunk c computes and chunk c-1's out/lse/dq download.
+// Only dK/dV (complete after the last tile and the reduction) download at the end.
 // --------------------------------------------------------------------------------------
-extern "C" int agpt_b200_attn_fwd_bwd_host(const agpt_plan *p, const float *h_q, const float *h_k, const float *h_v,
+extern "C" int agpt_b200_attn_fwd_bwd_host(const agpt_plan *cp, const float *h_q, const float *h_k, const float *h_v,
                                            const float *h_dout, float *h_out, float *h_lse, float *h_dq, float *h_dk, float *h_dv,
                                            int kv_dtype, int n_heads, int head_dim, float scale) {
-    int rc = check_common(p, n_heads, head_dim, "attn_fwd_bwd_host");
+    int rc = check_common(cp, n_heads, head_dim, "attn_fwd_bwd_host");
     if (rc) return rc;
     if (!h_q || !h_k || !h_v || !h_dout || !h_out || !h_lse || !h_dq || !h_dk || !h_dv)
         return agpt_set_error(AGPT_E_ARG, "attn_fwd_bwd_host: null buffer");
+    if (kv_dtype != AGPT_KV_F32 && kv_dtype != AGPT_KV_BF16) return agpt_set_error(AGPT_E_ARG, "attn_fwd_bwd_host: bad kv_dtype");
+    agpt_plan *p = const_cast<agpt_plan *>(cp);        // the cached arena is the only state a call changes
     CUDA_TRY(cudaSetDevice(p->device));
-    const int D = n_heads * head_dim;
-    const size_t rowb = (size_t)p->n * D * sizeof(float);
-    const int64_t wsb = agpt_b200_attn_bwd_workspace_bytes(p, D);
-    float *d[9] = {nullptr};   // q k v dout out dq dk dv lse
-    void *kb = nullptr, *vb = nullptr, *ws = nullptr;
-    cudaStream_t st = nullptr;
-    auto cleanup = [&]() {
-        for (float *x : d) cudaFree(x);
-        cudaFree(kb); cudaFree(vb); cudaFree(ws);
-        if (st) cudaStreamDestroy(st);
-    };
-#define TRY_OR_CLEAN(x)                                                                                      \
-    do {                                                                                                     \
-        cudaError_t e_ = (x);                                                                                \
-        if (e_ != cudaSuccess) { cleanup(); return agpt_set_error(AGPT_E_CUDA, "%s: %s", #x, cudaGetErrorString(e_)); } \
-    } while (0)
-    TRY_OR_CLEAN(cudaStreamCreate(&st));
-    for (int j = 0; j < 8; j++) TRY_OR_CLEAN(cudaMalloc((void **)&d[j], rowb));
-    TRY_OR_CLEAN(cudaMalloc((void **)&d[8], (size_t)p->n * n_heads * sizeof(float)));
-    TRY_OR_CLEAN(cudaMalloc(&ws, (size_t)wsb));
-    TRY_OR_CLEAN(cudaMemcpyAsync(d[0], h_q, rowb, cudaMemcpyHostToDevice, st));
-    TRY_OR_CLEAN(cudaMemcpyAsync(d[1], h_k, rowb, cudaMemcpyHostToDevice, st));
-    TRY_OR_CLEAN(cudaMemcpyAsync(d[2], h_v, rowb, cudaMemcpyHostToDevice, st));
-    TRY_OR_CLEAN(cudaMemcpyAsync(d[3], h_dout, rowb, cudaMemcpyHostToDevice, st));
-    const void *kk = d[1], *vv = d[2];
-    if (kv_dtype == AGPT_KV_BF16) {
-        TRY_OR_CLEAN(cudaMalloc(&kb, rowb / 2));
-        TRY_OR_CLEAN(cudaMalloc(&vb, rowb / 2));
-        if ((rc = agpt_b200_kv_store_write_bf16(d[1], kb, p->n, D, st)) || (rc = agpt_b200_kv_store_write_bf16(d[2], vb, p->n, D, st))) { cleanup(); return rc; }
-        kk = kb; vv = vb;
+    const int D = n_heads * head_dim, M = p->tile_m;
+    const int64_t n = p->n;
+    const size_t rowb = (size_t)D * sizeof(float);
+    const size_t tens = (((size_t)n * rowb) + 255) & ~(size_t)255;
+    const size_t lseb = (((size_t)n * n_heads * sizeof(float)) + 255) & ~(size_t)255;
+    const size_t wsb = (((size_t)agpt_b200_attn_bwd_workspace_bytes(p, D)) + 255) & ~(size_t)255;
+    const bool bf = kv_dtype == AGPT_KV_BF16;
+    const size_t need = 8 * tens + lseb + wsb + (bf ? tens : 0);
+    if (p->host_arena_bytes < need) {
+        if (p->host_arena) { CUDA_TRY(cudaFree(p->host_arena)); p->host_arena = nullptr; p->host_arena_bytes = 0; }
+        CUDA_TRY(cudaMalloc(&p->host_arena, need));
+        p->host_arena_bytes = need;
     }
-    if ((rc = agpt_b200_attn_fwd(p, d[0], kk, vv, kv_dtype, d[4], d[8], n_heads, head_dim, scale, st))) { cleanup(); return rc; }
-    if ((rc = agpt_b200_attn_bwd(p, d[0], kk, vv, kv_dtype, d[4], d[8], d[3], d[5], d[6], d[7], ws, wsb, n_heads, head_dim, scale, st))) { cleanup(); return rc; }
-    TRY_OR_CLEAN(cudaMemcpyAsync(h_out, d[4], rowb, cudaMemcpyDeviceToHost, st));
-    TRY_OR_CLEAN(cudaMemcpyAsync(h_lse, d[8], (size_t)p->n * n_heads * sizeof(float), cudaMemcpyDeviceToHost, st));
-    TRY_OR_CLEAN(cudaMemcpyAsync(h_dq, d[5], rowb, cudaMemcpyDeviceToHost, st));
-    TRY_OR_CLEAN(cudaMemcpyAsync(h_dk, d[6], rowb, cudaMemcpyDeviceToHost, st));
-    TRY_OR_CLEAN(cudaMemcpyAsync(h_dv, d[7], rowb, cudaMemcpyDeviceToHost, st));
-    TRY_OR_CLEAN(cudaStreamSynchronize(st));
-    cleanup();
+    for (int i = 0; i < 3; i++)
+        if (!p->host_streams[i]) { cudaStream_t st; CUDA_TRY(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking)); p->host_streams[i] = st; }
+    cudaStream_t s_up = (cudaStream_t)p->host_streams[0], s_run = (cudaStream_t)p->host_streams[1], s_down = (cudaStream_t)p->host_streams[2];
+    char *base = (char *)p->host_arena;
+    float *dq_in = (float *)base, *dk_in = (float *)(base + tens), *dv_in = (float *)(base + 2 * tens), *dg = (float *)(base + 3 * tens);
+    float *dout = (float *)(base + 4 * tens), *ddq = (float *)(base + 5 * tens), *ddk = (float *)(base + 6 * tens), *ddv = (float *)(base + 7 * tens);
+    float *dlse = (float *)(base + 8 * tens);
+    void *ws = base + 8 * tens + lseb;
+    __nv_bfloat16 *kb = bf ? (__nv_bfloat16 *)(base + 8 * tens + lseb + wsb) : nullptr;
+    __nv_bfloat16 *vb = bf ? kb + (size_t)n * D : nullptr;
+    const void *kk = bf ? (const void *)kb : (const void *)dk_in, *vv = bf ? (const void *)vb : (const void *)dv_in;
+    const int64_t rows = (int64_t)p->chain_ids.size();
+    float *pk = (float *)ws, *pv = pk + rows * D, *segk = pv + rows * D, *segv = segk + p->n_multi_items * D;
+
+    // chunks of about 64 MB per tensor, whole tiles
+    int64_t ch_rows = std::max<int64_t>(M, ((64ll << 20) / (int64_t)rowb) / M * M);
+    const int64_t n_ch = (n + ch_rows - 1) / ch_rows;
+    while ((int64_t)p->host_events.size() < 3 * n_ch + 1) {
+        cudaEvent_t e;
+        CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        p->host_events.push_back(e);
+    }
+    auto ev = [&](int64_t c, int k) { return (cudaEvent_t)p->host_events[3 * c + k]; };
+    for (int64_t c = 0; c < n_ch; c++) {
+        const int64_t r0 = c * ch_rows, r1 = std::min(n, r0 + ch_rows), nr = r1 - r0;
+        const size_t off = (size_t)r0 * D, bytes = (size_t)nr * rowb;
+        CUDA_TRY(cudaMemcpyAsync(dq_in + off, h_q + off, bytes, cudaMemcpyHostToDevice, s_up));
+        CUDA_TRY(cudaMemcpyAsync(dk_in + off, h_k + off, bytes, cudaMemcpyHostToDevice, s_up));
+        CUDA_TRY(cudaMemcpyAsync(dv_in + off, h_v + off, bytes, cudaMemcpyHostToDevice, s_up));
+        CUDA_TRY(cudaMemcpyAsync(dg + off, h_dout + off, bytes, cudaMemcpyHostToDevice, s_up));
+        CUDA_TRY(cudaEventRecord(ev(c, 0), s_up));
+        CUDA_TRY(cudaStreamWaitEvent(s_run, ev(c, 0), 0));
+        if (bf) {
+            if ((rc = agpt_b200_kv_store_write_bf16(dk_in + off, kb + off, nr, D, s_run))) return rc;
+            if ((rc = agpt_b200_kv_store_write_bf16(dv_in + off, vb + off, nr, D, s_run))) return rc;
+        }
+        const int t0 = (int)(r0 / M), nt = (int)((r1 + M - 1) / M) - t0;
+        if ((rc = fwd_dispatch(p, dq_in, kk, vv, kv_dtype, dout, dlse, n_heads, head_dim, scale, s_run, t0, nt))) return rc;
+        CUDA_TRY(cudaEventRecord(ev(c, 1), s_run));
+        if ((rc = bwd_dispatch(p, dq_in, kk, vv, kv_dtype, dout, dlse, dg, ddq, ddk, ddv, pk, pv, n_heads, head_dim, scale, s_run, t0, nt))) return rc;
+        CUDA_TRY(cudaEventRecord(ev(c, 2), s_run));
+        CUDA_TRY(cudaStreamWaitEvent(s_down, ev(c, 1), 0));
+        CUDA_TRY(cudaMemcpyAsync(h_out + off, dout + off, bytes, cudaMemcpyDeviceToHost, s_down));
+        CUDA_TRY(cudaMemcpyAsync(h_lse + (size_t)r0 * n_heads, dlse + (size_t)r0 * n_heads, (size_t)nr * n_heads * sizeof(float), cudaMemcpyDeviceToHost, s_down));
+        CUDA_TRY(cudaStreamWaitEvent(s_down, ev(c, 2), 0));
+        CUDA_TRY(cudaMemcpyAsync(h_dq + off, ddq + off, bytes, cudaMemcpyDeviceToHost, s_down));
+    }
+    if ((rc = run_reduce(p, pk, pv, segk, segv, ddk, ddv, D, s_run))) return rc;
+    cudaEvent_t done = (cudaEvent_t)p->host_events[3 * n_ch];
+    CUDA_TRY(cudaEventRecord(done, s_run));
+    CUDA_TRY(cudaStreamWaitEvent(s_down, done, 0));
+    CUDA_TRY(cudaMemcpyAsync(h_dk, ddk, (size_t)n * rowb, cudaMemcpyDeviceToHost, s_down));
+    CUDA_TRY(cudaMemcpyAsync(h_dv, ddv, (size_t)n * rowb, cudaMemcpyDeviceToHost, s_down));
+    CUDA_TRY(cudaStreamSynchronize(s_down));
+    CUDA_TRY(cudaStreamSynchronize(s_run));
+    CUDA_TRY(cudaStreamSynchronize(s_up));
     return AGPT_OK;
 }
 
@@ -1567,7 +1605,7 @@ extern "C" int agpt_b200_attn_bwd_static(const agpt_plan *p, const float *d_q, c
     const int64_t rows = (int64_t)p->chain_ids.size();
     float *pk = (float *)g_static_scratch_addr[cur], *pv = pk + rows * D, *segk = pv + rows * D, *segv = segk + p->n_multi_items * D;
     rc = bwd_dispatch(p, d_q, d_k, d_v, kv_dtype, d_out, d_lse, d_dout, d_dq, d_dk, d_dv, pk, pv, n_heads, head_dim, scale,
-                      (cudaStream_t)stream);
+                      (cudaStream_t)stream, 0, (int)p->n_tiles);
     if (rc) return rc;
     return run_reduce(p, pk, pv, segk, segv, d_dk, d_dv, D, (cudaStream_t)stream);
 }

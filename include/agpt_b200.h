@@ -263,7 +263,10 @@ int agpt_b200_loss_per_node(const float *d_logits, const int32_t *d_node_ids, co
 /* Host-buffer convenience of the same step (what gpu_batched_attention /
  * gpu_attention_backward_depth do around the kernels, src/agpt/batched_depth_forward.cr:745-823,
  * src/agpt/batched_depth_backward.cr:453-500): uploads q, k, v, d_out from host memory, runs forward
- * and backward, downloads out, lse, dq, dk, dv.  The device buffers are allocated per call. */
+ * and backward, downloads out, lse, dq, dk, dv.  Upload, compute and download run as a pipeline over row chunks
+ * on three internal streams (pinned host memory lets them overlap); the call returns when everything is on the
+ * host.  The device arena is allocated at the first call on a plan and kept until agpt_b200_plan_destroy, so one
+ * plan must not be used by two host threads at once. */
 int agpt_b200_attn_fwd_bwd_host(const agpt_plan *p, const float *h_q, const float *h_k, const float *h_v,
                                 const float *h_dout, float *h_out, float *h_lse, float *h_dq, float *h_dk,
                                 float *h_dv, int kv_dtype, int n_heads, int head_dim, float scale);
