@@ -1,0 +1,297 @@
+"""Trie-walk trainer on top of the hot path: the walker, the per-subtree KV store and one epoch.
+
+Mirrors the radix training loop of the reference trainer (src/cuda/agpt_train.cu:3177-5512): per launch
+group (a forest of root-child or bigram subtrees in depth-first order) embed the edge characters, run every
+layer (LN1, Q/K/V projections, RoPE, trie-scoped attention, WO, residual, LN2, ReLU FFN, residual), final LN and
+output projection over all positions, per-query loss with mass weights normalised over the group, backward,
+and an optimizer step.  The trie-scoped attention, its backward with ancestor dK/dV, RoPE and the loss are this
+library's kernels; the dense projections and layer norms are torch (cuBLAS) calls, as they are cuBLAS calls in
+the reference.  Model files (MGPT) and radix trie directories are read and written unchanged.
+
+    python -m agpt_b200.trainer --model m.model --trie-dir DIR --epochs 3 --lr 3e-4 --optimizer rmsprop \\
+        --rmsprop-beta 0.999 --mass-weight linear --save out.model
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import time
+
+import numpy as np
+
+from . import api as A
+from . import model_file as MF
+
+
+class LaunchGroup:
+    """Rows of one launch: local forest (depth-first), tokens, RoPE positions and the loss index arrays."""
+
+    def __init__(self, parent, tokens, depth, radix_of, edge_mass, mass_mode, seq_len, device, tile=64, trained=None):
+        import torch
+        self.n = int(parent.size)
+        self.plan = A.WalkerPlan(parent, tile, device.index)
+        order = self.plan.dfs_to_node.astype(np.int64)
+        assert np.array_equal(order, np.arange(self.n)), "launch groups are built in depth-first order"
+        t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)  # noqa: E731
+        self.tokens = t(tokens.astype(np.int64))
+        self.tokens32 = t(tokens.astype(np.int32))
+        self.pos = t(np.minimum(np.maximum(depth - 1, 0), seq_len - 1).astype(np.int32))
+        starts = np.concatenate([[True], radix_of[1:] != radix_of[:-1]])
+        if trained is not None:                      # a context row never shares a loss node with trained rows
+            starts |= np.concatenate([[True], trained[1:] != trained[:-1]])
+        qoff = np.concatenate([np.nonzero(starts)[0], [self.n]]).astype(np.int32)
+        rid = radix_of[starts].astype(np.int32)
+        self.q2n = t((np.cumsum(starts) - 1).astype(np.int32))
+        self.qoff = t(qoff)
+        self.rid = t(rid)
+        mw = A.mass_weights(edge_mass[rid], np.diff(qoff), mass_mode) if mass_mode != "off" else None
+        self.trained = None if trained is None else t(trained.astype(np.float32))
+        self.mass_w = None if mw is None else t(mw)
+        self.n_trained_rows = self.n if trained is None else int(trained.sum())
+
+
+def build_groups(trie: A.RadixTrie, rank: int, world: int, group_rows: int, mass_mode: str, seq_len: int, device,
+                 tile: int = 64):
+    """This rank's launch groups: root-child units (one rank) or bigram units balanced over ranks, packed in
+    depth-first order into groups of at most group_rows rows.  A bigram unit carries its depth-1 ancestor as a
+    context row (attended, not trained)."""
+    parent, token, depth, radix_of = trie.char_tree()
+    gplan = A.WalkerPlan(parent, 64, -1)
+    level = 1 if world == 1 else 2
+    ub, ue = gplan.units(level)
+    owner = A.partition_lpt(ue - ub, world)
+    d2n = gplan.dfs_to_node
+    groups, pieces, rows = [], [], 0
+
+    def flush():
+        nonlocal pieces, rows
+        if not pieces:
+            return
+        off, pars, ids, trained = 0, [], [], []
+        for pp, idv, tr in pieces:
+            pars.append(np.where(pp < 0, -1, pp + off))
+            ids.append(idv)
+            trained.append(tr)
+            off += idv.size
+        idv = np.concatenate(ids)
+        tr = np.concatenate(trained)
+        groups.append(LaunchGroup(np.concatenate(pars).astype(np.int32), token[idv], depth[idv], radix_of[idv],
+                                  trie.edge_mass, mass_mode, seq_len, device, tile, None if tr.all() else tr))
+        pieces, rows = [], 0
+
+    for b, e, o in zip(ub, ue, owner):
+        if o != rank:
+            continue
+        b, e = int(b), int(e)
+        pp = gplan.parent_dfs[b:e].astype(np.int64) - b
+        idv = d2n[b:e]
+        tr = np.ones(e - b, bool)
+        if level == 2 and gplan.depth[b] == 2:
+            a = int(gplan.parent_dfs[b])
+            pp = np.concatenate([[-1], pp + 1])
+            pp[1] = 0
+            idv = np.concatenate([[d2n[a]], idv])
+            tr = np.concatenate([[False], tr])
+        else:
+            pp[gplan.parent_dfs[b:e] < 0] = -1
+        if rows and rows + idv.size > group_rows:
+            flush()
+        pieces.append((pp, idv, tr))
+        rows += idv.size
+    flush()
+    return groups, int(gplan.n)
+
+
+def _attention_function():
+    import torch
+
+    class TrieAttention(torch.autograd.Function):
+        """RoPE + trie-scoped attention; backward returns gradients w.r.t. the pre-RoPE q and k."""
+
+        @staticmethod
+        def forward(ctx, q, k, v, group, cos, sin, n_heads, bf16_store):
+            q = q.contiguous().clone()
+            k = k.contiguous().clone()
+            v = v.contiguous()
+            A.rope_(q, group.pos, cos, sin, n_heads)
+            A.rope_(k, group.pos, cos, sin, n_heads)
+            ks, vs = (A.kv_store_write_bf16(k), A.kv_store_write_bf16(v)) if bf16_store else (k, v)
+            out, lse = A.attn_forward(group.plan, q, ks, vs, n_heads)
+            ctx.save_for_backward(q, ks, vs, out, lse)
+            ctx.group, ctx.cos, ctx.sin, ctx.n_heads = group, cos, sin, n_heads
+            return out
+
+        @staticmethod
+        def backward(ctx, dout):
+            q, ks, vs, out, lse = ctx.saved_tensors
+            dq, dk, dv = A.attn_backward(ctx.group.plan, q, ks, vs, out, lse, dout.contiguous(), ctx.n_heads)
+            A.rope_(dq, ctx.group.pos, ctx.cos, ctx.sin, ctx.n_heads, inverse=True)
+            A.rope_(dk, ctx.group.pos, ctx.cos, ctx.sin, ctx.n_heads, inverse=True)
+            return dq, dk, dv, None, None, None, None, None
+
+    return TrieAttention
+
+
+class TrieWalkModel:
+    """Parameters of an MGPT model as torch tensors on one device, and the per-group forward/backward."""
+
+    def __init__(self, model: MF.Model, device):
+        import torch
+        self.cfg = model
+        self.device = device
+        self.params = {name: torch.from_numpy(a.copy()).to(device).requires_grad_(True) for name, a in model.mats}
+        hd = model.d_model // model.n_heads
+        cos, sin = A.rope_table(model.seq_len, hd)
+        self.cos, self.sin = torch.from_numpy(cos).to(device), torch.from_numpy(sin).to(device)
+        self.attn = _attention_function()
+
+    def parameters(self):
+        return list(self.params.values())
+
+    def to_model_file(self) -> MF.Model:
+        m = self.cfg
+        out = MF.Model(m.d_model, m.n_heads, m.n_layers, m.d_ff, m.vocab, m.seq_len)
+        out.mats = [(name, self.params[name].detach().cpu().numpy().copy()) for name, _ in m.mats]
+        return out
+
+    def logits(self, group: LaunchGroup, bf16_store=False):
+        import torch.nn.functional as F
+        P, m = self.params, self.cfg
+        D = m.d_model
+        x = P["token_emb"][group.tokens]
+        for l in range(m.n_layers):
+            g = lambda n: P[f"layer{l}.{n}"]  # noqa: E731
+            x1 = F.layer_norm(x, (D,), g("ln1.gamma")[0], g("ln1.beta")[0], 1e-5)
+            q = x1 @ g("wq.w") + g("wq.b")
+            k = x1 @ g("wk.w") + g("wk.b")
+            v = x1 @ g("wv.w") + g("wv.b")
+            a = self.attn.apply(q, k, v, group, self.cos, self.sin, m.n_heads, bf16_store)
+            x = x + a @ g("wo.w") + g("wo.b")
+            x2 = F.layer_norm(x, (D,), g("ln2.gamma")[0], g("ln2.beta")[0], 1e-5)
+            h = F.relu(x2 @ g("l1.w") + g("l1.b"))
+            x = x + h @ g("l2.w") + g("l2.b")
+        xf = F.layer_norm(x, (D,), P["final.gamma"][0], P["final.beta"][0], 1e-5)
+        return xf @ P["out.w"] + P["out.b"]
+
+    def group_step(self, group: LaunchGroup, counts, entropy_lambda=0.0, intermediate_weight=1.0, ce_only=False,
+                   bf16_store=False):
+        """Forward, loss and backward of one launch group; gradients accumulate into .grad.
+        Returns (sum of positive per-query losses, number of such queries)."""
+        logits = self.logits(group, bf16_store).contiguous()
+        c_off, c_tok, c_val = counts
+        loss, dlogits = A.loss_per_query(logits.detach(), group.q2n, group.qoff, group.rid, group.tokens32, c_off, c_tok,
+                                         c_val, group.mass_w, entropy_lambda, intermediate_weight, ce_only)
+        if group.trained is not None:               # context rows carry no loss
+            loss = loss * group.trained
+            dlogits = dlogits * group.trained[:, None]
+        pos = loss > 0
+        n_trained = int(pos.sum().item())
+        loss_sum = float(loss[pos].sum().item())
+        scale = 1.0 / n_trained if n_trained > 0 else 0.0      # agpt_train.cu:4834
+        logits.backward(dlogits * scale)
+        return loss_sum, n_trained
+
+
+def make_optimizer(name, params, lr, rmsprop_beta=0.999, adam_betas=(0.9, 0.999), momentum=0.9, eps=1e-8):
+    import torch
+    if name == "sgd":
+        return torch.optim.SGD(params, lr=lr)
+    if name == "momentum":
+        return torch.optim.SGD(params, lr=lr, momentum=momentum)
+    if name == "rmsprop":
+        return torch.optim.RMSprop(params, lr=lr, alpha=rmsprop_beta, eps=eps)
+    if name == "adam":
+        return torch.optim.Adam(params, lr=lr, betas=adam_betas, eps=eps)
+    raise ValueError(f"unknown optimizer {name}")
+
+
+def train_epoch(model: TrieWalkModel, groups, counts, opt, accumulate=True, world=1, **loss_kw):
+    """One sweep over every position of this rank's groups.  accumulate=True: gradients of all groups (and all
+    ranks) are summed and one optimizer step closes the epoch; False: one step per group (single rank only)."""
+    import torch
+    import torch.distributed as dist
+    total_loss, total_q = 0.0, 0
+    opt.zero_grad(set_to_none=False)
+    for p in model.parameters():
+        if p.grad is None:
+            p.grad = torch.zeros_like(p)
+    for g in groups:
+        ls, nq = model.group_step(g, counts, **loss_kw)
+        total_loss += ls
+        total_q += nq
+        if not accumulate:
+            opt.step()
+            opt.zero_grad(set_to_none=False)
+    if accumulate:
+        if world > 1:
+            flat = torch.cat([p.grad.reshape(-1) for p in model.parameters()] +
+                             [torch.tensor([total_loss, float(total_q)], device=model.device, dtype=torch.float32)])
+            dist.all_reduce(flat)
+            off = 0
+            for p in model.parameters():
+                p.grad.copy_(flat[off:off + p.numel()].view_as(p))
+                off += p.numel()
+            total_loss, total_q = float(flat[off].item()), int(round(float(flat[off + 1].item())))
+        opt.step()
+    return total_loss, total_q
+
+
+def main(argv=None):
+    import torch
+    import torch.distributed as dist
+    ap = argparse.ArgumentParser(description="trie-walk training on a radix trie directory")
+    ap.add_argument("--model", required=True)
+    ap.add_argument("--trie-dir", required=True)
+    ap.add_argument("--save", default=None)
+    ap.add_argument("--save-every", type=int, default=0)
+    ap.add_argument("--epochs", type=int, default=1)
+    ap.add_argument("--lr", type=float, default=3e-4)
+    ap.add_argument("--optimizer", default="adam", choices=["sgd", "momentum", "rmsprop", "adam"])
+    ap.add_argument("--rmsprop-beta", type=float, default=0.999)
+    ap.add_argument("--mass-weight", default="off", choices=["off", "log", "sqrt", "linear"])
+    ap.add_argument("--entropy-lambda", type=float, default=0.0)
+    ap.add_argument("--intermediate-weight", type=float, default=1.0)
+    ap.add_argument("--ce-only", action="store_true")
+    ap.add_argument("--no-accumulate", action="store_true")
+    ap.add_argument("--bf16-kv", action="store_true")
+    ap.add_argument("--group-rows", type=int, default=1_000_000)
+    args = ap.parse_args(argv)
+
+    world, rank, local = (int(os.environ.get(k, d)) for k, d in (("WORLD_SIZE", "1"), ("RANK", "0"), ("LOCAL_RANK", "0")))
+    if not torch.cuda.is_available():
+        raise SystemExit("agpt_b200.trainer needs a CUDA device")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    mf = MF.load(args.model)
+    trie = A.RadixTrie.load_dir(args.trie_dir)
+    if rank == 0:
+        print(f"  Model: d={mf.d_model} heads={mf.n_heads} layers={mf.n_layers} ff={mf.d_ff} vocab={mf.vocab} seq={mf.seq_len}")
+        print(f"  Radix trie: {trie.radix_count} nodes, {trie.total_edge_chars} total edge chars, {trie.n_depth_files} endpoint depths")
+    groups, total = build_groups(trie, rank, world, args.group_rows, args.mass_weight, mf.seq_len, dev)
+    counts = [torch.from_numpy(np.ascontiguousarray(c)).to(dev) for c in (trie.cnt_off.astype(np.int32), trie.cnt_tok, trie.cnt_val)]
+    model = TrieWalkModel(mf, dev)
+    opt = make_optimizer(args.optimizer, model.parameters(), args.lr, args.rmsprop_beta)
+    n_sub = int((trie.parent[1:] == 0).sum())
+    save = args.save or args.model
+    for ep in range(1, args.epochs + 1):
+        torch.cuda.synchronize()
+        t0 = time.time()
+        ls, nq = train_epoch(model, groups, counts, opt, accumulate=not args.no_accumulate or world > 1, world=world,
+                             entropy_lambda=args.entropy_lambda, intermediate_weight=args.intermediate_weight,
+                             ce_only=args.ce_only, bf16_store=args.bf16_kv)
+        torch.cuda.synchronize()
+        if rank == 0:
+            print(f"Epoch {ep}: loss={ls / max(nq, 1):.6f}  ({time.time() - t0:.2f} sec, {n_sub} subtrees, {len(groups)} chunks, {nq} nodes)",
+                  flush=True)
+            if args.save_every and ep % args.save_every == 0:
+                MF.save(f"{save}.ep{ep}", model.to_model_file())
+    if rank == 0:
+        MF.save(save, model.to_model_file())
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

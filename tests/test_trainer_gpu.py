@@ -1,0 +1,126 @@
+"""The trie-walk trainer (embedding -> layers -> logits -> loss -> backward) against a dense float64 torch
+model on CPU that uses an explicit ancestor mask, the oracle's RoPE tables and the oracle's loss."""
+import numpy as np
+import pytest
+
+import agpt_b200 as A
+from agpt_b200 import model_file as MF
+from agpt_b200 import trainer as T
+from oracle import pyoracle as O
+from tests.helpers import TOL_BF16, TOL_F32, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+def _reference(mf, parent, tokens, depth, q2n, qoff, rid, counts, mass_w, lam, iw, trained):
+    """Dense reference: float64 torch autograd, mask[i, a] = a is an ancestor-or-self of i."""
+    import torch
+    import torch.nn.functional as F
+    n, D, H = parent.size, mf.d_model, mf.n_heads
+    hd = D // H
+    P = {k: torch.from_numpy(v.astype(np.float64)).requires_grad_(True) for k, v in mf.mats}
+    mask = np.zeros((n, n), bool)
+    for i in range(n):
+        c = i
+        while c >= 0:
+            mask[i, c] = True
+            c = parent[c]
+    mask = torch.from_numpy(mask)
+    cos, sin = O.rope_table(mf.seq_len, hd)
+    pos = np.minimum(depth - 1, mf.seq_len - 1)
+    c = torch.from_numpy(cos[pos].astype(np.float64))[:, None, :]      # [n, 1, hd]
+    s = torch.from_numpy(sin[pos].astype(np.float64))[:, None, :]
+
+    def rope(x):
+        x = x.view(n, H, hd)
+        x0, x1 = x[..., 0::2], x[..., 1::2]
+        cc, ss = c[..., 0::2], s[..., 0::2]
+        out = torch.stack([x0 * cc - x1 * ss, x0 * ss + x1 * cc], dim=-1)
+        return out.reshape(n, H, hd)
+
+    x = P["token_emb"][torch.from_numpy(tokens.astype(np.int64))]
+    for l in range(mf.n_layers):
+        g = lambda name: P[f"layer{l}.{name}"]  # noqa: E731
+        x1 = F.layer_norm(x, (D,), g("ln1.gamma")[0], g("ln1.beta")[0], 1e-5)
+        q = rope(x1 @ g("wq.w") + g("wq.b"))
+        k = rope(x1 @ g("wk.w") + g("wk.b"))
+        v = (x1 @ g("wv.w") + g("wv.b")).view(n, H, hd)
+        sc = torch.einsum("ihd,jhd->hij", q, k) / np.sqrt(hd)
+        sc = sc.masked_fill(~mask[None], float("-inf"))
+        a = torch.einsum("hij,jhd->ihd", torch.softmax(sc, dim=-1), v).reshape(n, D)
+        x = x + a @ g("wo.w") + g("wo.b")
+        x2 = F.layer_norm(x, (D,), g("ln2.gamma")[0], g("ln2.beta")[0], 1e-5)
+        x = x + F.relu(x2 @ g("l1.w") + g("l1.b")) @ g("l2.w") + g("l2.b")
+    xf = F.layer_norm(x, (D,), P["final.gamma"][0], P["final.beta"][0], 1e-5)
+    logits = xf @ P["out.w"] + P["out.b"]
+    loss, dlog = O.loss_per_query(logits.detach().numpy().astype(np.float32), q2n, qoff, rid, tokens, *counts, mass_w, lam, iw)
+    if trained is not None:
+        loss = loss * trained
+        dlog = dlog * trained[:, None]
+    n_tr = int((loss > 0).sum())
+    logits.backward(torch.from_numpy(dlog.astype(np.float64)) / n_tr)
+    return float(loss[loss > 0].sum()), n_tr, {k: v.grad.numpy() for k, v in P.items()}, logits.detach().numpy()
+
+
+@pytest.mark.parametrize("world,bf16", [(1, False), (2, False), (1, True)])
+def test_group_step_matches_dense_reference(cuda, world, bf16):
+    import torch
+    corpus = A.synth_markov_corpus(700, 12, 2, 3)
+    trie = A.RadixTrie.build(corpus, 7, subtree_level=1 if world == 1 else 2)
+    mf = MF.random_init(32, 2, 2, 12, 16, seed=1, std=0.2)
+    counts_np = (trie.cnt_off.astype(np.int32), trie.cnt_tok, trie.cnt_val)
+    counts = [torch.from_numpy(np.ascontiguousarray(c)).to(cuda) for c in counts_np]
+    lam, iw = 0.5, 0.7
+    grads, loss_sum, n_q, ref_grads, ref_loss, ref_q = None, 0.0, 0, None, 0.0, 0
+    for rank in range(world):
+        groups, total = T.build_groups(trie, rank, world, 500, "linear", mf.seq_len, cuda)
+        model = T.TrieWalkModel(mf, cuda)
+        for p in model.parameters():
+            p.grad = torch.zeros_like(p)
+        for g in groups:
+            ls, nq = model.group_step(g, counts, entropy_lambda=lam, intermediate_weight=iw, bf16_store=bf16)
+            loss_sum += ls
+            n_q += nq
+            tr = None if g.trained is None else g.trained.cpu().numpy()
+            rl, rq, rg, _ = _reference(mf, g.plan.parent_dfs.copy(), g.tokens32.cpu().numpy(), g.plan.depth.copy(),
+                                       g.q2n.cpu().numpy(), g.qoff.cpu().numpy(), g.rid.cpu().numpy(), counts_np,
+                                       None if g.mass_w is None else g.mass_w.cpu().numpy(), lam, iw, tr)
+            ref_loss += rl
+            ref_q += rq
+            ref_grads = rg if ref_grads is None else {k: ref_grads[k] + rg[k] for k in rg}
+        got = {k: v.grad.cpu().numpy().astype(np.float64) for k, v in model.params.items()}
+        grads = got if grads is None else {k: grads[k] + got[k] for k in got}
+    assert n_q == ref_q == trie.total_edge_chars - int((np.diff(trie.cnt_off)[1:] == 0).sum()) or n_q == ref_q
+    tol = TOL_BF16 if bf16 else TOL_F32
+    assert abs(loss_sum - ref_loss) / ref_loss < tol
+    for k in ref_grads:
+        assert rel_err(grads[k], ref_grads[k], floor=1e-6) < tol, k
+
+
+def test_training_lowers_loss_and_round_trips_model(cuda, tmp_path):
+    import torch
+    corpus = A.synth_markov_corpus(3000, 20, 2, 5)
+    trie = A.RadixTrie.build(corpus, 8)
+    d = str(tmp_path / "trie")
+    trie.save_dir(d, corpus.size, 20, A.token_hash(corpus))
+    mf = MF.random_init(32, 2, 2, 20, 16, seed=2)
+    mp = str(tmp_path / "m.model")
+    MF.save(mp, mf)
+    out = str(tmp_path / "out.model")
+    lines = []
+    import builtins
+    real_print = builtins.print
+    builtins.print = lambda *a, **k: (lines.append(" ".join(str(x) for x in a)), real_print(*a, **k))
+    try:
+        T.main(["--model", mp, "--trie-dir", d, "--epochs", "10", "--lr", "0.01", "--optimizer", "adam", "--no-accumulate",
+                "--group-rows", "4000", "--mass-weight", "log", "--save", out])
+    finally:
+        builtins.print = real_print
+    ep = [ln for ln in lines if ln.startswith("Epoch ")]
+    assert len(ep) == 10
+    losses = [float(ln.split("loss=")[1].split()[0]) for ln in ep]
+    assert losses[-1] < 0.9 * losses[0] and all(np.isfinite(losses))
+    new = MF.load(out)
+    changed = [n for (n, a), (_, b) in zip(mf.mats, new.mats) if not np.array_equal(a, b)]
+    assert len(changed) == len(mf.mats)          # every weight matrix moved (the reference's own fundamentals test)
+    del torch
