@@ -51,13 +51,14 @@ class LaunchGroup:
 
 
 def build_groups(trie: A.RadixTrie, rank: int, world: int, group_rows: int, mass_mode: str, seq_len: int, device,
-                 tile: int = 64):
+                 tile: int = 64, level: int | None = None):
     """This rank's launch groups: root-child units (one rank) or bigram units balanced over ranks, packed in
     depth-first order into groups of at most group_rows rows.  A bigram unit carries its depth-1 ancestor as a
     context row (attended, not trained)."""
     parent, token, depth, radix_of = trie.char_tree()
     gplan = A.WalkerPlan(parent, 64, -1)
-    level = 1 if world == 1 else 2
+    if level is None:
+        level = 1 if world == 1 else 2
     ub, ue = gplan.units(level)
     owner = A.partition_lpt(ue - ub, world)
     d2n = gplan.dfs_to_node
@@ -156,8 +157,14 @@ class TrieWalkModel:
 
     def logits(self, group: LaunchGroup, bf16_store=False):
         import torch.nn.functional as F
+        from torch.utils.checkpoint import checkpoint
         P, m = self.params, self.cfg
         D = m.d_model
+
+        def ffn(x, g2, b2, w1, b1, w2, bo):
+            x2 = F.layer_norm(x, (D,), g2, b2, 1e-5)
+            return x + F.relu(x2 @ w1 + b1) @ w2 + bo
+
         x = P["token_emb"][group.tokens]
         for l in range(m.n_layers):
             g = lambda n: P[f"layer{l}.{n}"]  # noqa: E731
@@ -167,9 +174,9 @@ class TrieWalkModel:
             v = x1 @ g("wv.w") + g("wv.b")
             a = self.attn.apply(q, k, v, group, self.cos, self.sin, m.n_heads, bf16_store)
             x = x + a @ g("wo.w") + g("wo.b")
-            x2 = F.layer_norm(x, (D,), g("ln2.gamma")[0], g("ln2.beta")[0], 1e-5)
-            h = F.relu(x2 @ g("l1.w") + g("l1.b"))
-            x = x + h @ g("l2.w") + g("l2.b")
+            # the d_ff-wide activations are recomputed in the backward instead of being kept
+            x = checkpoint(ffn, x, g("ln2.gamma")[0], g("ln2.beta")[0], g("l1.w"), g("l1.b"), g("l2.w"), g("l2.b"),
+                           use_reentrant=False)
         xf = F.layer_norm(x, (D,), P["final.gamma"][0], P["final.beta"][0], 1e-5)
         return xf @ P["out.w"] + P["out.b"]
 
@@ -255,6 +262,8 @@ def main(argv=None):
     ap.add_argument("--no-accumulate", action="store_true")
     ap.add_argument("--bf16-kv", action="store_true")
     ap.add_argument("--group-rows", type=int, default=1_000_000)
+    ap.add_argument("--partition-depth", type=int, default=0, choices=[0, 1, 2],
+                    help="1 = root-child units, 2 = bigram units; 0 = 1 on one rank, 2 on several")
     args = ap.parse_args(argv)
 
     world, rank, local = (int(os.environ.get(k, d)) for k, d in (("WORLD_SIZE", "1"), ("RANK", "0"), ("LOCAL_RANK", "0")))
@@ -269,7 +278,8 @@ def main(argv=None):
     if rank == 0:
         print(f"  Model: d={mf.d_model} heads={mf.n_heads} layers={mf.n_layers} ff={mf.d_ff} vocab={mf.vocab} seq={mf.seq_len}")
         print(f"  Radix trie: {trie.radix_count} nodes, {trie.total_edge_chars} total edge chars, {trie.n_depth_files} endpoint depths")
-    groups, total = build_groups(trie, rank, world, args.group_rows, args.mass_weight, mf.seq_len, dev)
+    groups, total = build_groups(trie, rank, world, args.group_rows, args.mass_weight, mf.seq_len, dev,
+                                 level=args.partition_depth or None)
     counts = [torch.from_numpy(np.ascontiguousarray(c)).to(dev) for c in (trie.cnt_off.astype(np.int32), trie.cnt_tok, trie.cnt_val)]
     model = TrieWalkModel(mf, dev)
     opt = make_optimizer(args.optimizer, model.parameters(), args.lr, args.rmsprop_beta)

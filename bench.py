@@ -387,6 +387,14 @@ def run_gpu(args):
                "sample": f"{len(chosen)} launch groups, {tot} of {n_rank} rows of rank 0; attention fwd+bwd through agpt_b200_attn_fwd_bwd_host"}
         del host
 
+    # whole-epoch time of the trie-walk trainer on the same trie (all layers, loss, backward, one gradient
+    # all-reduce and one optimizer step), every rank taking part
+    epoch = None
+    if args.epoch and not args.workload.startswith("micro"):
+        del big, logits, out, lse, dq, dk, dv, dlogits, loss, ws, plans, meta
+        torch.cuda.empty_cache()
+        epoch = run_epoch(args, cfg, rank, world, dev, log)
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         from oracle import pyoracle as O
@@ -407,10 +415,46 @@ def run_gpu(args):
                              "algorithmic_bytes_per_step": b_bwd, "seconds_per_step": t_bwd,
                              "fwd": {"achieved": ach_fwd, "frac": ach_fwd / peak, "algorithmic_bytes_per_step": b_fwd, "seconds_per_step": t_fwd},
                              "fwd_bwd": {"achieved": ach_all, "frac": ach_all / peak}, "loss_seconds_per_step": t_loss},
-                "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks}
+                "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "epoch": epoch}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_epoch(args, cfg, rank, world, dev, log):
+    """One timed epoch (after one untimed) of agpt_b200.trainer on the workload's trie with a seeded random-init
+    model of the config's shape (d_ff = 4 d_model, N(0, 0.02) weights), rmsprop, linear mass weighting."""
+    import torch
+    import torch.distributed as dist
+    import agpt_b200 as A
+    from agpt_b200 import model_file as MF
+    from agpt_b200 import trainer as T
+    D = cfg["heads"] * cfg["head_dim"]
+    corpus = A.synth_markov_corpus(cfg["chars"], cfg["vocab"], cfg["order"], 0)
+    trie = A.RadixTrie.build(corpus, cfg["depth"], subtree_level=2)
+    mf = MF.random_init(D, cfg["heads"], cfg["layers"], cfg["vocab"], max(128, cfg["depth"]), seed=0)
+    groups, total = T.build_groups(trie, rank, world, args.epoch_group_rows, "linear", mf.seq_len, dev, level=2)
+    counts = [torch.from_numpy(np.ascontiguousarray(c)).to(dev) for c in (trie.cnt_off.astype(np.int32), trie.cnt_tok, trie.cnt_val)]
+    model = T.TrieWalkModel(mf, dev)
+    opt = T.make_optimizer("rmsprop", model.parameters(), 3e-4, 0.999)
+    times, losses = [], []
+    for ep in range(2):
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        ls, nq = T.train_epoch(model, groups, counts, opt, accumulate=True, world=world)
+        torch.cuda.synchronize()
+        t = torch.tensor([time.perf_counter() - t0], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        times.append(float(t.item()))
+        losses.append(ls / max(nq, 1))
+        log(f"epoch {ep + 1}: loss={losses[-1]:.6f} ({times[-1]:.2f} s, {len(groups)} chunks, {nq} nodes)")
+    return {"seconds": times[-1], "positions_per_s": total / times[-1], "loss_first": losses[0], "loss_second": losses[-1],
+            "model": f"d_model {D}, {cfg['layers']} layers, {cfg['heads']} heads x {cfg['head_dim']}, d_ff {4 * D}, vocab {cfg['vocab']}, fp32",
+            "recipe": "rmsprop beta 0.999, lr 3e-4, linear mass weighting, one step per epoch (accumulate)",
+            "group_rows": args.epoch_group_rows, "partition": "bigram subtrees", "chunks_rank0": len(groups)}
 
 
 def main():
@@ -426,11 +470,15 @@ def main():
     ap.add_argument("--group-rows", type=int, default=4_000_000, help="rows per launch group (units are packed up to this)")
     ap.add_argument("--single-unit", action="store_true", help="one plan over the whole trie instead of per-subtree units")
     ap.add_argument("--profile", action="store_true", help="profiler capture mode: warm-up as given, no e2e, no CPU arm")
+    ap.add_argument("--no-epoch", dest="epoch", action="store_false",
+                    help="skip the whole-epoch timing of the trainer (all layers) on the same trie")
+    ap.add_argument("--epoch-group-rows", type=int, default=1_000_000)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     if args.profile:
         args.no_e2e = args.no_cpu = True
+        args.epoch = False
     if args.impl == "reference":
         run_reference(args)
     else:
