@@ -278,6 +278,11 @@ __device__ __forceinline__ void issue_chunk(const KVT *__restrict__ K, const KVT
     cp_async_commit();
 }
 
+template <int HD> struct FwdMmaStages { static constexpr int value = HD <= 16 ? 4 : 3; };
+template <int HD> constexpr size_t fwd_mma_smem_bytes() {
+    return (size_t)FwdMmaStages<HD>::value * 2 * KC * (HD + 4) * sizeof(float) + 2 * MAXKEYS * sizeof(int);
+}
+
 template <int HD, typename KVT>
 __global__ void __launch_bounds__(128) attn_fwd_mma_kernel(const float *__restrict__ Q, const KVT *__restrict__ K,
                                                            const KVT *__restrict__ V, float *__restrict__ O,
@@ -288,9 +293,14 @@ __global__ void __launch_bounds__(128) attn_fwd_mma_kernel(const float *__restri
                                                            float scale, int tile0) {
     constexpr int M = 64, KS = HD / 8;
     constexpr bool SPLIT_KV = sizeof(KVT) == 4;
-    __shared__ __align__(16) float sKb[2][KC][HD + 4];
-    __shared__ __align__(16) float sVb[2][KC][HD + 4];
-    __shared__ int s_kid[MAXKEYS], s_kend[MAXKEYS];
+    // NS key chunks are staged per round and consumed without any barrier in between, so the four warps (whose
+    // live key blocks differ a lot: later rows attend more of the tile) do not wait for each other per chunk
+    constexpr int NS = FwdMmaStages<HD>::value;
+    extern __shared__ __align__(16) unsigned char fwd_smem_raw[];
+    typedef float (*KvBuf)[KC][HD + 4];
+    KvBuf sKb = reinterpret_cast<KvBuf>(fwd_smem_raw);
+    KvBuf sVb = sKb + NS;
+    int *s_kid = reinterpret_cast<int *>(sVb + NS), *s_kend = s_kid + MAXKEYS;
     const int t = blockIdx.x + tile0, h = blockIdx.y, tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, tig = lane & 3;
     const int D = H * HD, hoff = h * HD;
@@ -304,7 +314,14 @@ __global__ void __launch_bounds__(128) attn_fwd_mma_kernel(const float *__restri
     const float qs = scale * LOG2E;
     load_key_meta(sub_end, chain, chain_end_all + coff, p, i0, nkeys, s_kid, s_kend);
     __syncthreads();
-    issue_chunk<HD, KVT>(K, V, s_kid, 0, min(KC, nkeys), D, hoff, sKb[0], sVb[0]);
+    auto issue_round = [&](int rb) {
+#pragma unroll
+        for (int st = 0; st < NS; st++) {
+            const int kc = rb + st * KC;
+            if (kc < nkeys) issue_chunk<HD, KVT>(K, V, s_kid, kc, min(KC, nkeys - kc), D, hoff, sKb[st], sVb[st]);
+        }
+    };
+    issue_round(0);
 
     uint32_t qh[KS][4], ql[KS][4];
 #pragma unroll
@@ -323,12 +340,14 @@ __global__ void __launch_bounds__(128) attn_fwd_mma_kernel(const float *__restri
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
     for (int kc = 0; kc < nkeys; kc += KC) {
-        const int buf = (kc / KC) & 1;
-        float (*sK)[HD + 4] = sKb[buf];
-        float (*sV)[HD + 4] = sVb[buf];
-        cp_async_wait_all();
-        __syncthreads();                              // chunk kc has landed; the other buffer is free again
-        if (kc + KC < nkeys) issue_chunk<HD, KVT>(K, V, s_kid, kc + KC, min(KC, nkeys - kc - KC), D, hoff, sKb[buf ^ 1], sVb[buf ^ 1]);
+        const int st = (kc / KC) % NS;
+        if (st == 0) {
+            if (kc > 0) { __syncthreads(); issue_round(kc); }      // every warp is done with the previous round
+            cp_async_wait_all();
+            __syncthreads();                                       // this round's chunks have landed
+        }
+        float (*sK)[HD + 4] = sKb[st];
+        float (*sV)[HD + 4] = sVb[st];
         float s[KC / 8][4];
         unsigned live = 0;
 #pragma unroll
@@ -932,7 +951,9 @@ template <int HD, typename KVT>
 static int launch_fwd_mma(const agpt_plan *p, const float *q, const void *k, const void *v, float *out, float *lse, int H,
                           float scale, cudaStream_t st, int tile0, int ntiles) {
     dim3 grid((unsigned)ntiles, (unsigned)H);
-    attn_fwd_mma_kernel<HD, KVT><<<grid, 128, 0, st>>>(q, (const KVT *)k, (const KVT *)v, out, lse, p->d_sub_end,
+    const size_t smem = fwd_mma_smem_bytes<HD>();
+    CUDA_TRY(cudaFuncSetAttribute(attn_fwd_mma_kernel<HD, KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attn_fwd_mma_kernel<HD, KVT><<<grid, 128, smem, st>>>(q, (const KVT *)k, (const KVT *)v, out, lse, p->d_sub_end,
                                                        p->d_chain_off, p->d_chain_ids, p->d_chain_end, (int)p->n, H, scale, tile0);
     return launch_status("attn_fwd_mma");
 }
