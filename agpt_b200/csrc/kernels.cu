@@ -252,27 +252,34 @@ __device__ __forceinline__ void load_key_meta(const int32_t *__restrict__ sub_en
     }
 }
 
-// Start the copy of keys [kc, kc+cnt) into one shared-memory buffer.  float32 stores go through cp.async (the
-// copy overlaps the MMAs on the other buffer); a bf16 store is widened on the way in.  Rows beyond cnt are
-// zero-filled: they enter MMAs with weight 0.  128 threads; the caller commits/waits and synchronises.
+// Shared-memory form of a staged K/V row: float32 rows as they are (padded by 4 floats), bf16 rows as raw
+// bf16 (padded by 8 elements) and widened when a fragment is read; both paddings make the MMA fragment reads
+// bank-conflict free and keep every row 16-byte aligned for cp.async.
+template <typename KVT> struct SmemKV;
+template <> struct SmemKV<float> { typedef float elem; static constexpr int PAD = 4; };
+template <> struct SmemKV<__nv_bfloat16> { typedef unsigned short elem; static constexpr int PAD = 8; };
+__device__ __forceinline__ float kv_f32(float x) { return x; }
+__device__ __forceinline__ float kv_f32(unsigned short x) { return __uint_as_float((unsigned)x << 16); }
+
+// Start the copy of keys [kc, kc+cnt) into one shared-memory buffer with cp.async (the copy overlaps the MMAs on
+// other buffers).  Rows beyond cnt are zero-filled: they enter MMAs with weight 0.  128 threads; the caller
+// waits and synchronises.
 template <int HD, typename KVT>
 __device__ __forceinline__ void issue_chunk(const KVT *__restrict__ K, const KVT *__restrict__ V, const int *s_kid, int kc,
-                                            int cnt, int D, int hoff, float (*sK)[HD + 4], float (*sV)[HD + 4]) {
-    constexpr int C4 = HD / 4;
-    for (int idx = threadIdx.x; idx < KC * C4; idx += 128) {
-        const int r = idx / C4, c = idx % C4;
+                                            int cnt, int D, int hoff,
+                                            typename SmemKV<KVT>::elem (*sK)[HD + SmemKV<KVT>::PAD],
+                                            typename SmemKV<KVT>::elem (*sV)[HD + SmemKV<KVT>::PAD]) {
+    constexpr int EPC = 16 / sizeof(KVT);          // elements per 16-byte copy
+    constexpr int CPR = HD / EPC;                   // copies per row
+    for (int idx = threadIdx.x; idx < KC * CPR; idx += 128) {
+        const int r = idx / CPR, c = idx % CPR;
         if (r < cnt) {
-            const int64_t base = (int64_t)s_kid[kc + r] * D + hoff + c * 4;
-            if (sizeof(KVT) == 4) {
-                cp_async16(&sK[r][c * 4], K + base);
-                cp_async16(&sV[r][c * 4], V + base);
-            } else {
-                *reinterpret_cast<float4 *>(&sK[r][c * 4]) = ld4(K + base);
-                *reinterpret_cast<float4 *>(&sV[r][c * 4]) = ld4(V + base);
-            }
+            const int64_t base = (int64_t)s_kid[kc + r] * D + hoff + c * EPC;
+            cp_async16(&sK[r][c * EPC], K + base);
+            cp_async16(&sV[r][c * EPC], V + base);
         } else {
-            *reinterpret_cast<float4 *>(&sK[r][c * 4]) = make_float4(0.f, 0.f, 0.f, 0.f);
-            *reinterpret_cast<float4 *>(&sV[r][c * 4]) = make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<uint4 *>(&sK[r][c * EPC]) = make_uint4(0u, 0u, 0u, 0u);
+            *reinterpret_cast<uint4 *>(&sV[r][c * EPC]) = make_uint4(0u, 0u, 0u, 0u);
         }
     }
     cp_async_commit();
@@ -280,7 +287,7 @@ __device__ __forceinline__ void issue_chunk(const KVT *__restrict__ K, const KVT
 
 template <int HD> struct FwdMmaStages { static constexpr int value = HD <= 16 ? 4 : 3; };
 template <int HD> constexpr size_t fwd_mma_smem_bytes() {
-    return (size_t)FwdMmaStages<HD>::value * 2 * KC * (HD + 4) * sizeof(float) + 2 * MAXKEYS * sizeof(int);
+    return (size_t)FwdMmaStages<HD>::value * 2 * KC * (HD + 8) * sizeof(float) + 2 * MAXKEYS * sizeof(int);   // upper bound
 }
 
 template <int HD, typename KVT>
@@ -297,7 +304,9 @@ __global__ void __launch_bounds__(128) attn_fwd_mma_kernel(const float *__restri
     // live key blocks differ a lot: later rows attend more of the tile) do not wait for each other per chunk
     constexpr int NS = FwdMmaStages<HD>::value;
     extern __shared__ __align__(16) unsigned char fwd_smem_raw[];
-    typedef float (*KvBuf)[KC][HD + 4];
+    typedef typename SmemKV<KVT>::elem SE;
+    constexpr int SP = HD + SmemKV<KVT>::PAD;
+    typedef SE (*KvBuf)[KC][SP];
     KvBuf sKb = reinterpret_cast<KvBuf>(fwd_smem_raw);
     KvBuf sVb = sKb + NS;
     int *s_kid = reinterpret_cast<int *>(sVb + NS), *s_kend = s_kid + MAXKEYS;
@@ -346,8 +355,8 @@ __global__ void __launch_bounds__(128) attn_fwd_mma_kernel(const float *__restri
             cp_async_wait_all();
             __syncthreads();                                       // this round's chunks have landed
         }
-        float (*sK)[HD + 4] = sKb[st];
-        float (*sV)[HD + 4] = sVb[st];
+        SE (*sK)[SP] = sKb[st];
+        SE (*sV)[SP] = sVb[st];
         float s[KC / 8][4];
         unsigned live = 0;
 #pragma unroll
@@ -364,7 +373,7 @@ __global__ void __launch_bounds__(128) attn_fwd_mma_kernel(const float *__restri
             float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int ks = 0; ks < KS; ks++) {
-                const float b0 = sK[nb * 8 + g][ks * 8 + tig], b1 = sK[nb * 8 + g][ks * 8 + tig + 4];
+                const float b0 = kv_f32(sK[nb * 8 + g][ks * 8 + tig]), b1 = kv_f32(sK[nb * 8 + g][ks * 8 + tig + 4]);
                 if (SPLIT_KV) {
                     uint32_t h0, lo0, h1, lo1;
                     tf32_split(b0, h0, lo0); tf32_split(b1, h1, lo1);
@@ -408,7 +417,7 @@ __global__ void __launch_bounds__(128) attn_fwd_mma_kernel(const float *__restri
             tf32_split(p1, ph[2], pl[2]); tf32_split(p3, ph[3], pl[3]);
 #pragma unroll
             for (int db = 0; db < KS; db++) {
-                const float b0 = sV[nb * 8 + 2 * tig][db * 8 + g], b1 = sV[nb * 8 + 2 * tig + 1][db * 8 + g];
+                const float b0 = kv_f32(sV[nb * 8 + 2 * tig][db * 8 + g]), b1 = kv_f32(sV[nb * 8 + 2 * tig + 1][db * 8 + g]);
                 if (SPLIT_KV) {
                     uint32_t h0, lo0, h1, lo1;
                     tf32_split(b0, h0, lo0); tf32_split(b1, h1, lo1);
@@ -589,10 +598,10 @@ __global__ void __launch_bounds__(M) attn_bwd_kernel(const float *__restrict__ Q
 //            in index order.
 // Output placement and the later reduction are those of attn_bwd_kernel.
 // --------------------------------------------------------------------------------------
-template <int HD>
+template <int HD, typename KVT>
 struct BwdMmaSmem {
-    float sKb[2][KC][HD + 4];
-    float sVb[2][KC][HD + 4];
+    typename SmemKV<KVT>::elem sKb[2][KC][HD + SmemKV<KVT>::PAD];
+    typename SmemKV<KVT>::elem sVb[2][KC][HD + SmemKV<KVT>::PAD];
     float sQ[64][HD + 8];
     float sG[64][HD + 8];
     float sP[64][KC + 8];
@@ -616,7 +625,9 @@ __global__ void __launch_bounds__(128) attn_bwd_mma_kernel(const float *__restri
     constexpr bool SPLIT_KV = sizeof(KVT) == 4;
     constexpr int NB2 = (KS + 1) / 2;          // head_dim blocks of 8 per warp in phase 2
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    BwdMmaSmem<HD> &S = *reinterpret_cast<BwdMmaSmem<HD> *>(smem_raw);
+    BwdMmaSmem<HD, KVT> &S = *reinterpret_cast<BwdMmaSmem<HD, KVT> *>(smem_raw);
+    typedef typename SmemKV<KVT>::elem SE;
+    constexpr int SP = HD + SmemKV<KVT>::PAD;
     const int t = blockIdx.x + tile0, h = blockIdx.y, tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, tig = lane & 3;
     const int D = H * HD, hoff = h * HD;
@@ -682,8 +693,8 @@ __global__ void __launch_bounds__(128) attn_bwd_mma_kernel(const float *__restri
     for (int kc = 0; kc < nkeys; kc += KC) {
         const int cnt = min(KC, nkeys - kc);
         const int buf = (kc / KC) & 1;
-        float (*sK)[HD + 4] = S.sKb[buf];
-        float (*sV)[HD + 4] = S.sVb[buf];
+        SE (*sK)[SP] = S.sKb[buf];
+        SE (*sV)[SP] = S.sVb[buf];
         cp_async_wait_all();
         __syncthreads();                              // chunk kc has landed; phase 2 of the previous chunk is over
         if (kc + KC < nkeys) issue_chunk<HD, KVT>(K, V, S.s_kid, kc + KC, min(KC, nkeys - kc - KC), D, hoff, S.sKb[buf ^ 1], S.sVb[buf ^ 1]);
@@ -714,8 +725,8 @@ __global__ void __launch_bounds__(128) attn_bwd_mma_kernel(const float *__restri
                     for (int u = 0; u < 2; u++) {
                         if (!on[u]) continue;
                         const int nb = nb2 + u;
-                        const float k0 = sK[nb * 8 + g][ks * 8 + tig], k1 = sK[nb * 8 + g][ks * 8 + tig + 4];
-                        const float w0 = sV[nb * 8 + g][ks * 8 + tig], w1 = sV[nb * 8 + g][ks * 8 + tig + 4];
+                        const float k0 = kv_f32(sK[nb * 8 + g][ks * 8 + tig]), k1 = kv_f32(sK[nb * 8 + g][ks * 8 + tig + 4]);
+                        const float w0 = kv_f32(sV[nb * 8 + g][ks * 8 + tig]), w1 = kv_f32(sV[nb * 8 + g][ks * 8 + tig + 4]);
                         if (SPLIT_KV) {
                             uint32_t h0, lo0, h1, lo1, x0, y0, x1, y1;
                             tf32_split(k0, h0, lo0); tf32_split(k1, h1, lo1);
@@ -747,7 +758,7 @@ __global__ void __launch_bounds__(128) attn_bwd_mma_kernel(const float *__restri
                     tf32_split(ds[1], ah[2], al[2]); tf32_split(ds[3], ah[3], al[3]);
 #pragma unroll
                     for (int db = 0; db < KS; db++) {
-                        const float b0 = sK[nb * 8 + 2 * tig][db * 8 + g], b1 = sK[nb * 8 + 2 * tig + 1][db * 8 + g];
+                        const float b0 = kv_f32(sK[nb * 8 + 2 * tig][db * 8 + g]), b1 = kv_f32(sK[nb * 8 + 2 * tig + 1][db * 8 + g]);
                         if (SPLIT_KV) {
                             uint32_t h0, lo0, h1, lo1;
                             tf32_split(b0, h0, lo0); tf32_split(b1, h1, lo1);
@@ -976,7 +987,7 @@ static int launch_bwd_mma(const agpt_plan *p, const float *q, const void *k, con
                           const float *dout, float *dq, float *dk, float *dv, float *pk, float *pv, int H, float scale,
                           cudaStream_t st, int tile0, int ntiles) {
     dim3 grid((unsigned)ntiles, (unsigned)H);
-    size_t smem = sizeof(BwdMmaSmem<HD>);
+    size_t smem = sizeof(BwdMmaSmem<HD, KVT>);
     CUDA_TRY(cudaFuncSetAttribute(attn_bwd_mma_kernel<HD, KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attn_bwd_mma_kernel<HD, KVT><<<grid, 128, smem, st>>>(q, (const KVT *)k, (const KVT *)v, o, lse, dout, dq, dk, dv, pk, pv,
                                                           p->d_sub_end, p->d_chain_off, p->d_chain_ids, p->d_chain_end, (int)p->n, H,

@@ -268,6 +268,10 @@ def run_gpu(args):
     ws_bytes = max(p.workspace_bytes(D) for p in plans)
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
     big = [torch.randn((n_rank, D), device=dev, generator=g) for _ in range(4)]          # q k v dO, resident
+    kv_bytes = 4
+    if args.kv == "bf16":        # the KV store holds bf16 rows (written once, outside the timed region, like a cache fill)
+        big[1], big[2] = A.kv_store_write_bf16(big[1]), A.kv_store_write_bf16(big[2])
+        kv_bytes = 2
     logits = torch.randn((n_rank, V), device=dev, generator=g)
     out = torch.empty((n_max, D), device=dev); lse = torch.empty((n_max, H), device=dev)
     dq = torch.empty_like(out); dk = torch.empty_like(out); dv = torch.empty_like(out)
@@ -350,9 +354,21 @@ def run_gpu(args):
     t_fwd = sum(ev[0].elapsed_time(ev[1]) for ev in timers) * 1e-3
     t_bwd = sum(ev[1].elapsed_time(ev[2]) for ev in timers) * 1e-3
     t_loss = sum(ev[2].elapsed_time(ev[3]) for ev in timers) * 1e-3
-    b_fwd = sum(p.algorithmic_bytes(D, H, 4)[0] for p in plans)
-    b_bwd = sum(p.algorithmic_bytes(D, H, 4)[1] for p in plans)
+    b_fwd = sum(p.algorithmic_bytes(D, H, kv_bytes)[0] for p in plans)
+    b_bwd = sum(p.algorithmic_bytes(D, H, kv_bytes)[1] for p in plans)
     peak, peak_kind = measured_peak_gbs()
+    # size-independent self-checks on the last group of the timing pass (outputs still in the buffers):
+    # every query's weights sum to one, so sum_a dV_a == sum_i dO_i; and sum_i dq_i.q_i == sum_a dk_a.k_a
+    u, m = units[-1], meta[-1]
+    sl = slice(m["row"], m["row"] + u.n)
+    qd, kd, god = big[0][sl].double(), big[1][sl].double(), big[3][sl].double()
+    sv, sg = dv[:u.n].double().sum(0), god.sum(0)
+    chk_dv = float((sv - sg).abs().max() / sg.abs().max())
+    lhs, rhs = float((dq[:u.n].double() * qd).sum()), float((dk[:u.n].double() * kd).sum())
+    chk_qk = abs(lhs - rhs) / max(abs(lhs), abs(rhs), 1e-30)
+    selfcheck = {"sum_dv_vs_sum_dout_rel": chk_dv, "dq_dot_q_vs_dk_dot_k_rel": chk_qk,
+                 "finite": bool(torch.isfinite(dq[:u.n]).all() and torch.isfinite(dk[:u.n]).all() and torch.isfinite(out[:u.n]).all())}
+    del qd, kd, god
     ach_bwd = b_bwd / t_bwd / 1e9
     ach_fwd = b_fwd / t_fwd / 1e9
     ach_all = (b_fwd + b_bwd) / (t_fwd + t_bwd) / 1e9
@@ -407,7 +423,7 @@ def run_gpu(args):
         line = {"metric": "trie_nodes_per_sec_attn_fwd_bwd", "value": value, "unit": "nodes/s", "n_gpus": world,
                 "steps": args.steps, "warmup": n_warm, "ms_per_step": ms_per_step, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": cfg["label"], "positions": total_nodes, "launch_groups_rank0": len(units), "group_rows": args.group_rows,
+                "config": {"workload": cfg["label"], "kv_store": args.kv, "positions": total_nodes, "launch_groups_rank0": len(units), "group_rows": args.group_rows,
                            "partition": "root-child subtrees" if world == 1 else f"bigram subtrees, LPT over {world} ranks",
                            "tile": args.tile, "l2": "inputs (GBs per tensor) far larger than the 126 MB L2"},
                 "roofline": {"bound": "hbm", "achieved": ach_bwd, "peak": peak, "unit": "GB/s", "frac": ach_bwd / peak,
@@ -415,7 +431,7 @@ def run_gpu(args):
                              "algorithmic_bytes_per_step": b_bwd, "seconds_per_step": t_bwd,
                              "fwd": {"achieved": ach_fwd, "frac": ach_fwd / peak, "algorithmic_bytes_per_step": b_fwd, "seconds_per_step": t_fwd},
                              "fwd_bwd": {"achieved": ach_all, "frac": ach_all / peak}, "loss_seconds_per_step": t_loss},
-                "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "epoch": epoch}
+                "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "epoch": epoch, "selfcheck": selfcheck}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -465,6 +481,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--tile", type=int, default=64)
+    ap.add_argument("--kv", default="f32", choices=["f32", "bf16"], help="element type of the KV store")
     ap.add_argument("--cpu-nodes", type=int, default=400_000, help="rows in the CPU arm's sample")
     ap.add_argument("--e2e-nodes", type=int, default=4_000_000, help="rows in the host-buffer sample")
     ap.add_argument("--group-rows", type=int, default=4_000_000, help="rows per launch group (units are packed up to this)")
