@@ -1147,9 +1147,12 @@ __device__ __forceinline__ int warp_sum_i(int v) {
 }
 
 // mode 0: per-query (radix); mode 1: per-node (leveled, node_ids index the counts).
-// One warp per row; the row lives in shared memory (lane l owns columns l, l+32, ...), so every logit is read
-// once, exponentiated once and every gradient element written once.
+// One warp per row.  NPL > 0: the row (V <= 32*NPL) lives in registers, lane l owning columns l, l+32, ...;
+// shared memory is touched only by rows that end a radix edge (sparse count lookups).  NPL == 0: any V, the row
+// lives in shared memory.  Either way every logit is read once, exponentiated once, and every gradient element
+// written once.
 #define LOSS_WPB 8
+template <int NPL>
 __global__ void __launch_bounds__(LOSS_WPB * 32)
 loss_kernel(const float *__restrict__ logits, const int32_t *__restrict__ query_to_node,
             const int32_t *__restrict__ query_offsets, const int32_t *__restrict__ ids,
@@ -1164,15 +1167,42 @@ loss_kernel(const float *__restrict__ logits, const int32_t *__restrict__ query_
     float *row = s_rows + (threadIdx.x >> 5) * V;
     const float *in = logits + qi * V;
     float *g = d_logits + qi * V;
-    float mx = -3.402823466e+38f;
-    for (int j = lane; j < V; j += 32) { float x = __ldcs(in + j); row[j] = x; mx = fmaxf(mx, x); }
-    mx = warp_max(mx);
-    float sum = 0.f;
-    for (int j = lane; j < V; j += 32) { float e = expf(row[j] - mx); row[j] = e; sum += e; }
-    sum = warp_sum(sum);
-    const float inv = 1.0f / sum;
-    for (int j = lane; j < V; j += 32) row[j] *= inv;          // probabilities
-    __syncwarp();
+    constexpr int NR = NPL > 0 ? NPL : 1;
+    float x[NR];
+    float mx = -3.402823466e+38f, sum = 0.f;
+    if (NPL > 0) {
+#pragma unroll
+        for (int k = 0; k < NR; k++) {
+            const int j = lane + 32 * k;
+            x[k] = j < V ? __ldcs(in + j) : -3.402823466e+38f;
+            mx = fmaxf(mx, x[k]);
+        }
+        mx = warp_max(mx);
+#pragma unroll
+        for (int k = 0; k < NR; k++) { x[k] = lane + 32 * k < V ? expf(x[k] - mx) : 0.f; sum += x[k]; }
+        sum = warp_sum(sum);
+        const float inv = 1.0f / sum;
+#pragma unroll
+        for (int k = 0; k < NR; k++) x[k] *= inv;                  // probabilities
+    } else {
+        for (int j = lane; j < V; j += 32) { float v = __ldcs(in + j); row[j] = v; mx = fmaxf(mx, v); }
+        mx = warp_max(mx);
+        for (int j = lane; j < V; j += 32) { float e = expf(row[j] - mx); row[j] = e; sum += e; }
+        sum = warp_sum(sum);
+        const float inv = 1.0f / sum;
+        for (int j = lane; j < V; j += 32) row[j] *= inv;
+        __syncwarp();
+    }
+    // probability of one column, the same for every lane
+    auto prob_of = [&](int col) -> float {
+        if (NPL > 0) {
+            float v = 0.f;
+#pragma unroll
+            for (int k = 0; k < NR; k++) { float t = __shfl_sync(0xffffffffu, x[k], col & 31); if (k == (col >> 5)) v = t; }
+            return v;
+        }
+        return row[col];
+    };
 
     bool endpoint_path;
     int cid = 0;
@@ -1188,6 +1218,11 @@ loss_kernel(const float *__restrict__ logits, const int32_t *__restrict__ query_
     if (endpoint_path) {
         const int start = counts_offset[cid], end = counts_offset[cid + 1];
         if (start != end) {
+            if (NPL > 0) {                       // sparse lookups go through shared memory
+#pragma unroll
+                for (int k = 0; k < NR; k++) if (lane + 32 * k < V) row[lane + 32 * k] = x[k];
+                __syncwarp();
+            }
             int total = 0;
             for (int e = start + lane; e < end; e += 32) total += counts_val[e];
             total = warp_sum_i(total);
@@ -1213,6 +1248,11 @@ loss_kernel(const float *__restrict__ logits, const int32_t *__restrict__ query_
                 row[tok] = pr - tgt;                             // tokens of one node are distinct
             }
             loss = warp_sum(loss) * weight;
+            __syncwarp();
+            if (NPL > 0) {
+#pragma unroll
+                for (int k = 0; k < NR; k++) if (lane + 32 * k < V) x[k] = row[lane + 32 * k];
+            }
         }
         // else: no observed continuation -- zero loss, and the row keeps the plain probabilities
     } else {
@@ -1220,14 +1260,36 @@ loss_kernel(const float *__restrict__ logits, const int32_t *__restrict__ query_
         if ((unsigned)target >= (unsigned)V) target = 0;         // never index outside the row
         weight = intermediate_weight;
         if (mass_weights) weight *= mass_weights[qi];
-        const float pr = row[target];
+        const float pr = prob_of(target);
         loss = -logf(pr + 1e-10f) * weight;
-        __syncwarp();
-        if (lane == 0) row[target] = pr - 1.0f;
+        if (NPL > 0) {
+#pragma unroll
+            for (int k = 0; k < NR; k++) if (lane + 32 * k == target) x[k] -= 1.0f;
+        } else {
+            __syncwarp();
+            if (lane == 0) row[target] = pr - 1.0f;
+        }
     }
-    __syncwarp();
-    for (int j = lane; j < V; j += 32) __stcs(g + j, row[j] * weight);
+    if (NPL > 0) {
+#pragma unroll
+        for (int k = 0; k < NR; k++) if (lane + 32 * k < V) __stcs(g + lane + 32 * k, x[k] * weight);
+    } else {
+        __syncwarp();
+        for (int j = lane; j < V; j += 32) __stcs(g + j, row[j] * weight);
+    }
     if (lane == 0) loss_out[qi] = loss;
+}
+
+template <typename... Args>
+static void launch_loss(int64_t rows, int V, cudaStream_t st, Args... args) {
+    const unsigned blocks = (unsigned)((rows + LOSS_WPB - 1) / LOSS_WPB);
+    const size_t smem = (size_t)LOSS_WPB * V * sizeof(float);
+    if (V <= 32) loss_kernel<1><<<blocks, LOSS_WPB * 32, smem, st>>>(args...);
+    else if (V <= 64) loss_kernel<2><<<blocks, LOSS_WPB * 32, smem, st>>>(args...);
+    else if (V <= 96) loss_kernel<3><<<blocks, LOSS_WPB * 32, smem, st>>>(args...);
+    else if (V <= 128) loss_kernel<4><<<blocks, LOSS_WPB * 32, smem, st>>>(args...);
+    else if (V <= 256) loss_kernel<8><<<blocks, LOSS_WPB * 32, smem, st>>>(args...);
+    else loss_kernel<0><<<blocks, LOSS_WPB * 32, smem, st>>>(args...);
 }
 
 extern "C" int agpt_b200_loss_per_query(const float *d_logits, const int32_t *d_query_to_node, const int32_t *d_query_offsets,
@@ -1240,10 +1302,8 @@ extern "C" int agpt_b200_loss_per_query(const float *d_logits, const int32_t *d_
         return agpt_set_error(AGPT_E_ARG, "loss_per_query: bad argument");
     if (T_q == 0) return AGPT_OK;
     if (V > 1400) return agpt_set_error(AGPT_E_LIMIT, "loss_per_query: vocabulary %d beyond 1400", V);
-    const int wpb = LOSS_WPB;
-    loss_kernel<<<(unsigned)((T_q + wpb - 1) / wpb), wpb * 32, (size_t)wpb * V * sizeof(float), (cudaStream_t)stream>>>(
-        d_logits, d_query_to_node, d_query_offsets, d_radix_ids, d_token_ids, d_counts_offset, d_counts_tok, d_counts_val,
-        d_mass_weights, d_dlogits, d_loss, T_q, V, entropy_lambda, intermediate_weight, ce_only, 0);
+    launch_loss(T_q, V, (cudaStream_t)stream, d_logits, d_query_to_node, d_query_offsets, d_radix_ids, d_token_ids, d_counts_offset,
+                d_counts_tok, d_counts_val, d_mass_weights, d_dlogits, d_loss, T_q, V, entropy_lambda, intermediate_weight, ce_only, 0);
     return launch_status("loss_per_query");
 }
 
@@ -1254,10 +1314,9 @@ extern "C" int agpt_b200_loss_per_node(const float *d_logits, const int32_t *d_n
         return agpt_set_error(AGPT_E_ARG, "loss_per_node: bad argument");
     if (N == 0) return AGPT_OK;
     if (V > 1400) return agpt_set_error(AGPT_E_LIMIT, "loss_per_node: vocabulary %d beyond 1400", V);
-    const int wpb = LOSS_WPB;
-    loss_kernel<<<(unsigned)((N + wpb - 1) / wpb), wpb * 32, (size_t)wpb * V * sizeof(float), (cudaStream_t)stream>>>(
-        d_logits, nullptr, nullptr, d_node_ids, nullptr, d_counts_offset, d_counts_tok, d_counts_val, nullptr, d_dlogits, d_loss,
-        N, V, 0.f, 1.f, 0, 1);
+    launch_loss(N, V, (cudaStream_t)stream, d_logits, (const int32_t *)nullptr, (const int32_t *)nullptr, d_node_ids,
+                (const int32_t *)nullptr, d_counts_offset, d_counts_tok, d_counts_val, (const float *)nullptr, d_dlogits, d_loss, N, V,
+                0.f, 1.f, 0, 1);
     return launch_status("loss_per_node");
 }
 

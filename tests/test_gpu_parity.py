@@ -376,3 +376,42 @@ def test_bad_arguments_are_reported_not_fatal(cuda):
     # the context is still usable afterwards
     out2, _ = A.attn_forward(plan, y, y, y, 2)
     assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("V", [7, 32, 64, 65, 96, 128, 200, 300, 1000])
+def test_loss_vocab_sizes(cuda, V):
+    """Every register/shared-memory variant of the loss kernel, endpoint and intermediate rows mixed."""
+    rng = np.random.default_rng(V)
+    n_nodes = 300
+    el = rng.integers(1, 5, size=n_nodes).astype(np.int32)
+    qoff = np.concatenate([[0], np.cumsum(el)]).astype(np.int32)
+    T = int(qoff[-1])
+    q2n = np.repeat(np.arange(n_nodes, dtype=np.int32), el)
+    toks = rng.integers(0, V, size=T).astype(np.int32)
+    off, tok, val = [0], [], []
+    for _ in range(n_nodes + 1):                      # radix ids 1..n_nodes; id 0 has no counts
+        m = int(rng.integers(0, min(V, 6) + 1)) if len(off) > 1 else 0
+        tok += sorted(int(t) for t in rng.choice(V, size=m, replace=False))
+        val += [int(x) for x in rng.integers(1, 50, size=m)]
+        off.append(len(tok))
+    ids = np.arange(1, n_nodes + 1, dtype=np.int32)
+    logits = (rng.standard_normal((T, V)) * 3).astype(np.float32)
+    mw = rng.uniform(0.2, 3.0, size=T).astype(np.float32)
+    off, tok, val = np.array(off, np.int32), np.array(tok + [0], np.int32), np.array(val + [0], np.int32)
+    want_l, want_g = O.loss_per_query(logits, q2n, qoff, ids, toks, off, tok, val, mw, 0.7, 0.5, False)
+    got_l, got_g = A.loss_per_query(_dev(logits, cuda), _dev(q2n, cuda), _dev(qoff, cuda), _dev(ids, cuda), _dev(toks, cuda),
+                                    _dev(off, cuda), _dev(tok, cuda), _dev(val, cuda), _dev(mw, cuda), 0.7, 0.5, False)
+    assert rel_err(got_l.cpu().numpy(), want_l) < TOL_F32
+    assert rel_err(got_g.cpu().numpy(), want_g) < TOL_F32
+
+
+def test_chain_deeper_than_the_tensor_path_holds(cuda):
+    """A 600-deep unary chain exceeds the key capacity of a tensor-core tile; the entry points fall back to the
+    FMA kernels and stay correct."""
+    H, hd = 2, 16
+    parent = chain_tree(600)
+    q, k, v, go = random_qkv(600, H * hd, 99)
+    ref = _oracle(parent, H, hd, q, k, v, go)
+    _, (out, lse, dq, dk, dv) = _run_native(parent, H, hd, q, k, v, go, cuda, 64)
+    for got, want in zip((out, dq, dk, dv), ref[:4]):
+        assert rel_err(got, want) < TOL_F32
