@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-SO = os.path.join(HERE, "libagpt_b200.so")
+# AGPT_B200_LIB selects another build of the same library (same ABI), e.g. one compiled with different flags
+SO = os.environ.get("AGPT_B200_LIB") or os.path.join(HERE, "libagpt_b200.so")
 
 vp, i32, i64, u64, f32, f64 = C.c_void_p, C.c_int32, C.c_int64, C.c_uint64, C.c_float, C.c_double
 P32, P64 = C.POINTER(C.c_int32), C.POINTER(C.c_int64)

@@ -600,8 +600,8 @@ __global__ void __launch_bounds__(M) attn_bwd_kernel(const float *__restrict__ Q
 // --------------------------------------------------------------------------------------
 template <int HD, typename KVT>
 struct BwdMmaSmem {
-    typename SmemKV<KVT>::elem sKb[2][KC][HD + SmemKV<KVT>::PAD];
-    typename SmemKV<KVT>::elem sVb[2][KC][HD + SmemKV<KVT>::PAD];
+    typename SmemKV<KVT>::elem sKb[KC][HD + SmemKV<KVT>::PAD];     // one buffer: the next chunk is copied during phase 2
+    typename SmemKV<KVT>::elem sVb[KC][HD + SmemKV<KVT>::PAD];
     float sQ[64][HD + 8];
     float sG[64][HD + 8];
     float sP[64][KC + 8];
@@ -611,7 +611,7 @@ struct BwdMmaSmem {
 };
 
 template <int HD, typename KVT>
-__global__ void __launch_bounds__(128) attn_bwd_mma_kernel(const float *__restrict__ Q, const KVT *__restrict__ K,
+__global__ void __launch_bounds__(128, HD <= 32 ? 4 : 1) attn_bwd_mma_kernel(const float *__restrict__ Q, const KVT *__restrict__ K,
                                                            const KVT *__restrict__ V, const float *__restrict__ O,
                                                            const float *__restrict__ LSE, const float *__restrict__ dO,
                                                            float *__restrict__ dQ, float *__restrict__ dK,
@@ -642,23 +642,34 @@ __global__ void __launch_bounds__(128) attn_bwd_mma_kernel(const float *__restri
     const int32_t *chain = chain_ids + coff;
     const float qs = scale * LOG2E;
 
-    load_key_meta(sub_end, chain, chain_end_all + coff, p, i0, nkeys, S.s_kid, S.s_kend);
-    // the tile's Q and dO rows, zero beyond the last row
+    // Everything the prologue needs is requested at once: the tile's Q, dO and O rows by cp.async (O lands in the
+    // area that later holds P; it is only needed for delta = dO.O), the key metadata by plain loads meanwhile.
+    static_assert(64 * (HD + 8) <= 2 * 64 * (KC + 8), "the O rows are staged in the (contiguous) P and dS areas");
+    float *sOflat = &S.sP[0][0];                 // viewed as [64][HD + 8]
     {
         constexpr int C4 = HD / 4;
         for (int idx = tid; idx < M * C4; idx += 128) {
-            int r = idx / C4, c = idx % C4;
-            float4 x = make_float4(0.f, 0.f, 0.f, 0.f), y = x;
+            const int r = idx / C4, c = idx % C4;
             if (r < nt) {
-                x = ld4(Q + (int64_t)(i0 + r) * D + hoff + c * 4);
-                y = ld4(dO + (int64_t)(i0 + r) * D + hoff + c * 4);
+                const int64_t off = (int64_t)(i0 + r) * D + hoff + c * 4;
+                cp_async16(&S.sQ[r][c * 4], Q + off);
+                cp_async16(&S.sG[r][c * 4], dO + off);
+                cp_async16(sOflat + r * (HD + 8) + c * 4, O + off);
+            } else {
+                *reinterpret_cast<float4 *>(&S.sQ[r][c * 4]) = make_float4(0.f, 0.f, 0.f, 0.f);
+                *reinterpret_cast<float4 *>(&S.sG[r][c * 4]) = make_float4(0.f, 0.f, 0.f, 0.f);
+                *reinterpret_cast<float4 *>(sOflat + r * (HD + 8) + c * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
             }
-            *reinterpret_cast<float4 *>(&S.sQ[r][c * 4]) = x;
-            *reinterpret_cast<float4 *>(&S.sG[r][c * 4]) = y;
         }
+        cp_async_commit();
     }
+    load_key_meta(sub_end, chain, chain_end_all + coff, p, i0, nkeys, S.s_kid, S.s_kend);
+    const float lse0 = act0 ? LSE[(int64_t)r0 * H + h] * LOG2E : 0.f;
+    const float lse1 = act1 ? LSE[(int64_t)r1 * H + h] * LOG2E : 0.f;
+    __syncthreads();                             // key metadata visible
+    issue_chunk<HD, KVT>(K, V, S.s_kid, 0, min(KC, nkeys), D, hoff, S.sKb, S.sVb);
+    asm volatile("cp.async.wait_group 1;" ::: "memory");      // the Q/dO/O group; chunk 0 may still be in flight
     __syncthreads();
-    issue_chunk<HD, KVT>(K, V, S.s_kid, 0, min(KC, nkeys), D, hoff, S.sKb[0], S.sVb[0]);
     uint32_t qh[KS][4], ql[KS][4], gh[KS][4], gl[KS][4];
     float delta0 = 0.f, delta1 = 0.f;
 #pragma unroll
@@ -670,19 +681,11 @@ __global__ void __launch_bounds__(128) attn_bwd_mma_kernel(const float *__restri
         tf32_split(x2 * qs, qh[ks][2], ql[ks][2]); tf32_split(x3 * qs, qh[ks][3], ql[ks][3]);
         tf32_split(y0, gh[ks][0], gl[ks][0]); tf32_split(y1, gh[ks][1], gl[ks][1]);
         tf32_split(y2, gh[ks][2], gl[ks][2]); tf32_split(y3, gh[ks][3], gl[ks][3]);
-        if (act0) {
-            delta0 = fmaf(y0, __ldg(O + (int64_t)r0 * D + hoff + d0), delta0);
-            delta0 = fmaf(y2, __ldg(O + (int64_t)r0 * D + hoff + d0 + 4), delta0);
-        }
-        if (act1) {
-            delta1 = fmaf(y1, __ldg(O + (int64_t)r1 * D + hoff + d0), delta1);
-            delta1 = fmaf(y3, __ldg(O + (int64_t)r1 * D + hoff + d0 + 4), delta1);
-        }
+        delta0 = fmaf(y0, sOflat[q0 * (HD + 8) + d0], delta0); delta0 = fmaf(y2, sOflat[q0 * (HD + 8) + d0 + 4], delta0);
+        delta1 = fmaf(y1, sOflat[q1 * (HD + 8) + d0], delta1); delta1 = fmaf(y3, sOflat[q1 * (HD + 8) + d0 + 4], delta1);
     }
     delta0 += __shfl_xor_sync(0xffffffffu, delta0, 1); delta0 += __shfl_xor_sync(0xffffffffu, delta0, 2);
     delta1 += __shfl_xor_sync(0xffffffffu, delta1, 1); delta1 += __shfl_xor_sync(0xffffffffu, delta1, 2);
-    const float lse0 = act0 ? LSE[(int64_t)r0 * H + h] * LOG2E : 0.f;
-    const float lse1 = act1 ? LSE[(int64_t)r1 * H + h] * LOG2E : 0.f;
     float dq[KS][4];
 #pragma unroll
     for (int db = 0; db < KS; db++) dq[db][0] = dq[db][1] = dq[db][2] = dq[db][3] = 0.f;
@@ -692,12 +695,11 @@ __global__ void __launch_bounds__(128) attn_bwd_mma_kernel(const float *__restri
 
     for (int kc = 0; kc < nkeys; kc += KC) {
         const int cnt = min(KC, nkeys - kc);
-        const int buf = (kc / KC) & 1;
-        SE (*sK)[SP] = S.sKb[buf];
-        SE (*sV)[SP] = S.sVb[buf];
+        SE (*sK)[SP] = S.sKb;
+        SE (*sV)[SP] = S.sVb;
         cp_async_wait_all();
-        __syncthreads();                              // chunk kc has landed; phase 2 of the previous chunk is over
-        if (kc + KC < nkeys) issue_chunk<HD, KVT>(K, V, S.s_kid, kc + KC, min(KC, nkeys - kc - KC), D, hoff, S.sKb[buf ^ 1], S.sVb[buf ^ 1]);
+        __syncthreads();                              // chunk kc has landed; phase 2 of the previous chunk (and the
+                                                      // delta pass over the O rows) is over
         // ---- phase 1 ----  (two key blocks at a time: four independent accumulator chains)
         unsigned live = 0;
 #pragma unroll
@@ -777,6 +779,8 @@ __global__ void __launch_bounds__(128) attn_bwd_mma_kernel(const float *__restri
         }
         if (lane == 0) S.s_live[warp] = live;
         __syncthreads();
+        // phase 2 does not touch K/V: the next chunk is copied while it runs
+        if (kc + KC < nkeys) issue_chunk<HD, KVT>(K, V, S.s_kid, kc + KC, min(KC, nkeys - kc - KC), D, hoff, S.sKb, S.sVb);
         // ---- phase 2 ----
         if (mb * 16 < cnt) {
             float ak[NB2][4], av[NB2][4];
