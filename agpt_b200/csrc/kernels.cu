@@ -1157,7 +1157,7 @@ __device__ __forceinline__ int warp_sum_i(int v) {
 // written once.
 #define LOSS_WPB 8
 template <int NPL>
-__global__ void __launch_bounds__(LOSS_WPB * 32)
+__global__ void __launch_bounds__(LOSS_WPB * 32, 8)
 loss_kernel(const float *__restrict__ logits, const int32_t *__restrict__ query_to_node,
             const int32_t *__restrict__ query_offsets, const int32_t *__restrict__ ids,
             const int32_t *__restrict__ token_ids, const int32_t *__restrict__ counts_offset,
@@ -1171,6 +1171,23 @@ loss_kernel(const float *__restrict__ logits, const int32_t *__restrict__ query_
     float *row = s_rows + (threadIdx.x >> 5) * V;
     const float *in = logits + qi * V;
     float *g = d_logits + qi * V;
+    // the index loads form a dependent chain (query -> node -> offsets); they are issued before the row is read so
+    // that their latency overlaps the row's
+    bool endpoint_path;
+    int cid = 0;
+    if (mode == 1) { endpoint_path = true; cid = ids[qi]; }
+    else {
+        int n_idx = query_to_node[qi];
+        bool is_endpoint = (qi + 1) == query_offsets[n_idx + 1];
+        bool ce_as_intermediate = ce_only && is_endpoint && (qi + 1 < T_q);
+        endpoint_path = is_endpoint && !ce_as_intermediate;
+        if (endpoint_path) cid = ids[n_idx];
+    }
+    int target = 0, c_start = 0, c_end = 0;
+    float mass_w = 1.0f;
+    if (endpoint_path) { c_start = counts_offset[cid]; c_end = counts_offset[cid + 1]; }
+    else target = token_ids[qi + 1];
+    if (mode == 0 && mass_weights) mass_w = mass_weights[qi];
     constexpr int NR = NPL > 0 ? NPL : 1;
     float x[NR];
     float mx = -3.402823466e+38f, sum = 0.f;
@@ -1208,19 +1225,9 @@ loss_kernel(const float *__restrict__ logits, const int32_t *__restrict__ query_
         return row[col];
     };
 
-    bool endpoint_path;
-    int cid = 0;
-    if (mode == 1) { endpoint_path = true; cid = ids[qi]; }
-    else {
-        int n_idx = query_to_node[qi];
-        bool is_endpoint = (qi + 1) == query_offsets[n_idx + 1];
-        bool ce_as_intermediate = ce_only && is_endpoint && (qi + 1 < T_q);
-        endpoint_path = is_endpoint && !ce_as_intermediate;
-        if (endpoint_path) cid = ids[n_idx];
-    }
     float weight = 1.0f, loss = 0.f;
     if (endpoint_path) {
-        const int start = counts_offset[cid], end = counts_offset[cid + 1];
+        const int start = c_start, end = c_end;
         if (start != end) {
             if (NPL > 0) {                       // sparse lookups go through shared memory
 #pragma unroll
@@ -1241,7 +1248,7 @@ loss_kernel(const float *__restrict__ logits, const int32_t *__restrict__ query_
                     Hh = warp_sum(Hh);
                     weight = 1.0f + entropy_lambda * (Hh / logf((float)V));
                 }
-                if (mass_weights) weight *= mass_weights[qi];
+                if (mass_weights) weight *= mass_w;
             }
             for (int e = start + lane; e < end; e += 32) {
                 int tok = counts_tok[e];
@@ -1260,10 +1267,9 @@ loss_kernel(const float *__restrict__ logits, const int32_t *__restrict__ query_
         }
         // else: no observed continuation -- zero loss, and the row keeps the plain probabilities
     } else {
-        int target = token_ids[qi + 1];
         if ((unsigned)target >= (unsigned)V) target = 0;         // never index outside the row
         weight = intermediate_weight;
-        if (mass_weights) weight *= mass_weights[qi];
+        if (mass_weights) weight *= mass_w;
         const float pr = prob_of(target);
         loss = -logf(pr + 1e-10f) * weight;
         if (NPL > 0) {

@@ -415,3 +415,23 @@ def test_chain_deeper_than_the_tensor_path_holds(cuda):
     _, (out, lse, dq, dk, dv) = _run_native(parent, H, hd, q, k, v, go, cuda, 64)
     for got, want in zip((out, dq, dk, dv), ref[:4]):
         assert rel_err(got, want) < TOL_F32
+
+
+def test_deep_pruned_trie_bf16_store(cuda):
+    """Shape of the deep configuration in miniature: order-4 corpus, depth-128 trie, count<2 pruning from depth 4,
+    bf16 KV store, 6 heads x 64."""
+    corpus = A.synth_markov_corpus(800, 96, 4, 21)
+    trie = A.RadixTrie.build(corpus, 128, prune_min_mass=2, prune_min_depth=4)
+    rx = O.Radix(O.Leveled(corpus, 128), 1, 2, 4)
+    assert trie.radix_count == rx.radix_count and np.array_equal(trie.edge_start, rx.edge_start)
+    parent, token, depth, _ = trie.char_tree()
+    assert depth.max() > 100
+    n, H, hd = parent.size, 6, 64
+    q, k, v, go = random_qkv(n, H * hd, 81)
+    plan, (out, lse, dq, dk, dv) = _run_native(parent, H, hd, q, k, v, go, cuda, 64, bf16=True)
+    ref = _oracle(parent, H, hd, q, k, v, go)
+    for got, want in zip((out, dq, dk, dv), ref[:4]):
+        assert rel_err(got, want) < TOL_BF16
+    ref_r = _oracle(parent, H, hd, q, _bf16_round(k), _bf16_round(v), go)
+    for got, want in zip((out, dq, dk, dv), ref_r[:4]):
+        assert rel_err(got, want) < TOL_F32
