@@ -525,7 +525,7 @@ extern "C" int agpt_b200_plan_create(const int32_t *parent, int64_t n, int tile_
         int64_t t0 = a / tile_m + 1, t1 = (P->sub_end[a] - 1) / tile_m;   // inclusive range [t0, t1]
         if (t1 < t0) continue;
         int64_t nseg = (t1 - t0 + 1 + SEG - 1) / SEG;
-        if (nseg > 1) { P->multi_node.push_back((int32_t)a); P->multi_first.push_back((int64_t)P->item_node.size()); P->multi_count.push_back((int32_t)nseg); }
+        if (nseg > 1) { P->multi_node.push_back((int32_t)a); P->multi_first.push_back((int64_t)P->n_multi_items); P->multi_count.push_back((int32_t)nseg); }
         for (int64_t s = 0; s < nseg; s++) {
             P->item_node.push_back((int32_t)a);
             P->item_t0.push_back((int32_t)(t0 + s * SEG));
@@ -533,6 +533,13 @@ extern "C" int agpt_b200_plan_create(const int32_t *parent, int64_t n, int tile_
             P->item_slot.push_back(nseg > 1 ? (int32_t)(P->n_multi_items++) : -1);
         }
         P->n_reduce_nodes++;
+    }
+    {   // items ordered by their last tile, so that "every item whose tiles are all done" is a prefix of the list
+        std::vector<int64_t> ord(P->item_node.size());
+        std::iota(ord.begin(), ord.end(), 0);
+        std::stable_sort(ord.begin(), ord.end(), [&](int64_t x, int64_t y) { return P->item_t1[x] < P->item_t1[y]; });
+        auto permute = [&](std::vector<int32_t> &v) { std::vector<int32_t> w(v.size()); for (size_t i = 0; i < ord.size(); i++) w[i] = v[ord[i]]; v.swap(w); };
+        permute(P->item_node); permute(P->item_t0); permute(P->item_t1); permute(P->item_slot);
     }
     P->device = -1;
     if (device >= 0) {

@@ -25,7 +25,7 @@ struct agpt_plan {
     // is cut into several items whose sums meet in a second pass
     std::vector<int32_t> item_node, item_t0, item_t1, item_slot;
     std::vector<int32_t> multi_node, multi_count;
-    std::vector<int64_t> multi_first;
+    std::vector<int64_t> multi_first;          // first segment slot of each multi-segment node (its slots are consecutive)
     // device copies (owned)
     int device = -1;
     int32_t *d_depth = nullptr, *d_sub_end = nullptr, *d_chain_ids = nullptr, *d_chain_end = nullptr;
@@ -38,6 +38,8 @@ struct agpt_plan {
     size_t host_arena_bytes = 0;
     void *host_streams[3] = {nullptr, nullptr, nullptr};
     std::vector<void *> host_events;
+    void *host_fix = nullptr;                  // pinned staging for rows re-downloaded at the end of a host-buffer step
+    size_t host_fix_bytes = 0;
     ~agpt_plan();
 };
 

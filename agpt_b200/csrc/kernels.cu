@@ -13,6 +13,8 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
+#include <vector>
 
 #include "../../include/agpt_b200.h"
 #include "internal.h"
@@ -68,6 +70,7 @@ agpt_plan::~agpt_plan() {
         cudaFree(d_item_node); cudaFree(d_item_t0); cudaFree(d_item_t1); cudaFree(d_item_slot);
         cudaFree(d_multi_node); cudaFree(d_multi_count); cudaFree(d_multi_first);
         cudaFree(host_arena);
+        if (host_fix) cudaFreeHost(host_fix);
         for (void *e : host_events) cudaEventDestroy((cudaEvent_t)e);
         for (void *st : host_streams) if (st) cudaStreamDestroy((cudaStream_t)st);
         if (cur >= 0) cudaSetDevice(cur);
@@ -844,9 +847,10 @@ __global__ void reduce_items_kernel(const float *__restrict__ Pk, const float *_
                                     const int64_t *__restrict__ chain_off, const int32_t *__restrict__ depth,
                                     const int32_t *__restrict__ item_node, const int32_t *__restrict__ item_t0,
                                     const int32_t *__restrict__ item_t1, const int32_t *__restrict__ item_slot,
-                                    int64_t n_items, int D) {
+                                    int64_t item0, int64_t n_items, int D) {
     int64_t it = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (it >= n_items) return;
+    it += item0;
     const int lane = threadIdx.x & 31;
     const int a = item_node[it], t0 = item_t0[it], t1 = item_t1[it], slot = item_slot[it];
     const int row = depth[a] - 1;
@@ -881,7 +885,8 @@ __global__ void reduce_multi_kernel(const float *__restrict__ segk, const float 
     if (mi >= n_multi) return;
     const int lane = threadIdx.x & 31;
     const int a = multi_node[mi], cnt = multi_count[mi];
-    const int slot0 = item_slot[multi_first[mi]];     // slots of one node are consecutive
+    const int slot0 = (int)multi_first[mi];           // slots of one node are consecutive
+    (void)item_slot;
     for (int c = lane * 4; c < D; c += 128) {
         float4 sk = make_float4(0.f, 0.f, 0.f, 0.f), sv = sk;
         for (int s = 0; s < cnt; s++) {
@@ -1024,19 +1029,20 @@ extern "C" int agpt_b200_attn_fwd(const agpt_plan *p, const float *d_q, const vo
     return fwd_dispatch(p, d_q, d_k, d_v, kv_dtype, d_out, d_lse, n_heads, head_dim, scale, (cudaStream_t)stream, 0, (int)p->n_tiles);
 }
 
-static int run_reduce(const agpt_plan *p, float *pk, float *pv, float *segk, float *segv, float *dk, float *dv, int D,
-                      cudaStream_t st) {
-    int64_t n_items = (int64_t)p->item_node.size();
+// Reduction pass 1 over items [item0, item1) (the list is ordered by last tile), then, if requested, pass 2.
+static int run_reduce_range(const agpt_plan *p, float *pk, float *pv, float *segk, float *segv, float *dk, float *dv, int D,
+                            cudaStream_t st, int64_t item0, int64_t item1, bool multi_pass) {
+    const int64_t n_items = item1 - item0;
     if (n_items > 0) {
         const int wpb = 8;
         reduce_items_kernel<<<(unsigned)((n_items + wpb - 1) / wpb), wpb * 32, 0, st>>>(
             pk, pv, dk, dv, segk, segv, p->d_chain_off, p->d_depth, p->d_item_node, p->d_item_t0, p->d_item_t1,
-            p->d_item_slot, n_items, D);
+            p->d_item_slot, item0, n_items, D);
         int rc = launch_status("reduce_items");
         if (rc) return rc;
     }
     int64_t n_multi = (int64_t)p->multi_node.size();
-    if (n_multi > 0) {
+    if (multi_pass && n_multi > 0) {
         const int wpb = 4;
         reduce_multi_kernel<<<(unsigned)((n_multi + wpb - 1) / wpb), wpb * 32, 0, st>>>(
             segk, segv, dk, dv, p->d_multi_node, p->d_multi_count, p->d_multi_first, p->d_item_slot, n_multi, D);
@@ -1044,6 +1050,11 @@ static int run_reduce(const agpt_plan *p, float *pk, float *pv, float *segk, flo
         if (rc) return rc;
     }
     return AGPT_OK;
+}
+
+static int run_reduce(const agpt_plan *p, float *pk, float *pv, float *segk, float *segv, float *dk, float *dv, int D,
+                      cudaStream_t st) {
+    return run_reduce_range(p, pk, pv, segk, segv, dk, dv, D, st, 0, (int64_t)p->item_node.size(), true);
 }
 
 extern "C" int agpt_b200_attn_bwd(const agpt_plan *p, const float *d_q, const void *d_k, const void *d_v, int kv_dtype,
@@ -1592,7 +1603,11 @@ extern "C" int agpt_b200_attn_fwd_bwd_host(const agpt_plan *cp, const float *h_q
     const size_t lseb = (((size_t)n * n_heads * sizeof(float)) + 255) & ~(size_t)255;
     const size_t wsb = (((size_t)agpt_b200_attn_bwd_workspace_bytes(p, D)) + 255) & ~(size_t)255;
     const bool bf = kv_dtype == AGPT_KV_BF16;
-    const size_t need = 8 * tens + lseb + wsb + (bf ? tens : 0);
+    // chunks of about 64 MB per tensor, whole tiles
+    const int64_t ch_rows = std::max<int64_t>(M, ((64ll << 20) / (int64_t)rowb) / M * M);
+    const int64_t n_ch = (n + ch_rows - 1) / ch_rows;
+    const size_t fix_dev_cap = (((size_t)n_ch * (size_t)p->max_depth + p->multi_node.size()) * (2 * rowb + sizeof(int32_t)) + 511) & ~(size_t)255;
+    const size_t need = 8 * tens + lseb + wsb + (bf ? tens : 0) + fix_dev_cap;
     if (p->host_arena_bytes < need) {
         if (p->host_arena) { CUDA_TRY(cudaFree(p->host_arena)); p->host_arena = nullptr; p->host_arena_bytes = 0; }
         CUDA_TRY(cudaMalloc(&p->host_arena, need));
@@ -1608,19 +1623,36 @@ extern "C" int agpt_b200_attn_fwd_bwd_host(const agpt_plan *cp, const float *h_q
     void *ws = base + 8 * tens + lseb;
     __nv_bfloat16 *kb = bf ? (__nv_bfloat16 *)(base + 8 * tens + lseb + wsb) : nullptr;
     __nv_bfloat16 *vb = bf ? kb + (size_t)n * D : nullptr;
+    char *fix_dev = base + 8 * tens + lseb + wsb + (bf ? tens : 0);
     const void *kk = bf ? (const void *)kb : (const void *)dk_in, *vv = bf ? (const void *)vb : (const void *)dv_in;
     const int64_t rows = (int64_t)p->chain_ids.size();
     float *pk = (float *)ws, *pv = pk + rows * D, *segk = pv + rows * D, *segv = segk + p->n_multi_items * D;
 
-    // chunks of about 64 MB per tensor, whole tiles
-    int64_t ch_rows = std::max<int64_t>(M, ((64ll << 20) / (int64_t)rowb) / M * M);
-    const int64_t n_ch = (n + ch_rows - 1) / ch_rows;
     while ((int64_t)p->host_events.size() < 3 * n_ch + 1) {
         cudaEvent_t e;
         CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
         p->host_events.push_back(e);
     }
     auto ev = [&](int64_t c, int k) { return (cudaEvent_t)p->host_events[3 * c + k]; };
+    // dK/dV rows of a chunk are final once every tile of their subtree has run and been reduced.  After chunk c
+    // (rows below r1) that holds for all rows except the strict ancestors of row r1, whose subtrees go on, and
+    // the few nodes whose reduction needs the second pass.  Chunks therefore download dK/dV right away and those
+    // rows ("fix rows": at most depth per chunk boundary) are downloaded again at the end.
+    std::vector<int32_t> fix(p->multi_node.begin(), p->multi_node.end());
+    for (int64_t c = 0; c + 1 < n_ch; c++)
+        for (int32_t a = p->parent_dfs[(c + 1) * ch_rows]; a >= 0; a = p->parent_dfs[a]) fix.push_back(a);
+    std::sort(fix.begin(), fix.end());
+    fix.erase(std::unique(fix.begin(), fix.end()), fix.end());
+    const size_t nfix = fix.size();
+    const size_t fix_bytes = nfix * (2 * rowb + sizeof(int32_t)) + 256;
+    if (fix_dev_cap < fix_bytes) return agpt_set_error(AGPT_E_LIMIT, "attn_fwd_bwd_host: fix-row staging too small");
+    if (p->host_fix_bytes < fix_bytes) {
+        if (p->host_fix) { CUDA_TRY(cudaFreeHost(p->host_fix)); p->host_fix = nullptr; p->host_fix_bytes = 0; }
+        CUDA_TRY(cudaMallocHost(&p->host_fix, fix_bytes));
+        p->host_fix_bytes = fix_bytes;
+    }
+    int64_t item_done = 0;
+    const int64_t n_items = (int64_t)p->item_node.size();
     for (int64_t c = 0; c < n_ch; c++) {
         const int64_t r0 = c * ch_rows, r1 = std::min(n, r0 + ch_rows), nr = r1 - r0;
         const size_t off = (size_t)r0 * D, bytes = (size_t)nr * rowb;
@@ -1638,22 +1670,42 @@ extern "C" int agpt_b200_attn_fwd_bwd_host(const agpt_plan *cp, const float *h_q
         if ((rc = fwd_dispatch(p, dq_in, kk, vv, kv_dtype, dout, dlse, n_heads, head_dim, scale, s_run, t0, nt))) return rc;
         CUDA_TRY(cudaEventRecord(ev(c, 1), s_run));
         if ((rc = bwd_dispatch(p, dq_in, kk, vv, kv_dtype, dout, dlse, dg, ddq, ddk, ddv, pk, pv, n_heads, head_dim, scale, s_run, t0, nt))) return rc;
+        // every reduction item whose last tile has now run
+        const int64_t item_end = std::upper_bound(p->item_t1.begin(), p->item_t1.end(), (int32_t)(t0 + nt - 1)) - p->item_t1.begin();
+        if ((rc = run_reduce_range(p, pk, pv, segk, segv, ddk, ddv, D, s_run, item_done, item_end, c + 1 == n_ch))) return rc;
+        item_done = item_end;
         CUDA_TRY(cudaEventRecord(ev(c, 2), s_run));
         CUDA_TRY(cudaStreamWaitEvent(s_down, ev(c, 1), 0));
         CUDA_TRY(cudaMemcpyAsync(h_out + off, dout + off, bytes, cudaMemcpyDeviceToHost, s_down));
         CUDA_TRY(cudaMemcpyAsync(h_lse + (size_t)r0 * n_heads, dlse + (size_t)r0 * n_heads, (size_t)nr * n_heads * sizeof(float), cudaMemcpyDeviceToHost, s_down));
         CUDA_TRY(cudaStreamWaitEvent(s_down, ev(c, 2), 0));
         CUDA_TRY(cudaMemcpyAsync(h_dq + off, ddq + off, bytes, cudaMemcpyDeviceToHost, s_down));
+        CUDA_TRY(cudaMemcpyAsync(h_dk + off, ddk + off, bytes, cudaMemcpyDeviceToHost, s_down));
+        CUDA_TRY(cudaMemcpyAsync(h_dv + off, ddv + off, bytes, cudaMemcpyDeviceToHost, s_down));
     }
-    if ((rc = run_reduce(p, pk, pv, segk, segv, ddk, ddv, D, s_run))) return rc;
-    cudaEvent_t done = (cudaEvent_t)p->host_events[3 * n_ch];
-    CUDA_TRY(cudaEventRecord(done, s_run));
-    CUDA_TRY(cudaStreamWaitEvent(s_down, done, 0));
-    CUDA_TRY(cudaMemcpyAsync(h_dk, ddk, (size_t)n * rowb, cudaMemcpyDeviceToHost, s_down));
-    CUDA_TRY(cudaMemcpyAsync(h_dv, ddv, (size_t)n * rowb, cudaMemcpyDeviceToHost, s_down));
+    if (item_done != n_items) return agpt_set_error(AGPT_E_CUDA, "attn_fwd_bwd_host: reduction list not exhausted");
+    if (nfix > 0) {
+        // gather the fix rows (now final) and download them after the chunk downloads
+        char *hf = (char *)p->host_fix;
+        int32_t *h_idx = (int32_t *)(hf + nfix * 2 * rowb);
+        std::copy(fix.begin(), fix.end(), h_idx);
+        int32_t *d_idx = (int32_t *)(fix_dev + nfix * 2 * rowb);
+        float *d_fk = (float *)fix_dev, *d_fv = d_fk + nfix * D;
+        CUDA_TRY(cudaMemcpyAsync(d_idx, h_idx, nfix * sizeof(int32_t), cudaMemcpyHostToDevice, s_run));
+        if ((rc = agpt_b200_gather_rows(ddk, d_idx, d_fk, (int64_t)nfix, D, s_run))) return rc;
+        if ((rc = agpt_b200_gather_rows(ddv, d_idx, d_fv, (int64_t)nfix, D, s_run))) return rc;
+        cudaEvent_t done = (cudaEvent_t)p->host_events[3 * n_ch];
+        CUDA_TRY(cudaEventRecord(done, s_run));
+        CUDA_TRY(cudaStreamWaitEvent(s_down, done, 0));
+        CUDA_TRY(cudaMemcpyAsync(hf, d_fk, nfix * 2 * rowb, cudaMemcpyDeviceToHost, s_down));
+    }
     CUDA_TRY(cudaStreamSynchronize(s_down));
     CUDA_TRY(cudaStreamSynchronize(s_run));
     CUDA_TRY(cudaStreamSynchronize(s_up));
+    for (size_t i = 0; i < nfix; i++) {
+        memcpy(h_dk + (size_t)fix[i] * D, (char *)p->host_fix + i * rowb, rowb);
+        memcpy(h_dv + (size_t)fix[i] * D, (char *)p->host_fix + (nfix + i) * rowb, rowb);
+    }
     return AGPT_OK;
 }
 

@@ -187,7 +187,7 @@ def build_units(wl, rank, world, log, single_unit=False, group_rows=4_000_000):
 # ----------------------------------------------------------------------------------------------------------
 # the CPU arm: the oracle restatement of the reference's CPU path on the host cores
 # ----------------------------------------------------------------------------------------------------------
-def cpu_arm(units, cfg, budget_nodes, steps=1, warmup=0):
+def cpu_arm(units, cfg, budget_nodes, counts, steps=1, warmup=0):
     """Grouped forward + backward + per-query loss of the oracle on a bounded sample of units.
     Returns (nodes per second, cores, description)."""
     from oracle import pyoracle as O
@@ -211,13 +211,14 @@ def cpu_arm(units, cfg, budget_nodes, steps=1, warmup=0):
             roots = np.nonzero(u.parent < 0)[0]
             unit_off = np.concatenate([roots, [u.n]]).astype(np.int32)
             O.attn_bwd(u.parent, H, hd, q, k, v, w, w_off, go, unit_off=unit_off)
+            O.loss_per_query(logits, u.q2n, u.qoff, u.radix_ids, u.tokens, counts[0], counts[1], counts[2], u.mass_w)
     for _ in range(warmup):
         one_pass()
     t0 = time.perf_counter()
     for _ in range(steps):
         one_pass()
     dt = (time.perf_counter() - t0) / steps
-    return tot / dt, O.num_threads(), f"{len(sample)} launch groups of the same trie, {tot} positions, attention fwd+bwd (oracle, OpenMP)", dt
+    return tot / dt, O.num_threads(), f"{len(sample)} launch groups of the same trie, {tot} positions, attention fwd+bwd + loss (oracle; attention under OpenMP)", dt
 
 
 def run_reference(args):
@@ -228,7 +229,7 @@ def run_reference(args):
     units, counts, total, plan = build_units(args.workload, 0, 1, lambda s: print(s, file=sys.stderr), group_rows=100_000)
     from oracle import pyoracle as O
     O.set_num_threads(os.cpu_count() or 1)      # torchrun pins OMP_NUM_THREADS=1; this arm may use every host core
-    nps, cores, sample, dt = cpu_arm(units, cfg, args.cpu_nodes, steps=max(1, args.steps), warmup=min(args.warmup, 1))
+    nps, cores, sample, dt = cpu_arm(units, cfg, args.cpu_nodes, counts, steps=max(1, args.steps), warmup=min(args.warmup, 1))
     line = {"impl": "reference", "metric": "trie_nodes_per_sec_attn_fwd_bwd", "value": nps, "unit": "nodes/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -416,7 +417,7 @@ def run_gpu(args):
         from oracle import pyoracle as O
         O.set_num_threads(os.cpu_count() or 1)
         small, _, _, _ = build_units(args.workload, 0, 1, lambda s: None, group_rows=100_000)
-        nps, cores, sample, _ = cpu_arm(small, cfg, args.cpu_nodes)
+        nps, cores, sample, _ = cpu_arm(small, cfg, args.cpu_nodes, counts)
         cpu = {"value": nps, "unit": "nodes/s", "cores": cores, "kind": "port", "sample": sample}
 
     if rank == 0:

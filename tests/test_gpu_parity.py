@@ -435,3 +435,23 @@ def test_deep_pruned_trie_bf16_store(cuda):
     ref_r = _oracle(parent, H, hd, q, _bf16_round(k), _bf16_round(v), go)
     for got, want in zip((out, dq, dk, dv), ref_r[:4]):
         assert rel_err(got, want) < TOL_F32
+
+
+def test_host_buffer_entry_point_multi_chunk(cuda):
+    """Enough rows for several upload/compute/download chunks, with subtrees that span chunk boundaries (their
+    dK/dV rows are downloaded again at the end) and nodes whose reduction needs the second pass."""
+    H, hd = 4, 16
+    parent = A.synth_tree(700_000, 20, 5, 0.3, 8, 100_000, 11)
+    n = parent.size
+    q, k, v, go = random_qkv(n, H * hd, 63)
+    plan = A.WalkerPlan(parent, 64, 0)
+    assert n * H * hd * 4 > 2 * (64 << 20) and plan.info.n_reduce_multi > 0
+    order, inv = plan.dfs_to_node.astype(np.int64), plan.node_to_dfs.astype(np.int64)
+    ins = [np.ascontiguousarray(x[order]) for x in (q, k, v, go)]
+    o, lse, dq, dk, dv = A.attn_fwd_bwd_host(plan, *ins, H)
+    ref = _oracle(parent, H, hd, q, k, v, go)
+    for got, want in zip((o, dq, dk, dv), ref[:4]):
+        assert rel_err(got[inv], want) < TOL_F32
+    # second call on the same plan reuses the cached arena and gives the same bits
+    o2, lse2, dq2, dk2, dv2 = A.attn_fwd_bwd_host(plan, *ins, H)
+    assert np.array_equal(dk, dk2) and np.array_equal(dv, dv2) and np.array_equal(o, o2)
