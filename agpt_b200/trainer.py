@@ -103,6 +103,32 @@ def build_groups(trie: A.RadixTrie, rank: int, world: int, group_rows: int, mass
     return groups, int(gplan.n)
 
 
+def _embedding_function():
+    import torch
+
+    class TokenEmbedding(torch.autograd.Function):
+        """Row gather whose backward is a one-hot GEMM: with a vocabulary of tens of symbols and millions of rows,
+        torch's index_put backward serialises on the collisions; onehot^T @ grad is a plain (and repeatable) GEMM."""
+
+        @staticmethod
+        def forward(ctx, emb, tokens):
+            ctx.save_for_backward(tokens)
+            ctx.vocab = emb.shape[0]
+            return emb.index_select(0, tokens)
+
+        @staticmethod
+        def backward(ctx, grad):
+            (tokens,) = ctx.saved_tensors
+            out = torch.zeros((ctx.vocab, grad.shape[1]), dtype=grad.dtype, device=grad.device)
+            step = 1 << 20                                  # bound the transient one-hot matrix
+            for a in range(0, tokens.numel(), step):
+                oh = torch.nn.functional.one_hot(tokens[a:a + step], ctx.vocab).to(grad.dtype)
+                out.addmm_(oh.t(), grad[a:a + step])
+            return out, None
+
+    return TokenEmbedding
+
+
 def _attention_function():
     import torch
 
@@ -145,6 +171,7 @@ class TrieWalkModel:
         cos, sin = A.rope_table(model.seq_len, hd)
         self.cos, self.sin = torch.from_numpy(cos).to(device), torch.from_numpy(sin).to(device)
         self.attn = _attention_function()
+        self.embed = _embedding_function()
 
     def parameters(self):
         return list(self.params.values())
@@ -165,7 +192,7 @@ class TrieWalkModel:
             x2 = F.layer_norm(x, (D,), g2, b2, 1e-5)
             return x + F.relu(x2 @ w1 + b1) @ w2 + bo
 
-        x = P["token_emb"][group.tokens]
+        x = self.embed.apply(P["token_emb"], group.tokens)
         for l in range(m.n_layers):
             g = lambda n: P[f"layer{l}.{n}"]  # noqa: E731
             x1 = F.layer_norm(x, (D,), g("ln1.gamma")[0], g("ln1.beta")[0], 1e-5)
