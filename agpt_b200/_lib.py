@@ -59,6 +59,13 @@ SIGNATURES = {
     "agpt_b200_plan_units": (i64, [vp, C.c_int, i64, vp, vp]),
     "agpt_b200_partition_lpt": (C.c_int, [vp, i64, C.c_int, vp]),
     "agpt_b200_gather_rows": (C.c_int, [vp, vp, vp, i64, C.c_int, vp]),
+    "cuda_layer_norm_forward": (None, [vp] * 6 + [C.c_int, C.c_int]),
+    "cuda_layer_norm_backward": (None, [vp] * 7 + [C.c_int, C.c_int]),
+    "agpt_b200_layer_norm_fwd": (C.c_int, [vp] * 6 + [i64, C.c_int, vp]),
+    "agpt_b200_layer_norm_bwd": (C.c_int, [vp] * 7 + [i64, C.c_int, vp, i64, vp]),
+    "agpt_b200_layer_norm_bwd_workspace_bytes": (i64, [i64, C.c_int]),
+    "agpt_b200_gemm_f32": (C.c_int, [C.c_int] * 5 + [f32, vp, C.c_int, vp, C.c_int, f32, vp, C.c_int, vp, C.c_int, C.c_int, vp, i64, vp]),
+    "agpt_b200_gemm_f32_workspace_bytes": (i64, [C.c_int] * 6),
     "agpt_b200_rope_table": (C.c_int, [vp, vp, C.c_int, C.c_int, f32]),
     "agpt_b200_rope": (C.c_int, [vp, vp, vp, vp, i64, C.c_int, C.c_int, C.c_int, vp]),
     "agpt_b200_kv_store_write_bf16": (C.c_int, [vp, vp, i64, C.c_int, vp]),

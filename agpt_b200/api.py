@@ -267,6 +267,57 @@ def rope_(x, pos, cos, sin, n_heads: int, inverse: bool = False):
     return x
 
 
+_gemm_ws = {}
+
+
+def gemm_f32(a, b, trans_a=False, trans_b=False, bias=None, out=None, split_k=1):
+    """out = op(a) @ op(b) (+ bias row), float32 on the tensor cores with float32-level accuracy.
+    a, b: contiguous 2-D float32 CUDA tensors."""
+    import torch
+    _chk_f32(a, "a")
+    _chk_f32(b, "b")
+    M, K = (a.shape[1], a.shape[0]) if trans_a else a.shape
+    K2, N = (b.shape[1], b.shape[0]) if trans_b else b.shape
+    if K != K2:
+        raise AgptError(f"gemm_f32: inner dimensions differ ({K} vs {K2})")
+    out = torch.empty((M, N), dtype=torch.float32, device=a.device) if out is None else out
+    need = lib().agpt_b200_gemm_f32_workspace_bytes(int(trans_a), int(trans_b), M, N, K, split_k)
+    if need < 0:
+        check(int(need), "gemm_f32_workspace_bytes")
+    ws = _gemm_ws.get(a.device.index)
+    if need and (ws is None or ws.numel() < need):
+        ws = _gemm_ws[a.device.index] = torch.empty(int(need), dtype=torch.uint8, device=a.device)
+    check(lib().agpt_b200_gemm_f32(int(trans_a), int(trans_b), M, N, K, 1.0, _dp(a), a.shape[1], _dp(b), b.shape[1],
+                                   1.0 if bias is not None else 0.0, _dp(bias), 0, _dp(out), N, split_k, _dp(ws) if need else None, int(need),
+                                   _stream()), "gemm_f32")
+    return out
+
+
+def layer_norm_forward(x, gamma, beta):
+    """y = norm * gamma + beta; returns (y, norm, std_inv) with the reference's saved state."""
+    import torch
+    _chk_f32(x, "x")
+    rows, cols = x.shape
+    y, norm = torch.empty_like(x), torch.empty_like(x)
+    sinv = torch.empty(rows, dtype=torch.float32, device=x.device)
+    check(lib().agpt_b200_layer_norm_fwd(_dp(x), _dp(y), _dp(norm), _dp(sinv), _dp(gamma), _dp(beta), rows, cols, _stream()),
+          "layer_norm_fwd")
+    return y, norm, sinv
+
+
+def layer_norm_backward(grad, norm, sinv, gamma, dgamma, dbeta):
+    """dx (returned); dgamma and dbeta are accumulated into."""
+    import torch
+    _chk_f32(grad, "grad")
+    rows, cols = grad.shape
+    dx = torch.empty_like(grad)
+    wsb = check(lib().agpt_b200_layer_norm_bwd_workspace_bytes(rows, cols), "layer_norm_bwd_workspace_bytes")
+    ws = torch.empty(wsb, dtype=torch.uint8, device=grad.device)
+    check(lib().agpt_b200_layer_norm_bwd(_dp(grad), _dp(norm), _dp(sinv), _dp(gamma), _dp(dx), _dp(dgamma), _dp(dbeta), rows,
+                                         cols, _dp(ws), wsb, _stream()), "layer_norm_bwd")
+    return dx
+
+
 def kv_store_write_bf16(src):
     import torch
     _chk_f32(src, "src")

@@ -129,6 +129,54 @@ def _embedding_function():
     return TokenEmbedding
 
 
+def _layer_norm_function():
+    import torch
+
+    class RowLayerNorm(torch.autograd.Function):
+        """Layer norm over the last dimension with the library's kernels (saved state: normalised rows, 1/std)."""
+
+        @staticmethod
+        def forward(ctx, x, gamma, beta):
+            y, norm, sinv = A.layer_norm_forward(x.contiguous(), gamma.contiguous(), beta.contiguous())
+            ctx.save_for_backward(norm, sinv, gamma)
+            return y
+
+        @staticmethod
+        def backward(ctx, grad):
+            norm, sinv, gamma = ctx.saved_tensors
+            dgamma, dbeta = torch.zeros_like(gamma), torch.zeros_like(gamma)
+            dx = A.layer_norm_backward(grad.contiguous(), norm, sinv, gamma.contiguous(), dgamma, dbeta)
+            return dx, dgamma, dbeta
+
+    return RowLayerNorm
+
+
+def _linear_function():
+    import torch
+
+    class TensorLinear(torch.autograd.Function):
+        """y = x @ w + b with the library's float32-accurate tensor-core GEMM; the weight gradient cuts the row
+        dimension into slices that are summed in a fixed order."""
+
+        @staticmethod
+        def forward(ctx, x, w, b):
+            x = x.contiguous()
+            ctx.save_for_backward(x, w)
+            return A.gemm_f32(x, w, bias=b)
+
+        @staticmethod
+        def backward(ctx, grad):
+            x, w = ctx.saved_tensors
+            grad = grad.contiguous()
+            dx = A.gemm_f32(grad, w, trans_b=True)
+            tiles = -(-w.shape[0] // 128) * -(-w.shape[1] // 64)
+            split_k = max(1, min(x.shape[0] // 2048, -(-592 // tiles)))
+            dw = A.gemm_f32(x, grad, trans_a=True, split_k=split_k)
+            return dx, dw, grad.sum(0)
+
+    return TensorLinear
+
+
 def _attention_function():
     import torch
 
@@ -172,6 +220,10 @@ class TrieWalkModel:
         self.cos, self.sin = torch.from_numpy(cos).to(device), torch.from_numpy(sin).to(device)
         self.attn = _attention_function()
         self.embed = _embedding_function()
+        self.ln = _layer_norm_function()
+        self.linear = _linear_function()
+        self.dense_impl = "tensor"       # "tensor": the library's 3xTF32 GEMM; "torch": torch.addmm (cuBLAS float32)
+        self.ffn_recompute = False       # True: recompute the d_ff-wide activations in the backward instead of keeping them
 
     def parameters(self):
         return list(self.params.values())
@@ -183,29 +235,34 @@ class TrieWalkModel:
         return out
 
     def logits(self, group: LaunchGroup, bf16_store=False):
-        import torch.nn.functional as F
+        import torch
         from torch.utils.checkpoint import checkpoint
         P, m = self.params, self.cfg
-        D = m.d_model
+        ln = self.ln.apply
+
+        def lin(x, w, b):
+            # the library GEMM needs 16-byte aligned rows; other widths (a vocabulary of 65) go to torch
+            if self.dense_impl == "tensor" and w.shape[0] % 4 == 0 and w.shape[1] % 4 == 0:
+                return self.linear.apply(x, w, b)
+            return torch.addmm(b, x, w)
 
         def ffn(x, g2, b2, w1, b1, w2, bo):
-            x2 = F.layer_norm(x, (D,), g2, b2, 1e-5)
-            return x + F.relu(x2 @ w1 + b1) @ w2 + bo
+            h = torch.relu(lin(ln(x, g2, b2), w1, b1))
+            return x + lin(h, w2, bo)
 
         x = self.embed.apply(P["token_emb"], group.tokens)
         for l in range(m.n_layers):
             g = lambda n: P[f"layer{l}.{n}"]  # noqa: E731
-            x1 = F.layer_norm(x, (D,), g("ln1.gamma")[0], g("ln1.beta")[0], 1e-5)
-            q = x1 @ g("wq.w") + g("wq.b")
-            k = x1 @ g("wk.w") + g("wk.b")
-            v = x1 @ g("wv.w") + g("wv.b")
+            x1 = ln(x, g("ln1.gamma")[0], g("ln1.beta")[0])
+            q = lin(x1, g("wq.w"), g("wq.b")[0])
+            k = lin(x1, g("wk.w"), g("wk.b")[0])
+            v = lin(x1, g("wv.w"), g("wv.b")[0])
             a = self.attn.apply(q, k, v, group, self.cos, self.sin, m.n_heads, bf16_store)
-            x = x + a @ g("wo.w") + g("wo.b")
-            # the d_ff-wide activations are recomputed in the backward instead of being kept
-            x = checkpoint(ffn, x, g("ln2.gamma")[0], g("ln2.beta")[0], g("l1.w"), g("l1.b"), g("l2.w"), g("l2.b"),
-                           use_reentrant=False)
-        xf = F.layer_norm(x, (D,), P["final.gamma"][0], P["final.beta"][0], 1e-5)
-        return xf @ P["out.w"] + P["out.b"]
+            x = x + lin(a, g("wo.w"), g("wo.b")[0])
+            args = (x, g("ln2.gamma")[0], g("ln2.beta")[0], g("l1.w"), g("l1.b")[0], g("l2.w"), g("l2.b")[0])
+            x = checkpoint(ffn, *args, use_reentrant=False) if self.ffn_recompute else ffn(*args)
+        xf = ln(x, P["final.gamma"][0], P["final.beta"][0])
+        return lin(xf, P["out.w"], P["out.b"][0])
 
     def group_step(self, group: LaunchGroup, counts, entropy_lambda=0.0, intermediate_weight=1.0, ce_only=False,
                    bf16_store=False):
@@ -289,6 +346,7 @@ def main(argv=None):
     ap.add_argument("--no-accumulate", action="store_true")
     ap.add_argument("--bf16-kv", action="store_true")
     ap.add_argument("--group-rows", type=int, default=1_000_000)
+    ap.add_argument("--ffn-recompute", action="store_true", help="recompute the FFN activations in the backward (less memory)")
     ap.add_argument("--partition-depth", type=int, default=0, choices=[0, 1, 2],
                     help="1 = root-child units, 2 = bigram units; 0 = 1 on one rank, 2 on several")
     args = ap.parse_args(argv)
@@ -309,6 +367,7 @@ def main(argv=None):
                                  level=args.partition_depth or None)
     counts = [torch.from_numpy(np.ascontiguousarray(c)).to(dev) for c in (trie.cnt_off.astype(np.int32), trie.cnt_tok, trie.cnt_val)]
     model = TrieWalkModel(mf, dev)
+    model.ffn_recompute = args.ffn_recompute
     opt = make_optimizer(args.optimizer, model.parameters(), args.lr, args.rmsprop_beta)
     n_sub = int((trie.parent[1:] == 0).sum())
     save = args.save or args.model

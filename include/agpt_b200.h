@@ -204,6 +204,36 @@ int agpt_b200_rope_table(float *cos_out, float *sin_out, int max_seq, int head_d
 int agpt_b200_rope(float *d_x, const int32_t *d_pos, const float *d_cos, const float *d_sin, int64_t n,
                    int n_heads, int head_dim, int inverse, void *stream);
 
+/* Replace cuda_layer_norm_forward / cuda_layer_norm_backward of the reference's kernel dependency (declared
+ * src/cuda/agpt_train.cu:50-55; called :4671, :4762, :4801, :4850, :4907, :5066), with the arithmetic the reference
+ * states on CPU (src/agpt/incremental_forward.cr:143-163, src/agpt/batched_depth_backward.cr:751-799): float32 mean
+ * and biased variance, std_inv = 1/sqrt(var + 1e-5); output = norm*gamma + beta; norm_out and std_inv_out are the
+ * saved state.  Backward: dx may alias grad; dgamma and dbeta are accumulated into, in a fixed order.  cols must
+ * be a multiple of 4, at most 1024.  The legacy symbols run on the default stream and keep a per-device scratch. */
+void cuda_layer_norm_forward(const float *input, float *output, float *norm_out, float *std_inv_out,
+                             const float *gamma, const float *beta, int rows, int cols);
+void cuda_layer_norm_backward(const float *grad, const float *norm, const float *std_inv, const float *gamma,
+                              float *dx, float *dgamma, float *dbeta, int rows, int cols);
+int agpt_b200_layer_norm_fwd(const float *d_x, float *d_y, float *d_norm, float *d_std_inv, const float *d_gamma,
+                             const float *d_beta, int64_t rows, int cols, void *stream);
+int agpt_b200_layer_norm_bwd(const float *d_grad, const float *d_norm, const float *d_std_inv, const float *d_gamma,
+                             float *d_dx, float *d_dgamma, float *d_dbeta, int64_t rows, int cols, void *d_workspace,
+                             int64_t workspace_bytes, void *stream);
+int64_t agpt_b200_layer_norm_bwd_workspace_bytes(int64_t rows, int cols);
+
+/* Replaces the cublasSgemm calls of the dense projections (src/cuda/agpt_train.cu:4675-4683, :4752, :4766-4771,
+ * :4803, :4840-5061) with a tensor-core GEMM of float32-level accuracy (three TF32 MMAs per product).  Row-major:
+ *     out[M, N] = alpha * op(A)[M, K] * op(B)[K, N] + beta * C
+ * trans_a / trans_b select A^T / B^T (not both).  ldc == 0 broadcasts one row (a bias) as the source; d_c may be
+ * NULL when beta == 0.  split_k > 1 cuts K into slices (for weight gradients, whose K is the number of trie
+ * positions): the slices run as one batched GEMM into partial matrices in d_workspace
+ * (agpt_b200_gemm_f32_workspace_bytes, 0 when split_k == 1) and are added in slice order, so the result is
+ * repeatable bit for bit.  Pointers and leading dimensions must be multiples of 4 floats. */
+int agpt_b200_gemm_f32(int trans_a, int trans_b, int M, int N, int K, float alpha, const float *d_a, int lda,
+                       const float *d_b, int ldb, float beta, const float *d_c, int ldc, float *d_out, int ldd,
+                       int split_k, void *d_workspace, int64_t workspace_bytes, void *stream);
+int64_t agpt_b200_gemm_f32_workspace_bytes(int trans_a, int trans_b, int M, int N, int K, int split_k);
+
 /* Replaces kv_scatter_kernel_bf16 (src/cuda/agpt_train.cu:1537-1554) for a store laid out in
  * depth-first order: d_store[i, :] = bf16(d_src[i, :]). */
 int agpt_b200_kv_store_write_bf16(const float *d_src, void *d_store_bf16, int64_t n, int cols, void *stream);

@@ -884,6 +884,41 @@ ORC_API void orc_mass_weights(const int32_t *edge_mass, const int32_t *edge_len,
     free(nw);
 }
 
+/* Layer norm of the reference's CPU path: float32 mean and biased variance, std_inv = 1/sqrt(var + 1e-5)
+   (src/agpt/incremental_forward.cr:143-163); backward with float64 row means, dgamma/dbeta accumulated
+   (src/agpt/batched_depth_backward.cr:751-799). */
+ORC_API void orc_layer_norm_fwd(const float *x, float *y, float *norm, float *std_inv, const float *gamma,
+                                const float *beta, int64_t rows, int cols) {
+    for (int64_t r = 0; r < rows; r++) {
+        const float *xr = x + r * cols;
+        float mean = 0.f;
+        for (int j = 0; j < cols; j++) mean += xr[j];
+        mean /= cols;
+        float var = 0.f;
+        for (int j = 0; j < cols; j++) { float d = xr[j] - mean; var += d * d; }
+        var /= cols;
+        float sinv = (float)(1.0 / sqrt((double)(var + 1e-5f)));
+        std_inv[r] = sinv;
+        for (int j = 0; j < cols; j++) {
+            float nrm = (xr[j] - mean) * sinv;
+            norm[r * cols + j] = nrm;
+            y[r * cols + j] = nrm * gamma[j] + beta[j];
+        }
+    }
+}
+
+ORC_API void orc_layer_norm_bwd(const float *grad, const float *norm, const float *std_inv, const float *gamma,
+                                float *dx, float *dgamma, float *dbeta, int64_t rows, int cols) {
+    for (int64_t r = 0; r < rows; r++) {
+        const float *g = grad + r * cols, *nm = norm + r * cols;
+        double sinv = std_inv[r], mean_dn = 0.0, mean_dn_n = 0.0;
+        for (int j = 0; j < cols; j++) { dgamma[j] += g[j] * nm[j]; dbeta[j] += g[j]; }
+        for (int j = 0; j < cols; j++) { float dn = g[j] * gamma[j]; mean_dn += dn; mean_dn_n += dn * nm[j]; }
+        mean_dn /= cols; mean_dn_n /= cols;
+        for (int j = 0; j < cols; j++) { float dn = g[j] * gamma[j]; dx[r * cols + j] = (float)((dn - mean_dn - nm[j] * mean_dn_n) * sinv); }
+    }
+}
+
 ORC_API void orc_set_num_threads(int n) {
 #ifdef _OPENMP
     if (n > 0) omp_set_num_threads(n);

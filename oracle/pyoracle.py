@@ -364,6 +364,23 @@ def mass_weights(edge_mass, edge_len, mode):
     return out
 
 
+def layer_norm_fwd(x, gamma, beta):
+    x = f32(x)
+    rows, cols = x.shape
+    y, norm, sinv = np.zeros_like(x), np.zeros_like(x), np.zeros(rows, np.float32)
+    lib().orc_layer_norm_fwd(_p(x), _p(y), _p(norm), _p(sinv), _p(f32(gamma)), _p(f32(beta)), C.c_int64(rows), C.c_int(cols))
+    return y, norm, sinv
+
+
+def layer_norm_bwd(grad, norm, sinv, gamma):
+    grad = f32(grad)
+    rows, cols = grad.shape
+    dx, dg, db = np.zeros_like(grad), np.zeros(cols, np.float32), np.zeros(cols, np.float32)
+    lib().orc_layer_norm_bwd(_p(grad), _p(f32(norm)), _p(f32(sinv)), _p(f32(gamma)), _p(dx), _p(dg), _p(db), C.c_int64(rows),
+                             C.c_int(cols))
+    return dx, dg, db
+
+
 def set_num_threads(n: int) -> None:
     lib().orc_set_num_threads(C.c_int(n))
 

@@ -455,3 +455,57 @@ def test_host_buffer_entry_point_multi_chunk(cuda):
     # second call on the same plan reuses the cached arena and gives the same bits
     o2, lse2, dq2, dk2, dv2 = A.attn_fwd_bwd_host(plan, *ins, H)
     assert np.array_equal(dk, dk2) and np.array_equal(dv, dv2) and np.array_equal(o, o2)
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 4), (1000, 64), (4097, 128), (513, 384), (77, 1024)])
+def test_layer_norm_kernels(cuda, rows, cols):
+    import torch
+    rng = np.random.default_rng(cols)
+    x = (rng.standard_normal((rows, cols)) * 2 + 0.5).astype(np.float32)
+    gamma = rng.uniform(0.5, 1.5, cols).astype(np.float32)
+    beta = rng.standard_normal(cols).astype(np.float32)
+    grad = rng.standard_normal((rows, cols)).astype(np.float32)
+    wy, wn, ws = O.layer_norm_fwd(x, gamma, beta)
+    wdx, wdg, wdb = O.layer_norm_bwd(grad, wn, ws, gamma)
+    y, norm, sinv = A.layer_norm_forward(_dev(x, cuda), _dev(gamma, cuda), _dev(beta, cuda))
+    assert rel_err(y.cpu().numpy(), wy) < TOL_F32 and rel_err(norm.cpu().numpy(), wn) < TOL_F32
+    assert rel_err(sinv.cpu().numpy(), ws) < TOL_F32
+    dg, db = torch.ones(cols, device=cuda), torch.full((cols,), 2.0, device=cuda)      # accumulated into
+    dx = A.layer_norm_backward(_dev(grad, cuda), norm, sinv, _dev(gamma, cuda), dg, db)
+    assert rel_err(dx.cpu().numpy(), wdx) < TOL_F32
+    assert rel_err(dg.cpu().numpy() - 1.0, wdg) < TOL_F32 and rel_err(db.cpu().numpy() - 2.0, wdb) < TOL_F32
+    # legacy symbols, in place, default stream
+    g2, n2 = _dev(grad, cuda), norm.clone()
+    dg2, db2 = torch.zeros(cols, device=cuda), torch.zeros(cols, device=cuda)
+    A.lib().cuda_layer_norm_backward(g2.data_ptr(), n2.data_ptr(), sinv.data_ptr(), _dev(gamma, cuda).data_ptr(), g2.data_ptr(),
+                                     dg2.data_ptr(), db2.data_ptr(), rows, cols)
+    A.lib().cuda_sync()
+    assert torch.equal(g2, dx) and rel_err(dg2.cpu().numpy(), wdg) < TOL_F32
+
+
+@pytest.mark.parametrize("shape", [(1000, 128, 128), (70001, 128, 512), (4099, 512, 128), (64, 32, 64), (3, 4, 8)])
+def test_gemm_f32_tensor_core(shape):
+    """The three layouts of the float32-accurate tensor-core GEMM (projection, input gradient, weight gradient with
+    K cut into slices) against float64 products; tolerance 1e-5 of the largest entry (float32 rounding of a
+    length-K sum)."""
+    import torch
+    rows, din, dout = shape
+    g = torch.Generator(device="cuda").manual_seed(rows)
+    x = torch.randn(rows, din, device="cuda", generator=g)
+    w = torch.randn(din, dout, device="cuda", generator=g)
+    b = torch.randn(dout, device="cuda", generator=g)
+    dy = torch.randn(rows, dout, device="cuda", generator=g)
+
+    def close(got, want):
+        assert float((got.double() - want).abs().max() / want.abs().max()) < 1e-5
+
+    close(A.gemm_f32(x, w, bias=b), x.double() @ w.double() + b.double())
+    close(A.gemm_f32(x, w), x.double() @ w.double())
+    close(A.gemm_f32(dy, w, trans_b=True), dy.double() @ w.double().t())
+    want = x.double().t() @ dy.double()
+    for split_k in (1, 2, 7, 64):
+        got = A.gemm_f32(x, dy, trans_a=True, split_k=split_k)
+        close(got, want)
+        assert torch.equal(got, A.gemm_f32(x, dy, trans_a=True, split_k=split_k))      # repeatable bit for bit
+    with pytest.raises(A.AgptError):
+        A.gemm_f32(x, w.t().contiguous(), trans_a=True, trans_b=True)
