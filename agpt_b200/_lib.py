@@ -66,6 +66,7 @@ SIGNATURES = {
     "agpt_b200_layer_norm_bwd_workspace_bytes": (i64, [i64, C.c_int]),
     "agpt_b200_gemm_f32": (C.c_int, [C.c_int] * 5 + [f32, vp, C.c_int, vp, C.c_int, f32, vp, C.c_int, vp, C.c_int, C.c_int, vp, i64, vp]),
     "agpt_b200_gemm_f32_workspace_bytes": (i64, [C.c_int] * 6),
+    "agpt_b200_set_gemm_impl": (C.c_int, [C.c_int]),
     "agpt_b200_rope_table": (C.c_int, [vp, vp, C.c_int, C.c_int, f32]),
     "agpt_b200_rope": (C.c_int, [vp, vp, vp, vp, i64, C.c_int, C.c_int, C.c_int, vp]),
     "agpt_b200_kv_store_write_bf16": (C.c_int, [vp, vp, i64, C.c_int, vp]),

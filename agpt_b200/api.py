@@ -368,6 +368,11 @@ def attn_backward(plan: WalkerPlan, q, k, v, out, lse, dout, n_heads: int, scale
     return dq, dk, dv
 
 
+def set_gemm_impl(impl: int) -> None:
+    """0: mma.sync with three TF32 products; 1 (default): tcgen05 on bfloat16 splits."""
+    check(lib().agpt_b200_set_gemm_impl(impl), "set_gemm_impl")
+
+
 def set_attn_impl(impl: int) -> None:
     """1 = tensor-core kernels (default), 0 = FP32 FMA kernels."""
     check(lib().agpt_b200_set_attn_impl(impl), "set_attn_impl")

@@ -1,6 +1,8 @@
-// float32 GEMM on the tensor cores with float32-level accuracy for the dense projections around the trie
-// attention (replaces the reference's cublasSgemm calls, src/cuda/agpt_train.cu:4675-4683, :4752, :4766-4771,
-// :4803, :4840-5061).  CUTLASS's "fast accurate" TF32 operator splits both operands into big and small TF32
+// Entry points of the float32-accurate tensor-core GEMM for the dense projections around the trie attention
+// (replaces the reference's cublasSgemm calls, src/cuda/agpt_train.cu:4675-4683, :4752, :4766-4771, :4803,
+// :4840-5061), and its second implementation.  Implementation 1 (default) is the tcgen05 kernel in gemm_sm100.cu;
+// implementation 0, in this file, runs on mma.sync and also serves the cases the first does not take (a general
+// source matrix, the tail of a sliced reduction).  Here CUTLASS's "fast accurate" TF32 operator splits both operands into big and small TF32
 // parts and issues three tensor-core MMAs per product (the same compensation the attention kernels use), so
 // results agree with an IEEE float32 GEMM to about 1e-6 relative while running on mma.sync instead of the FP32
 // FMA pipe.  All matrices are row-major; op(A) is A or A^T, op(B) is B or B^T:
@@ -9,6 +11,8 @@
 // positions).  Slices run as one batched GEMM into partial matrices in the workspace and a second small kernel
 // adds them in slice order, so the result is repeatable bit for bit and no thread block waits on another.
 #include <cuda_runtime.h>
+
+#include <cstdlib>
 
 #include "../../include/agpt_b200.h"
 #include "internal.h"
@@ -22,6 +26,7 @@ extern "C" int agpt_b200_gemm_f32(int, int, int, int, int, float, const float *,
                                   float *, int, int, void *, int64_t, void *) {
     return agpt_set_error(AGPT_E_ARG, "gemm_f32: this build of the library has no CUTLASS headers");
 }
+extern "C" int agpt_b200_set_gemm_impl(int) { return agpt_set_error(AGPT_E_ARG, "gemm_f32: this build of the library has no CUTLASS headers"); }
 #else
 
 #include "cutlass/cutlass.h"
@@ -77,12 +82,27 @@ __global__ void __launch_bounds__(256) sum_slices_kernel(const float4 *__restric
     *reinterpret_cast<float4 *>(out + r * ldd + c) = acc;
 }
 
+int g_gemm_impl = -1;
+int gemm_impl() {
+    if (g_gemm_impl < 0) {
+        const char *e = getenv("AGPT_B200_GEMM_IMPL");
+        g_gemm_impl = (e && e[0] == '0') ? 0 : 1;
+    }
+    return g_gemm_impl;
+}
+
 template <typename G, bool TA, bool TB>
 int run(int M, int N, int K, float alpha, const float *A, int lda, const float *B, int ldb, float beta, const float *Csrc,
         int ldc, float *D, int ldd, int split_k, void *ws, int64_t ws_bytes, cudaStream_t st) {
     using Mode = cutlass::gemm::GemmUniversalMode;
     int ks = split_k > 1 ? slice_len(K, split_k) : 0;
+    // the tcgen05 kernel takes products without a source matrix, or with a bias row as the source
+    const bool bias_row = beta == 1.f && ldc == 0;
+    const bool sm100 = gemm_impl() == 1 && N % 4 == 0 && lda % 4 == 0 && ldb % 4 == 0 && ldd % 4 == 0 &&
+                       (((uintptr_t)A | (uintptr_t)B | (uintptr_t)D | (uintptr_t)Csrc) & 15) == 0;
     if (ks == 0) {
+        if (sm100 && (beta == 0.f || bias_row))
+            return agpt_gemm_sm100(TA, TB, M, N, K, 1, alpha, A, lda, 0, B, ldb, 0, bias_row ? Csrc : nullptr, D, ldd, 0, st);
         typename G::Arguments args(Mode::kGemm, {M, N, K}, 1, {alpha, beta}, A, B, Csrc, D, 0, 0, 0, 0, (int64_t)lda, (int64_t)ldb, (int64_t)ldc, (int64_t)ldd);
         return launch<G>(args, st);
     }
@@ -92,8 +112,13 @@ int run(int M, int N, int K, float alpha, const float *A, int lda, const float *
     // a slice of K is ks columns of a row-major operand, ks rows of a transposed one
     int64_t sa = TA ? (int64_t)ks * lda : ks, sb = TB ? ks : (int64_t)ks * ldb;
     float *part = (float *)ws;
-    typename G::Arguments args(Mode::kBatched, {M, N, ks}, split_k, {alpha, 0.f}, A, B, part, part, sa, sb, mn, mn, (int64_t)lda, (int64_t)ldb, (int64_t)N, (int64_t)N);
-    int rc = launch<G>(args, st);
+    int rc;
+    if (sm100) {
+        rc = agpt_gemm_sm100(TA, TB, M, N, ks, split_k, alpha, A, lda, sa, B, ldb, sb, nullptr, part, N, mn, st);
+    } else {
+        typename G::Arguments args(Mode::kBatched, {M, N, ks}, split_k, {alpha, 0.f}, A, B, part, part, sa, sb, mn, mn, (int64_t)lda, (int64_t)ldb, (int64_t)N, (int64_t)N);
+        rc = launch<G>(args, st);
+    }
     if (rc) return rc;
     int64_t mn4 = mn / 4;
     sum_slices_kernel<<<(unsigned)((mn4 + 255) / 256), 256, 0, st>>>((const float4 *)part, split_k, mn4, N / 4, beta, Csrc, ldc, D, ldd);
@@ -115,6 +140,12 @@ extern "C" int64_t agpt_b200_gemm_f32_workspace_bytes(int trans_a, int trans_b, 
     if (M <= 0 || N <= 0 || K <= 0 || split_k < 1) return agpt_set_error(AGPT_E_ARG, "gemm_f32_workspace_bytes: bad argument");
     if (trans_a && trans_b) return agpt_set_error(AGPT_E_ARG, "gemm_f32: A^T * B^T is not provided");
     return (split_k > 1 && slice_len(K, split_k) > 0) ? (int64_t)split_k * M * N * 4 : 0;
+}
+
+extern "C" int agpt_b200_set_gemm_impl(int impl) {
+    if (impl != 0 && impl != 1) return agpt_set_error(AGPT_E_ARG, "set_gemm_impl: 0 (mma.sync, three TF32 products) or 1 (tcgen05, bf16 splits)");
+    g_gemm_impl = impl;
+    return AGPT_OK;
 }
 
 extern "C" int agpt_b200_gemm_f32(int trans_a, int trans_b, int M, int N, int K, float alpha, const float *d_a, int lda,

@@ -1,0 +1,106 @@
+// float32 GEMM on the fifth-generation tensor cores (tcgen05 MMAs with accumulators in tensor memory, operands
+// brought in by TMA) for the dense projections around the trie attention.  Each float32 operand tile is split on
+// chip into three bfloat16 matrices (x = b0 + b1 + b2 to 24 bits) and the product is rebuilt from the bf16 x bf16
+// partial products with float32 accumulation, so results match an IEEE float32 GEMM to a few 1e-7 relative: the
+// accuracy of the reference's cublasSgemm calls (src/cuda/agpt_train.cu:4675-4683, :4752, :4766-4771, :4803,
+// :4840-5061) at several times their speed.  The kernel is CUTLASS's SM100 warp-specialised "fast FP32" mainloop
+// (TMA load warp -> transform warps -> MMA warp -> epilogue warps), instantiated here for one CTA per tile
+// (no cluster multicast), a 128x128x16 tile, and an epilogue that adds a per-column bias row.
+#include <cuda_runtime.h>
+
+#include "../../include/agpt_b200.h"
+#include "internal.h"
+
+#ifndef AGPT_NO_CUTLASS
+
+#include "cute/tensor.hpp"
+#include "cutlass/cutlass.h"
+#include "cutlass/epilogue/collective/collective_builder.hpp"
+#include "cutlass/epilogue/fusion/operations.hpp"
+#include "cutlass/gemm/collective/collective_builder.hpp"
+#include "cutlass/gemm/device/gemm_universal_adapter.h"
+#include "cutlass/gemm/kernel/gemm_universal.hpp"
+
+namespace {
+
+using namespace cute;
+using Row = cutlass::layout::RowMajor;
+using Col = cutlass::layout::ColumnMajor;
+
+template <typename LayoutA, typename LayoutB>
+struct Sm100Gemm {
+    using TileShape = Shape<_128, _128, _16>;
+    using ClusterShape = Shape<_1, _1, _1>;
+    // D = alpha * acc + bias[column]; no source matrix is read (ElementC = void)
+    using Fusion = cutlass::epilogue::fusion::LinCombPerColBias<float, float, float, float, float, 4>;
+    using Epilogue = typename cutlass::epilogue::collective::CollectiveBuilder<
+        cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, TileShape, ClusterShape, cutlass::epilogue::collective::EpilogueTileAuto,
+        float, float, void, Row, 4, float, Row, 4, cutlass::epilogue::TmaWarpSpecialized1Sm, Fusion>::CollectiveOp;
+    using Mainloop = typename cutlass::gemm::collective::CollectiveBuilder<
+        cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, float, LayoutA, 4, float, LayoutB, 4, float, TileShape, ClusterShape,
+        cutlass::gemm::collective::StageCountAutoCarveout<static_cast<int>(sizeof(typename Epilogue::SharedStorage))>,
+        cutlass::gemm::KernelTmaWarpSpecialized1SmFastFP32Sm100>::CollectiveOp;
+    using Kernel = cutlass::gemm::kernel::GemmUniversal<Shape<int, int, int, int>, Mainloop, Epilogue, void>;
+    using Gemm = cutlass::gemm::device::GemmUniversalAdapter<Kernel>;
+};
+
+int sm_count_of(int dev) {
+    static int cached[64] = {0};
+    if (dev < 0 || dev >= 64) return cutlass::KernelHardwareInfo::query_device_multiprocessor_count(dev);
+    if (!cached[dev]) cached[dev] = cutlass::KernelHardwareInfo::query_device_multiprocessor_count(dev);
+    return cached[dev];
+}
+
+template <typename G>
+int run(int M, int N, int K, int L, float alpha, const float *A, int64_t lda, int64_t batch_a, const float *B, int64_t ldb,
+        int64_t batch_b, const float *bias, float *D, int64_t ldd, int64_t batch_d, cudaStream_t st) {
+    using Gemm = typename G::Gemm;
+    typename Gemm::GemmKernel::StrideA dA;
+    typename Gemm::GemmKernel::StrideB dB;
+    typename Gemm::GemmKernel::StrideD dD;
+    // of each (row, column) stride pair one entry is the compile-time 1, the other the leading dimension; the
+    // third mode is the batch (a slice of K when the caller cuts the reduction)
+    if constexpr (is_static<decltype(get<1>(dA))>::value) get<0>(dA) = lda; else get<1>(dA) = lda;
+    get<2>(dA) = batch_a;
+    if constexpr (is_static<decltype(get<1>(dB))>::value) get<0>(dB) = ldb; else get<1>(dB) = ldb;
+    get<2>(dB) = batch_b;
+    get<0>(dD) = ldd;
+    get<2>(dD) = batch_d;
+    typename Gemm::Arguments args{cutlass::gemm::GemmUniversalMode::kGemm, {M, N, K, L}, {A, dA, B, dB}, {{}, nullptr, dD, D, dD}};
+    args.epilogue.thread.alpha = alpha;
+    args.epilogue.thread.beta = 0.f;
+    args.epilogue.thread.bias_ptr = bias;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    // the tensor maps are encoded through the driver API, which needs the device's primary context current on
+    // this host thread; a thread that has only queried the runtime so far (an autograd worker) has none yet
+    cudaSetDevice(dev);
+    args.hw_info.device_id = dev;
+    args.hw_info.sm_count = sm_count_of(dev);
+    Gemm op;
+    cutlass::Status s = op.can_implement(args);
+    if (s != cutlass::Status::kSuccess)
+        return agpt_set_error(AGPT_E_ARG, "gemm_f32: unsupported shape or alignment (%s); leading dimensions and pointers must be multiples of 4 floats",
+                              cutlass::cutlassGetStatusString(s));
+    if (Gemm::get_workspace_size(args) != 0) return agpt_set_error(AGPT_E_ARG, "gemm_f32: unexpected CUTLASS workspace");
+    s = op.initialize(args, nullptr, st);
+    if (s != cutlass::Status::kSuccess) return agpt_set_error(AGPT_E_CUDA, "gemm_f32: initialize: %s", cutlass::cutlassGetStatusString(s));
+    s = op.run(st);
+    if (s != cutlass::Status::kSuccess) return agpt_set_error(AGPT_E_CUDA, "gemm_f32: run: %s", cutlass::cutlassGetStatusString(s));
+    return AGPT_OK;
+}
+
+}  // namespace
+
+// D[l] = alpha * op(A[l]) * op(B[l]) + bias, l < L; row-major storage, op as in agpt_b200_gemm_f32
+int agpt_gemm_sm100(int trans_a, int trans_b, int M, int N, int K, int L, float alpha, const float *A, int64_t lda, int64_t batch_a,
+                    const float *B, int64_t ldb, int64_t batch_b, const float *bias, float *D, int64_t ldd, int64_t batch_d,
+                    void *stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    // a transposed row-major operand is the same memory read as column-major
+    if (!trans_a && !trans_b) return run<Sm100Gemm<Row, Row>>(M, N, K, L, alpha, A, lda, batch_a, B, ldb, batch_b, bias, D, ldd, batch_d, st);
+    if (!trans_a && trans_b) return run<Sm100Gemm<Row, Col>>(M, N, K, L, alpha, A, lda, batch_a, B, ldb, batch_b, bias, D, ldd, batch_d, st);
+    if (trans_a && !trans_b) return run<Sm100Gemm<Col, Row>>(M, N, K, L, alpha, A, lda, batch_a, B, ldb, batch_b, bias, D, ldd, batch_d, st);
+    return agpt_set_error(AGPT_E_ARG, "gemm_f32: A^T * B^T is not provided");
+}
+#endif  // AGPT_NO_CUTLASS

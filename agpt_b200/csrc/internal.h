@@ -44,3 +44,8 @@ struct agpt_plan {
 };
 
 int agpt_plan_upload(agpt_plan *p, int device);
+
+// tcgen05 float32 GEMM (gemm_sm100.cu): D[l] = alpha * op(A[l]) * op(B[l]) + bias row, l < L batches
+int agpt_gemm_sm100(int trans_a, int trans_b, int M, int N, int K, int L, float alpha, const float *A, int64_t lda, int64_t batch_a,
+                    const float *B, int64_t ldb, int64_t batch_b, const float *bias, float *D, int64_t ldd, int64_t batch_d,
+                    void *stream);

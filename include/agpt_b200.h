@@ -233,6 +233,10 @@ int agpt_b200_gemm_f32(int trans_a, int trans_b, int M, int N, int K, float alph
                        const float *d_b, int ldb, float beta, const float *d_c, int ldc, float *d_out, int ldd,
                        int split_k, void *d_workspace, int64_t workspace_bytes, void *stream);
 int64_t agpt_b200_gemm_f32_workspace_bytes(int trans_a, int trans_b, int M, int N, int K, int split_k);
+/* Two implementations compute agpt_b200_gemm_f32: 1 (default) tcgen05 MMAs on bfloat16 splits of the operands with
+ * TMA loads and tensor-memory accumulators; 0 mma.sync with three TF32 products (also set by the environment
+ * variable AGPT_B200_GEMM_IMPL=0).  Both agree with a float32 GEMM to about 1e-6. */
+int agpt_b200_set_gemm_impl(int impl);
 
 /* Replaces kv_scatter_kernel_bf16 (src/cuda/agpt_train.cu:1537-1554) for a store laid out in
  * depth-first order: d_store[i, :] = bf16(d_src[i, :]). */

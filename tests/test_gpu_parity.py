@@ -483,13 +483,15 @@ def test_layer_norm_kernels(cuda, rows, cols):
     assert torch.equal(g2, dx) and rel_err(dg2.cpu().numpy(), wdg) < TOL_F32
 
 
+@pytest.mark.parametrize("gemm_impl", [1, 0])
 @pytest.mark.parametrize("shape", [(1000, 128, 128), (70001, 128, 512), (4099, 512, 128), (64, 32, 64), (3, 4, 8)])
-def test_gemm_f32_tensor_core(shape):
+def test_gemm_f32_tensor_core(shape, gemm_impl):
     """The three layouts of the float32-accurate tensor-core GEMM (projection, input gradient, weight gradient with
     K cut into slices) against float64 products; tolerance 1e-5 of the largest entry (float32 rounding of a
     length-K sum)."""
     import torch
     rows, din, dout = shape
+    A.set_gemm_impl(gemm_impl)
     g = torch.Generator(device="cuda").manual_seed(rows)
     x = torch.randn(rows, din, device="cuda", generator=g)
     w = torch.randn(din, dout, device="cuda", generator=g)
@@ -509,3 +511,4 @@ def test_gemm_f32_tensor_core(shape):
         assert torch.equal(got, A.gemm_f32(x, dy, trans_a=True, split_k=split_k))      # repeatable bit for bit
     with pytest.raises(A.AgptError):
         A.gemm_f32(x, w.t().contiguous(), trans_a=True, trans_b=True)
+    A.set_gemm_impl(1)
