@@ -64,6 +64,30 @@ SIGNATURES = {
     "agpt_b200_layer_norm_fwd": (C.c_int, [vp] * 6 + [i64, C.c_int, vp]),
     "agpt_b200_layer_norm_bwd": (C.c_int, [vp] * 7 + [i64, C.c_int, vp, i64, vp]),
     "agpt_b200_layer_norm_bwd_workspace_bytes": (i64, [i64, C.c_int]),
+    "cuda_bias_add": (None, [vp, vp, C.c_int, C.c_int]),
+    "cuda_fused_bias_relu": (None, [vp] * 4 + [C.c_int, C.c_int]),
+    "cuda_relu_backward": (None, [vp] * 3 + [C.c_int]),
+    "cuda_softmax_rows": (None, [vp, vp, C.c_int, C.c_int]),
+    "cuda_softmax_backward": (None, [vp] * 3 + [C.c_int, C.c_int]),
+    "cuda_embedding_gather": (None, [vp] * 3 + [C.c_int, C.c_int]),
+    "cuda_embedding_scatter_add": (None, [vp] * 3 + [C.c_int, C.c_int]),
+    "agpt_b200_bias_act": (C.c_int, [vp] * 4 + [i64, C.c_int, C.c_int, vp]),
+    "agpt_b200_relu_bwd": (C.c_int, [vp] * 3 + [i64, vp]),
+    "agpt_b200_col_sum": (C.c_int, [vp] * 3 + [i64, C.c_int, f32, C.c_int, vp, vp, i64, vp]),
+    "agpt_b200_col_sum_workspace_bytes": (i64, [i64, C.c_int]),
+    "agpt_b200_softmax_rows": (C.c_int, [vp, vp, i64, C.c_int, vp]),
+    "agpt_b200_softmax_bwd": (C.c_int, [vp] * 3 + [i64, C.c_int, vp]),
+    "agpt_b200_embedding_gather": (C.c_int, [vp] * 3 + [i64, C.c_int, C.c_int, vp]),
+    "agpt_b200_embedding_grad": (C.c_int, [vp] * 3 + [i64, C.c_int, C.c_int, C.c_int, vp, i64, vp]),
+    "agpt_b200_embedding_grad_workspace_bytes": (i64, [i64, C.c_int, C.c_int]),
+    "cuda_adam_bulk": (None, [vp] * 4 + [f32] * 4 + [C.c_int, C.c_int]),
+    "cuda_sgd_bulk": (None, [vp, vp, f32, C.c_int]),
+    "cuda_momentum_bulk": (None, [vp] * 3 + [f32, f32, C.c_int]),
+    "cuda_rmsprop_bulk": (None, [vp] * 3 + [f32] * 3 + [C.c_int]),
+    "cuda_weight_decay": (None, [vp, f32, f32, C.c_int]),
+    "cuda_grad_clip_by_norm": (None, [vp, f32, C.c_int, vp, vp]),
+    "agpt_b200_optimizer_step": (C.c_int, [C.c_int] + [vp] * 4 + [i64] + [f32] * 4 + [C.c_int, f32, f32, C.c_int, vp, vp]),
+    "agpt_b200_optimizer_scratch_bytes": (i64, []),
     "agpt_b200_gemm_f32": (C.c_int, [C.c_int] * 5 + [f32, vp, C.c_int, vp, C.c_int, f32, vp, C.c_int, vp, C.c_int, C.c_int, vp, i64, vp]),
     "agpt_b200_gemm_f32_workspace_bytes": (i64, [C.c_int] * 6),
     "agpt_b200_set_gemm_impl": (C.c_int, [C.c_int]),

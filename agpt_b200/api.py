@@ -368,6 +368,112 @@ def attn_backward(plan: WalkerPlan, q, k, v, out, lse, dout, n_heads: int, scale
     return dq, dk, dv
 
 
+_scratch = {}
+
+
+def _workspace(device, key, nbytes):
+    """A per-device scratch tensor kept between calls (grown on demand)."""
+    import torch
+    t = _scratch.get((device.index, key))
+    if t is None or t.numel() < nbytes:
+        t = _scratch[(device.index, key)] = torch.empty(max(int(nbytes), 16), dtype=torch.uint8, device=device)
+    return t
+
+
+def bias_act(x, bias, relu=False, out=None, mask=None):
+    """out = x + bias, or max(x + bias, 0) with an optional 0/1 mask; out may be x itself."""
+    import torch
+    _chk_f32(x, "x")
+    _chk_f32(bias, "bias")
+    out = torch.empty_like(x) if out is None else out
+    check(lib().agpt_b200_bias_act(_dp(x), _dp(bias), _dp(out), _dp(mask), x.shape[0], x.shape[1], int(relu), _stream()), "bias_act")
+    return out
+
+
+def relu_backward(grad, mask, out=None):
+    import torch
+    _chk_f32(grad, "grad")
+    _chk_f32(mask, "mask")
+    out = torch.empty_like(grad) if out is None else out
+    check(lib().agpt_b200_relu_bwd(_dp(grad), _dp(mask), _dp(out), grad.numel(), _stream()), "relu_bwd")
+    return out
+
+
+def col_sum(grad, act=None, grad_out=None, out=None, scale=1.0, accumulate=False):
+    """Column sums of grad [rows, cols] (a bias gradient).  With act, grad is first masked by act > 0 and the
+    masked gradient is written to grad_out (default: in place).  Returns (sums, masked gradient or None)."""
+    import torch
+    _chk_f32(grad, "grad")
+    rows, cols = grad.shape
+    if act is not None:
+        _chk_f32(act, "act")
+        grad_out = grad if grad_out is None else grad_out
+    out = torch.zeros(cols, dtype=torch.float32, device=grad.device) if out is None else out
+    wsb = check(lib().agpt_b200_col_sum_workspace_bytes(rows, cols), "col_sum_workspace_bytes")
+    ws = _workspace(grad.device, "col_sum", wsb)
+    check(lib().agpt_b200_col_sum(_dp(grad), _dp(act), _dp(grad_out), rows, cols, scale, int(accumulate), _dp(out), _dp(ws), wsb,
+                                  _stream()), "col_sum")
+    return out, grad_out
+
+
+def softmax_rows(x):
+    import torch
+    _chk_f32(x, "x")
+    out = torch.empty_like(x)
+    check(lib().agpt_b200_softmax_rows(_dp(x), _dp(out), x.shape[0], x.shape[1], _stream()), "softmax_rows")
+    return out
+
+
+def softmax_backward(s, ds):
+    import torch
+    _chk_f32(s, "s")
+    _chk_f32(ds, "ds")
+    out = torch.empty_like(s)
+    check(lib().agpt_b200_softmax_bwd(_dp(s), _dp(ds), _dp(out), s.shape[0], s.shape[1], _stream()), "softmax_bwd")
+    return out
+
+
+def embedding_gather(emb, ids32):
+    import torch
+    _chk_f32(emb, "emb")
+    out = torch.empty((ids32.numel(), emb.shape[1]), dtype=torch.float32, device=emb.device)
+    check(lib().agpt_b200_embedding_gather(_dp(emb), _dp(ids32), _dp(out), ids32.numel(), emb.shape[1], emb.shape[0], _stream()),
+          "embedding_gather")
+    return out
+
+
+def embedding_grad(grad, ids32, vocab, out=None, accumulate=False):
+    """Gradient of the embedding table, [vocab, d_model], summed in a fixed order."""
+    import torch
+    _chk_f32(grad, "grad")
+    n, d = grad.shape
+    out = torch.zeros((vocab, d), dtype=torch.float32, device=grad.device) if out is None else out
+    wsb = check(lib().agpt_b200_embedding_grad_workspace_bytes(n, d, vocab), "embedding_grad_workspace_bytes")
+    ws = _workspace(grad.device, "embedding_grad", wsb)
+    check(lib().agpt_b200_embedding_grad(_dp(grad), _dp(ids32), _dp(out), n, d, vocab, int(accumulate), _dp(ws), wsb, _stream()),
+          "embedding_grad")
+    return out
+
+
+OPTIMIZER_KINDS = {"sgd": 0, "momentum": 1, "rmsprop": 2, "adam": 3}
+
+
+def optimizer_step(kind, params, grads, m=None, v=None, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, t=1, weight_decay=0.0,
+                   clip_norm=0.0, zero_grads=False):
+    """Clip, update and decay over flat float32 CUDA buffers, in place.  Returns the gradient norm tensor (one float)
+    when clipping is on, else None."""
+    import torch
+    _chk_f32(params, "params")
+    _chk_f32(grads, "grads")
+    scratch = None
+    if clip_norm > 0:
+        scratch = _workspace(params.device, "optimizer", lib().agpt_b200_optimizer_scratch_bytes())
+    check(lib().agpt_b200_optimizer_step(OPTIMIZER_KINDS[kind], _dp(params), _dp(grads), _dp(m), _dp(v), params.numel(), lr, beta1,
+                                         beta2, eps, t, weight_decay, clip_norm, int(zero_grads), _dp(scratch), _stream()),
+          "optimizer_step")
+    return scratch.view(torch.float32)[1024:1025] if scratch is not None else None
+
+
 def set_gemm_impl(impl: int) -> None:
     """0: mma.sync with three TF32 products; 1 (default): tcgen05 on bfloat16 splits."""
     check(lib().agpt_b200_set_gemm_impl(impl), "set_gemm_impl")

@@ -107,24 +107,19 @@ def _embedding_function():
     import torch
 
     class TokenEmbedding(torch.autograd.Function):
-        """Row gather whose backward is a one-hot GEMM: with a vocabulary of tens of symbols and millions of rows,
-        torch's index_put backward serialises on the collisions; onehot^T @ grad is a plain (and repeatable) GEMM."""
+        """Row gather; the gradient of the table is summed per symbol in a fixed order (with a vocabulary of tens of
+        symbols and millions of rows an index_put backward serialises on the collisions)."""
 
         @staticmethod
-        def forward(ctx, emb, tokens):
-            ctx.save_for_backward(tokens)
+        def forward(ctx, emb, tokens32):
+            ctx.save_for_backward(tokens32)
             ctx.vocab = emb.shape[0]
-            return emb.index_select(0, tokens)
+            return A.embedding_gather(emb, tokens32)
 
         @staticmethod
         def backward(ctx, grad):
-            (tokens,) = ctx.saved_tensors
-            out = torch.zeros((ctx.vocab, grad.shape[1]), dtype=grad.dtype, device=grad.device)
-            step = 1 << 20                                  # bound the transient one-hot matrix
-            for a in range(0, tokens.numel(), step):
-                oh = torch.nn.functional.one_hot(tokens[a:a + step], ctx.vocab).to(grad.dtype)
-                out.addmm_(oh.t(), grad[a:a + step])
-            return out, None
+            (tokens32,) = ctx.saved_tensors
+            return A.embedding_grad(grad.contiguous(), tokens32, ctx.vocab), None
 
     return TokenEmbedding
 
@@ -155,24 +150,33 @@ def _linear_function():
     import torch
 
     class TensorLinear(torch.autograd.Function):
-        """y = x @ w + b with the library's float32-accurate tensor-core GEMM; the weight gradient cuts the row
+        """y = x @ w + b (relu: max(., 0)) with the library's float32-accurate tensor-core GEMM.  Backward: the
+        ReLU mask and the bias gradient are one pass over the incoming gradient; the weight gradient cuts the row
         dimension into slices that are summed in a fixed order."""
 
         @staticmethod
-        def forward(ctx, x, w, b):
+        def forward(ctx, x, w, b, relu):
             x = x.contiguous()
-            ctx.save_for_backward(x, w)
-            return A.gemm_f32(x, w, bias=b)
+            y = A.gemm_f32(x, w, bias=b)
+            if relu:
+                y = torch.relu_(y)
+            ctx.relu = relu
+            ctx.save_for_backward(x, w, y if relu else None)
+            return y
 
         @staticmethod
         def backward(ctx, grad):
-            x, w = ctx.saved_tensors
+            x, w, y = ctx.saved_tensors
             grad = grad.contiguous()
+            if ctx.relu:
+                db, grad = A.col_sum(grad, act=y, grad_out=torch.empty_like(grad))
+            else:
+                db, _ = A.col_sum(grad)
             dx = A.gemm_f32(grad, w, trans_b=True)
-            tiles = -(-w.shape[0] // 128) * -(-w.shape[1] // 64)
-            split_k = max(1, min(x.shape[0] // 2048, -(-592 // tiles)))
+            tiles = -(-w.shape[0] // 128) * -(-w.shape[1] // 128)
+            split_k = max(1, min(x.shape[0] // 2048, -(-296 // tiles)))
             dw = A.gemm_f32(x, grad, trans_a=True, split_k=split_k)
-            return dx, dw, grad.sum(0)
+            return dx, dw, db, None
 
     return TensorLinear
 
@@ -185,9 +189,8 @@ def _attention_function():
 
         @staticmethod
         def forward(ctx, q, k, v, group, cos, sin, n_heads, bf16_store):
-            q = q.contiguous().clone()
-            k = k.contiguous().clone()
-            v = v.contiguous()
+            # q and k are rotated in place: they are fresh projection outputs that nothing else reads or saves
+            q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
             A.rope_(q, group.pos, cos, sin, n_heads)
             A.rope_(k, group.pos, cos, sin, n_heads)
             ks, vs = (A.kv_store_write_bf16(k), A.kv_store_write_bf16(v)) if bf16_store else (k, v)
@@ -214,7 +217,23 @@ class TrieWalkModel:
         import torch
         self.cfg = model
         self.device = device
-        self.params = {name: torch.from_numpy(a.copy()).to(device).requires_grad_(True) for name, a in model.mats}
+        # one flat weight buffer and one flat gradient buffer (the reference's d_weights / d_grads), each matrix on a
+        # 16-byte boundary; the gradient buffer ends with two floats for the epoch's loss sum and query count so that
+        # one all-reduce carries everything
+        offs, off = [], 0
+        for _, a in model.mats:
+            offs.append(off)
+            off += (a.size + 3) & ~3
+        self.n_flat = off
+        self.flat = torch.zeros(off, dtype=torch.float32, device=device)
+        self.flat_grad = torch.zeros(off + 4, dtype=torch.float32, device=device)
+        self.params = {}
+        for (name, a), o in zip(model.mats, offs):
+            p = self.flat[o:o + a.size].view(a.shape)
+            p.copy_(torch.from_numpy(np.ascontiguousarray(a)))
+            self.params[name] = p.requires_grad_(True)
+        self._offs = offs
+        self.bind_grads()
         hd = model.d_model // model.n_heads
         cos, sin = A.rope_table(model.seq_len, hd)
         self.cos, self.sin = torch.from_numpy(cos).to(device), torch.from_numpy(sin).to(device)
@@ -228,6 +247,13 @@ class TrieWalkModel:
     def parameters(self):
         return list(self.params.values())
 
+    def bind_grads(self):
+        """Make every parameter's .grad the matching slice of the flat gradient buffer (autograd accumulates in place)."""
+        for p, o in zip(self.params.values(), self._offs):
+            want = self.flat_grad[o:o + p.numel()].view(p.shape)
+            if p.grad is None or p.grad.data_ptr() != want.data_ptr():
+                p.grad = want
+
     def to_model_file(self) -> MF.Model:
         m = self.cfg
         out = MF.Model(m.d_model, m.n_heads, m.n_layers, m.d_ff, m.vocab, m.seq_len)
@@ -240,17 +266,17 @@ class TrieWalkModel:
         P, m = self.params, self.cfg
         ln = self.ln.apply
 
-        def lin(x, w, b):
+        def lin(x, w, b, relu=False):
             # the library GEMM needs 16-byte aligned rows; other widths (a vocabulary of 65) go to torch
             if self.dense_impl == "tensor" and w.shape[0] % 4 == 0 and w.shape[1] % 4 == 0:
-                return self.linear.apply(x, w, b)
-            return torch.addmm(b, x, w)
+                return self.linear.apply(x, w, b, relu)
+            y = torch.addmm(b, x, w)
+            return torch.relu(y) if relu else y
 
         def ffn(x, g2, b2, w1, b1, w2, bo):
-            h = torch.relu(lin(ln(x, g2, b2), w1, b1))
-            return x + lin(h, w2, bo)
+            return x + lin(lin(ln(x, g2, b2), w1, b1, True), w2, bo)
 
-        x = self.embed.apply(P["token_emb"], group.tokens)
+        x = self.embed.apply(P["token_emb"], group.tokens32)
         for l in range(m.n_layers):
             g = lambda n: P[f"layer{l}.{n}"]  # noqa: E731
             x1 = ln(x, g("ln1.gamma")[0], g("ln1.beta")[0])
@@ -265,9 +291,11 @@ class TrieWalkModel:
         return lin(xf, P["out.w"], P["out.b"][0])
 
     def group_step(self, group: LaunchGroup, counts, entropy_lambda=0.0, intermediate_weight=1.0, ce_only=False,
-                   bf16_store=False):
+                   bf16_store=False, sync=True):
         """Forward, loss and backward of one launch group; gradients accumulate into .grad.
-        Returns (sum of positive per-query losses, number of such queries)."""
+        Returns (sum of positive per-query losses, number of such queries): Python numbers, or with sync=False a
+        float32 device tensor of the two, so that the host does not wait for the device between groups."""
+        import torch
         logits = self.logits(group, bf16_store).contiguous()
         c_off, c_tok, c_val = counts
         loss, dlogits = A.loss_per_query(logits.detach(), group.q2n, group.qoff, group.rid, group.tokens32, c_off, c_tok,
@@ -276,15 +304,49 @@ class TrieWalkModel:
             loss = loss * group.trained
             dlogits = dlogits * group.trained[:, None]
         pos = loss > 0
-        n_trained = int(pos.sum().item())
-        loss_sum = float(loss[pos].sum().item())
-        scale = 1.0 / n_trained if n_trained > 0 else 0.0      # agpt_train.cu:4834
+        n_trained = pos.sum()
+        loss_sum = torch.where(pos, loss, torch.zeros_like(loss)).sum(dtype=torch.float64)
+        # every gradient of the group is scaled by 1 / (its trained queries) (src/cuda/agpt_train.cu:4834)
+        scale = torch.where(n_trained > 0, 1.0 / n_trained.clamp(min=1).to(torch.float32), torch.zeros((), device=loss.device))
         logits.backward(dlogits * scale)
-        return loss_sum, n_trained
+        if sync:
+            return float(loss_sum.item()), int(n_trained.item())
+        return torch.stack([loss_sum.to(torch.float32), n_trained.to(torch.float32)])
 
 
-def make_optimizer(name, params, lr, rmsprop_beta=0.999, adam_betas=(0.9, 0.999), momentum=0.9, eps=1e-8):
+class FlatOptimizer:
+    """The library's fused step (clip, update, decay, clear gradients) over the model's flat buffers."""
+
+    def __init__(self, model, kind, lr, beta1, beta2, eps, weight_decay=0.0, clip_norm=0.0):
+        import torch
+        self.model, self.kind, self.lr, self.beta1, self.beta2, self.eps = model, kind, lr, beta1, beta2, eps
+        self.weight_decay, self.clip_norm, self.t = weight_decay, clip_norm, 0
+        z = lambda: torch.zeros(model.n_flat, dtype=torch.float32, device=model.device)  # noqa: E731
+        self.m = z() if kind in ("momentum", "adam") else None
+        self.v = z() if kind in ("rmsprop", "adam") else None
+
+    def step(self):
+        self.t += 1
+        m = self.model
+        return A.optimizer_step(self.kind, m.flat, m.flat_grad[:m.n_flat], self.m, self.v, lr=self.lr, beta1=self.beta1,
+                                beta2=self.beta2, eps=self.eps, t=self.t, weight_decay=self.weight_decay,
+                                clip_norm=self.clip_norm, zero_grads=True)
+
+    def zero_grad(self, set_to_none=False):
+        self.model.flat_grad.zero_()
+
+
+def make_optimizer(name, model, lr, rmsprop_beta=0.999, adam_betas=(0.9, 0.999), momentum=0.9, eps=1e-8, weight_decay=0.0,
+                   clip_norm=0.0):
+    """Optimizer over a TrieWalkModel (the library's fused step) or, given a plain parameter list, torch's own."""
     import torch
+    if isinstance(model, TrieWalkModel):
+        beta1 = momentum if name == "momentum" else adam_betas[0]
+        beta2 = rmsprop_beta if name == "rmsprop" else adam_betas[1]
+        if name not in A.OPTIMIZER_KINDS:
+            raise ValueError(f"unknown optimizer {name}")
+        return FlatOptimizer(model, name, lr, beta1, beta2, eps, weight_decay, clip_norm)
+    params = model
     if name == "sgd":
         return torch.optim.SGD(params, lr=lr)
     if name == "momentum":
@@ -298,33 +360,22 @@ def make_optimizer(name, params, lr, rmsprop_beta=0.999, adam_betas=(0.9, 0.999)
 
 def train_epoch(model: TrieWalkModel, groups, counts, opt, accumulate=True, world=1, **loss_kw):
     """One sweep over every position of this rank's groups.  accumulate=True: gradients of all groups (and all
-    ranks) are summed and one optimizer step closes the epoch; False: one step per group (single rank only)."""
-    import torch
+    ranks) are summed and one optimizer step closes the epoch; False: one step per group (single rank only).
+    The loss sum and query count ride at the end of the flat gradient buffer: one all-reduce, one host read."""
     import torch.distributed as dist
-    total_loss, total_q = 0.0, 0
+    model.bind_grads()
     opt.zero_grad(set_to_none=False)
-    for p in model.parameters():
-        if p.grad is None:
-            p.grad = torch.zeros_like(p)
+    tail = model.flat_grad[model.n_flat:model.n_flat + 2]
     for g in groups:
-        ls, nq = model.group_step(g, counts, **loss_kw)
-        total_loss += ls
-        total_q += nq
+        tail += model.group_step(g, counts, sync=False, **loss_kw)
         if not accumulate:
-            opt.step()
-            opt.zero_grad(set_to_none=False)
+            opt.step()                       # clears the parameter gradients, not the two statistics behind them
     if accumulate:
         if world > 1:
-            flat = torch.cat([p.grad.reshape(-1) for p in model.parameters()] +
-                             [torch.tensor([total_loss, float(total_q)], device=model.device, dtype=torch.float32)])
-            dist.all_reduce(flat)
-            off = 0
-            for p in model.parameters():
-                p.grad.copy_(flat[off:off + p.numel()].view_as(p))
-                off += p.numel()
-            total_loss, total_q = float(flat[off].item()), int(round(float(flat[off + 1].item())))
+            dist.all_reduce(model.flat_grad)
         opt.step()
-    return total_loss, total_q
+    stats = tail.cpu()
+    return float(stats[0]), int(round(float(stats[1])))
 
 
 def main(argv=None):
@@ -339,6 +390,8 @@ def main(argv=None):
     ap.add_argument("--lr", type=float, default=3e-4)
     ap.add_argument("--optimizer", default="adam", choices=["sgd", "momentum", "rmsprop", "adam"])
     ap.add_argument("--rmsprop-beta", type=float, default=0.999)
+    ap.add_argument("--weight-decay", type=float, default=0.0)
+    ap.add_argument("--grad-clip-norm", type=float, default=0.0)
     ap.add_argument("--mass-weight", default="off", choices=["off", "log", "sqrt", "linear"])
     ap.add_argument("--entropy-lambda", type=float, default=0.0)
     ap.add_argument("--intermediate-weight", type=float, default=1.0)
@@ -368,7 +421,8 @@ def main(argv=None):
     counts = [torch.from_numpy(np.ascontiguousarray(c)).to(dev) for c in (trie.cnt_off.astype(np.int32), trie.cnt_tok, trie.cnt_val)]
     model = TrieWalkModel(mf, dev)
     model.ffn_recompute = args.ffn_recompute
-    opt = make_optimizer(args.optimizer, model.parameters(), args.lr, args.rmsprop_beta)
+    opt = make_optimizer(args.optimizer, model, args.lr, args.rmsprop_beta, weight_decay=args.weight_decay,
+                         clip_norm=args.grad_clip_norm)
     n_sub = int((trie.parent[1:] == 0).sum())
     save = args.save or args.model
     for ep in range(1, args.epochs + 1):

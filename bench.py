@@ -453,7 +453,7 @@ def run_epoch(args, cfg, rank, world, dev, log):
     groups, total = T.build_groups(trie, rank, world, args.epoch_group_rows, "linear", mf.seq_len, dev, level=2)
     counts = [torch.from_numpy(np.ascontiguousarray(c)).to(dev) for c in (trie.cnt_off.astype(np.int32), trie.cnt_tok, trie.cnt_val)]
     model = T.TrieWalkModel(mf, dev)
-    opt = T.make_optimizer("rmsprop", model.parameters(), 3e-4, 0.999)
+    opt = T.make_optimizer("rmsprop", model, 3e-4, 0.999)
     times, losses = [], []
     for ep in range(2):
         torch.cuda.synchronize()

@@ -221,6 +221,69 @@ int agpt_b200_layer_norm_bwd(const float *d_grad, const float *d_norm, const flo
                              int64_t workspace_bytes, void *stream);
 int64_t agpt_b200_layer_norm_bwd_workspace_bytes(int64_t rows, int cols);
 
+/* Replace the row-wise kernels of the reference's kernel dependency (declared src/cuda/agpt_train.cu:48-49,
+ * :56-63; called :4646, :4677-4683, :4754, :4768-4772, :4805, :4893, :5073) and its bias_grad_accum_kernel
+ * (:1774-1797).  Legacy symbols: void, default stream, 32-bit sizes, same argument order.
+ *   cuda_bias_add              data += bias (row broadcast), in place
+ *   cuda_fused_bias_relu       output = max(input + bias, 0); mask = 1.0 where output > 0 else 0.0 (output may alias input)
+ *   cuda_relu_backward         output = grad where mask > 0 else 0 (so the saved activation works as the mask too)
+ *   cuda_softmax_rows          row softmax;   cuda_softmax_backward   result = s * (ds - sum_c s*ds)
+ *   cuda_embedding_gather      output[i] = token_emb[ids[i]] (ids < 0 give a zero row)
+ *   cuda_embedding_scatter_add d_token_emb[ids[i]] += grad[i] with atomic adds (the vocabulary size is not an argument);
+ *                              agpt_b200_embedding_grad is the repeatable form. */
+void cuda_bias_add(float *data, const float *bias, int rows, int cols);
+void cuda_fused_bias_relu(const float *input, const float *bias, float *output, float *mask, int rows, int cols);
+void cuda_relu_backward(const float *grad, const float *mask, float *output, int n);
+void cuda_softmax_rows(const float *input, float *output, int rows, int cols);
+void cuda_softmax_backward(const float *s, const float *ds, float *result, int rows, int cols);
+void cuda_embedding_gather(const float *token_emb, const int *ids, float *output, int seq_len, int d_model);
+void cuda_embedding_scatter_add(const float *grad, const int *ids, float *d_token_emb, int seq_len, int d_model);
+/* Native forms with a stream and 64-bit row counts.  bias_act: relu != 0 selects bias + ReLU, d_mask may be NULL.
+ * col_sum: d_out[c] = (accumulate ? d_out[c] : 0) + scale * sum_r g[r][c], the bias gradient; with d_act != NULL the
+ * gradient is first masked by d_act > 0 and the masked gradient written to d_grad_out (may alias d_grad): ReLU
+ * backward and the bias gradient of the layer below it in one pass.  embedding_grad: the gradient of the embedding
+ * table from per-block partial tables added in a fixed order (vocab up to 400).  Both reductions repeat bit for bit. */
+int agpt_b200_bias_act(const float *d_in, const float *d_bias, float *d_out, float *d_mask, int64_t rows, int cols,
+                       int relu, void *stream);
+int agpt_b200_relu_bwd(const float *d_grad, const float *d_mask, float *d_out, int64_t n, void *stream);
+int agpt_b200_col_sum(const float *d_grad, const float *d_act, float *d_grad_out, int64_t rows, int cols, float scale,
+                      int accumulate, float *d_out, void *d_workspace, int64_t workspace_bytes, void *stream);
+int64_t agpt_b200_col_sum_workspace_bytes(int64_t rows, int cols);
+int agpt_b200_softmax_rows(const float *d_in, float *d_out, int64_t rows, int cols, void *stream);
+int agpt_b200_softmax_bwd(const float *d_s, const float *d_ds, float *d_out, int64_t rows, int cols, void *stream);
+int agpt_b200_embedding_gather(const float *d_emb, const int32_t *d_ids, float *d_out, int64_t n, int d_model,
+                               int vocab, void *stream);
+int agpt_b200_embedding_grad(const float *d_grad, const int32_t *d_ids, float *d_emb_grad, int64_t n, int d_model,
+                             int vocab, int accumulate, void *d_workspace, int64_t workspace_bytes, void *stream);
+int64_t agpt_b200_embedding_grad_workspace_bytes(int64_t n, int d_model, int vocab);
+
+/* Replace the optimizer kernels of the reference's kernel dependency (declared src/cuda/agpt_train.cu:64-72;
+ * called in the order clip, update, decay at :5135-5162 and :5190-5214).  The dependency's source is not part of
+ * the reference; the rules implemented are
+ *   sgd p -= lr*g;   momentum m = beta*m + g, p -= lr*m;   rmsprop s = beta*s + (1-beta)*g*g, p -= lr*g/(sqrt(s)+eps);
+ *   adam m = b1*m + (1-b1)*g, v = b2*v + (1-b2)*g*g, p -= lr*(m/(1-b1^t))/(sqrt(v/(1-b2^t))+eps), t from 1;
+ *   weight decay p -= lr*wd*p;   clip g *= max_norm/||g|| when ||g|| > max_norm (norm_scratch[0] receives ||g||;
+ *   partials_scratch holds ceil(n/256) floats as the reference allocates, at most 1024 are used). */
+void cuda_adam_bulk(float *params, float *grads, float *m, float *v, float lr, float beta1, float beta2, float eps,
+                    int t, int n);
+void cuda_sgd_bulk(float *params, float *grads, float lr, int n);
+void cuda_momentum_bulk(float *params, float *grads, float *m, float lr, float beta, int n);
+void cuda_rmsprop_bulk(float *params, float *grads, float *s, float lr, float beta, float eps, int n);
+void cuda_weight_decay(float *params, float lr, float wd, int n);
+void cuda_grad_clip_by_norm(float *grads, float max_norm, int n, float *partials_scratch, float *norm_scratch);
+/* The whole step in two launches over the flat buffers: clip (clip_norm > 0; needs d_scratch of
+ * agpt_b200_optimizer_scratch_bytes(), whose last float receives the gradient norm), update by `kind`, decay
+ * (weight_decay > 0), and clearing of the gradients (zero_grads != 0).  beta1 is the momentum / first-moment
+ * coefficient, beta2 the RMSProp / second-moment coefficient. */
+#define AGPT_OPT_SGD 0
+#define AGPT_OPT_MOMENTUM 1
+#define AGPT_OPT_RMSPROP 2
+#define AGPT_OPT_ADAM 3
+int agpt_b200_optimizer_step(int kind, float *d_params, float *d_grads, float *d_m, float *d_v, int64_t n, float lr,
+                             float beta1, float beta2, float eps, int t, float weight_decay, float clip_norm,
+                             int zero_grads, void *d_scratch, void *stream);
+int64_t agpt_b200_optimizer_scratch_bytes(void);
+
 /* Replaces the cublasSgemm calls of the dense projections (src/cuda/agpt_train.cu:4675-4683, :4752, :4766-4771,
  * :4803, :4840-5061) with a tensor-core GEMM of float32-level accuracy (three TF32 MMAs per product).  Row-major:
  *     out[M, N] = alpha * op(A)[M, K] * op(B)[K, N] + beta * C

@@ -387,3 +387,73 @@ def set_num_threads(n: int) -> None:
 
 def num_threads() -> int:
     return int(lib().orc_num_threads())
+
+
+# ---- dense-step row kernels and optimizer rules (numpy restatements; float32 arithmetic) ------------------------------
+# Follow the reference's CPU statements of the same steps: bias add and ReLU of the feed-forward block
+# (src/agpt/incremental_forward.cr:165-217), the bias gradient as a column sum (src/cuda/agpt_train.cu:1771-1790),
+# softmax backward s*(ds - sum s*ds) (src/agpt/batched_depth_backward.cr:605-695 uses the same identity per head),
+# and the optimizer call order clip -> update -> decay (src/cuda/agpt_train.cu:5135-5162).
+
+def bias_relu(x, bias, relu):
+    y = (f32(x) + f32(bias)[None, :]).astype(np.float32)
+    if not relu:
+        return y, None
+    return np.maximum(y, np.float32(0)), (y > 0).astype(np.float32)
+
+
+def relu_bwd(grad, mask):
+    return np.where(f32(mask) > 0, f32(grad), np.float32(0)).astype(np.float32)
+
+
+def col_sum(grad):
+    return f32(grad).astype(np.float64).sum(axis=0)
+
+
+def softmax_rows(x):
+    x = f32(x).astype(np.float64)
+    e = np.exp(x - x.max(axis=1, keepdims=True))
+    return e / e.sum(axis=1, keepdims=True)
+
+
+def softmax_bwd(s, ds):
+    s, ds = f32(s).astype(np.float64), f32(ds).astype(np.float64)
+    return s * (ds - (s * ds).sum(axis=1, keepdims=True))
+
+
+def embedding_grad(grad, ids, vocab):
+    out = np.zeros((vocab, grad.shape[1]), np.float64)
+    np.add.at(out, np.asarray(ids)[np.asarray(ids) >= 0], f32(grad).astype(np.float64)[np.asarray(ids) >= 0])
+    return out
+
+
+def optimizer_step(kind, p, g, m, v, lr, beta1, beta2, eps, t, weight_decay=0.0, clip_norm=0.0):
+    """One step in float32, element by element as the kernels do.  Returns (p, m, v, gradient norm)."""
+    one = np.float32(1)
+    p, g = f32(p).copy(), f32(g).copy()
+    m = None if m is None else f32(m).copy()
+    v = None if v is None else f32(v).copy()
+    lr, beta1, beta2, eps = np.float32(lr), np.float32(beta1), np.float32(beta2), np.float32(eps)
+    norm = float(np.sqrt((g.astype(np.float64) ** 2).sum()))
+    if clip_norm > 0 and norm > clip_norm:
+        g = (g * np.float32(clip_norm / norm)).astype(np.float32)
+    if kind == "sgd":
+        p = p - lr * g
+    elif kind == "momentum":
+        m = beta1 * m + g
+        p = p - lr * m
+    elif kind == "rmsprop":
+        v = beta2 * v + (one - beta2) * g * g
+        p = p - lr * g / (np.sqrt(v) + eps)
+    elif kind == "adam":
+        m = beta1 * m + (one - beta1) * g
+        v = beta2 * v + (one - beta2) * g * g
+        bc1 = one - np.float32(np.float32(beta1) ** np.float32(t))
+        bc2 = one - np.float32(np.float32(beta2) ** np.float32(t))
+        p = p - lr * (m / bc1) / (np.sqrt(v / bc2) + eps)
+    else:
+        raise ValueError(kind)
+    p = p.astype(np.float32)
+    if weight_decay > 0:
+        p = (p - lr * np.float32(weight_decay) * p).astype(np.float32)
+    return p, m, v, norm

@@ -124,3 +124,32 @@ def test_training_lowers_loss_and_round_trips_model(cuda, tmp_path):
     changed = [n for (n, a), (_, b) in zip(mf.mats, new.mats) if not np.array_equal(a, b)]
     assert len(changed) == len(mf.mats)          # every weight matrix moved (the reference's own fundamentals test)
     del torch
+
+
+@pytest.mark.parametrize("name", ["sgd", "momentum", "rmsprop", "adam"])
+def test_flat_optimizer_matches_torch(cuda, name):
+    """Two accumulated epochs with the library's fused step move the weights as torch's optimizer of the same
+    rule does from the same gradients (1e-5 of the largest weight)."""
+    import torch
+    corpus = A.synth_markov_corpus(600, 12, 2, 9)
+    trie = A.RadixTrie.build(corpus, 6)
+    mf = MF.random_init(32, 2, 1, 12, 16, seed=4, std=0.2)
+    counts = [torch.from_numpy(np.ascontiguousarray(c)).to(cuda) for c in (trie.cnt_off.astype(np.int32), trie.cnt_tok, trie.cnt_val)]
+    groups, _ = T.build_groups(trie, 0, 1, 100000, "off", mf.seq_len, cuda)
+    model = T.TrieWalkModel(mf, cuda)
+    opt = T.make_optimizer(name, model, 1e-2)
+    assert isinstance(opt, T.FlatOptimizer)
+    shadow = [p.detach().clone().requires_grad_(True) for p in model.parameters()]
+    topt = T.make_optimizer(name, shadow, 1e-2)
+    for _ in range(2):
+        model.bind_grads()
+        opt.zero_grad()
+        for g in groups:
+            model.group_step(g, counts)
+        for sp, p in zip(shadow, model.parameters()):
+            sp.grad = p.grad.clone()
+        opt.step()
+        topt.step()
+        assert float(model.flat_grad[:model.n_flat].abs().max()) == 0.0
+        for sp, p in zip(shadow, model.parameters()):
+            assert float((sp - p).abs().max()) < 1e-5 * max(1.0, float(p.abs().max()))
