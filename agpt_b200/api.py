@@ -474,6 +474,13 @@ def optimizer_step(kind, params, grads, m=None, v=None, lr=1e-3, beta1=0.9, beta
     return scratch.view(torch.float32)[1024:1025] if scratch is not None else None
 
 
+def device_status() -> int:
+    """The current GPU's status word (0 = every kernel ran to completion); synchronises."""
+    out = C.c_int32(0)
+    check(lib().agpt_b200_device_status(C.byref(out)), "device_status")
+    return int(out.value)
+
+
 def set_gemm_impl(impl: int) -> None:
     """0: mma.sync with three TF32 products; 1 (default): tcgen05 on bfloat16 splits."""
     check(lib().agpt_b200_set_gemm_impl(impl), "set_gemm_impl")

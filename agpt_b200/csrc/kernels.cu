@@ -382,8 +382,9 @@ __global__ void __launch_bounds__(128) attn_fwd_mma_kernel(const float *__restri
                     tf32_split(b0, h0, lo0); tf32_split(b1, h1, lo1);
                     mma_tf32(c, qh[ks], h0, h1); mma_tf32(c, ql[ks], h0, h1); mma_tf32(c, qh[ks], lo0, lo1);
                 } else {
+                    // bf16 store: K is exact in TF32 and the store's own rounding (2^-9) dwarfs TF32's (2^-11) on Q,
+                    // so one product is enough for the bf16-store tolerance
                     mma_tf32(c, qh[ks], __float_as_uint(b0), __float_as_uint(b1));
-                    mma_tf32(c, ql[ks], __float_as_uint(b0), __float_as_uint(b1));
                 }
             }
             if (v0) s[nb][0] = c[0];
@@ -427,7 +428,6 @@ __global__ void __launch_bounds__(128) attn_fwd_mma_kernel(const float *__restri
                     mma_tf32(o[db], ph, h0, h1); mma_tf32(o[db], pl, h0, h1); mma_tf32(o[db], ph, lo0, lo1);
                 } else {
                     mma_tf32(o[db], ph, __float_as_uint(b0), __float_as_uint(b1));
-                    mma_tf32(o[db], pl, __float_as_uint(b0), __float_as_uint(b1));
                 }
             }
         }
@@ -740,10 +740,9 @@ __global__ void __launch_bounds__(128, HD <= 32 ? 4 : 1) attn_bwd_mma_kernel(con
                             mma_tf32(c[u], ql[ks], h0, h1); mma_tf32(e[u], gl[ks], x0, x1);
                             mma_tf32(c[u], qh[ks], lo0, lo1); mma_tf32(e[u], gh[ks], y0, y1);
                         } else {
+                            // bf16 store: single TF32 products throughout (see the forward kernel)
                             mma_tf32(c[u], qh[ks], __float_as_uint(k0), __float_as_uint(k1));
                             mma_tf32(e[u], gh[ks], __float_as_uint(w0), __float_as_uint(w1));
-                            mma_tf32(c[u], ql[ks], __float_as_uint(k0), __float_as_uint(k1));
-                            mma_tf32(e[u], gl[ks], __float_as_uint(w0), __float_as_uint(w1));
                         }
                     }
                 }
@@ -770,7 +769,6 @@ __global__ void __launch_bounds__(128, HD <= 32 ? 4 : 1) attn_bwd_mma_kernel(con
                             mma_tf32(dq[db], ah, h0, h1); mma_tf32(dq[db], al, h0, h1); mma_tf32(dq[db], ah, lo0, lo1);
                         } else {
                             mma_tf32(dq[db], ah, __float_as_uint(b0), __float_as_uint(b1));
-                            mma_tf32(dq[db], al, __float_as_uint(b0), __float_as_uint(b1));
                         }
                     }
                 }
@@ -805,9 +803,11 @@ __global__ void __launch_bounds__(128, HD <= 32 ? 4 : 1) attn_bwd_mma_kernel(con
                     if ((db0 + j) * 8 >= HD) continue;
                     uint32_t h0, lo0, h1, lo1;
                     tf32_split(S.sQ[qa][dcol], h0, lo0); tf32_split(S.sQ[qa + 4][dcol], h1, lo1);
-                    mma_tf32(ak[j], sh, h0, h1); mma_tf32(ak[j], sl, h0, h1); mma_tf32(ak[j], sh, lo0, lo1);
+                    mma_tf32(ak[j], sh, h0, h1);
+                    if (SPLIT_KV) { mma_tf32(ak[j], sl, h0, h1); mma_tf32(ak[j], sh, lo0, lo1); }
                     tf32_split(S.sG[qa][dcol], h0, lo0); tf32_split(S.sG[qa + 4][dcol], h1, lo1);
-                    mma_tf32(av[j], ph, h0, h1); mma_tf32(av[j], pl, h0, h1); mma_tf32(av[j], ph, lo0, lo1);
+                    mma_tf32(av[j], ph, h0, h1);
+                    if (SPLIT_KV) { mma_tf32(av[j], pl, h0, h1); mma_tf32(av[j], ph, lo0, lo1); }
                 }
             }
 #pragma unroll
@@ -1162,11 +1162,15 @@ __device__ __forceinline__ int warp_sum_i(int v) {
 }
 
 // mode 0: per-query (radix); mode 1: per-node (leveled, node_ids index the counts).
-// One warp per row.  NPL > 0: the row (V <= 32*NPL) lives in registers, lane l owning columns l, l+32, ...;
-// shared memory is touched only by rows that end a radix edge (sparse count lookups).  NPL == 0: any V, the row
-// lives in shared memory.  Either way every logit is read once, exponentiated once, and every gradient element
-// written once.
+// One warp per batch of 32 consecutive rows.  The index loads of a row form a dependent chain (query -> node ->
+// offsets -> counts) several memory latencies long; lane l walks the chain of row l of the batch, so the 32 chains
+// are in flight together and their loads coalesce, and the row loop then takes each row's indices from its lane
+// by shuffle.  The logits of row k+1 are requested before row k is reduced.  NPL > 0: a row (V <= 32*NPL) lives
+// in registers, lane l owning columns l, l+32, ...; shared memory is touched only by rows that end a radix edge
+// (sparse count lookups).  NPL == 0: any V, the row lives in shared memory.  Either way every logit is read once,
+// exponentiated once, and every gradient element written once.
 #define LOSS_WPB 8
+#define LOSS_ROWS_PER_BLOCK (LOSS_WPB * 32)
 template <int NPL>
 __global__ void __launch_bounds__(LOSS_WPB * 32, 8)
 loss_kernel(const float *__restrict__ logits, const int32_t *__restrict__ query_to_node,
@@ -1176,141 +1180,336 @@ loss_kernel(const float *__restrict__ logits, const int32_t *__restrict__ query_
             const float *__restrict__ mass_weights, float *__restrict__ d_logits, float *__restrict__ loss_out,
             int64_t T_q, int V, float entropy_lambda, float intermediate_weight, int ce_only, int mode) {
     extern __shared__ float s_rows[];
-    int64_t qi = (int64_t)blockIdx.x * LOSS_WPB + (threadIdx.x >> 5);
-    if (qi >= T_q) return;
+    const int64_t r0 = ((int64_t)blockIdx.x * LOSS_WPB + (threadIdx.x >> 5)) * 32;
+    if (r0 >= T_q) return;
+    const int nrows = (T_q - r0 < 32) ? (int)(T_q - r0) : 32;
     const int lane = threadIdx.x & 31;
     float *row = s_rows + (threadIdx.x >> 5) * V;
-    const float *in = logits + qi * V;
-    float *g = d_logits + qi * V;
-    // the index loads form a dependent chain (query -> node -> offsets); they are issued before the row is read so
-    // that their latency overlaps the row's
-    bool endpoint_path;
-    int cid = 0;
-    if (mode == 1) { endpoint_path = true; cid = ids[qi]; }
-    else {
-        int n_idx = query_to_node[qi];
-        bool is_endpoint = (qi + 1) == query_offsets[n_idx + 1];
-        bool ce_as_intermediate = ce_only && is_endpoint && (qi + 1 < T_q);
-        endpoint_path = is_endpoint && !ce_as_intermediate;
-        if (endpoint_path) cid = ids[n_idx];
-    }
-    int target = 0, c_start = 0, c_end = 0;
-    float mass_w = 1.0f;
-    if (endpoint_path) { c_start = counts_offset[cid]; c_end = counts_offset[cid + 1]; }
-    else target = token_ids[qi + 1];
-    if (mode == 0 && mass_weights) mass_w = mass_weights[qi];
     constexpr int NR = NPL > 0 ? NPL : 1;
-    float x[NR];
-    float mx = -3.402823466e+38f, sum = 0.f;
+    constexpr float NEG = -3.402823466e+38f;
+
+    // lane-parallel index chains of the batch
+    int my_ep = 0, my_target = 0, my_cs = 0, my_ce = 0;
+    float my_mw = 1.0f;
+    if (lane < nrows) {
+        const int64_t qi = r0 + lane;
+        bool endpoint_path;
+        int cid = 0;
+        if (mode == 1) { endpoint_path = true; cid = ids[qi]; }
+        else {
+            int n_idx = query_to_node[qi];
+            bool is_endpoint = (qi + 1) == query_offsets[n_idx + 1];
+            bool ce_as_intermediate = ce_only && is_endpoint && (qi + 1 < T_q);
+            endpoint_path = is_endpoint && !ce_as_intermediate;
+            if (endpoint_path) cid = ids[n_idx];
+        }
+        if (endpoint_path) { my_cs = counts_offset[cid]; my_ce = counts_offset[cid + 1]; }
+        else my_target = token_ids[qi + 1];
+        if (mode == 0 && mass_weights) my_mw = mass_weights[qi];
+        my_ep = endpoint_path ? 1 : 0;
+    }
+
+    float xn[NR];
     if (NPL > 0) {
 #pragma unroll
-        for (int k = 0; k < NR; k++) {
-            const int j = lane + 32 * k;
-            x[k] = j < V ? __ldcs(in + j) : -3.402823466e+38f;
-            mx = fmaxf(mx, x[k]);
-        }
-        mx = warp_max(mx);
-#pragma unroll
-        for (int k = 0; k < NR; k++) { x[k] = lane + 32 * k < V ? expf(x[k] - mx) : 0.f; sum += x[k]; }
-        sum = warp_sum(sum);
-        const float inv = 1.0f / sum;
-#pragma unroll
-        for (int k = 0; k < NR; k++) x[k] *= inv;                  // probabilities
-    } else {
-        for (int j = lane; j < V; j += 32) { float v = __ldcs(in + j); row[j] = v; mx = fmaxf(mx, v); }
-        mx = warp_max(mx);
-        for (int j = lane; j < V; j += 32) { float e = expf(row[j] - mx); row[j] = e; sum += e; }
-        sum = warp_sum(sum);
-        const float inv = 1.0f / sum;
-        for (int j = lane; j < V; j += 32) row[j] *= inv;
-        __syncwarp();
+        for (int k = 0; k < NR; k++) { const int j = lane + 32 * k; xn[k] = j < V ? __ldcs(logits + r0 * V + j) : NEG; }
     }
-    // probability of one column, the same for every lane
-    auto prob_of = [&](int col) -> float {
+    for (int rr = 0; rr < nrows; rr++) {
+        const int64_t qi = r0 + rr;
+        const float *in = logits + qi * V;
+        float *g = d_logits + qi * V;
+        const bool endpoint_path = __shfl_sync(0xffffffffu, my_ep, rr) != 0;
+        const int c_start = __shfl_sync(0xffffffffu, my_cs, rr), c_end = __shfl_sync(0xffffffffu, my_ce, rr);
+        int target = __shfl_sync(0xffffffffu, my_target, rr);
+        const float mass_w = __shfl_sync(0xffffffffu, my_mw, rr);
+        float x[NR];
+        float mx = NEG, sum = 0.f;
         if (NPL > 0) {
-            float v = 0.f;
 #pragma unroll
-            for (int k = 0; k < NR; k++) { float t = __shfl_sync(0xffffffffu, x[k], col & 31); if (k == (col >> 5)) v = t; }
-            return v;
-        }
-        return row[col];
-    };
-
-    float weight = 1.0f, loss = 0.f;
-    if (endpoint_path) {
-        const int start = c_start, end = c_end;
-        if (start != end) {
-            if (NPL > 0) {                       // sparse lookups go through shared memory
+            for (int k = 0; k < NR; k++) { x[k] = xn[k]; mx = fmaxf(mx, x[k]); }
+            if (rr + 1 < nrows) {
 #pragma unroll
-                for (int k = 0; k < NR; k++) if (lane + 32 * k < V) row[lane + 32 * k] = x[k];
-                __syncwarp();
+                for (int k = 0; k < NR; k++) { const int j = lane + 32 * k; xn[k] = j < V ? __ldcs(in + V + j) : NEG; }
             }
-            int total = 0;
-            for (int e = start + lane; e < end; e += 32) total += counts_val[e];
-            total = warp_sum_i(total);
-            const float total_f = (float)total;
-            if (mode == 0) {
-                if (entropy_lambda > 0.0f && (end - start) > 1) {
-                    float Hh = 0.f;
-                    for (int e = start + lane; e < end; e += 32) {
-                        float qe = counts_val[e] / total_f;
-                        if (qe > 0.f) Hh -= qe * logf(qe);
-                    }
-                    Hh = warp_sum(Hh);
-                    weight = 1.0f + entropy_lambda * (Hh / logf((float)V));
-                }
-                if (mass_weights) weight *= mass_w;
-            }
-            for (int e = start + lane; e < end; e += 32) {
-                int tok = counts_tok[e];
-                if ((unsigned)tok >= (unsigned)V) continue;      // a token outside the vocabulary is ignored, not written
-                float tgt = counts_val[e] / total_f;
-                float pr = row[tok];
-                loss -= tgt * logf(pr + 1e-10f);
-                row[tok] = pr - tgt;                             // tokens of one node are distinct
-            }
-            loss = warp_sum(loss) * weight;
+            mx = warp_max(mx);
+#pragma unroll
+            for (int k = 0; k < NR; k++) { x[k] = lane + 32 * k < V ? expf(x[k] - mx) : 0.f; sum += x[k]; }
+            sum = warp_sum(sum);
+            const float inv = 1.0f / sum;
+#pragma unroll
+            for (int k = 0; k < NR; k++) x[k] *= inv;                  // probabilities
+        } else {
+            for (int j = lane; j < V; j += 32) { float v = __ldcs(in + j); row[j] = v; mx = fmaxf(mx, v); }
+            mx = warp_max(mx);
+            for (int j = lane; j < V; j += 32) { float e = expf(row[j] - mx); row[j] = e; sum += e; }
+            sum = warp_sum(sum);
+            const float inv = 1.0f / sum;
+            for (int j = lane; j < V; j += 32) row[j] *= inv;
             __syncwarp();
+        }
+        // probability of one column, the same for every lane
+        auto prob_of = [&](int col) -> float {
+            if (NPL > 0) {
+                float v = 0.f;
+#pragma unroll
+                for (int k = 0; k < NR; k++) { float t = __shfl_sync(0xffffffffu, x[k], col & 31); if (k == (col >> 5)) v = t; }
+                return v;
+            }
+            return row[col];
+        };
+
+        float weight = 1.0f, loss = 0.f;
+        if (endpoint_path) {
+            const int start = c_start, end = c_end;
+            if (start != end) {
+                if (NPL > 0) {                       // sparse lookups go through shared memory
+#pragma unroll
+                    for (int k = 0; k < NR; k++) if (lane + 32 * k < V) row[lane + 32 * k] = x[k];
+                    __syncwarp();
+                }
+                int total = 0;
+                for (int e = start + lane; e < end; e += 32) total += counts_val[e];
+                total = warp_sum_i(total);
+                const float total_f = (float)total;
+                if (mode == 0) {
+                    if (entropy_lambda > 0.0f && (end - start) > 1) {
+                        float Hh = 0.f;
+                        for (int e = start + lane; e < end; e += 32) {
+                            float qe = counts_val[e] / total_f;
+                            if (qe > 0.f) Hh -= qe * logf(qe);
+                        }
+                        Hh = warp_sum(Hh);
+                        weight = 1.0f + entropy_lambda * (Hh / logf((float)V));
+                    }
+                    if (mass_weights) weight *= mass_w;
+                }
+                for (int e = start + lane; e < end; e += 32) {
+                    int tok = counts_tok[e];
+                    if ((unsigned)tok >= (unsigned)V) continue;      // a token outside the vocabulary is ignored, not written
+                    float tgt = counts_val[e] / total_f;
+                    float pr = row[tok];
+                    loss -= tgt * logf(pr + 1e-10f);
+                    row[tok] = pr - tgt;                             // tokens of one node are distinct
+                }
+                loss = warp_sum(loss) * weight;
+                __syncwarp();
+                if (NPL > 0) {
+#pragma unroll
+                    for (int k = 0; k < NR; k++) if (lane + 32 * k < V) x[k] = row[lane + 32 * k];
+                }
+            }
+            // else: no observed continuation -- zero loss, and the row keeps the plain probabilities
+        } else {
+            if ((unsigned)target >= (unsigned)V) target = 0;         // never index outside the row
+            weight = intermediate_weight;
+            if (mass_weights) weight *= mass_w;
+            const float pr = prob_of(target);
+            loss = -logf(pr + 1e-10f) * weight;
             if (NPL > 0) {
 #pragma unroll
-                for (int k = 0; k < NR; k++) if (lane + 32 * k < V) x[k] = row[lane + 32 * k];
+                for (int k = 0; k < NR; k++) if (lane + 32 * k == target) x[k] -= 1.0f;
+            } else {
+                __syncwarp();
+                if (lane == 0) row[target] = pr - 1.0f;
             }
         }
-        // else: no observed continuation -- zero loss, and the row keeps the plain probabilities
-    } else {
-        if ((unsigned)target >= (unsigned)V) target = 0;         // never index outside the row
-        weight = intermediate_weight;
-        if (mass_weights) weight *= mass_w;
-        const float pr = prob_of(target);
-        loss = -logf(pr + 1e-10f) * weight;
         if (NPL > 0) {
 #pragma unroll
-            for (int k = 0; k < NR; k++) if (lane + 32 * k == target) x[k] -= 1.0f;
+            for (int k = 0; k < NR; k++) if (lane + 32 * k < V) __stcs(g + lane + 32 * k, x[k] * weight);
+            __syncwarp();                            // the next row may reuse the shared row
         } else {
             __syncwarp();
-            if (lane == 0) row[target] = pr - 1.0f;
+            for (int j = lane; j < V; j += 32) __stcs(g + j, row[j] * weight);
+            __syncwarp();
         }
+        if (lane == 0) loss_out[qi] = loss;
     }
-    if (NPL > 0) {
-#pragma unroll
-        for (int k = 0; k < NR; k++) if (lane + 32 * k < V) __stcs(g + lane + 32 * k, x[k] * weight);
+}
+
+// ---- batch form of the loss (V <= 256): one warp per 32 consecutive rows, one lane per row ------------------------
+// The 32 rows of a batch are contiguous in memory (32*V floats, a multiple of 128 bytes), so the warp brings them
+// into shared memory with ONE bulk asynchronous copy (cp.async.bulk, completion on an mbarrier) and writes the
+// gradient rows back with one bulk store: full-line traffic although single rows (260 bytes at V = 65) straddle
+// sectors, and the whole batch is in flight at once.  While the copy runs, lane l walks the dependent index chain
+// of row l.  Then lane l owns row l: maximum, exponentials and sum, scaling -- three sweeps over its row in shared
+// memory (column order skewed by the lane when V is even, so that the 32 lanes hit 32 banks), no shuffles.  The
+// sparse count entries of an endpoint row are applied by its lane.  The wait on the mbarrier is bounded: if it ran
+// out the warp sets bit 0 of the device status word and returns without storing.
+__device__ int g_device_status = 0;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+#define LOSSB_WARPS 4
+#define LOSSB_WAIT_LIMIT (1 << 22)
+__global__ void __launch_bounds__(LOSSB_WARPS * 32)
+loss_batch_kernel(const float *__restrict__ logits, const int32_t *__restrict__ query_to_node,
+                  const int32_t *__restrict__ query_offsets, const int32_t *__restrict__ ids,
+                  const int32_t *__restrict__ token_ids, const int32_t *__restrict__ counts_offset,
+                  const int32_t *__restrict__ counts_tok, const int32_t *__restrict__ counts_val,
+                  const float *__restrict__ mass_weights, float *__restrict__ d_logits, float *__restrict__ loss_out,
+                  int64_t T_q, int V, float entropy_lambda, float intermediate_weight, int ce_only, int mode, int aligned16) {
+    extern __shared__ __align__(128) unsigned char lossb_smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t r0 = ((int64_t)blockIdx.x * LOSSB_WARPS + warp) * 32;
+    if (r0 >= T_q) return;                                  // whole warp; warps of a block never synchronise with each other
+    const int nrows = (T_q - r0 < 32) ? (int)(T_q - r0) : 32;
+    float *tile = reinterpret_cast<float *>(lossb_smem) + (size_t)warp * 32 * V;
+    uint64_t *bar = reinterpret_cast<uint64_t *>(lossb_smem + (size_t)LOSSB_WARPS * 32 * V * sizeof(float)) + warp;
+    const uint32_t bytes = (uint32_t)nrows * V * sizeof(float);
+    const bool bulk = aligned16 && (bytes & 15u) == 0;
+    const float *src = logits + r0 * V;
+    float *dst = d_logits + r0 * V;
+    if (bulk) {
+        if (lane == 0) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(bar)));
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(tile)),
+                         "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                         : "memory");
+        }
+    } else {
+        for (int i = lane; i < nrows * V; i += 32) tile[i] = __ldcs(src + i);
+    }
+
+    // the row's index chain (query -> node -> offsets), 32 chains in flight per warp
+    bool endpoint_path = false;
+    int target = 0, c_start = 0, c_end = 0;
+    float mass_w = 1.0f;
+    const int64_t qi = r0 + lane;
+    if (lane < nrows) {
+        int cid = 0;
+        if (mode == 1) { endpoint_path = true; cid = ids[qi]; }
+        else {
+            int n_idx = query_to_node[qi];
+            bool is_endpoint = (qi + 1) == query_offsets[n_idx + 1];
+            bool ce_as_intermediate = ce_only && is_endpoint && (qi + 1 < T_q);
+            endpoint_path = is_endpoint && !ce_as_intermediate;
+            if (endpoint_path) cid = ids[n_idx];
+        }
+        if (endpoint_path) { c_start = counts_offset[cid]; c_end = counts_offset[cid + 1]; }
+        else target = token_ids[qi + 1];
+        if (mode == 0 && mass_weights) mass_w = mass_weights[qi];
+    }
+
+    if (bulk) {
+        uint32_t done = 0;
+        if (lane == 0) {
+            for (int it = 0; it < LOSSB_WAIT_LIMIT && !done; it++)
+                asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0; selp.u32 %0, 1, 0, p; }"
+                             : "=r"(done)
+                             : "r"(smem_u32(bar))
+                             : "memory");
+            if (!done) atomicOr(&g_device_status, 1);
+        }
+        done = __shfl_sync(0xffffffffu, done, 0);
+        if (!done) return;
     } else {
         __syncwarp();
-        for (int j = lane; j < V; j += 32) __stcs(g + j, row[j] * weight);
     }
-    if (lane == 0) loss_out[qi] = loss;
+
+    float loss = 0.f;
+    if (lane < nrows) {
+        float *row = tile + lane * V;
+        // lane-skewed column order: with row stride V the banks of the 32 lanes differ iff the per-lane step V + skew is odd
+        const int first = (V & 1) ? 0 : (lane % V);
+        float mx = -3.402823466e+38f;
+        for (int jj = 0; jj < V; jj++) { int j = first + jj; if (j >= V) j -= V; mx = fmaxf(mx, row[j]); }
+        float sum = 0.f;
+        const float mxl = mx * LOG2E;
+        for (int jj = 0; jj < V; jj++) {
+            int j = first + jj; if (j >= V) j -= V;
+            const float e = exp2f(fmaf(row[j], LOG2E, -mxl));
+            row[j] = e;
+            sum += e;
+        }
+        const float inv = 1.0f / sum;
+        float weight = 1.0f, total_f = 1.0f;
+        if (endpoint_path) {
+            if (c_start != c_end) {
+                int total = 0;
+                for (int e = c_start; e < c_end; e++) total += counts_val[e];
+                total_f = (float)total;
+                if (mode == 0) {
+                    if (entropy_lambda > 0.0f && (c_end - c_start) > 1) {
+                        float Hh = 0.f;
+                        for (int e = c_start; e < c_end; e++) {
+                            float qe = counts_val[e] / total_f;
+                            if (qe > 0.f) Hh -= qe * logf(qe);
+                        }
+                        weight = 1.0f + entropy_lambda * (Hh / logf((float)V));
+                    }
+                    if (mass_weights) weight *= mass_w;
+                }
+                for (int e = c_start; e < c_end; e++) {
+                    int tok = counts_tok[e];
+                    if ((unsigned)tok >= (unsigned)V) continue;      // a token outside the vocabulary is ignored, not written
+                    loss -= (counts_val[e] / total_f) * logf(row[tok] * inv + 1e-10f);
+                }
+                loss *= weight;
+            }
+            // else: no observed continuation -- zero loss, and the row keeps the plain probabilities
+        } else {
+            if ((unsigned)target >= (unsigned)V) target = 0;         // never index outside the row
+            weight = intermediate_weight;
+            if (mass_weights) weight *= mass_w;
+            loss = -logf(row[target] * inv + 1e-10f) * weight;
+        }
+        const float f = inv * weight;
+        for (int jj = 0; jj < V; jj++) { int j = first + jj; if (j >= V) j -= V; row[j] *= f; }
+        if (endpoint_path) {
+            for (int e = c_start; e < c_end; e++) {                  // tokens of one node are distinct
+                int tok = counts_tok[e];
+                if ((unsigned)tok < (unsigned)V) row[tok] -= (counts_val[e] / total_f) * weight;
+            }
+        } else {
+            row[target] -= weight;
+        }
+        loss_out[qi] = loss;
+    }
+    if (bulk) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the rows written above become visible to the bulk store
+        __syncwarp();
+        if (lane == 0) {
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(tile)), "r"(bytes) : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // shared memory must outlive the read
+        }
+    } else {
+        __syncwarp();
+        for (int i = lane; i < nrows * V; i += 32) __stcs(dst + i, tile[i]);
+    }
 }
 
 template <typename... Args>
-static void launch_loss(int64_t rows, int V, cudaStream_t st, Args... args) {
-    const unsigned blocks = (unsigned)((rows + LOSS_WPB - 1) / LOSS_WPB);
+static int launch_loss(int64_t rows, int V, cudaStream_t st, const float *logits, float *dlogits, Args... args) {
+    if (V <= 256) {
+        const size_t smem = (size_t)LOSSB_WARPS * 32 * V * sizeof(float) + LOSSB_WARPS * sizeof(uint64_t);
+        static bool attr_set[64];
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+            CUDA_TRY(cudaFuncSetAttribute(loss_batch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LOSSB_WARPS * 32 * 256 * 4 + 64));
+            attr_set[dev] = true;
+        }
+        const int rows_per_block = LOSSB_WARPS * 32;
+        const unsigned blocks = (unsigned)((rows + rows_per_block - 1) / rows_per_block);
+        const int aligned16 = ((reinterpret_cast<uintptr_t>(logits) | reinterpret_cast<uintptr_t>(dlogits)) & 15) == 0;
+        loss_batch_kernel<<<blocks, LOSSB_WARPS * 32, smem, st>>>(args..., aligned16);
+        return AGPT_OK;
+    }
+    const unsigned blocks = (unsigned)((rows + LOSS_ROWS_PER_BLOCK - 1) / LOSS_ROWS_PER_BLOCK);
     const size_t smem = (size_t)LOSS_WPB * V * sizeof(float);
-    if (V <= 32) loss_kernel<1><<<blocks, LOSS_WPB * 32, smem, st>>>(args...);
-    else if (V <= 64) loss_kernel<2><<<blocks, LOSS_WPB * 32, smem, st>>>(args...);
-    else if (V <= 96) loss_kernel<3><<<blocks, LOSS_WPB * 32, smem, st>>>(args...);
-    else if (V <= 128) loss_kernel<4><<<blocks, LOSS_WPB * 32, smem, st>>>(args...);
-    else if (V <= 256) loss_kernel<8><<<blocks, LOSS_WPB * 32, smem, st>>>(args...);
-    else loss_kernel<0><<<blocks, LOSS_WPB * 32, smem, st>>>(args...);
+    loss_kernel<0><<<blocks, LOSS_WPB * 32, smem, st>>>(args...);
+    return AGPT_OK;
+}
+
+extern "C" int agpt_b200_device_status(int32_t *status_out) {
+    if (!status_out) return agpt_set_error(AGPT_E_ARG, "device_status: null output");
+    int v = 0;
+    CUDA_TRY(cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)));      // synchronises with the work issued so far
+    *status_out = v;
+    return AGPT_OK;
 }
 
 extern "C" int agpt_b200_loss_per_query(const float *d_logits, const int32_t *d_query_to_node, const int32_t *d_query_offsets,
@@ -1323,8 +1522,9 @@ extern "C" int agpt_b200_loss_per_query(const float *d_logits, const int32_t *d_
         return agpt_set_error(AGPT_E_ARG, "loss_per_query: bad argument");
     if (T_q == 0) return AGPT_OK;
     if (V > 1400) return agpt_set_error(AGPT_E_LIMIT, "loss_per_query: vocabulary %d beyond 1400", V);
-    launch_loss(T_q, V, (cudaStream_t)stream, d_logits, d_query_to_node, d_query_offsets, d_radix_ids, d_token_ids, d_counts_offset,
+    int rc = launch_loss(T_q, V, (cudaStream_t)stream, d_logits, d_dlogits, d_logits, d_query_to_node, d_query_offsets, d_radix_ids, d_token_ids, d_counts_offset,
                 d_counts_tok, d_counts_val, d_mass_weights, d_dlogits, d_loss, T_q, V, entropy_lambda, intermediate_weight, ce_only, 0);
+    if (rc) return rc;
     return launch_status("loss_per_query");
 }
 
@@ -1335,9 +1535,10 @@ extern "C" int agpt_b200_loss_per_node(const float *d_logits, const int32_t *d_n
         return agpt_set_error(AGPT_E_ARG, "loss_per_node: bad argument");
     if (N == 0) return AGPT_OK;
     if (V > 1400) return agpt_set_error(AGPT_E_LIMIT, "loss_per_node: vocabulary %d beyond 1400", V);
-    launch_loss(N, V, (cudaStream_t)stream, d_logits, (const int32_t *)nullptr, (const int32_t *)nullptr, d_node_ids,
+    int rc = launch_loss(N, V, (cudaStream_t)stream, d_logits, d_dlogits, d_logits, (const int32_t *)nullptr, (const int32_t *)nullptr, d_node_ids,
                 (const int32_t *)nullptr, d_counts_offset, d_counts_tok, d_counts_val, (const float *)nullptr, d_dlogits, d_loss, N, V,
                 0.f, 1.f, 0, 1);
+    if (rc) return rc;
     return launch_status("loss_per_node");
 }
 

@@ -344,6 +344,11 @@ int agpt_b200_attn_bwd_static(const agpt_plan *p, const float *d_q, const void *
                               void *stream);
 int64_t agpt_b200_static_scratch_bytes(void);
 
+/* Device status word of the current GPU (waits for the work issued so far): 0 when every kernel ran to completion.
+ * Bit 0: a bounded wait for a bulk asynchronous copy in the loss kernel ran out; the affected rows were not
+ * written.  Kernels never trap; this word is how a failure on the device reaches the host. */
+int agpt_b200_device_status(int32_t *status_out);
+
 /* Replaces agpt_loss_per_query_kernel (src/cuda/agpt_train.cu:2069-2216).  Same arguments. */
 int agpt_b200_loss_per_query(const float *d_logits, const int32_t *d_query_to_node,
                              const int32_t *d_query_offsets, const int32_t *d_radix_ids,

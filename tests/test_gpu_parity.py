@@ -138,10 +138,11 @@ def test_bf16_store(cuda, hd, tile):
     ref = _oracle(parent, H, hd, q, k, v, go)
     for got, want in zip((out, dq, dk, dv), ref[:4]):
         assert rel_err(got, want) < TOL_BF16
-    # ... and within the float32 tolerance of the oracle fed the rounded store
+    # ... and, against the oracle fed the rounded store, within what single TF32 products leave (the bf16-store
+    # kernels do not compensate TF32 rounding: 2^-11 per operand, below the store's own 2^-9); the FMA family is exact
     ref_r = _oracle(parent, H, hd, q, _bf16_round(k), _bf16_round(v), go)
     for got, want in zip((out, dq, dk, dv), ref_r[:4]):
-        assert rel_err(got, want) < TOL_F32
+        assert rel_err(got, want) < 2e-3
 
 
 def test_backward_is_bitwise_repeatable(cuda):
@@ -434,7 +435,7 @@ def test_deep_pruned_trie_bf16_store(cuda):
         assert rel_err(got, want) < TOL_BF16
     ref_r = _oracle(parent, H, hd, q, _bf16_round(k), _bf16_round(v), go)
     for got, want in zip((out, dq, dk, dv), ref_r[:4]):
-        assert rel_err(got, want) < TOL_F32
+        assert rel_err(got, want) < 2e-3         # single TF32 products on a bf16 store (see test_bf16_store)
 
 
 def test_host_buffer_entry_point_multi_chunk(cuda):
@@ -512,3 +513,8 @@ def test_gemm_f32_tensor_core(shape, gemm_impl):
     with pytest.raises(A.AgptError):
         A.gemm_f32(x, w.t().contiguous(), trans_a=True, trans_b=True)
     A.set_gemm_impl(1)
+
+
+def test_device_status_word_is_clear(cuda):
+    """Every bounded wait on the device completed: the status word stays 0 after the kernels above ran."""
+    assert A.device_status() == 0
