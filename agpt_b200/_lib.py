@@ -89,7 +89,8 @@ SIGNATURES = {
     "agpt_b200_optimizer_step": (C.c_int, [C.c_int] + [vp] * 4 + [i64] + [f32] * 4 + [C.c_int, f32, f32, C.c_int, vp, vp]),
     "agpt_b200_optimizer_scratch_bytes": (i64, []),
     "agpt_b200_device_status": (C.c_int, [vp]),
-    "agpt_b200_gemm_f32": (C.c_int, [C.c_int] * 5 + [f32, vp, C.c_int, vp, C.c_int, f32, vp, C.c_int, vp, C.c_int, C.c_int, vp, i64, vp]),
+    "agpt_b200_gemm_f32": (C.c_int, [C.c_int] * 5 + [f32, vp, C.c_int, vp, C.c_int, f32, vp, C.c_int, vp, C.c_int, vp, C.c_int, C.c_int, vp,
+                                     i64, vp]),
     "agpt_b200_gemm_f32_workspace_bytes": (i64, [C.c_int] * 6),
     "agpt_b200_set_gemm_impl": (C.c_int, [C.c_int]),
     "agpt_b200_rope_table": (C.c_int, [vp, vp, C.c_int, C.c_int, f32]),

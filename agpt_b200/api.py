@@ -270,9 +270,9 @@ def rope_(x, pos, cos, sin, n_heads: int, inverse: bool = False):
 _gemm_ws = {}
 
 
-def gemm_f32(a, b, trans_a=False, trans_b=False, bias=None, out=None, split_k=1):
-    """out = op(a) @ op(b) (+ bias row), float32 on the tensor cores with float32-level accuracy.
-    a, b: contiguous 2-D float32 CUDA tensors."""
+def gemm_f32(a, b, trans_a=False, trans_b=False, bias=None, out=None, split_k=1, residual=None, relu=False):
+    """out = act(op(a) @ op(b) + residual + bias row), float32 on the tensor cores with float32-level accuracy.
+    a, b (and residual): contiguous 2-D float32 CUDA tensors."""
     import torch
     _chk_f32(a, "a")
     _chk_f32(b, "b")
@@ -287,9 +287,13 @@ def gemm_f32(a, b, trans_a=False, trans_b=False, bias=None, out=None, split_k=1)
     ws = _gemm_ws.get(a.device.index)
     if need and (ws is None or ws.numel() < need):
         ws = _gemm_ws[a.device.index] = torch.empty(int(need), dtype=torch.uint8, device=a.device)
+    if residual is not None:
+        _chk_f32(residual, "residual")
+        if tuple(residual.shape) != (M, N):
+            raise AgptError("gemm_f32: residual shape differs from the output's")
     check(lib().agpt_b200_gemm_f32(int(trans_a), int(trans_b), M, N, K, 1.0, _dp(a), a.shape[1], _dp(b), b.shape[1],
-                                   1.0 if bias is not None else 0.0, _dp(bias), 0, _dp(out), N, split_k, _dp(ws) if need else None, int(need),
-                                   _stream()), "gemm_f32")
+                                   1.0 if residual is not None else 0.0, _dp(residual), N, _dp(bias), int(relu), _dp(out), N, split_k,
+                                   _dp(ws) if need else None, int(need), _stream()), "gemm_f32")
     return out
 
 

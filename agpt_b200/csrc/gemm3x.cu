@@ -6,7 +6,7 @@
 // parts and issues three tensor-core MMAs per product (the same compensation the attention kernels use), so
 // results agree with an IEEE float32 GEMM to about 1e-6 relative while running on mma.sync instead of the FP32
 // FMA pipe.  All matrices are row-major; op(A) is A or A^T, op(B) is B or B^T:
-//     C[M, N] = alpha * op(A)[M, K] * op(B)[K, N] + beta * C            (ldc == 0 broadcasts a bias row as C's source)
+//     out[M, N] = act(alpha * op(A)[M, K] * op(B)[K, N] + beta * C + bias row)
 // The reduction over K can be cut into slices (weight gradients need that: their K is the number of trie
 // positions).  Slices run as one batched GEMM into partial matrices in the workspace and a second small kernel
 // adds them in slice order, so the result is repeatable bit for bit and no thread block waits on another.
@@ -23,7 +23,7 @@ extern "C" int64_t agpt_b200_gemm_f32_workspace_bytes(int, int, int, int, int, i
     return agpt_set_error(AGPT_E_ARG, "gemm_f32: this build of the library has no CUTLASS headers");
 }
 extern "C" int agpt_b200_gemm_f32(int, int, int, int, int, float, const float *, int, const float *, int, float, const float *, int,
-                                  float *, int, int, void *, int64_t, void *) {
+                                  const float *, int, float *, int, int, void *, int64_t, void *) {
     return agpt_set_error(AGPT_E_ARG, "gemm_f32: this build of the library has no CUTLASS headers");
 }
 extern "C" int agpt_b200_set_gemm_impl(int) { return agpt_set_error(AGPT_E_ARG, "gemm_f32: this build of the library has no CUTLASS headers"); }
@@ -91,21 +91,57 @@ int gemm_impl() {
     return g_gemm_impl;
 }
 
+// out = act(out + bias): the epilogue steps implementation 0 cannot fuse (a bias row together with a source
+// matrix, or the ReLU)
+__global__ void __launch_bounds__(256) post_bias_relu_kernel(float *__restrict__ out, int64_t M, int N, int ldd, const float *__restrict__ bias,
+                                                              int relu) {
+    const int64_t total = M * N;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t r = i / N;
+        int c = (int)(i - r * N);
+        float v = out[r * ldd + c];
+        if (bias) v += __ldg(bias + c);
+        if (relu) v = fmaxf(v, 0.f);
+        out[r * ldd + c] = v;
+    }
+}
+
+struct Extra {                       // what follows the product: out = act(alpha*AB + beta*C + bias)
+    float beta;
+    const float *C;
+    int ldc;
+    const float *bias;
+    int relu;
+};
+
 template <typename G, bool TA, bool TB>
-int run(int M, int N, int K, float alpha, const float *A, int lda, const float *B, int ldb, float beta, const float *Csrc,
-        int ldc, float *D, int ldd, int split_k, void *ws, int64_t ws_bytes, cudaStream_t st) {
+int run(int M, int N, int K, float alpha, const float *A, int lda, const float *B, int ldb, const Extra &x, float *D, int ldd,
+        int split_k, void *ws, int64_t ws_bytes, cudaStream_t st) {
     using Mode = cutlass::gemm::GemmUniversalMode;
     int ks = split_k > 1 ? slice_len(K, split_k) : 0;
-    // the tcgen05 kernel takes products without a source matrix, or with a bias row as the source
-    const bool bias_row = beta == 1.f && ldc == 0;
-    const bool sm100 = gemm_impl() == 1 && N % 4 == 0 && lda % 4 == 0 && ldb % 4 == 0 && ldd % 4 == 0 &&
-                       (((uintptr_t)A | (uintptr_t)B | (uintptr_t)D | (uintptr_t)Csrc) & 15) == 0;
+    const bool sm100 = gemm_impl() == 1 && N % 4 == 0 && lda % 4 == 0 && ldb % 4 == 0 && ldd % 4 == 0 && (!x.C || x.ldc % 4 == 0) &&
+                       (((uintptr_t)A | (uintptr_t)B | (uintptr_t)D | (uintptr_t)x.C | (uintptr_t)x.bias) & 15) == 0;
     if (ks == 0) {
-        if (sm100 && (beta == 0.f || bias_row))
-            return agpt_gemm_sm100(TA, TB, M, N, K, 1, alpha, A, lda, 0, B, ldb, 0, bias_row ? Csrc : nullptr, D, ldd, 0, st);
-        typename G::Arguments args(Mode::kGemm, {M, N, K}, 1, {alpha, beta}, A, B, Csrc, D, 0, 0, 0, 0, (int64_t)lda, (int64_t)ldb, (int64_t)ldc, (int64_t)ldd);
-        return launch<G>(args, st);
+        if (sm100 && agpt_gemm_sm100_takes(TA, TB, x.relu, x.C != nullptr))
+            return agpt_gemm_sm100(TA, TB, M, N, K, 1, alpha, A, lda, 0, B, ldb, 0, x.bias, x.relu, x.beta, x.C, x.ldc, D, ldd, 0, st);
+        // implementation 0: the source operand is C, else the bias row broadcast (leading dimension 0); what is left
+        // (bias on top of a source matrix, ReLU) runs as a second pass
+        const bool bias_as_source = !x.C && x.bias;
+        const float *src = x.C ? x.C : (bias_as_source ? x.bias : D);
+        typename G::Arguments args(Mode::kGemm, {M, N, K}, 1, {alpha, x.C ? x.beta : (bias_as_source ? 1.f : 0.f)}, A, B, src, D, 0, 0, 0, 0,
+                                   (int64_t)lda, (int64_t)ldb, (int64_t)(x.C ? x.ldc : (bias_as_source ? 0 : ldd)), (int64_t)ldd);
+        int rc = launch<G>(args, st);
+        if (rc) return rc;
+        const float *late_bias = (x.C && x.bias) ? x.bias : nullptr;
+        if (late_bias || x.relu) {
+            int64_t blocks = ((int64_t)M * N + 255) / 256;
+            post_bias_relu_kernel<<<(unsigned)(blocks < 148 * 16 ? blocks : 148 * 16), 256, 0, st>>>(D, M, N, ldd, late_bias, x.relu);
+        }
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return agpt_set_error(AGPT_E_CUDA, "gemm_f32: %s", cudaGetErrorString(e));
+        return AGPT_OK;
     }
+    if (x.bias || x.relu) return agpt_set_error(AGPT_E_ARG, "gemm_f32: split_k takes no bias or activation");
     if (N % 4 || ldd % 4 || ((uintptr_t)ws & 15)) return agpt_set_error(AGPT_E_ARG, "gemm_f32: split_k needs N and ldd multiples of 4");
     int64_t mn = (int64_t)M * N;
     if (ws_bytes < (int64_t)split_k * mn * 4) return agpt_set_error(AGPT_E_ARG, "gemm_f32: workspace too small");
@@ -114,18 +150,18 @@ int run(int M, int N, int K, float alpha, const float *A, int lda, const float *
     float *part = (float *)ws;
     int rc;
     if (sm100) {
-        rc = agpt_gemm_sm100(TA, TB, M, N, ks, split_k, alpha, A, lda, sa, B, ldb, sb, nullptr, part, N, mn, st);
+        rc = agpt_gemm_sm100(TA, TB, M, N, ks, split_k, alpha, A, lda, sa, B, ldb, sb, nullptr, 0, 0.f, nullptr, 0, part, N, mn, st);
     } else {
         typename G::Arguments args(Mode::kBatched, {M, N, ks}, split_k, {alpha, 0.f}, A, B, part, part, sa, sb, mn, mn, (int64_t)lda, (int64_t)ldb, (int64_t)N, (int64_t)N);
         rc = launch<G>(args, st);
     }
     if (rc) return rc;
     int64_t mn4 = mn / 4;
-    sum_slices_kernel<<<(unsigned)((mn4 + 255) / 256), 256, 0, st>>>((const float4 *)part, split_k, mn4, N / 4, beta, Csrc, ldc, D, ldd);
+    sum_slices_kernel<<<(unsigned)((mn4 + 255) / 256), 256, 0, st>>>((const float4 *)part, split_k, mn4, N / 4, x.C ? x.beta : 0.f, x.C, x.ldc, D, ldd);
     int tail = K - split_k * ks;
     if (tail > 0) {
-        typename G::Arguments targs(Mode::kGemm, {M, N, tail}, 1, {alpha, 1.f}, A + split_k * sa, B + split_k * sb, D, D, 0, 0, 0, 0, lda,
-                                    ldb, ldd, ldd);
+        typename G::Arguments targs(Mode::kGemm, {M, N, tail}, 1, {alpha, 1.f}, A + split_k * sa, B + split_k * sb, D, D, 0, 0, 0, 0, (int64_t)lda,
+                                    (int64_t)ldb, (int64_t)ldd, (int64_t)ldd);
         rc = launch<G>(targs, st);
         if (rc) return rc;
     }
@@ -149,17 +185,18 @@ extern "C" int agpt_b200_set_gemm_impl(int impl) {
 }
 
 extern "C" int agpt_b200_gemm_f32(int trans_a, int trans_b, int M, int N, int K, float alpha, const float *d_a, int lda,
-                                  const float *d_b, int ldb, float beta, const float *d_c, int ldc, float *d_out, int ldd,
-                                  int split_k, void *d_workspace, int64_t workspace_bytes, void *stream) {
+                                  const float *d_b, int ldb, float beta, const float *d_c, int ldc, const float *d_bias, int relu,
+                                  float *d_out, int ldd, int split_k, void *d_workspace, int64_t workspace_bytes, void *stream) {
     if (M <= 0 || N <= 0 || K <= 0 || split_k < 1 || !d_a || !d_b || !d_out)
         return agpt_set_error(AGPT_E_ARG, "gemm_f32: bad argument");
     if (beta != 0.f && !d_c) return agpt_set_error(AGPT_E_ARG, "gemm_f32: beta != 0 needs a source matrix");
+    if (d_c && ldc < N) return agpt_set_error(AGPT_E_ARG, "gemm_f32: ldc smaller than N");
     cudaStream_t st = (cudaStream_t)stream;
-    const float *c = d_c ? d_c : d_out;
+    Extra x{beta, beta != 0.f ? d_c : nullptr, ldc, d_bias, relu ? 1 : 0};
     // a transposed row-major operand is the same memory read as column-major
-    if (!trans_a && !trans_b) return run<Gemm3x<Row, Row>, false, false>(M, N, K, alpha, d_a, lda, d_b, ldb, beta, c, ldc, d_out, ldd, split_k, d_workspace, workspace_bytes, st);
-    if (!trans_a && trans_b) return run<Gemm3x<Row, Col>, false, true>(M, N, K, alpha, d_a, lda, d_b, ldb, beta, c, ldc, d_out, ldd, split_k, d_workspace, workspace_bytes, st);
-    if (trans_a && !trans_b) return run<Gemm3x<Col, Row>, true, false>(M, N, K, alpha, d_a, lda, d_b, ldb, beta, c, ldc, d_out, ldd, split_k, d_workspace, workspace_bytes, st);
+    if (!trans_a && !trans_b) return run<Gemm3x<Row, Row>, false, false>(M, N, K, alpha, d_a, lda, d_b, ldb, x, d_out, ldd, split_k, d_workspace, workspace_bytes, st);
+    if (!trans_a && trans_b) return run<Gemm3x<Row, Col>, false, true>(M, N, K, alpha, d_a, lda, d_b, ldb, x, d_out, ldd, split_k, d_workspace, workspace_bytes, st);
+    if (trans_a && !trans_b) return run<Gemm3x<Col, Row>, true, false>(M, N, K, alpha, d_a, lda, d_b, ldb, x, d_out, ldd, split_k, d_workspace, workspace_bytes, st);
     return agpt_set_error(AGPT_E_ARG, "gemm_f32: A^T * B^T is not provided");
 }
 #endif  // AGPT_NO_CUTLASS

@@ -5,7 +5,8 @@
 // accuracy of the reference's cublasSgemm calls (src/cuda/agpt_train.cu:4675-4683, :4752, :4766-4771, :4803,
 // :4840-5061) at several times their speed.  The kernel is CUTLASS's SM100 warp-specialised "fast FP32" mainloop
 // (TMA load warp -> transform warps -> MMA warp -> epilogue warps), instantiated here for one CTA per tile
-// (no cluster multicast), a 128x128x16 tile, and an epilogue that adds a per-column bias row.
+// (no cluster multicast), a 128x128x16 tile, and three epilogues: bias row; bias row + ReLU (the first
+// feed-forward projection); bias row + a source matrix (the residual stream added in the same pass).
 #include <cuda_runtime.h>
 
 #include "../../include/agpt_b200.h"
@@ -27,15 +28,20 @@ using namespace cute;
 using Row = cutlass::layout::RowMajor;
 using Col = cutlass::layout::ColumnMajor;
 
-template <typename LayoutA, typename LayoutB>
+enum { EPI_BIAS = 0, EPI_BIAS_RELU = 1, EPI_BIAS_SOURCE = 2 };
+
+template <typename LayoutA, typename LayoutB, int EPI = EPI_BIAS>
 struct Sm100Gemm {
     using TileShape = Shape<_128, _128, _16>;
     using ClusterShape = Shape<_1, _1, _1>;
-    // D = alpha * acc + bias[column]; no source matrix is read (ElementC = void)
-    using Fusion = cutlass::epilogue::fusion::LinCombPerColBias<float, float, float, float, float, 4>;
+    // D = act(alpha * acc + beta * C + bias[column]); without a source matrix none is read (ElementC = void)
+    using Fusion = cute::conditional_t<EPI == EPI_BIAS_RELU,
+                                       cutlass::epilogue::fusion::LinCombPerColBiasEltAct<cutlass::epilogue::thread::ReLu, float, float, float, float, float, 4>,
+                                       cutlass::epilogue::fusion::LinCombPerColBias<float, float, float, float, float, 4>>;
+    using ElementC = cute::conditional_t<EPI == EPI_BIAS_SOURCE, float, void>;
     using Epilogue = typename cutlass::epilogue::collective::CollectiveBuilder<
         cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, TileShape, ClusterShape, cutlass::epilogue::collective::EpilogueTileAuto,
-        float, float, void, Row, 4, float, Row, 4, cutlass::epilogue::TmaWarpSpecialized1Sm, Fusion>::CollectiveOp;
+        float, float, ElementC, Row, 4, float, Row, 4, cutlass::epilogue::TmaWarpSpecialized1Sm, Fusion>::CollectiveOp;
     using Mainloop = typename cutlass::gemm::collective::CollectiveBuilder<
         cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, float, LayoutA, 4, float, LayoutB, 4, float, TileShape, ClusterShape,
         cutlass::gemm::collective::StageCountAutoCarveout<static_cast<int>(sizeof(typename Epilogue::SharedStorage))>,
@@ -53,7 +59,8 @@ int sm_count_of(int dev) {
 
 template <typename G>
 int run(int M, int N, int K, int L, float alpha, const float *A, int64_t lda, int64_t batch_a, const float *B, int64_t ldb,
-        int64_t batch_b, const float *bias, float *D, int64_t ldd, int64_t batch_d, cudaStream_t st) {
+        int64_t batch_b, const float *bias, float beta, const float *C, int64_t ldc, float *D, int64_t ldd, int64_t batch_d,
+        cudaStream_t st) {
     using Gemm = typename G::Gemm;
     typename Gemm::GemmKernel::StrideA dA;
     typename Gemm::GemmKernel::StrideB dB;
@@ -66,9 +73,13 @@ int run(int M, int N, int K, int L, float alpha, const float *A, int64_t lda, in
     get<2>(dB) = batch_b;
     get<0>(dD) = ldd;
     get<2>(dD) = batch_d;
-    typename Gemm::Arguments args{cutlass::gemm::GemmUniversalMode::kGemm, {M, N, K, L}, {A, dA, B, dB}, {{}, nullptr, dD, D, dD}};
+    typename Gemm::GemmKernel::StrideC dC = dD;
+    get<0>(dC) = ldc;
+    get<2>(dC) = 0;
+    using PtrC = decltype(typename Gemm::Arguments{}.epilogue.ptr_C);
+    typename Gemm::Arguments args{cutlass::gemm::GemmUniversalMode::kGemm, {M, N, K, L}, {A, dA, B, dB}, {{}, (PtrC)C, dC, D, dD}};
     args.epilogue.thread.alpha = alpha;
-    args.epilogue.thread.beta = 0.f;
+    args.epilogue.thread.beta = beta;
     args.epilogue.thread.bias_ptr = bias;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -92,15 +103,27 @@ int run(int M, int N, int K, int L, float alpha, const float *A, int64_t lda, in
 
 }  // namespace
 
-// D[l] = alpha * op(A[l]) * op(B[l]) + bias, l < L; row-major storage, op as in agpt_b200_gemm_f32
+// which (layout, epilogue) pairs are instantiated: every layout with the bias epilogue; the ReLU and source epilogues
+// only for the forward projection layout (A and B as stored)
+bool agpt_gemm_sm100_takes(int trans_a, int trans_b, int relu, int has_source) {
+    if (trans_a && trans_b) return false;
+    if (relu && has_source) return false;
+    return (!relu && !has_source) || (!trans_a && !trans_b);
+}
+
+// D[l] = act(alpha * op(A[l]) * op(B[l]) + beta * C + bias), l < L; row-major storage, op as in agpt_b200_gemm_f32
 int agpt_gemm_sm100(int trans_a, int trans_b, int M, int N, int K, int L, float alpha, const float *A, int64_t lda, int64_t batch_a,
-                    const float *B, int64_t ldb, int64_t batch_b, const float *bias, float *D, int64_t ldd, int64_t batch_d,
-                    void *stream) {
+                    const float *B, int64_t ldb, int64_t batch_b, const float *bias, int relu, float beta, const float *C, int64_t ldc,
+                    float *D, int64_t ldd, int64_t batch_d, void *stream) {
     cudaStream_t st = (cudaStream_t)stream;
+    if (!agpt_gemm_sm100_takes(trans_a, trans_b, relu, C != nullptr)) return agpt_set_error(AGPT_E_ARG, "gemm_f32: combination not instantiated");
     // a transposed row-major operand is the same memory read as column-major
-    if (!trans_a && !trans_b) return run<Sm100Gemm<Row, Row>>(M, N, K, L, alpha, A, lda, batch_a, B, ldb, batch_b, bias, D, ldd, batch_d, st);
-    if (!trans_a && trans_b) return run<Sm100Gemm<Row, Col>>(M, N, K, L, alpha, A, lda, batch_a, B, ldb, batch_b, bias, D, ldd, batch_d, st);
-    if (trans_a && !trans_b) return run<Sm100Gemm<Col, Row>>(M, N, K, L, alpha, A, lda, batch_a, B, ldb, batch_b, bias, D, ldd, batch_d, st);
-    return agpt_set_error(AGPT_E_ARG, "gemm_f32: A^T * B^T is not provided");
+    if (!trans_a && !trans_b) {
+        if (relu) return run<Sm100Gemm<Row, Row, EPI_BIAS_RELU>>(M, N, K, L, alpha, A, lda, batch_a, B, ldb, batch_b, bias, 0.f, nullptr, ldd, D, ldd, batch_d, st);
+        if (C) return run<Sm100Gemm<Row, Row, EPI_BIAS_SOURCE>>(M, N, K, L, alpha, A, lda, batch_a, B, ldb, batch_b, bias, beta, C, ldc, D, ldd, batch_d, st);
+        return run<Sm100Gemm<Row, Row>>(M, N, K, L, alpha, A, lda, batch_a, B, ldb, batch_b, bias, 0.f, nullptr, ldd, D, ldd, batch_d, st);
+    }
+    if (!trans_a && trans_b) return run<Sm100Gemm<Row, Col>>(M, N, K, L, alpha, A, lda, batch_a, B, ldb, batch_b, bias, 0.f, nullptr, ldd, D, ldd, batch_d, st);
+    return run<Sm100Gemm<Col, Row>>(M, N, K, L, alpha, A, lda, batch_a, B, ldb, batch_b, bias, 0.f, nullptr, ldd, D, ldd, batch_d, st);
 }
 #endif  // AGPT_NO_CUTLASS

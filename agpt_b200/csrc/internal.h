@@ -45,7 +45,8 @@ struct agpt_plan {
 
 int agpt_plan_upload(agpt_plan *p, int device);
 
-// tcgen05 float32 GEMM (gemm_sm100.cu): D[l] = alpha * op(A[l]) * op(B[l]) + bias row, l < L batches
+// tcgen05 float32 GEMM (gemm_sm100.cu): D[l] = act(alpha * op(A[l]) * op(B[l]) + beta * C + bias row), l < L batches
+bool agpt_gemm_sm100_takes(int trans_a, int trans_b, int relu, int has_source);
 int agpt_gemm_sm100(int trans_a, int trans_b, int M, int N, int K, int L, float alpha, const float *A, int64_t lda, int64_t batch_a,
-                    const float *B, int64_t ldb, int64_t batch_b, const float *bias, float *D, int64_t ldd, int64_t batch_d,
-                    void *stream);
+                    const float *B, int64_t ldb, int64_t batch_b, const float *bias, int relu, float beta, const float *C, int64_t ldc,
+                    float *D, int64_t ldd, int64_t batch_d, void *stream);

@@ -1391,6 +1391,16 @@ loss_batch_kernel(const float *__restrict__ logits, const int32_t *__restrict__ 
         else target = token_ids[qi + 1];
         if (mode == 0 && mass_weights) mass_w = mass_weights[qi];
     }
+    // an endpoint row's first count entries are fetched now, under the bulk copy, instead of as three dependent
+    // global-memory loops after it (nearly every batch holds an endpoint row, and its lane would stall the warp)
+    constexpr int CPRE = 8;
+    int ptok[CPRE], pval[CPRE];
+    const int ncnt = c_end - c_start;
+#pragma unroll
+    for (int e = 0; e < CPRE; e++) {
+        ptok[e] = e < ncnt ? counts_tok[c_start + e] : -1;
+        pval[e] = e < ncnt ? counts_val[c_start + e] : 0;
+    }
 
     if (bulk) {
         uint32_t done = 0;
@@ -1428,12 +1438,19 @@ loss_batch_kernel(const float *__restrict__ logits, const int32_t *__restrict__ 
         if (endpoint_path) {
             if (c_start != c_end) {
                 int total = 0;
-                for (int e = c_start; e < c_end; e++) total += counts_val[e];
+#pragma unroll
+                for (int e = 0; e < CPRE; e++) total += pval[e];
+                for (int e = c_start + CPRE; e < c_end; e++) total += counts_val[e];
                 total_f = (float)total;
                 if (mode == 0) {
-                    if (entropy_lambda > 0.0f && (c_end - c_start) > 1) {
+                    if (entropy_lambda > 0.0f && ncnt > 1) {
                         float Hh = 0.f;
-                        for (int e = c_start; e < c_end; e++) {
+#pragma unroll
+                        for (int e = 0; e < CPRE; e++) {
+                            float qe = pval[e] / total_f;
+                            if (e < ncnt && qe > 0.f) Hh -= qe * logf(qe);
+                        }
+                        for (int e = c_start + CPRE; e < c_end; e++) {
                             float qe = counts_val[e] / total_f;
                             if (qe > 0.f) Hh -= qe * logf(qe);
                         }
@@ -1441,9 +1458,12 @@ loss_batch_kernel(const float *__restrict__ logits, const int32_t *__restrict__ 
                     }
                     if (mass_weights) weight *= mass_w;
                 }
-                for (int e = c_start; e < c_end; e++) {
+#pragma unroll
+                for (int e = 0; e < CPRE; e++)                       // a token outside the vocabulary is ignored, not written
+                    if ((unsigned)ptok[e] < (unsigned)V) loss -= (pval[e] / total_f) * logf(row[ptok[e]] * inv + 1e-10f);
+                for (int e = c_start + CPRE; e < c_end; e++) {
                     int tok = counts_tok[e];
-                    if ((unsigned)tok >= (unsigned)V) continue;      // a token outside the vocabulary is ignored, not written
+                    if ((unsigned)tok >= (unsigned)V) continue;
                     loss -= (counts_val[e] / total_f) * logf(row[tok] * inv + 1e-10f);
                 }
                 loss *= weight;
@@ -1458,7 +1478,10 @@ loss_batch_kernel(const float *__restrict__ logits, const int32_t *__restrict__ 
         const float f = inv * weight;
         for (int jj = 0; jj < V; jj++) { int j = first + jj; if (j >= V) j -= V; row[j] *= f; }
         if (endpoint_path) {
-            for (int e = c_start; e < c_end; e++) {                  // tokens of one node are distinct
+#pragma unroll
+            for (int e = 0; e < CPRE; e++)                           // tokens of one node are distinct
+                if ((unsigned)ptok[e] < (unsigned)V) row[ptok[e]] -= (pval[e] / total_f) * weight;
+            for (int e = c_start + CPRE; e < c_end; e++) {
                 int tok = counts_tok[e];
                 if ((unsigned)tok < (unsigned)V) row[tok] -= (counts_val[e] / total_f) * weight;
             }

@@ -150,17 +150,15 @@ def _linear_function():
     import torch
 
     class TensorLinear(torch.autograd.Function):
-        """y = x @ w + b (relu: max(., 0)) with the library's float32-accurate tensor-core GEMM.  Backward: the
+        """y = x @ w + b (+ residual; relu: max(., 0)) in one GEMM launch of the library.  Backward: the
         ReLU mask and the bias gradient are one pass over the incoming gradient; the weight gradient cuts the row
         dimension into slices that are summed in a fixed order."""
 
         @staticmethod
-        def forward(ctx, x, w, b, relu):
+        def forward(ctx, x, w, b, relu, residual):
             x = x.contiguous()
-            y = A.gemm_f32(x, w, bias=b)
-            if relu:
-                y = torch.relu_(y)
-            ctx.relu = relu
+            y = A.gemm_f32(x, w, bias=b, relu=relu, residual=None if residual is None else residual.contiguous())
+            ctx.relu, ctx.has_residual = relu, residual is not None
             ctx.save_for_backward(x, w, y if relu else None)
             return y
 
@@ -176,7 +174,7 @@ def _linear_function():
             tiles = -(-w.shape[0] // 128) * -(-w.shape[1] // 128)
             split_k = max(1, min(x.shape[0] // 2048, -(-296 // tiles)))
             dw = A.gemm_f32(x, grad, trans_a=True, split_k=split_k)
-            return dx, dw, db, None
+            return dx, dw, db, None, (grad if ctx.has_residual else None)
 
     return TensorLinear
 
@@ -266,15 +264,16 @@ class TrieWalkModel:
         P, m = self.params, self.cfg
         ln = self.ln.apply
 
-        def lin(x, w, b, relu=False):
+        def lin(x, w, b, relu=False, residual=None):
             # the library GEMM needs 16-byte aligned rows; other widths (a vocabulary of 65) go to torch
             if self.dense_impl == "tensor" and w.shape[0] % 4 == 0 and w.shape[1] % 4 == 0:
-                return self.linear.apply(x, w, b, relu)
+                return self.linear.apply(x, w, b, relu, residual)
             y = torch.addmm(b, x, w)
-            return torch.relu(y) if relu else y
+            y = torch.relu(y) if relu else y
+            return y if residual is None else residual + y
 
         def ffn(x, g2, b2, w1, b1, w2, bo):
-            return x + lin(lin(ln(x, g2, b2), w1, b1, True), w2, bo)
+            return lin(lin(ln(x, g2, b2), w1, b1, relu=True), w2, bo, residual=x)
 
         x = self.embed.apply(P["token_emb"], group.tokens32)
         for l in range(m.n_layers):
@@ -284,7 +283,7 @@ class TrieWalkModel:
             k = lin(x1, g("wk.w"), g("wk.b")[0])
             v = lin(x1, g("wv.w"), g("wv.b")[0])
             a = self.attn.apply(q, k, v, group, self.cos, self.sin, m.n_heads, bf16_store)
-            x = x + lin(a, g("wo.w"), g("wo.b")[0])
+            x = lin(a, g("wo.w"), g("wo.b")[0], residual=x)
             args = (x, g("ln2.gamma")[0], g("ln2.beta")[0], g("l1.w"), g("l1.b")[0], g("l2.w"), g("l2.b")[0])
             x = checkpoint(ffn, *args, use_reentrant=False) if self.ffn_recompute else ffn(*args)
         xf = ln(x, P["final.gamma"][0], P["final.beta"][0])

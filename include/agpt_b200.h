@@ -286,15 +286,16 @@ int64_t agpt_b200_optimizer_scratch_bytes(void);
 
 /* Replaces the cublasSgemm calls of the dense projections (src/cuda/agpt_train.cu:4675-4683, :4752, :4766-4771,
  * :4803, :4840-5061) with a tensor-core GEMM of float32-level accuracy (three TF32 MMAs per product).  Row-major:
- *     out[M, N] = alpha * op(A)[M, K] * op(B)[K, N] + beta * C
- * trans_a / trans_b select A^T / B^T (not both).  ldc == 0 broadcasts one row (a bias) as the source; d_c may be
- * NULL when beta == 0.  split_k > 1 cuts K into slices (for weight gradients, whose K is the number of trie
- * positions): the slices run as one batched GEMM into partial matrices in d_workspace
- * (agpt_b200_gemm_f32_workspace_bytes, 0 when split_k == 1) and are added in slice order, so the result is
- * repeatable bit for bit.  Pointers and leading dimensions must be multiples of 4 floats. */
+ *     out[M, N] = act(alpha * op(A)[M, K] * op(B)[K, N] + beta * C + bias)
+ * trans_a / trans_b select A^T / B^T (not both).  d_c (with beta != 0) is a source matrix such as the residual
+ * stream, d_bias a row added to every row, relu != 0 applies max(., 0); each may be absent (NULL / 0).  split_k > 1
+ * cuts K into slices (for weight gradients, whose K is the number of trie positions; no bias or activation then): the
+ * slices run as one batched GEMM into partial matrices in d_workspace (agpt_b200_gemm_f32_workspace_bytes, 0 when
+ * split_k == 1) and are added in slice order, so the result is repeatable bit for bit.  Pointers and leading
+ * dimensions must be multiples of 4 floats. */
 int agpt_b200_gemm_f32(int trans_a, int trans_b, int M, int N, int K, float alpha, const float *d_a, int lda,
-                       const float *d_b, int ldb, float beta, const float *d_c, int ldc, float *d_out, int ldd,
-                       int split_k, void *d_workspace, int64_t workspace_bytes, void *stream);
+                       const float *d_b, int ldb, float beta, const float *d_c, int ldc, const float *d_bias, int relu,
+                       float *d_out, int ldd, int split_k, void *d_workspace, int64_t workspace_bytes, void *stream);
 int64_t agpt_b200_gemm_f32_workspace_bytes(int trans_a, int trans_b, int M, int N, int K, int split_k);
 /* Two implementations compute agpt_b200_gemm_f32: 1 (default) tcgen05 MMAs on bfloat16 splits of the operands with
  * TMA loads and tensor-memory accumulators; 0 mma.sync with three TF32 products (also set by the environment

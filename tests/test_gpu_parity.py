@@ -504,6 +504,12 @@ def test_gemm_f32_tensor_core(shape, gemm_impl):
 
     close(A.gemm_f32(x, w, bias=b), x.double() @ w.double() + b.double())
     close(A.gemm_f32(x, w), x.double() @ w.double())
+    res = torch.randn(rows, dout, device="cuda", generator=g)
+    close(A.gemm_f32(x, w, bias=b, relu=True), torch.relu(x.double() @ w.double() + b.double()))
+    close(A.gemm_f32(x, w, bias=b, residual=res), x.double() @ w.double() + b.double() + res.double())
+    close(A.gemm_f32(x, w, residual=res), x.double() @ w.double() + res.double())
+    close(A.gemm_f32(dy, w, trans_b=True, bias=torch.ones(din, device="cuda"), relu=True),
+          torch.relu(dy.double() @ w.double().t() + 1.0))
     close(A.gemm_f32(dy, w, trans_b=True), dy.double() @ w.double().t())
     want = x.double().t() @ dy.double()
     for split_k in (1, 2, 7, 64):
