@@ -1337,6 +1337,13 @@ loss_kernel(const float *__restrict__ logits, const int32_t *__restrict__ query_
 // out the warp sets bit 0 of the device status word and returns without storing.
 __device__ int g_device_status = 0;
 
+// 2^x for x <= 0 (softmax exponents): the hardware approximation, relative error about 2^-22; flushes below 2^-126
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 #define LOSSB_WARPS 4
@@ -1421,17 +1428,32 @@ loss_batch_kernel(const float *__restrict__ logits, const int32_t *__restrict__ 
     float loss = 0.f;
     if (lane < nrows) {
         float *row = tile + lane * V;
-        // lane-skewed column order: with row stride V the banks of the 32 lanes differ iff the per-lane step V + skew is odd
+        // lane-skewed column order: with row stride V the banks of the 32 lanes differ iff the per-lane step V + skew
+        // is odd, so an even V starts lane l at column l (two plain segments: [first, V) then [0, first))
         const int first = (V & 1) ? 0 : (lane % V);
         float mx = -3.402823466e+38f;
-        for (int jj = 0; jj < V; jj++) { int j = first + jj; if (j >= V) j -= V; mx = fmaxf(mx, row[j]); }
+        {
+            float m0 = mx, m1 = mx, m2 = mx, m3 = mx;
+            int j = first;
+            for (; j + 3 < V; j += 4) { m0 = fmaxf(m0, row[j]); m1 = fmaxf(m1, row[j + 1]); m2 = fmaxf(m2, row[j + 2]); m3 = fmaxf(m3, row[j + 3]); }
+            for (; j < V; j++) m0 = fmaxf(m0, row[j]);
+            for (j = 0; j < first; j++) m1 = fmaxf(m1, row[j]);
+            mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+        }
         float sum = 0.f;
         const float mxl = mx * LOG2E;
-        for (int jj = 0; jj < V; jj++) {
-            int j = first + jj; if (j >= V) j -= V;
-            const float e = exp2f(fmaf(row[j], LOG2E, -mxl));
-            row[j] = e;
-            sum += e;
+        {
+            float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+            int j = first;
+            for (; j + 3 < V; j += 4) {
+                const float e0 = fast_exp2(fmaf(row[j], LOG2E, -mxl)), e1 = fast_exp2(fmaf(row[j + 1], LOG2E, -mxl));
+                const float e2 = fast_exp2(fmaf(row[j + 2], LOG2E, -mxl)), e3 = fast_exp2(fmaf(row[j + 3], LOG2E, -mxl));
+                row[j] = e0; row[j + 1] = e1; row[j + 2] = e2; row[j + 3] = e3;
+                s0 += e0; s1 += e1; s2 += e2; s3 += e3;
+            }
+            for (; j < V; j++) { const float e = fast_exp2(fmaf(row[j], LOG2E, -mxl)); row[j] = e; s0 += e; }
+            for (j = 0; j < first; j++) { const float e = fast_exp2(fmaf(row[j], LOG2E, -mxl)); row[j] = e; s1 += e; }
+            sum = (s0 + s1) + (s2 + s3);
         }
         const float inv = 1.0f / sum;
         float weight = 1.0f, total_f = 1.0f;
@@ -1476,7 +1498,12 @@ loss_batch_kernel(const float *__restrict__ logits, const int32_t *__restrict__ 
             loss = -logf(row[target] * inv + 1e-10f) * weight;
         }
         const float f = inv * weight;
-        for (int jj = 0; jj < V; jj++) { int j = first + jj; if (j >= V) j -= V; row[j] *= f; }
+        {
+            int j = first;
+            for (; j + 3 < V; j += 4) { row[j] *= f; row[j + 1] *= f; row[j + 2] *= f; row[j + 3] *= f; }
+            for (; j < V; j++) row[j] *= f;
+            for (j = 0; j < first; j++) row[j] *= f;
+        }
         if (endpoint_path) {
 #pragma unroll
             for (int e = 0; e < CPRE; e++)                           // tokens of one node are distinct
