@@ -636,7 +636,9 @@ __global__ void __launch_bounds__(128, HD <= 32 ? 4 : 1) attn_bwd_mma_kernel(con
     const int D = H * HD, hoff = h * HD;
     const int i0 = t * M;
     const int nt = min(M, n - i0);
-    const int q0 = warp * 16 + g, q1 = q0 + 8;            // tile-local query rows of this thread
+    // tile-local query rows of this thread (pairing an early with a late group of 8 rows per warp, to even out the
+    // triangular work between the warps, was measured slower: more 16 x 8 blocks become live)
+    const int q0 = warp * 16 + g, q1 = q0 + 8;
     const int r0 = i0 + q0, r1 = i0 + q1;
     const bool act0 = r0 < n, act1 = r1 < n;
     const int64_t coff = chain_off[t];
