@@ -84,6 +84,26 @@ class RadixTrie:
         return cls(h)
 
     @classmethod
+    def build_gpu(cls, corpus, max_depth: int, subtree_level: int = 1, prune_min_mass: int = 1, prune_min_depth: int = 4,
+                  device: int = 0) -> "RadixTrie":
+        """The same trie as build(), with the suffix ordering done on the GPU."""
+        c = _np_i32(corpus)
+        h = C.c_void_p()
+        check(lib().agpt_b200_trie_build_gpu(_vp(c), c.size, max_depth, subtree_level, prune_min_mass, prune_min_depth, device,
+                                             C.byref(h)), "trie_build_gpu")
+        return cls(h)
+
+    @classmethod
+    def from_suffix_order(cls, corpus, max_depth: int, sa, lcp, subtree_level: int = 1, prune_min_mass: int = 1,
+                          prune_min_depth: int = 4) -> "RadixTrie":
+        """The same trie as build(), assembled from a given suffix order (see agpt_b200_trie_from_suffix_order)."""
+        c, sa, lcp = _np_i32(corpus), _np_i32(sa), _np_i32(lcp)
+        h = C.c_void_p()
+        check(lib().agpt_b200_trie_from_suffix_order(_vp(c), c.size, max_depth, subtree_level, prune_min_mass, prune_min_depth,
+                                                     _vp(sa), _vp(lcp), C.byref(h)), "trie_from_suffix_order")
+        return cls(h)
+
+    @classmethod
     def load_dir(cls, path: str) -> "RadixTrie":
         h = C.c_void_p()
         check(lib().agpt_b200_trie_load_dir(path.encode(), C.byref(h)), "trie_load_dir")
@@ -476,6 +496,15 @@ def optimizer_step(kind, params, grads, m=None, v=None, lr=1e-3, beta1=0.9, beta
                                          beta2, eps, t, weight_decay, clip_norm, int(zero_grads), _dp(scratch), _stream()),
           "optimizer_step")
     return scratch.view(torch.float32)[1024:1025] if scratch is not None else None
+
+
+def suffix_order_gpu(corpus, key_len: int, device: int = 0):
+    """(sa, lcp, device milliseconds): start positions 0..n-2 ordered by their first key_len tokens, on the GPU."""
+    c = _np_i32(corpus)
+    sa, lcp = np.empty(c.size - 1, np.int32), np.empty(c.size - 1, np.int32)
+    ms = C.c_float(0)
+    check(lib().agpt_b200_suffix_order_gpu(_vp(c), c.size, key_len, device, _vp(sa), _vp(lcp), C.byref(ms)), "suffix_order_gpu")
+    return sa, lcp, float(ms.value)
 
 
 def device_status() -> int:

@@ -10,7 +10,8 @@ SO = os.path.join(HERE, "libagpt_b200.so")
 SOURCES = [os.path.join(HERE, "csrc", "kernels.cu"), os.path.join(HERE, "csrc", "dense.cu"),
            os.path.join(HERE, "csrc", "rowops.cu"), os.path.join(HERE, "csrc", "optim.cu"),
            os.path.join(HERE, "csrc", "gemm3x.cu"), os.path.join(HERE, "csrc", "gemm_sm100.cu"),
-           os.path.join(HERE, "csrc", "host_trie.cpp")]
+           os.path.join(HERE, "csrc", "host_trie.cpp"), os.path.join(HERE, "csrc", "trie_suffix.cpp"),
+           os.path.join(HERE, "csrc", "trie_gpu.cu")]
 
 
 def cutlass_include():

@@ -128,25 +128,6 @@ extern "C" int agpt_b200_rope_table(float *cos_out, float *sin_out, int max_seq,
 // --------------------------------------------------------------------------------------
 // radix trie
 // --------------------------------------------------------------------------------------
-struct agpt_trie {
-    int32_t radix_count = 0, n_depth_files = 0;
-    int64_t total_edge_chars = 0, leveled_nodes = 0;
-    std::vector<int32_t> parent, first_char_depth, edge_len, edge_mass, endpoint_depth, subtree_key, edge_start;
-    std::vector<int64_t> edge_off, cnt_off;
-    std::vector<int32_t> edge_tok, cnt_tok, cnt_val;
-    void finish_char_positions() {
-        // char positions follow depth-file order (src/cuda/agpt_train.cu:813-846)
-        edge_start.assign(radix_count, 0);
-        std::vector<int64_t> per_depth(n_depth_files + 1, 0);
-        for (int32_t r = 1; r < radix_count; r++) per_depth[endpoint_depth[r] + 1] += edge_len[r];
-        for (int d = 0; d < n_depth_files; d++) per_depth[d + 1] += per_depth[d];
-        for (int32_t r = 1; r < radix_count; r++) {
-            edge_start[r] = (int32_t)per_depth[endpoint_depth[r]];
-            per_depth[endpoint_depth[r]] += edge_len[r];
-        }
-    }
-};
-
 namespace {
 // Depth-capped suffix trie in level order; children of a node are id-contiguous.
 struct Leveled {

@@ -7,6 +7,27 @@
 
 int agpt_set_error(int code, const char *fmt, ...);
 
+// Radix trie with the reference's node numbering (ids in the builder's breadth-first emission order), counts, edge
+// mass and char positions.
+struct agpt_trie {
+    int32_t radix_count = 0, n_depth_files = 0;
+    int64_t total_edge_chars = 0, leveled_nodes = 0;
+    std::vector<int32_t> parent, first_char_depth, edge_len, edge_mass, endpoint_depth, subtree_key, edge_start;
+    std::vector<int64_t> edge_off, cnt_off;
+    std::vector<int32_t> edge_tok, cnt_tok, cnt_val;
+    void finish_char_positions() {
+        // char positions follow depth-file order (src/cuda/agpt_train.cu:813-846)
+        edge_start.assign(radix_count, 0);
+        std::vector<int64_t> per_depth(n_depth_files + 1, 0);
+        for (int32_t r = 1; r < radix_count; r++) per_depth[endpoint_depth[r] + 1] += edge_len[r];
+        for (int d = 0; d < n_depth_files; d++) per_depth[d + 1] += per_depth[d];
+        for (int32_t r = 1; r < radix_count; r++) {
+            edge_start[r] = (int32_t)per_depth[endpoint_depth[r]];
+            per_depth[endpoint_depth[r]] += edge_len[r];
+        }
+    }
+};
+
 // Walker plan: a tree laid out in depth-first pre-order.  Position i's subtree is the
 // interval [i, sub_end[i]); a is an ancestor-or-self of i iff a <= i < sub_end[a].  Queries
 // are processed in tiles of tile_m consecutive positions; a tile's keys are the ancestor

@@ -136,6 +136,21 @@ int agpt_b200_trie_load_dir(const char *dir, agpt_trie **out);
 int agpt_b200_trie_save_dir(const agpt_trie *t, const char *dir, int per_subtree, int32_t corpus_tokens,
                             int32_t vocab, uint64_t corpus_hash, const char *tokenizer_tag);
 int agpt_b200_trie_info(const agpt_trie *t, agpt_trie_info *out);
+/* The same trie (identical arrays, node for node) built from a suffix order: sa[0 .. n-2] are the start positions
+ * 0 .. n-2 ordered by their first max_depth + 1 tokens (a position past the end of the corpus orders before every
+ * token), lcp[i] the number of equal leading tokens of sa[i-1] and sa[i] within those max_depth + 1 (lcp[0] = 0).
+ * agpt_b200_suffix_order_gpu computes both on the device (one stable radix pass per token of the key, then one
+ * thread per neighbouring pair; device_ms_out, if not NULL, receives the device time); agpt_b200_trie_build_gpu
+ * chains the two.  They replace the bucket refinement of the level-by-level build
+ * (src/agpt/streaming_leveled_builder.cr:31-118) and the breadth-first compression
+ * (src/agpt/streaming_radix_builder.cr:103-343) by a sort and a linear pass.  n must be at least max_depth + 2. */
+int agpt_b200_trie_from_suffix_order(const int32_t *corpus, int64_t n, int max_depth, int subtree_level,
+                                     int prune_min_mass, int prune_min_depth, const int32_t *sa, const int32_t *lcp,
+                                     agpt_trie **out);
+int agpt_b200_suffix_order_gpu(const int32_t *corpus, int64_t n, int key_len, int device, int32_t *sa_out,
+                               int32_t *lcp_out, float *device_ms_out);
+int agpt_b200_trie_build_gpu(const int32_t *corpus, int64_t n, int max_depth, int subtree_level, int prune_min_mass,
+                             int prune_min_depth, int device, agpt_trie **out);
 void agpt_b200_trie_free(agpt_trie *t);
 /* FNV-1a corpus hash (src/agpt/trie_corpus.cr:120-134). */
 uint64_t agpt_b200_token_hash(const int32_t *tokens, int64_t n);

@@ -128,3 +128,30 @@ class MemTrie:
                 nxt += [self.children[v][t] for t in sorted(self.children[v])]
             level = nxt
         return out
+
+
+def suffix_order(corpus, key_len):
+    """Start positions 0..n-2 ordered by their first key_len tokens (a shorter key orders before its extensions), and
+    the number of equal leading tokens of neighbours: the input of the suffix-order trie builder, in plain Python."""
+    c = [int(x) for x in corpus]
+    n = len(c)
+    sa = sorted(range(n - 1), key=lambda s: (tuple(c[s:s + key_len]), s))
+    lcp = [0] * (n - 1)
+    for i in range(1, n - 1):
+        a, b = c[sa[i - 1]:sa[i - 1] + key_len], c[sa[i]:sa[i] + key_len]
+        l = 0
+        while l < len(a) and l < len(b) and a[l] == b[l]:
+            l += 1
+        lcp[i] = l
+    return np.asarray(sa, np.int32), np.asarray(lcp, np.int32)
+
+
+TRIE_ARRAYS = ("parent", "first_char_depth", "edge_len", "edge_mass", "endpoint_depth", "subtree_key", "edge_start", "edge_off",
+               "edge_tok", "cnt_off", "cnt_tok", "cnt_val")
+
+
+def assert_same_trie(a, b):
+    assert (a.radix_count, a.n_depth_files, a.total_edge_chars, a.leveled_nodes) == \
+        (b.radix_count, b.n_depth_files, b.total_edge_chars, b.leveled_nodes)
+    for name in TRIE_ARRAYS:
+        assert np.array_equal(getattr(a, name), getattr(b, name)), name

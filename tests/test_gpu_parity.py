@@ -524,3 +524,26 @@ def test_gemm_f32_tensor_core(shape, gemm_impl):
 def test_device_status_word_is_clear(cuda):
     """Every bounded wait on the device completed: the status word stays 0 after the kernels above ran."""
     assert A.device_status() == 0
+
+
+@pytest.mark.parametrize("n,vocab,order,depth", [(200, 3, 1, 12), (20_000, 65, 2, 8), (150_000, 65, 3, 32), (30_000, 300, 2, 10),
+                                                   (40_000, 96, 4, 128)])
+def test_trie_build_gpu_equals_host_builder(cuda, n, vocab, order, depth):
+    """Suffix order on the GPU (bit-exact against a plain sort on the small case) and the trie assembled from it
+    against the level-by-level host builder, array for array, with bigram keys and pruning."""
+    from tests.helpers import assert_same_trie, suffix_order
+    corpus = A.synth_markov_corpus(n, vocab, order, 17)
+    if vocab == 300:
+        corpus = np.random.default_rng(3).integers(0, 300, n).astype(np.int32)        # more symbols than one byte holds
+    sa, lcp, ms = A.suffix_order_gpu(corpus, depth + 1)
+    assert sorted(sa.tolist()) == list(range(n - 1)) and ms > 0
+    if n <= 20_000:
+        want_sa, want_lcp = suffix_order(corpus, depth + 1)
+        assert np.array_equal(lcp, want_lcp)
+        # equal keys may come in any order; compare the keys themselves
+        key = lambda s: tuple(corpus[s:s + depth + 1].tolist())  # noqa: E731
+        assert [key(s) for s in sa] == [key(s) for s in want_sa]
+    for level, mass, mdepth in ((1, 1, 4), (2, 2, 4)):
+        want = A.RadixTrie.build(corpus, depth, subtree_level=level, prune_min_mass=mass, prune_min_depth=mdepth)
+        got = A.RadixTrie.build_gpu(corpus, depth, subtree_level=level, prune_min_mass=mass, prune_min_depth=mdepth)
+        assert_same_trie(got, want)

@@ -198,3 +198,26 @@ def test_rope_table_matches_oracle():
         c, s = A.rope_table(128, hd)
         co, so = O.rope_table(128, hd)
         assert np.array_equal(c, co) and np.array_equal(s, so)
+
+
+@pytest.mark.parametrize("vocab,order,n,depth", [(2, 1, 40, 6), (3, 1, 200, 8), (4, 2, 500, 5), (12, 2, 1500, 8), (65, 3, 3000, 16),
+                                                   (5, 1, 64, 30), (2, 1, 12, 10), (96, 4, 2500, 40)])
+def test_trie_from_suffix_order_equals_level_builder(vocab, order, n, depth):
+    """The linear assembly from a suffix order reproduces the level-by-level builder array for array: ids, edges,
+    masses, counts, keys, char positions; unigram and bigram keys; with and without pruning; small alphabets and deep
+    tries make many suffixes run into the end of the corpus."""
+    from tests.helpers import assert_same_trie, suffix_order
+    for seed in range(4):
+        corpus = A.synth_markov_corpus(n, vocab, order, seed)
+        sa, lcp = suffix_order(corpus, depth + 1)
+        for level, mass, mdepth in ((1, 1, 4), (2, 1, 4), (1, 2, 2), (2, 3, 1), (1, 2, 4)):
+            want = A.RadixTrie.build(corpus, depth, subtree_level=level, prune_min_mass=mass, prune_min_depth=mdepth)
+            got = A.RadixTrie.from_suffix_order(corpus, depth, sa, lcp, subtree_level=level, prune_min_mass=mass,
+                                                prune_min_depth=mdepth)
+            assert_same_trie(got, want)
+
+
+def test_trie_from_suffix_order_rejects_short_corpus():
+    corpus = A.synth_markov_corpus(8, 3, 1, 0)
+    with pytest.raises(A.AgptError):
+        A.RadixTrie.from_suffix_order(corpus, 8, np.arange(7, dtype=np.int32), np.zeros(7, np.int32))
