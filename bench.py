@@ -104,7 +104,7 @@ class Unit:
     __slots__ = ("parent", "n", "tokens", "q2n", "qoff", "radix_ids", "mass_w", "n_ctx")
 
 
-def build_units(wl, rank, world, log, single_unit=False, group_rows=4_000_000):
+def build_units(wl, rank, world, log, single_unit=False, group_rows=4_000_000, device=None):
     import agpt_b200 as A
     cfg = WORKLOADS[wl]
     t0 = time.time()
@@ -117,7 +117,10 @@ def build_units(wl, rank, world, log, single_unit=False, group_rows=4_000_000):
                   np.ones(parent.size + 1, np.int32))
     else:
         corpus = A.synth_markov_corpus(cfg["chars"], cfg["vocab"], cfg["order"], 0)
-        trie = A.RadixTrie.build(corpus, cfg["depth"], subtree_level=1 if world == 1 else 2)
+        # the GPU arm orders the suffixes on its device; the CPU arm uses the level-by-level host builder (same arrays)
+        level_key = 1 if world == 1 else 2
+        trie = (A.RadixTrie.build(corpus, cfg["depth"], subtree_level=level_key) if device is None else
+                A.RadixTrie.build_gpu(corpus, cfg["depth"], subtree_level=level_key, device=device))
         parent, token, _, radix_of = trie.char_tree()
         edge_mass = trie.edge_mass
         counts = (trie.cnt_off.astype(np.int32), trie.cnt_tok, trie.cnt_val)
@@ -260,7 +263,7 @@ def run_gpu(args):
     cfg = WORKLOADS[args.workload]
     H, hd, V = cfg["heads"], cfg["head_dim"], cfg["vocab"]
     D = H * hd
-    units, counts, total_nodes, gplan = build_units(args.workload, rank, world, log, args.single_unit, args.group_rows)
+    units, counts, total_nodes, gplan = build_units(args.workload, rank, world, log, args.single_unit, args.group_rows, device=local)
     n_rank = sum(u.n for u in units)
     n_max = max(u.n for u in units)
     log(f"{len(units)} launch groups, {n_rank} rows on this rank (largest {n_max}); {total_nodes} positions in the trie")
@@ -416,7 +419,7 @@ def run_gpu(args):
     if rank == 0 and world == 1 and not args.no_cpu:
         from oracle import pyoracle as O
         O.set_num_threads(os.cpu_count() or 1)
-        small, _, _, _ = build_units(args.workload, 0, 1, lambda s: None, group_rows=100_000)
+        small, _, _, _ = build_units(args.workload, 0, 1, lambda s: None, group_rows=100_000, device=local)
         nps, cores, sample, _ = cpu_arm(small, cfg, args.cpu_nodes, counts)
         cpu = {"value": nps, "unit": "nodes/s", "cores": cores, "kind": "port", "sample": sample}
 
@@ -448,7 +451,7 @@ def run_epoch(args, cfg, rank, world, dev, log):
     from agpt_b200 import trainer as T
     D = cfg["heads"] * cfg["head_dim"]
     corpus = A.synth_markov_corpus(cfg["chars"], cfg["vocab"], cfg["order"], 0)
-    trie = A.RadixTrie.build(corpus, cfg["depth"], subtree_level=2)
+    trie = A.RadixTrie.build_gpu(corpus, cfg["depth"], subtree_level=2, device=dev.index)
     mf = MF.random_init(D, cfg["heads"], cfg["layers"], cfg["vocab"], max(128, cfg["depth"]), seed=0)
     groups, total = T.build_groups(trie, rank, world, args.epoch_group_rows, "linear", mf.seq_len, dev, level=2)
     counts = [torch.from_numpy(np.ascontiguousarray(c)).to(dev) for c in (trie.cnt_off.astype(np.int32), trie.cnt_tok, trie.cnt_val)]
