@@ -603,6 +603,30 @@ def mass_weights(edge_mass, edge_len, mode: str = "linear") -> np.ndarray:
     return np.repeat((w / mean).astype(np.float32), el)
 
 
+def mass_weights_by_unit(edge_mass, edge_len, unit_of_node, counted, n_units: int, mode: str = "linear") -> np.ndarray:
+    """Per-query mass weights where the mean is taken inside each unit (a root-child or bigram subtree) instead of over
+    whatever rows share a launch: the weights then do not depend on how units are packed or spread over ranks.
+    edge_mass, edge_len, unit_of_node, counted: one entry per loss node; nodes with counted == False (context rows)
+    get a weight but do not enter the mean."""
+    em = np.asarray(edge_mass, dtype=np.float32)
+    el = np.asarray(edge_len, dtype=np.int64)
+    un = np.asarray(unit_of_node, dtype=np.int64)
+    inc = np.asarray(counted, dtype=bool)
+    if mode == "log":
+        w = np.log(np.float32(1.0) + em, dtype=np.float32)
+    elif mode == "sqrt":
+        w = np.sqrt(em, dtype=np.float32)
+    elif mode == "linear":
+        w = em
+    else:
+        w = np.ones_like(em)
+    tot = np.bincount(un[inc], weights=(w.astype(np.float64) * el)[inc], minlength=n_units)
+    tq = np.bincount(un[inc], weights=el[inc].astype(np.float64), minlength=n_units)
+    mean = np.where(tq > 0, tot / np.maximum(tq, 1), 1.0).astype(np.float32)
+    mean[mean <= 0] = np.float32(1.0)
+    return np.repeat((w / mean[un]).astype(np.float32), el)
+
+
 # legacy kernel boundary -------------------------------------------------------------------
 def legacy_attention(q, k, v, kv_offsets, kv_lengths, n_heads, head_dim, max_len, scale, query_to_node=None,
                      query_offsets=None):

@@ -373,20 +373,25 @@ __global__ void __launch_bounds__(128) attn_fwd_mma_kernel(const float *__restri
             s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = -INFINITY;
             if (!__any_sync(0xffffffffu, v0 | v1 | v2 | v3)) continue;
             live |= 1u << nb;
-            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            // the three products of a score accumulate in separate chains (two at head_dim <= 32, where a third
+            // accumulator would cost a resident block): dependent MMAs are what a warp waits on here
+            float c[4] = {0.f, 0.f, 0.f, 0.f}, cx[4] = {0.f, 0.f, 0.f, 0.f}, cy[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int ks = 0; ks < KS; ks++) {
                 const float b0 = kv_f32(sK[nb * 8 + g][ks * 8 + tig]), b1 = kv_f32(sK[nb * 8 + g][ks * 8 + tig + 4]);
                 if (SPLIT_KV) {
                     uint32_t h0, lo0, h1, lo1;
                     tf32_split(b0, h0, lo0); tf32_split(b1, h1, lo1);
-                    mma_tf32(c, qh[ks], h0, h1); mma_tf32(c, ql[ks], h0, h1); mma_tf32(c, qh[ks], lo0, lo1);
+                    mma_tf32(c, qh[ks], h0, h1); mma_tf32(cx, ql[ks], h0, h1);
+                    if (HD >= 64) mma_tf32(cy, qh[ks], lo0, lo1);
+                    else mma_tf32(cx, qh[ks], lo0, lo1);
                 } else {
                     // bf16 store: K is exact in TF32 and the store's own rounding (2^-9) dwarfs TF32's (2^-11) on Q,
                     // so one product is enough for the bf16-store tolerance
                     mma_tf32(c, qh[ks], __float_as_uint(b0), __float_as_uint(b1));
                 }
             }
+            c[0] += cx[0] + cy[0]; c[1] += cx[1] + cy[1]; c[2] += cx[2] + cy[2]; c[3] += cx[3] + cy[3];
             if (v0) s[nb][0] = c[0];
             if (v1) s[nb][1] = c[1];
             if (v2) s[nb][2] = c[2];

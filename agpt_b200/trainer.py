@@ -24,9 +24,15 @@ from . import model_file as MF
 
 
 class LaunchGroup:
-    """Rows of one launch: local forest (depth-first), tokens, RoPE positions and the loss index arrays."""
+    """Rows of one launch: local forest (depth-first), tokens, RoPE positions and the loss index arrays.
 
-    def __init__(self, parent, tokens, depth, radix_of, edge_mass, mass_mode, seq_len, device, tile=64, trained=None):
+    A launch packs several units (root-child or bigram subtrees).  What the reference normalises per chunk -- the
+    mass weights by their mean (src/cuda/agpt_train.cu:4608-4637) and the gradient by the number of trained queries
+    (:4834) -- is normalised here per unit (unit_of_row), so that results do not depend on how units are packed into
+    launches or spread over ranks."""
+
+    def __init__(self, parent, tokens, depth, radix_of, edge_mass, mass_mode, seq_len, device, tile=64, trained=None,
+                 unit_of_row=None):
         import torch
         self.n = int(parent.size)
         self.plan = A.WalkerPlan(parent, tile, device.index)
@@ -39,12 +45,18 @@ class LaunchGroup:
         starts = np.concatenate([[True], radix_of[1:] != radix_of[:-1]])
         if trained is not None:                      # a context row never shares a loss node with trained rows
             starts |= np.concatenate([[True], trained[1:] != trained[:-1]])
+        unit_of_row = np.zeros(self.n, np.int64) if unit_of_row is None else np.asarray(unit_of_row, np.int64)
+        starts |= np.concatenate([[True], unit_of_row[1:] != unit_of_row[:-1]])
+        self.n_units = int(unit_of_row.max()) + 1 if self.n else 0
+        self.unit_of_row = t(unit_of_row)
         qoff = np.concatenate([np.nonzero(starts)[0], [self.n]]).astype(np.int32)
         rid = radix_of[starts].astype(np.int32)
         self.q2n = t((np.cumsum(starts) - 1).astype(np.int32))
         self.qoff = t(qoff)
         self.rid = t(rid)
-        mw = A.mass_weights(edge_mass[rid], np.diff(qoff), mass_mode) if mass_mode != "off" else None
+        counted = np.ones(rid.size, bool) if trained is None else trained[starts]
+        mw = (A.mass_weights_by_unit(edge_mass[rid], np.diff(qoff), unit_of_row[starts], counted, self.n_units, mass_mode)
+              if mass_mode != "off" else None)
         self.trained = None if trained is None else t(trained.astype(np.float32))
         self.mass_w = None if mw is None else t(mw)
         self.n_trained_rows = self.n if trained is None else int(trained.sum())
@@ -68,16 +80,18 @@ def build_groups(trie: A.RadixTrie, rank: int, world: int, group_rows: int, mass
         nonlocal pieces, rows
         if not pieces:
             return
-        off, pars, ids, trained = 0, [], [], []
-        for pp, idv, tr in pieces:
+        off, pars, ids, trained, units = 0, [], [], [], []
+        for u, (pp, idv, tr) in enumerate(pieces):
             pars.append(np.where(pp < 0, -1, pp + off))
             ids.append(idv)
             trained.append(tr)
+            units.append(np.full(idv.size, u, np.int64))
             off += idv.size
         idv = np.concatenate(ids)
         tr = np.concatenate(trained)
         groups.append(LaunchGroup(np.concatenate(pars).astype(np.int32), token[idv], depth[idv], radix_of[idv],
-                                  trie.edge_mass, mass_mode, seq_len, device, tile, None if tr.all() else tr))
+                                  trie.edge_mass, mass_mode, seq_len, device, tile, None if tr.all() else tr,
+                                  np.concatenate(units)))
         pieces, rows = [], 0
 
     for b, e, o in zip(ub, ue, owner):
@@ -305,9 +319,11 @@ class TrieWalkModel:
         pos = loss > 0
         n_trained = pos.sum()
         loss_sum = torch.where(pos, loss, torch.zeros_like(loss)).sum(dtype=torch.float64)
-        # every gradient of the group is scaled by 1 / (its trained queries) (src/cuda/agpt_train.cu:4834)
-        scale = torch.where(n_trained > 0, 1.0 / n_trained.clamp(min=1).to(torch.float32), torch.zeros((), device=loss.device))
-        logits.backward(dlogits * scale)
+        # every gradient row is scaled by 1 / (trained queries of its unit): the reference's per-chunk scaling
+        # (src/cuda/agpt_train.cu:4834) with the unit as the chunk
+        per_unit = torch.zeros(group.n_units, dtype=torch.float32, device=loss.device).index_add_(0, group.unit_of_row, pos.to(torch.float32))
+        scale = torch.where(per_unit > 0, 1.0 / per_unit.clamp(min=1.0), torch.zeros_like(per_unit))
+        logits.backward(dlogits * scale[group.unit_of_row][:, None])
         if sync:
             return float(loss_sum.item()), int(n_trained.item())
         return torch.stack([loss_sum.to(torch.float32), n_trained.to(torch.float32)])

@@ -12,7 +12,7 @@ from tests.helpers import TOL_BF16, TOL_F32, rel_err
 pytestmark = pytest.mark.gpu
 
 
-def _reference(mf, parent, tokens, depth, q2n, qoff, rid, counts, mass_w, lam, iw, trained):
+def _reference(mf, parent, tokens, depth, q2n, qoff, rid, counts, mass_w, lam, iw, trained, unit_of_row):
     """Dense reference: float64 torch autograd, mask[i, a] = a is an ancestor-or-self of i."""
     import torch
     import torch.nn.functional as F
@@ -58,7 +58,9 @@ def _reference(mf, parent, tokens, depth, q2n, qoff, rid, counts, mass_w, lam, i
         loss = loss * trained
         dlog = dlog * trained[:, None]
     n_tr = int((loss > 0).sum())
-    logits.backward(torch.from_numpy(dlog.astype(np.float64)) / n_tr)
+    per_unit = np.bincount(unit_of_row, weights=(loss > 0).astype(np.float64), minlength=int(unit_of_row.max()) + 1)
+    scale = np.where(per_unit > 0, 1.0 / np.maximum(per_unit, 1), 0.0)[unit_of_row]      # per-unit 1 / trained queries
+    logits.backward(torch.from_numpy(dlog.astype(np.float64) * scale[:, None]))
     return float(loss[loss > 0].sum()), n_tr, {k: v.grad.numpy() for k, v in P.items()}, logits.detach().numpy()
 
 
@@ -84,7 +86,8 @@ def test_group_step_matches_dense_reference(cuda, world, bf16):
             tr = None if g.trained is None else g.trained.cpu().numpy()
             rl, rq, rg, _ = _reference(mf, g.plan.parent_dfs.copy(), g.tokens32.cpu().numpy(), g.plan.depth.copy(),
                                        g.q2n.cpu().numpy(), g.qoff.cpu().numpy(), g.rid.cpu().numpy(), counts_np,
-                                       None if g.mass_w is None else g.mass_w.cpu().numpy(), lam, iw, tr)
+                                       None if g.mass_w is None else g.mass_w.cpu().numpy(), lam, iw, tr,
+                                       g.unit_of_row.cpu().numpy())
             ref_loss += rl
             ref_q += rq
             ref_grads = rg if ref_grads is None else {k: ref_grads[k] + rg[k] for k in rg}
@@ -153,3 +156,31 @@ def test_flat_optimizer_matches_torch(cuda, name):
         assert float(model.flat_grad[:model.n_flat].abs().max()) == 0.0
         for sp, p in zip(shadow, model.parameters()):
             assert float((sp - p).abs().max()) < 1e-5 * max(1.0, float(p.abs().max()))
+
+
+def test_gradients_do_not_depend_on_packing_or_rank_count(cuda):
+    """Same bigram units, packed into launches of different sizes and spread over 1 or 3 ranks: the summed loss and
+    the summed gradients agree (mass weights and the 1/trained-queries scale are normalised per unit)."""
+    import torch
+    corpus = A.synth_markov_corpus(1500, 12, 2, 8)
+    trie = A.RadixTrie.build(corpus, 7, subtree_level=2)
+    mf = MF.random_init(32, 2, 1, 12, 16, seed=3, std=0.2)
+    counts = [torch.from_numpy(np.ascontiguousarray(c)).to(cuda) for c in (trie.cnt_off.astype(np.int32), trie.cnt_tok, trie.cnt_val)]
+    results = []
+    for world, rows in ((1, 100000), (1, 300), (3, 700)):
+        total = None
+        loss_sum, n_q = 0.0, 0
+        for rank in range(world):
+            groups, _ = T.build_groups(trie, rank, world, rows, "linear", mf.seq_len, cuda, level=2)
+            model = T.TrieWalkModel(mf, cuda)
+            for g in groups:
+                ls, nq = model.group_step(g, counts, entropy_lambda=0.3)
+                loss_sum += ls
+                n_q += nq
+            flat = model.flat_grad[:model.n_flat].double().cpu().numpy()
+            total = flat if total is None else total + flat
+        results.append((loss_sum, n_q, total))
+    for loss_sum, n_q, total in results[1:]:
+        assert n_q == results[0][1]
+        assert abs(loss_sum - results[0][0]) / results[0][0] < 1e-5
+        assert rel_err(total, results[0][2], floor=1e-6) < 1e-4
