@@ -230,7 +230,7 @@ class TrieWalkModel:
         self.cfg = model
         self.device = device
         # one flat weight buffer and one flat gradient buffer (the reference's d_weights / d_grads), each matrix on a
-        # 16-byte boundary; the gradient buffer ends with two floats for the epoch's loss sum and query count so that
+        # 16-byte boundary; the gradient buffer ends with the epoch's loss sum and query count (three floats) so that
         # one all-reduce carries everything
         offs, off = [], 0
         for _, a in model.mats:
@@ -307,7 +307,8 @@ class TrieWalkModel:
                    bf16_store=False, sync=True):
         """Forward, loss and backward of one launch group; gradients accumulate into .grad.
         Returns (sum of positive per-query losses, number of such queries): Python numbers, or with sync=False a
-        float32 device tensor of the two, so that the host does not wait for the device between groups."""
+        float32 device tensor (loss sum, count // 4096, count % 4096), so that the host does not wait for the device
+        between groups."""
         import torch
         logits = self.logits(group, bf16_store).contiguous()
         c_off, c_tok, c_val = counts
@@ -326,7 +327,8 @@ class TrieWalkModel:
         logits.backward(dlogits * scale[group.unit_of_row][:, None])
         if sync:
             return float(loss_sum.item()), int(n_trained.item())
-        return torch.stack([loss_sum.to(torch.float32), n_trained.to(torch.float32)])
+        # the count rides in float32 next to the gradients: split so that sums over groups and ranks stay exact
+        return torch.stack([loss_sum.to(torch.float32), (n_trained // 4096).to(torch.float32), (n_trained % 4096).to(torch.float32)])
 
 
 class FlatOptimizer:
@@ -380,7 +382,7 @@ def train_epoch(model: TrieWalkModel, groups, counts, opt, accumulate=True, worl
     import torch.distributed as dist
     model.bind_grads()
     opt.zero_grad(set_to_none=False)
-    tail = model.flat_grad[model.n_flat:model.n_flat + 2]
+    tail = model.flat_grad[model.n_flat:model.n_flat + 3]
     for g in groups:
         tail += model.group_step(g, counts, sync=False, **loss_kw)
         if not accumulate:
@@ -390,7 +392,7 @@ def train_epoch(model: TrieWalkModel, groups, counts, opt, accumulate=True, worl
             dist.all_reduce(model.flat_grad)
         opt.step()
     stats = tail.cpu()
-    return float(stats[0]), int(round(float(stats[1])))
+    return float(stats[0]), int(round(float(stats[1]))) * 4096 + int(round(float(stats[2])))
 
 
 def main(argv=None):
