@@ -117,6 +117,21 @@ class RadixTrie:
         check(lib().agpt_b200_trie_save_dir(self._h, path.encode(), int(per_subtree), corpus_tokens, vocab,
                                             corpus_hash, tag.encode()), "trie_save_dir")
 
+    def lightning_sample(self, sampler: int, steps: int, rng_state: int, p_stop: float = 0.3, max_mass: int = 0):
+        """`steps` stochastic training units (see agpt_b200_lightning_sample).  Returns (sampled radix ids, ancestor
+        counts, node offsets, masses, node ids, new generator state)."""
+        st = C.c_uint32(rng_state)
+        total = lib().agpt_b200_lightning_sample(self._h, sampler, steps, p_stop, max_mass, C.byref(st), None, None, None, None, None, 0)
+        if total < 0:
+            check(int(total), "lightning_sample")
+        rs, na = np.zeros(steps, np.int32), np.zeros(steps, np.int32)
+        off, mass, nodes = np.zeros(steps + 1, np.int64), np.zeros(steps, np.float64), np.zeros(max(int(total), 1), np.int32)
+        got = lib().agpt_b200_lightning_sample(self._h, sampler, steps, p_stop, max_mass, C.byref(st), _vp(rs), _vp(na), _vp(off),
+                                               _vp(mass), _vp(nodes), nodes.size)
+        if got < 0:
+            check(int(got), "lightning_sample")
+        return rs, na, off, mass, nodes[:int(total)], int(st.value)
+
     def char_tree(self):
         """(parent, token, depth, radix_of_char) per char position, trainer numbering."""
         n = self.total_edge_chars

@@ -433,6 +433,107 @@ extern "C" int agpt_b200_trie_char_tree(const agpt_trie *t, int32_t *parent, int
 }
 
 // --------------------------------------------------------------------------------------
+// stochastic subtree sampling ("lightning" training units, src/cuda/agpt_train.cu:152-200, :3928-3943, :4060-4241)
+// --------------------------------------------------------------------------------------
+static inline uint32_t xorshift32(uint32_t *st) {
+    uint32_t x = *st;
+    x ^= x << 13; x ^= x >> 17; x ^= x << 5;
+    *st = x ? x : 1u;
+    return *st;
+}
+static inline float xorshift_unit(uint32_t *st) { return (float)xorshift32(st) / 4294967296.0f; }
+
+// One super-epoch of `steps` samples.  sampler: 1 uniform over radix nodes, 2 uniform over root children, 3 mass-weighted
+// walk from the root that stops with probability p_stop per level (never above max_mass when that is > 0), 4 the same
+// walk to a leaf.  A sample's training set is its ancestors, then the sampled node and its descendants breadth
+// first (sampler 4: the root-to-node path), stably ordered by endpoint depth.  Call with nodes_out == NULL to learn
+// the total number of node ids (the generator state is then left untouched), then again to fill.
+extern "C" int64_t agpt_b200_lightning_sample(const agpt_trie *t, int sampler, int steps, float p_stop, int64_t max_mass,
+                                              uint32_t *rng_state, int32_t *sample_out, int32_t *n_anc_out, int64_t *node_off_out,
+                                              double *mass_out, int32_t *nodes_out, int64_t nodes_cap) {
+    if (!t || !rng_state || steps < 0 || sampler < 1 || sampler > 4) return agpt_set_error(AGPT_E_ARG, "lightning_sample: bad argument");
+    const int32_t R = t->radix_count;
+    std::vector<int64_t> coff(R + 1, 0);
+    for (int32_t r = 1; r < R; r++) coff[t->parent[r] + 1]++;
+    for (int32_t r = 0; r < R; r++) coff[r + 1] += coff[r];
+    std::vector<int32_t> child((size_t)std::max<int64_t>(coff[R], 1));
+    {
+        std::vector<int64_t> pos(coff.begin(), coff.end() - 1);
+        for (int32_t r = 1; r < R; r++) child[pos[t->parent[r]]++] = r;
+    }
+    uint32_t rng = *rng_state;
+    auto root_child = [&]() -> int32_t {
+        int64_t nc = coff[1] - coff[0];
+        return nc > 0 ? child[coff[0] + (int64_t)(xorshift32(&rng) % (uint32_t)nc)] : 0;
+    };
+    std::vector<int32_t> buf, sorted;
+    int64_t total = 0;
+    for (int s = 0; s < steps; s++) {
+        int32_t pick_r = 0;
+        if (sampler == 3 || sampler == 4) {
+            const float stop = sampler == 4 ? 0.0f : p_stop;
+            int32_t cur = 0;
+            for (;;) {
+                const bool forced = max_mass > 0 && cur != 0 && (int64_t)t->edge_mass[cur] > max_mass;
+                if (cur != 0 && stop > 0.0f && !forced && xorshift_unit(&rng) < stop) break;
+                const int64_t cs = coff[cur], ce = coff[cur + 1];
+                if (ce == cs) break;
+                double tot = 0.0;
+                for (int64_t j = cs; j < ce; j++) tot += (double)t->edge_mass[child[j]];
+                int64_t pick;
+                if (tot <= 0.0) pick = cs + (int64_t)(xorshift32(&rng) % (uint32_t)(ce - cs));
+                else {
+                    const double u = (double)xorshift_unit(&rng) * tot;
+                    double acc = 0.0;
+                    pick = ce - 1;
+                    for (int64_t j = cs; j < ce; j++) {
+                        acc += (double)t->edge_mass[child[j]];
+                        if (u <= acc) { pick = j; break; }
+                    }
+                }
+                cur = child[pick];
+            }
+            pick_r = cur;
+        } else if (sampler == 1) {
+            if (R > 1) pick_r = 1 + (int32_t)(xorshift32(&rng) % (uint32_t)(R - 1));
+        } else pick_r = root_child();
+        if (pick_r == 0) pick_r = root_child();
+        buf.clear();
+        double mass = 0.0;
+        int32_t n_anc = 0;
+        if (sampler == 4) {
+            for (int32_t c = pick_r; c > 0; c = t->parent[c]) { buf.push_back(c); mass += (double)t->edge_mass[c]; }
+            std::reverse(buf.begin(), buf.end());
+        } else {
+            for (int32_t c = t->parent[pick_r]; c > 0; c = t->parent[c]) { buf.push_back(c); mass += (double)t->edge_mass[c]; }
+            std::reverse(buf.begin(), buf.end());
+            n_anc = (int32_t)buf.size();
+            size_t head = buf.size();
+            buf.push_back(pick_r);
+            mass += (double)t->edge_mass[pick_r];
+            while (head < buf.size()) {
+                const int32_t c = buf[head++];
+                for (int64_t j = coff[c]; j < coff[c + 1]; j++) { buf.push_back(child[j]); mass += (double)t->edge_mass[child[j]]; }
+            }
+        }
+        if (nodes_out) {
+            if (total + (int64_t)buf.size() > nodes_cap) return agpt_set_error(AGPT_E_ARG, "lightning_sample: node buffer too small");
+            // stable order by endpoint depth
+            sorted.assign(buf.begin(), buf.end());
+            std::stable_sort(sorted.begin(), sorted.end(), [&](int32_t a, int32_t b) { return t->endpoint_depth[a] < t->endpoint_depth[b]; });
+            std::copy(sorted.begin(), sorted.end(), nodes_out + total);
+            if (sample_out) sample_out[s] = pick_r;
+            if (n_anc_out) n_anc_out[s] = n_anc;
+            if (mass_out) mass_out[s] = mass;
+            if (node_off_out) { node_off_out[s] = total; node_off_out[s + 1] = total + (int64_t)buf.size(); }
+        }
+        total += (int64_t)buf.size();
+    }
+    if (nodes_out) *rng_state = rng;
+    return total;
+}
+
+// --------------------------------------------------------------------------------------
 // walker plan
 // --------------------------------------------------------------------------------------
 extern "C" int agpt_b200_plan_create(const int32_t *parent, int64_t n, int tile_m, int device, agpt_plan **out) {

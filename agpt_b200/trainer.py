@@ -331,6 +331,59 @@ class TrieWalkModel:
         return torch.stack([loss_sum.to(torch.float32), (n_trained // 4096).to(torch.float32), (n_trained % 4096).to(torch.float32)])
 
 
+class SampleSpace:
+    """What building the launch group of a sampled node set needs: the char tree of the whole trie in depth-first order."""
+
+    def __init__(self, trie: A.RadixTrie):
+        self.trie = trie
+        self.parent, self.token, self.depth, self.radix_of = trie.char_tree()
+        self.plan = A.WalkerPlan(self.parent, 64, -1)
+
+    def group(self, node_ids, context_ids, mass_mode, seq_len, device, tile=64) -> LaunchGroup:
+        """Launch group of the chars of the radix nodes node_ids (closed under "parent"); chars of context_ids are
+        attended but carry no loss (the sampled node's ancestors, src/cuda/agpt_train.cu:4160-4180)."""
+        t = self.trie
+        node_ids = np.asarray(node_ids, np.int64)
+        lens = t.edge_len[node_ids].astype(np.int64)
+        starts = t.edge_start[node_ids].astype(np.int64)
+        chars = np.repeat(starts - np.concatenate([[0], np.cumsum(lens)[:-1]]), lens) + np.arange(int(lens.sum()))
+        pos = self.plan.node_to_dfs[chars].astype(np.int64)
+        order = np.argsort(pos, kind="stable")
+        chars, pos = chars[order], pos[order]
+        ppos = self.plan.parent_dfs[pos].astype(np.int64)
+        local_parent = np.where(ppos < 0, -1, np.searchsorted(pos, ppos)).astype(np.int32)
+        if np.any((ppos >= 0) & (pos[np.minimum(local_parent, pos.size - 1)] != ppos)):
+            raise ValueError("the node set is not closed under parent")
+        trained = ~np.isin(self.radix_of[chars], np.asarray(context_ids, np.int64))
+        return LaunchGroup(local_parent, self.token[chars], self.depth[chars], self.radix_of[chars], t.edge_mass, mass_mode, seq_len,
+                           device, tile, None if trained.all() else trained)
+
+
+def train_lightning_epoch(model: TrieWalkModel, space: SampleSpace, counts, opt, sampler: int, steps: int, rng_state: int,
+                          mass_mode="off", p_stop=0.3, max_mass=0, **loss_kw):
+    """One super-epoch of the reference's lightning mode: `steps` sampled units, each its own gradient and optimizer step
+    (src/cuda/agpt_train.cu:152-157).  Returns (loss sum, queries, nodes trained, new generator state)."""
+    rs, na, off, _, nodes, rng_state = space.trie.lightning_sample(sampler, steps, rng_state, p_stop, max_mass)
+    model.bind_grads()
+    loss_sum, n_q, n_nodes = 0.0, 0, 0
+    for s in range(steps):
+        ids = nodes[off[s]:off[s + 1]]
+        context = []
+        if sampler != 4:                                         # the ancestors of the sampled node are context only
+            c = int(space.trie.parent[rs[s]])
+            while c > 0:
+                context.append(c)
+                c = int(space.trie.parent[c])
+        g = space.group(ids, context, mass_mode, model.cfg.seq_len, model.device)
+        opt.zero_grad(set_to_none=False)
+        ls, nq = model.group_step(g, counts, **loss_kw)
+        opt.step()
+        loss_sum += ls
+        n_q += nq
+        n_nodes += int(ids.size)
+    return loss_sum, n_q, n_nodes, rng_state
+
+
 class FlatOptimizer:
     """The library's fused step (clip, update, decay, clear gradients) over the model's flat buffers."""
 
@@ -417,6 +470,12 @@ def main(argv=None):
     ap.add_argument("--bf16-kv", action="store_true")
     ap.add_argument("--group-rows", type=int, default=1_000_000)
     ap.add_argument("--ffn-recompute", action="store_true", help="recompute the FFN activations in the backward (less memory)")
+    ap.add_argument("--lightning-sampler", default=None, choices=["l1", "l2", "l3", "l4"],
+                    help="stochastic training units instead of the deterministic sweep (one rank)")
+    ap.add_argument("--lightning-steps", type=int, default=65)
+    ap.add_argument("--lightning-p-stop", type=float, default=0.3)
+    ap.add_argument("--lightning-seed", type=lambda v: int(v, 0), default=0x5c115e1)
+    ap.add_argument("--lightning-max-mass", type=int, default=0)
     ap.add_argument("--partition-depth", type=int, default=0, choices=[0, 1, 2],
                     help="1 = root-child units, 2 = bigram units; 0 = 1 on one rank, 2 on several")
     args = ap.parse_args(argv)
@@ -433,8 +492,15 @@ def main(argv=None):
     if rank == 0:
         print(f"  Model: d={mf.d_model} heads={mf.n_heads} layers={mf.n_layers} ff={mf.d_ff} vocab={mf.vocab} seq={mf.seq_len}")
         print(f"  Radix trie: {trie.radix_count} nodes, {trie.total_edge_chars} total edge chars, {trie.n_depth_files} endpoint depths")
-    groups, total = build_groups(trie, rank, world, args.group_rows, args.mass_weight, mf.seq_len, dev,
-                                 level=args.partition_depth or None)
+    lightning = args.lightning_sampler is not None
+    if lightning and world > 1:
+        raise SystemExit("lightning sampling runs on one rank")
+    if lightning:
+        space, groups, total = SampleSpace(trie), [], trie.total_edge_chars
+    else:
+        groups, total = build_groups(trie, rank, world, args.group_rows, args.mass_weight, mf.seq_len, dev,
+                                     level=args.partition_depth or None)
+    rng_state = args.lightning_seed
     counts = [torch.from_numpy(np.ascontiguousarray(c)).to(dev) for c in (trie.cnt_off.astype(np.int32), trie.cnt_tok, trie.cnt_val)]
     model = TrieWalkModel(mf, dev)
     model.ffn_recompute = args.ffn_recompute
@@ -445,12 +511,19 @@ def main(argv=None):
     for ep in range(1, args.epochs + 1):
         torch.cuda.synchronize()
         t0 = time.time()
-        ls, nq = train_epoch(model, groups, counts, opt, accumulate=not args.no_accumulate or world > 1, world=world,
-                             entropy_lambda=args.entropy_lambda, intermediate_weight=args.intermediate_weight,
-                             ce_only=args.ce_only, bf16_store=args.bf16_kv)
+        loss_kw = dict(entropy_lambda=args.entropy_lambda, intermediate_weight=args.intermediate_weight, ce_only=args.ce_only,
+                       bf16_store=args.bf16_kv)
+        if lightning:
+            ls, nq, _, rng_state = train_lightning_epoch(model, space, counts, opt, int(args.lightning_sampler[1]), args.lightning_steps,
+                                                         rng_state, args.mass_weight, args.lightning_p_stop, args.lightning_max_mass,
+                                                         **loss_kw)
+            units, chunks = args.lightning_steps, args.lightning_steps
+        else:
+            ls, nq = train_epoch(model, groups, counts, opt, accumulate=not args.no_accumulate or world > 1, world=world, **loss_kw)
+            units, chunks = n_sub, len(groups)
         torch.cuda.synchronize()
         if rank == 0:
-            print(f"Epoch {ep}: loss={ls / max(nq, 1):.6f}  ({time.time() - t0:.2f} sec, {n_sub} subtrees, {len(groups)} chunks, {nq} nodes)",
+            print(f"Epoch {ep}: loss={ls / max(nq, 1):.6f}  ({time.time() - t0:.2f} sec, {units} subtrees, {chunks} chunks, {nq} nodes)",
                   flush=True)
             if args.save_every and ep % args.save_every == 0:
                 MF.save(f"{save}.ep{ep}", model.to_model_file())

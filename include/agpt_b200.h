@@ -151,6 +151,17 @@ int agpt_b200_suffix_order_gpu(const int32_t *corpus, int64_t n, int key_len, in
                                int32_t *lcp_out, float *device_ms_out);
 int agpt_b200_trie_build_gpu(const int32_t *corpus, int64_t n, int max_depth, int subtree_level, int prune_min_mass,
                              int prune_min_depth, int device, agpt_trie **out);
+/* Stochastic training units of the reference's "lightning" mode (src/cuda/agpt_train.cu:152-200, :4060-4241): `steps`
+ * samples from a 32-bit xorshift generator (*rng_state, the reference seeds it with 0x5c115e1).  sampler 1: uniform
+ * over radix nodes; 2: uniform over root children; 3: mass-weighted walk from the root that stops with probability
+ * p_stop at each level (forced on while the node's mass exceeds max_mass > 0); 4: the same walk down to a leaf.  A
+ * sample's node set is its ancestors (n_anc_out of them: context only), the sampled node and its descendants
+ * breadth first (sampler 4: the root-to-node path), stably ordered by endpoint depth; mass_out is the summed edge
+ * mass.  Returns the total number of node ids; with nodes_out == NULL nothing is written and the generator state is
+ * left as it was (call once to size nodes_out, once to fill). */
+int64_t agpt_b200_lightning_sample(const agpt_trie *t, int sampler, int steps, float p_stop, int64_t max_mass,
+                                   uint32_t *rng_state, int32_t *sample_out, int32_t *n_anc_out, int64_t *node_off_out,
+                                   double *mass_out, int32_t *nodes_out, int64_t nodes_cap);
 void agpt_b200_trie_free(agpt_trie *t);
 /* FNV-1a corpus hash (src/agpt/trie_corpus.cr:120-134). */
 uint64_t agpt_b200_token_hash(const int32_t *tokens, int64_t n);

@@ -457,3 +457,88 @@ def optimizer_step(kind, p, g, m, v, lr, beta1, beta2, eps, t, weight_decay=0.0,
     if weight_decay > 0:
         p = (p - lr * np.float32(weight_decay) * p).astype(np.float32)
     return p, m, v, norm
+
+
+# ---- stochastic training units ("lightning" sampling) ------------------------------------------------------------------
+# Restates src/cuda/agpt_train.cu:188-200 (generator), :3928-3943 (child adjacency in id order) and :4060-4241 (the four
+# samplers, the node set of a sample, its endpoint-depth bucket order).  Plain Python: for small tries only.
+
+def xorshift32(state):
+    x = state & 0xFFFFFFFF
+    x ^= (x << 13) & 0xFFFFFFFF
+    x ^= x >> 17
+    x ^= (x << 5) & 0xFFFFFFFF
+    return x if x else 1
+
+
+def lightning_sample(parent, edge_mass, first_char_depth, edge_len, sampler, steps, state, p_stop=0.3, max_mass=0):
+    """Returns ([(sampled id, ancestor count, summed mass, node ids)], new generator state)."""
+    R = len(parent)
+    kids = [[] for _ in range(R)]
+    for r in range(1, R):
+        kids[int(parent[r])].append(r)
+
+    def unit():
+        nonlocal state
+        state = xorshift32(state)
+        return float(np.float32(state) / np.float32(4294967296.0))
+
+    def below(n):
+        nonlocal state
+        state = xorshift32(state)
+        return state % n
+
+    def root_child():
+        return kids[0][below(len(kids[0]))] if kids[0] else 0
+
+    out = []
+    for _ in range(steps):
+        pick = 0
+        if sampler in (3, 4):
+            stop = np.float32(0.0 if sampler == 4 else p_stop)
+            cur = 0
+            while True:
+                forced = max_mass > 0 and cur != 0 and int(edge_mass[cur]) > max_mass
+                if cur != 0 and stop > 0 and not forced and np.float32(unit()) < stop:
+                    break
+                ch = kids[cur]
+                if not ch:
+                    break
+                tot = float(sum(float(edge_mass[c]) for c in ch))
+                if tot <= 0.0:
+                    nxt = ch[below(len(ch))]
+                else:
+                    u = unit() * tot
+                    acc, nxt = 0.0, ch[-1]
+                    for c in ch:
+                        acc += float(edge_mass[c])
+                        if u <= acc:
+                            nxt = c
+                            break
+                cur = nxt
+            pick = cur
+        elif sampler == 1:
+            if R > 1:
+                pick = 1 + below(R - 1)
+        else:
+            pick = root_child()
+        if pick == 0:
+            pick = root_child()
+        anc, c = [], int(parent[pick])
+        while c > 0:
+            anc.append(c)
+            c = int(parent[c])
+        anc.reverse()
+        if sampler == 4:
+            nodes, n_anc = anc + [pick], 0
+        else:
+            nodes, n_anc = anc + [pick], len(anc)
+            head = len(anc)
+            while head < len(nodes):
+                nodes.extend(kids[nodes[head]])
+                head += 1
+        mass = float(sum(float(edge_mass[x]) for x in nodes))
+        ep = lambda x: int(first_char_depth[x]) + int(edge_len[x]) - 1  # noqa: E731
+        nodes = sorted(nodes, key=ep)              # sorted() is stable, like the reference's bucket pass
+        out.append((pick, n_anc, mass, nodes))
+    return out, state

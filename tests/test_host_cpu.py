@@ -221,3 +221,24 @@ def test_trie_from_suffix_order_rejects_short_corpus():
     corpus = A.synth_markov_corpus(8, 3, 1, 0)
     with pytest.raises(A.AgptError):
         A.RadixTrie.from_suffix_order(corpus, 8, np.arange(7, dtype=np.int32), np.zeros(7, np.int32))
+
+
+@pytest.mark.parametrize("sampler", [1, 2, 3, 4])
+def test_lightning_sampler_matches_oracle(sampler):
+    """Sampled node sets, ancestor counts, masses and the generator state against the restatement, bit for bit, over
+    several super-epochs that continue one generator stream (with and without the mass cap)."""
+    corpus = A.synth_markov_corpus(4000, 20, 2, 7)
+    trie = A.RadixTrie.build(corpus, 10)
+    for max_mass in (0, 40):
+        state = 0x5c115e1
+        want_state = state
+        for _ in range(3):
+            rs, na, off, mass, nodes, state = trie.lightning_sample(sampler, 9, state, p_stop=0.3, max_mass=max_mass)
+            want, want_state = O.lightning_sample(trie.parent, trie.edge_mass, trie.first_char_depth, trie.edge_len, sampler, 9,
+                                                  want_state, 0.3, max_mass)
+            assert state == want_state
+            for i, (pick, n_anc, m, ids) in enumerate(want):
+                assert (int(rs[i]), int(na[i])) == (pick, n_anc) and mass[i] == m
+                assert nodes[off[i]:off[i + 1]].tolist() == ids
+                if sampler != 4:      # the set is closed under "parent" up to the root and holds the whole subtree of the pick
+                    assert set(int(trie.parent[x]) for x in ids) <= set(ids) | {0}

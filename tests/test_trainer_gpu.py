@@ -184,3 +184,55 @@ def test_gradients_do_not_depend_on_packing_or_rank_count(cuda):
         assert n_q == results[0][1]
         assert abs(loss_sum - results[0][0]) / results[0][0] < 1e-5
         assert rel_err(total, results[0][2], floor=1e-6) < 1e-4
+
+
+@pytest.mark.parametrize("sampler", [3, 4])
+def test_lightning_unit_matches_dense_reference(cuda, sampler):
+    """A sampled training unit (ancestors as context, the sampled subtree or the root-to-leaf path trained): loss and
+    every weight gradient against the dense float64 model on the same rows."""
+    import torch
+    corpus = A.synth_markov_corpus(900, 12, 2, 13)
+    trie = A.RadixTrie.build(corpus, 7)
+    mf = MF.random_init(32, 2, 2, 12, 16, seed=6, std=0.2)
+    counts_np = (trie.cnt_off.astype(np.int32), trie.cnt_tok, trie.cnt_val)
+    counts = [torch.from_numpy(np.ascontiguousarray(c)).to(cuda) for c in counts_np]
+    space = T.SampleSpace(trie)
+    rs, na, off, _, nodes, _ = trie.lightning_sample(sampler, 4, 0x5c115e1, p_stop=0.4)
+    checked = 0
+    for s in range(4):
+        ids = nodes[off[s]:off[s + 1]]
+        context = []
+        c = int(trie.parent[rs[s]])
+        while c > 0 and sampler != 4:
+            context.append(c)
+            c = int(trie.parent[c])
+        g = space.group(ids, context, "linear", mf.seq_len, cuda)
+        assert g.n == int(trie.edge_len[ids].sum())
+        model = T.TrieWalkModel(mf, cuda)
+        ls, nq = model.group_step(g, counts, entropy_lambda=0.2)
+        tr = None if g.trained is None else g.trained.cpu().numpy()
+        rl, rq, rg, _ = _reference(mf, g.plan.parent_dfs.copy(), g.tokens32.cpu().numpy(), g.plan.depth.copy(), g.q2n.cpu().numpy(),
+                                   g.qoff.cpu().numpy(), g.rid.cpu().numpy(), counts_np,
+                                   None if g.mass_w is None else g.mass_w.cpu().numpy(), 0.2, 1.0, tr, g.unit_of_row.cpu().numpy())
+        assert nq == rq and abs(ls - rl) <= TOL_F32 * max(rl, 1e-6)
+        # a root-to-leaf path is a handful of rows: bias gradients there are sums of a few terms that nearly cancel,
+        # so float32 products leave 1e-4 of the largest entry; 3e-4 for these units
+        for k, v in model.params.items():
+            assert rel_err(v.grad.cpu().numpy().astype(np.float64), rg[k], floor=1e-6) < 3 * TOL_F32, k
+        checked += nq
+    assert checked > 0
+
+
+def test_lightning_training_runs_from_the_command_line(cuda, tmp_path):
+    corpus = A.synth_markov_corpus(3000, 20, 2, 5)
+    trie = A.RadixTrie.build(corpus, 8)
+    d = str(tmp_path / "trie")
+    trie.save_dir(d, corpus.size, 20, A.token_hash(corpus))
+    mf = MF.random_init(32, 2, 2, 20, 16, seed=2)
+    mp, out = str(tmp_path / "m.model"), str(tmp_path / "out.model")
+    MF.save(mp, mf)
+    T.main(["--model", mp, "--trie-dir", d, "--epochs", "2", "--lr", "0.003", "--optimizer", "rmsprop", "--lightning-sampler", "l3",
+            "--lightning-steps", "12", "--lightning-max-mass", "400", "--mass-weight", "log", "--save", out])
+    new = MF.load(out)
+    assert all(np.isfinite(a).all() for _, a in new.mats)
+    assert any(not np.array_equal(a, b) for (_, a), (_, b) in zip(mf.mats, new.mats))
