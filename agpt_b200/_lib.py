@@ -89,6 +89,7 @@ SIGNATURES = {
     "agpt_b200_optimizer_step": (C.c_int, [C.c_int] + [vp] * 4 + [i64] + [f32] * 4 + [C.c_int, f32, f32, C.c_int, vp, vp]),
     "agpt_b200_optimizer_scratch_bytes": (i64, []),
     "agpt_b200_device_status": (C.c_int, [vp]),
+    "agpt_b200_compute_lr": (f32, [f32, C.c_int, C.c_int, C.c_int, C.c_int]),
     "agpt_b200_lightning_sample": (i64, [vp, C.c_int, C.c_int, f32, i64, vp, vp, vp, vp, vp, vp, i64]),
     "agpt_b200_trie_from_suffix_order": (C.c_int, [vp, i64, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp, C.POINTER(vp)]),
     "agpt_b200_suffix_order_gpu": (C.c_int, [vp, i64, C.c_int, C.c_int, vp, vp, C.POINTER(C.c_float)]),

@@ -522,6 +522,14 @@ def suffix_order_gpu(corpus, key_len: int, device: int = 0):
     return sa, lcp, float(ms.value)
 
 
+LR_SCHEDULES = {"constant": 0, "cosine": 1, "warmup-cosine": 2}
+
+
+def compute_lr(base_lr: float, step: int, total_steps: int, warmup_steps: int, schedule: str = "constant") -> float:
+    """Learning rate of optimizer step `step` (steps already taken), float32 like the reference."""
+    return float(lib().agpt_b200_compute_lr(base_lr, step, total_steps, warmup_steps, LR_SCHEDULES[schedule]))
+
+
 def device_status() -> int:
     """The current GPU's status word (0 = every kernel ran to completion); synchronises."""
     out = C.c_int32(0)

@@ -533,6 +533,18 @@ extern "C" int64_t agpt_b200_lightning_sample(const agpt_trie *t, int sampler, i
     return total;
 }
 
+// learning-rate schedule of the trainer (src/cuda/agpt_train.cu:146-216): schedule 0 constant, 1 cosine, 2 linear
+// warm-up over warmup_steps then cosine; `step` counts the optimizer steps already taken
+extern "C" float agpt_b200_compute_lr(float base_lr, int step, int total_steps, int warmup_steps, int schedule) {
+    if (total_steps <= 1 || schedule == 0) return base_lr;
+    if (schedule == 2 && step < warmup_steps) return base_lr * ((float)(step + 1) / (float)warmup_steps);
+    const int cos_start = schedule == 2 ? warmup_steps : 0;
+    if (total_steps <= cos_start) return base_lr;
+    float progress = (float)(step - cos_start) / (float)(total_steps - cos_start);
+    if (progress > 1.0f) progress = 1.0f;
+    return 0.5f * base_lr * (1.0f + cosf(3.14159265358979323846f * progress));
+}
+
 // --------------------------------------------------------------------------------------
 // walker plan
 // --------------------------------------------------------------------------------------

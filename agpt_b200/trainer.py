@@ -390,12 +390,17 @@ class FlatOptimizer:
     def __init__(self, model, kind, lr, beta1, beta2, eps, weight_decay=0.0, clip_norm=0.0):
         import torch
         self.model, self.kind, self.lr, self.beta1, self.beta2, self.eps = model, kind, lr, beta1, beta2, eps
+        self.base_lr = lr
         self.weight_decay, self.clip_norm, self.t = weight_decay, clip_norm, 0
+        self.schedule = None             # (name, total steps, warm-up steps): lr of each step from A.compute_lr
         z = lambda: torch.zeros(model.n_flat, dtype=torch.float32, device=model.device)  # noqa: E731
         self.m = z() if kind in ("momentum", "adam") else None
         self.v = z() if kind in ("rmsprop", "adam") else None
 
     def step(self):
+        if self.schedule is not None:
+            name, total, warm = self.schedule
+            self.lr = A.compute_lr(self.base_lr, self.t, total, warm, name)
         self.t += 1
         m = self.model
         return A.optimizer_step(self.kind, m.flat, m.flat_grad[:m.n_flat], self.m, self.v, lr=self.lr, beta1=self.beta1,
@@ -460,6 +465,8 @@ def main(argv=None):
     ap.add_argument("--lr", type=float, default=3e-4)
     ap.add_argument("--optimizer", default="adam", choices=["sgd", "momentum", "rmsprop", "adam"])
     ap.add_argument("--rmsprop-beta", type=float, default=0.999)
+    ap.add_argument("--lr-schedule", default="constant", choices=["constant", "cosine", "warmup-cosine"])
+    ap.add_argument("--warmup-epochs", type=int, default=0)
     ap.add_argument("--weight-decay", type=float, default=0.0)
     ap.add_argument("--grad-clip-norm", type=float, default=0.0)
     ap.add_argument("--mass-weight", default="off", choices=["off", "log", "sqrt", "linear"])
@@ -507,6 +514,10 @@ def main(argv=None):
     opt = make_optimizer(args.optimizer, model, args.lr, args.rmsprop_beta, weight_decay=args.weight_decay,
                          clip_norm=args.grad_clip_norm)
     n_sub = int((trie.parent[1:] == 0).sum())
+    # optimizer steps per epoch, as the reference counts them for its schedule (src/cuda/agpt_train.cu:5100-5117)
+    per_epoch = args.lightning_steps if lightning else (len(groups) if (args.no_accumulate and world == 1) else 1)
+    if args.lr_schedule != "constant":
+        opt.schedule = (args.lr_schedule, max(per_epoch * args.epochs, 1), args.warmup_epochs * per_epoch)
     save = args.save or args.model
     for ep in range(1, args.epochs + 1):
         torch.cuda.synchronize()

@@ -162,6 +162,9 @@ int agpt_b200_trie_build_gpu(const int32_t *corpus, int64_t n, int max_depth, in
 int64_t agpt_b200_lightning_sample(const agpt_trie *t, int sampler, int steps, float p_stop, int64_t max_mass,
                                    uint32_t *rng_state, int32_t *sample_out, int32_t *n_anc_out, int64_t *node_off_out,
                                    double *mass_out, int32_t *nodes_out, int64_t nodes_cap);
+/* Learning rate of optimizer step number `step` (steps already taken) out of total_steps: schedule 0 constant,
+ * 1 cosine decay, 2 linear warm-up over warmup_steps then cosine decay (src/cuda/agpt_train.cu:146-216), float32. */
+float agpt_b200_compute_lr(float base_lr, int step, int total_steps, int warmup_steps, int schedule);
 void agpt_b200_trie_free(agpt_trie *t);
 /* FNV-1a corpus hash (src/agpt/trie_corpus.cr:120-134). */
 uint64_t agpt_b200_token_hash(const int32_t *tokens, int64_t n);

@@ -542,3 +542,17 @@ def lightning_sample(parent, edge_mass, first_char_depth, edge_len, sampler, ste
         nodes = sorted(nodes, key=ep)              # sorted() is stable, like the reference's bucket pass
         out.append((pick, n_anc, mass, nodes))
     return out, state
+
+
+def compute_lr(base_lr, step, total_steps, warmup_steps, schedule):
+    """src/cuda/agpt_train.cu:202-216 in float32; schedule 0 constant, 1 cosine, 2 warm-up then cosine."""
+    f = np.float32
+    if total_steps <= 1 or schedule == 0:
+        return f(base_lr)
+    if schedule == 2 and step < warmup_steps:
+        return f(f(base_lr) * (f(step + 1) / f(warmup_steps)))
+    cos_start = warmup_steps if schedule == 2 else 0
+    if total_steps <= cos_start:
+        return f(base_lr)
+    progress = min(f(step - cos_start) / f(total_steps - cos_start), f(1.0))
+    return f(f(0.5) * f(base_lr) * (f(1.0) + np.cos(f(f(3.14159265358979323846) * progress), dtype=np.float32)))

@@ -242,3 +242,12 @@ def test_lightning_sampler_matches_oracle(sampler):
                 assert nodes[off[i]:off[i + 1]].tolist() == ids
                 if sampler != 4:      # the set is closed under "parent" up to the root and holds the whole subtree of the pick
                     assert set(int(trie.parent[x]) for x in ids) <= set(ids) | {0}
+
+
+def test_lr_schedule_matches_oracle():
+    for sched, code in (("constant", 0), ("cosine", 1), ("warmup-cosine", 2)):
+        for total, warm in ((1, 0), (10, 3), (130, 13), (5, 9)):
+            for step in range(0, total + 3):
+                got, want = A.compute_lr(3e-4, step, total, warm, sched), float(O.compute_lr(3e-4, step, total, warm, code))
+                assert abs(got - want) <= 1e-6 * 3e-4, (sched, total, warm, step)
+    assert A.compute_lr(1.0, 0, 100, 10, "warmup-cosine") == pytest.approx(0.1) and A.compute_lr(1.0, 100, 100, 10, "cosine") == pytest.approx(0.0, abs=1e-7)

@@ -232,7 +232,8 @@ def test_lightning_training_runs_from_the_command_line(cuda, tmp_path):
     mp, out = str(tmp_path / "m.model"), str(tmp_path / "out.model")
     MF.save(mp, mf)
     T.main(["--model", mp, "--trie-dir", d, "--epochs", "2", "--lr", "0.003", "--optimizer", "rmsprop", "--lightning-sampler", "l3",
-            "--lightning-steps", "12", "--lightning-max-mass", "400", "--mass-weight", "log", "--save", out])
+            "--lightning-steps", "12", "--lightning-max-mass", "400", "--mass-weight", "log", "--lr-schedule", "warmup-cosine",
+            "--warmup-epochs", "1", "--save", out])
     new = MF.load(out)
     assert all(np.isfinite(a).all() for _, a in new.mats)
     assert any(not np.array_equal(a, b) for (_, a), (_, b) in zip(mf.mats, new.mats))
