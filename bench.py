@@ -32,6 +32,10 @@ WORKLOADS = {
                label="depth-32 radix trie, 1.1M-char order-3 Markov corpus (vocab 65), d_model 128, 4 heads x 32, fp32"),
     "c1": dict(chars=20_000, vocab=65, order=2, depth=8, heads=4, head_dim=16, layers=2,
                label="depth-8 radix trie, 20k-char order-2 Markov corpus (vocab 65), d_model 64, 4 heads x 16, fp32"),
+    # the 5M-char configuration: 126M positions; its inputs do not fit one GPU at once, so every launch group reads the
+    # same resident input buffers (sized for the largest group)
+    "c4": dict(chars=5_000_000, vocab=96, order=3, depth=32, heads=8, head_dim=32, layers=6,
+               label="depth-32 radix trie, 5M-char order-3 Markov corpus (vocab 96), d_model 256, 8 heads x 32, fp32"),
     # reduced copies of the two above for profiler captures (inputs still larger than L2, a few GB on the device)
     "c2s": dict(chars=50_000, vocab=65, order=3, depth=32, heads=4, head_dim=32, layers=4,
                 label="depth-32 radix trie, 50k-char order-3 Markov corpus (vocab 65), d_model 128, 4 heads x 32, fp32"),
@@ -104,6 +108,12 @@ class Unit:
     __slots__ = ("parent", "n", "tokens", "q2n", "qoff", "radix_ids", "mass_w", "n_ctx")
 
 
+def unit_level(wl, world):
+    """Root-child units on one rank, bigram units on several -- and always for the 126M-position configuration, whose
+    largest root child (a quarter of all positions) would not fit one GPU as a single launch."""
+    return 2 if (world > 1 or wl == "c4") else 1
+
+
 def build_units(wl, rank, world, log, single_unit=False, group_rows=4_000_000, device=None):
     import agpt_b200 as A
     cfg = WORKLOADS[wl]
@@ -118,7 +128,7 @@ def build_units(wl, rank, world, log, single_unit=False, group_rows=4_000_000, d
     else:
         corpus = A.synth_markov_corpus(cfg["chars"], cfg["vocab"], cfg["order"], 0)
         # the GPU arm orders the suffixes on its device; the CPU arm uses the level-by-level host builder (same arrays)
-        level_key = 1 if world == 1 else 2
+        level_key = unit_level(wl, world)
         trie = (A.RadixTrie.build(corpus, cfg["depth"], subtree_level=level_key) if device is None else
                 A.RadixTrie.build_gpu(corpus, cfg["depth"], subtree_level=level_key, device=device))
         parent, token, _, radix_of = trie.char_tree()
@@ -126,7 +136,7 @@ def build_units(wl, rank, world, log, single_unit=False, group_rows=4_000_000, d
         counts = (trie.cnt_off.astype(np.int32), trie.cnt_tok, trie.cnt_val)
     log(f"trie built: {parent.size} positions in {time.time() - t0:.1f}s")
     plan = A.WalkerPlan(parent, 64, -1)
-    level = 1 if world == 1 else 2
+    level = unit_level(wl, world)
     ub, ue = plan.units(level)
     if single_unit:       # the whole forest as one launch (profiling); its depth-1 nodes stay roots
         ub, ue = np.array([0], np.int64), np.array([plan.n], np.int64)
@@ -271,12 +281,16 @@ def run_gpu(args):
     plans = [A.WalkerPlan(u.parent, args.tile, local) for u in units]
     ws_bytes = max(p.workspace_bytes(D) for p in plans)
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
-    big = [torch.randn((n_rank, D), device=dev, generator=g) for _ in range(4)]          # q k v dO, resident
+    # q k v dO resident for every row of the rank; when that exceeds 60 GB (the 126M-position configuration) all launch
+    # groups read one set of buffers sized for the largest group instead (each group's rows are still far larger than L2)
+    shared_inputs = 4 * n_rank * D * 4 > 60e9
+    n_in = n_max if shared_inputs else n_rank
+    big = [torch.randn((n_in, D), device=dev, generator=g) for _ in range(4)]
     kv_bytes = 4
     if args.kv == "bf16":        # the KV store holds bf16 rows (written once, outside the timed region, like a cache fill)
         big[1], big[2] = A.kv_store_write_bf16(big[1]), A.kv_store_write_bf16(big[2])
         kv_bytes = 2
-    logits = torch.randn((n_rank, V), device=dev, generator=g)
+    logits = torch.randn((n_in, V), device=dev, generator=g)
     out = torch.empty((n_max, D), device=dev); lse = torch.empty((n_max, H), device=dev)
     dq = torch.empty_like(out); dk = torch.empty_like(out); dv = torch.empty_like(out)
     dlogits = torch.empty((n_max, V), device=dev); loss = torch.empty(n_max, device=dev)
@@ -285,7 +299,7 @@ def run_gpu(args):
     meta = []
     row = 0
     for u in units:
-        meta.append(dict(row=row, q2n=torch.from_numpy(u.q2n).to(dev), qoff=torch.from_numpy(u.qoff).to(dev),
+        meta.append(dict(row=0 if shared_inputs else row, q2n=torch.from_numpy(u.q2n).to(dev), qoff=torch.from_numpy(u.qoff).to(dev),
                          rid=torch.from_numpy(u.radix_ids).to(dev), tok=torch.from_numpy(u.tokens).to(dev),
                          mw=torch.from_numpy(u.mass_w).to(dev)))
         row += u.n
@@ -428,8 +442,9 @@ def run_gpu(args):
                 "steps": args.steps, "warmup": n_warm, "ms_per_step": ms_per_step, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": {"workload": cfg["label"], "kv_store": args.kv, "positions": total_nodes, "launch_groups_rank0": len(units), "group_rows": args.group_rows,
-                           "partition": "root-child subtrees" if world == 1 else f"bigram subtrees, LPT over {world} ranks",
-                           "tile": args.tile, "l2": "inputs (GBs per tensor) far larger than the 126 MB L2"},
+                           "partition": "root-child subtrees" if unit_level(args.workload, world) == 1 else f"bigram subtrees, LPT over {world} rank(s)",
+                           "tile": args.tile, "l2": "inputs (GBs per tensor) far larger than the 126 MB L2",
+                           "inputs": "one buffer set shared by all launch groups" if shared_inputs else "resident for every row"},
                 "roofline": {"bound": "hbm", "achieved": ach_bwd, "peak": peak, "unit": "GB/s", "frac": ach_bwd / peak,
                              "traffic": (None if D != 128 else 4.44e3 * n_rank), "kernel": "attention backward tile kernel + dK/dV reduction", "peak_kind": f"of {peak_kind}", "traffic_note": "ncu dram bytes per position of the reduced case c2s (4.44 KB backward, 2.18 KB forward) x positions; profiles/attn_mma_kernels_c2s_ncu_full.md",
                              "algorithmic_bytes_per_step": b_bwd, "seconds_per_step": t_bwd,
