@@ -619,7 +619,7 @@ struct BwdMmaSmem {
 };
 
 template <int HD, typename KVT>
-__global__ void __launch_bounds__(128, HD <= 32 ? 4 : 1) attn_bwd_mma_kernel(const float *__restrict__ Q, const KVT *__restrict__ K,
+__global__ void __launch_bounds__(128, HD <= 32 ? 4 : (sizeof(KVT) == 2 ? 3 : 1)) attn_bwd_mma_kernel(const float *__restrict__ Q, const KVT *__restrict__ K,
                                                            const KVT *__restrict__ V, const float *__restrict__ O,
                                                            const float *__restrict__ LSE, const float *__restrict__ dO,
                                                            float *__restrict__ dQ, float *__restrict__ dK,

@@ -36,6 +36,9 @@ WORKLOADS = {
     # same resident input buffers (sized for the largest group)
     "c4": dict(chars=5_000_000, vocab=96, order=3, depth=32, heads=8, head_dim=32, layers=6,
                label="depth-32 radix trie, 5M-char order-3 Markov corpus (vocab 96), d_model 256, 8 heads x 32, fp32"),
+    # the deep configuration: 20M chars, depth 128, nodes of count < 2 pruned from depth 4 (run it with --kv bf16)
+    "c5": dict(chars=20_000_000, vocab=96, order=4, depth=128, heads=6, head_dim=64, layers=8, prune=(2, 4),
+               label="depth-128 radix trie pruned at count<2, 20M-char order-4 Markov corpus (vocab 96), d_model 384, 6 heads x 64"),
     # reduced copies of the two above for profiler captures (inputs still larger than L2, a few GB on the device)
     "c2s": dict(chars=50_000, vocab=65, order=3, depth=32, heads=4, head_dim=32, layers=4,
                 label="depth-32 radix trie, 50k-char order-3 Markov corpus (vocab 65), d_model 128, 4 heads x 32, fp32"),
@@ -109,9 +112,9 @@ class Unit:
 
 
 def unit_level(wl, world):
-    """Root-child units on one rank, bigram units on several -- and always for the 126M-position configuration, whose
+    """Root-child units on one rank, bigram units on several -- and always for the 126M-position and the deep configurations, whose
     largest root child (a quarter of all positions) would not fit one GPU as a single launch."""
-    return 2 if (world > 1 or wl == "c4") else 1
+    return 2 if (world > 1 or wl in ("c4", "c5")) else 1
 
 
 def build_units(wl, rank, world, log, single_unit=False, group_rows=4_000_000, device=None):
@@ -129,8 +132,9 @@ def build_units(wl, rank, world, log, single_unit=False, group_rows=4_000_000, d
         corpus = A.synth_markov_corpus(cfg["chars"], cfg["vocab"], cfg["order"], 0)
         # the GPU arm orders the suffixes on its device; the CPU arm uses the level-by-level host builder (same arrays)
         level_key = unit_level(wl, world)
-        trie = (A.RadixTrie.build(corpus, cfg["depth"], subtree_level=level_key) if device is None else
-                A.RadixTrie.build_gpu(corpus, cfg["depth"], subtree_level=level_key, device=device))
+        pm, pd = cfg.get("prune", (1, 4))
+        trie = (A.RadixTrie.build(corpus, cfg["depth"], level_key, pm, pd) if device is None else
+                A.RadixTrie.build_gpu(corpus, cfg["depth"], level_key, pm, pd, device=device))
         parent, token, _, radix_of = trie.char_tree()
         edge_mass = trie.edge_mass
         counts = (trie.cnt_off.astype(np.int32), trie.cnt_tok, trie.cnt_val)
