@@ -195,6 +195,38 @@ class WalkerPlan:
         check(lib().agpt_b200_plan_units(self._h, level, cnt, _vp(b), _vp(e)), "plan_units")
         return b, e
 
+    def units_capped(self, level: int, cap: int):
+        """Units of at most `cap` rows where the tree allows it: a unit larger than cap is cut into the unary chain
+        at its top (up to and including the first branching node) and the subtrees below it, recursively -- the
+        reference's partition by deeper ancestor groups (--partition-depth, src/cuda/agpt_train.cu:3808-3890), applied
+        only where a subtree is too large.  Depth-first [begin, end) ranges in depth-first order; a range is a whole
+        subtree or such a chain."""
+        ub, ue = self.units(level)
+        sub_end = self.sub_end
+        out_b, out_e = [], []
+        stack = [(int(b), int(e)) for b, e in zip(ub[::-1], ue[::-1])]
+        while stack:
+            b, e = stack.pop()
+            if e - b <= cap:
+                out_b.append(b)
+                out_e.append(e)
+                continue
+            j = b
+            while j + 1 < e and int(sub_end[j + 1]) == e:        # exactly one child: the chain goes on
+                j += 1
+            if j + 1 >= e:                                        # a bare chain: nothing to cut
+                out_b.append(b)
+                out_e.append(e)
+                continue
+            out_b.append(b)
+            out_e.append(j + 1)
+            kids, c = [], j + 1
+            while c < e:
+                kids.append((c, int(sub_end[c])))
+                c = int(sub_end[c])
+            stack.extend(reversed(kids))
+        return np.asarray(out_b, np.int64), np.asarray(out_e, np.int64)
+
     def algorithmic_bytes(self, d_model: int, n_heads: int, kv_bytes: int = 4):
         """Bytes of the sibling-group-shared traffic model for one forward+backward of one layer:
         each sibling group reads its parent's ancestor chain once per direction and every per-node

@@ -63,15 +63,17 @@ class LaunchGroup:
 
 
 def build_groups(trie: A.RadixTrie, rank: int, world: int, group_rows: int, mass_mode: str, seq_len: int, device,
-                 tile: int = 64, level: int | None = None):
+                 tile: int = 64, level: int | None = None, unit_cap: int | None = None):
     """This rank's launch groups: root-child units (one rank) or bigram units balanced over ranks, packed in
-    depth-first order into groups of at most group_rows rows.  A bigram unit carries its depth-1 ancestor as a
-    context row (attended, not trained)."""
+    depth-first order into groups of at most group_rows rows.  With unit_cap, units larger than that are cut deeper
+    (WalkerPlan.units_capped), which bounds the activation memory of a launch.  A unit that does not start at depth 1
+    carries its ancestors as context rows (attended, and differentiated through, but not trained), so every chain is
+    complete and the summed gradient does not depend on the partition."""
     parent, token, depth, radix_of = trie.char_tree()
     gplan = A.WalkerPlan(parent, 64, -1)
     if level is None:
         level = 1 if world == 1 else 2
-    ub, ue = gplan.units(level)
+    ub, ue = gplan.units(level) if unit_cap is None else gplan.units_capped(level, unit_cap)
     owner = A.partition_lpt(ue - ub, world)
     d2n = gplan.dfs_to_node
     groups, pieces, rows = [], [], 0
@@ -98,17 +100,20 @@ def build_groups(trie: A.RadixTrie, rank: int, world: int, group_rows: int, mass
         if o != rank:
             continue
         b, e = int(b), int(e)
-        pp = gplan.parent_dfs[b:e].astype(np.int64) - b
+        chain, a = [], int(gplan.parent_dfs[b])
+        while a >= 0:
+            chain.append(a)
+            a = int(gplan.parent_dfs[a])
+        chain.reverse()
+        k = len(chain)
+        pp = gplan.parent_dfs[b:e].astype(np.int64) - b + k
+        pp[0] = k - 1                                        # the unit's first row hangs under its context chain (-1: a root)
         idv = d2n[b:e]
         tr = np.ones(e - b, bool)
-        if level == 2 and gplan.depth[b] == 2:
-            a = int(gplan.parent_dfs[b])
-            pp = np.concatenate([[-1], pp + 1])
-            pp[1] = 0
-            idv = np.concatenate([[d2n[a]], idv])
-            tr = np.concatenate([[False], tr])
-        else:
-            pp[gplan.parent_dfs[b:e] < 0] = -1
+        if k:
+            pp = np.concatenate([np.arange(-1, k - 1), pp])
+            idv = np.concatenate([d2n[np.asarray(chain)], idv])
+            tr = np.concatenate([np.zeros(k, bool), tr])
         if rows and rows + idv.size > group_rows:
             flush()
         pieces.append((pp, idv, tr))

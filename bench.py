@@ -472,7 +472,8 @@ def run_epoch(args, cfg, rank, world, dev, log):
     corpus = A.synth_markov_corpus(cfg["chars"], cfg["vocab"], cfg["order"], 0)
     trie = A.RadixTrie.build_gpu(corpus, cfg["depth"], subtree_level=2, device=dev.index)
     mf = MF.random_init(D, cfg["heads"], cfg["layers"], cfg["vocab"], max(128, cfg["depth"]), seed=0)
-    groups, total = T.build_groups(trie, rank, world, args.epoch_group_rows, "linear", mf.seq_len, dev, level=2)
+    groups, total = T.build_groups(trie, rank, world, args.epoch_group_rows, "linear", mf.seq_len, dev, level=2,
+                                   unit_cap=args.epoch_group_rows)
     counts = [torch.from_numpy(np.ascontiguousarray(c)).to(dev) for c in (trie.cnt_off.astype(np.int32), trie.cnt_tok, trie.cnt_val)]
     model = T.TrieWalkModel(mf, dev)
     opt = T.make_optimizer("rmsprop", model, 3e-4, 0.999)

@@ -251,3 +251,23 @@ def test_lr_schedule_matches_oracle():
                 got, want = A.compute_lr(3e-4, step, total, warm, sched), float(O.compute_lr(3e-4, step, total, warm, code))
                 assert abs(got - want) <= 1e-6 * 3e-4, (sched, total, warm, step)
     assert A.compute_lr(1.0, 0, 100, 10, "warmup-cosine") == pytest.approx(0.1) and A.compute_lr(1.0, 100, 100, 10, "cosine") == pytest.approx(0.0, abs=1e-7)
+
+
+def test_units_capped_partition_all_rows():
+    """Capped units tile the depth-first order exactly; a unit over the cap can only be a bare chain; without a
+    cap they are the plain units."""
+    corpus = A.synth_markov_corpus(5000, 12, 2, 1)
+    parent = A.RadixTrie.build(corpus, 9).char_tree()[0]
+    plan = A.WalkerPlan(parent, 64, -1)
+    for level in (1, 2):
+        ub, ue = plan.units(level)
+        b, e = plan.units_capped(level, 10 ** 9)
+        assert np.array_equal(b, ub) and np.array_equal(e, ue)
+        for cap in (10, 100, 1000):
+            b, e = plan.units_capped(level, cap)
+            assert b[0] == 0 and e[-1] == plan.n and np.array_equal(b[1:], e[:-1])
+            for bb, ee in zip(b, e):
+                whole = plan.sub_end[bb] == ee
+                chain = all(plan.sub_end[j] == plan.sub_end[bb] for j in range(bb, ee))
+                assert whole or chain                       # a subtree, or the unary top of one
+                assert ee - bb <= cap or chain

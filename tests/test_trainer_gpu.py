@@ -64,8 +64,8 @@ def _reference(mf, parent, tokens, depth, q2n, qoff, rid, counts, mass_w, lam, i
     return float(loss[loss > 0].sum()), n_tr, {k: v.grad.numpy() for k, v in P.items()}, logits.detach().numpy()
 
 
-@pytest.mark.parametrize("world,bf16", [(1, False), (2, False), (1, True)])
-def test_group_step_matches_dense_reference(cuda, world, bf16):
+@pytest.mark.parametrize("world,bf16,unit_cap", [(1, False, None), (2, False, None), (1, True, None), (2, False, 40)])
+def test_group_step_matches_dense_reference(cuda, world, bf16, unit_cap):
     import torch
     corpus = A.synth_markov_corpus(700, 12, 2, 3)
     trie = A.RadixTrie.build(corpus, 7, subtree_level=1 if world == 1 else 2)
@@ -75,7 +75,9 @@ def test_group_step_matches_dense_reference(cuda, world, bf16):
     lam, iw = 0.5, 0.7
     grads, loss_sum, n_q, ref_grads, ref_loss, ref_q = None, 0.0, 0, None, 0.0, 0
     for rank in range(world):
-        groups, total = T.build_groups(trie, rank, world, 500, "linear", mf.seq_len, cuda)
+        groups, total = T.build_groups(trie, rank, world, 500, "linear", mf.seq_len, cuda, unit_cap=unit_cap)
+        if unit_cap:     # units cut below the bigram level carry context chains longer than one row
+            assert any(g.trained is not None and int((g.trained == 0).sum()) > g.n_units for g in groups)
         model = T.TrieWalkModel(mf, cuda)
         for p in model.parameters():
             p.grad = torch.zeros_like(p)
@@ -171,7 +173,7 @@ def test_gradients_do_not_depend_on_packing_or_rank_count(cuda):
         total = None
         loss_sum, n_q = 0.0, 0
         for rank in range(world):
-            groups, _ = T.build_groups(trie, rank, world, rows, "linear", mf.seq_len, cuda, level=2)
+            groups, _ = T.build_groups(trie, rank, world, rows, "linear", mf.seq_len, cuda, level=2, unit_cap=120)
             model = T.TrieWalkModel(mf, cuda)
             for g in groups:
                 ls, nq = model.group_step(g, counts, entropy_lambda=0.3)
