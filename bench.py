@@ -470,7 +470,8 @@ def run_epoch(args, cfg, rank, world, dev, log):
     from agpt_b200 import trainer as T
     D = cfg["heads"] * cfg["head_dim"]
     corpus = A.synth_markov_corpus(cfg["chars"], cfg["vocab"], cfg["order"], 0)
-    trie = A.RadixTrie.build_gpu(corpus, cfg["depth"], subtree_level=2, device=dev.index)
+    pm, pd = cfg.get("prune", (1, 4))
+    trie = A.RadixTrie.build_gpu(corpus, cfg["depth"], 2, pm, pd, device=dev.index)
     mf = MF.random_init(D, cfg["heads"], cfg["layers"], cfg["vocab"], max(128, cfg["depth"]), seed=0)
     groups, total = T.build_groups(trie, rank, world, args.epoch_group_rows, "linear", mf.seq_len, dev, level=2,
                                    unit_cap=args.epoch_group_rows)
@@ -483,7 +484,7 @@ def run_epoch(args, cfg, rank, world, dev, log):
         if world > 1:
             dist.barrier()
         t0 = time.perf_counter()
-        ls, nq = T.train_epoch(model, groups, counts, opt, accumulate=True, world=world)
+        ls, nq = T.train_epoch(model, groups, counts, opt, accumulate=True, world=world, bf16_store=(args.kv == "bf16"))
         torch.cuda.synchronize()
         t = torch.tensor([time.perf_counter() - t0], device=dev, dtype=torch.float64)
         if world > 1:
@@ -493,7 +494,7 @@ def run_epoch(args, cfg, rank, world, dev, log):
         log(f"epoch {ep + 1}: loss={losses[-1]:.6f} ({times[-1]:.2f} s, {len(groups)} chunks, {nq} nodes)")
     return {"seconds": times[-1], "positions_per_s": total / times[-1], "loss_first": losses[0], "loss_second": losses[-1],
             "model": f"d_model {D}, {cfg['layers']} layers, {cfg['heads']} heads x {cfg['head_dim']}, d_ff {4 * D}, vocab {cfg['vocab']}, fp32",
-            "recipe": "rmsprop beta 0.999, lr 3e-4, linear mass weighting, one step per epoch (accumulate)",
+            "recipe": "rmsprop beta 0.999, lr 3e-4, linear mass weighting, one step per epoch (accumulate)", "kv_store": args.kv,
             "group_rows": args.epoch_group_rows, "partition": "bigram subtrees", "chunks_rank0": len(groups)}
 
 
