@@ -552,55 +552,83 @@ extern "C" int agpt_b200_plan_create(const int32_t *parent, int64_t n, int tile_
     if (!parent || !out || n <= 0) return agpt_set_error(AGPT_E_ARG, "plan_create: bad argument");
     if (n >= (1LL << 31) - 256) return agpt_set_error(AGPT_E_LIMIT, "plan_create: more than 2^31 nodes in one plan");
     if (tile_m != 32 && tile_m != 64 && tile_m != 128) return agpt_set_error(AGPT_E_ARG, "plan_create: tile_m must be 32, 64 or 128");
-    // children lists (increasing id order) by counting sort on the parent
-    std::vector<int64_t> coff(n + 2, 0);
+    bool monotone = true;                       // every parent precedes its children (level-order and trie numberings)
     for (int64_t i = 0; i < n; i++) {
         int32_t p = parent[i];
         if (p < -1 || p >= n || p == i) return agpt_set_error(AGPT_E_ARG, "plan_create: parent[%lld]=%d out of range", (long long)i, p);
-        coff[p + 2]++;
-    }
-    for (int64_t i = 0; i <= n; i++) coff[i + 1] += coff[i];
-    std::vector<int32_t> child(n);
-    {
-        std::vector<int64_t> pos(coff.begin(), coff.end() - 1);
-        for (int64_t i = 0; i < n; i++) child[pos[parent[i] + 1]++] = (int32_t)i;
+        if (p >= i) monotone = false;
     }
     agpt_plan *P = new agpt_plan();
     P->n = n; P->tile_m = tile_m;
     P->dfs_to_node.resize(n); P->node_to_dfs.assign(n, -1); P->parent_dfs.resize(n); P->depth.resize(n); P->sub_end.resize(n);
-    // iterative pre-order walk; slot -1 (index 0 of coff) is the key-less root
-    std::vector<std::pair<int32_t, int64_t>> stack;   // (node, next child cursor)
-    stack.reserve(256);
-    int64_t pos = 0;
-    for (int64_t rc = coff[0]; rc < coff[1]; rc++) {
-        stack.clear();
-        int32_t root = child[rc];
-        auto visit = [&](int32_t v, int32_t par_pos, int32_t dep) {
-            P->dfs_to_node[pos] = v; P->node_to_dfs[v] = (int32_t)pos; P->parent_dfs[pos] = par_pos; P->depth[pos] = dep;
-            pos++;
-            stack.emplace_back(v, coff[v + 1]);
-        };
-        visit(root, -1, 1);
-        while (!stack.empty()) {
-            auto &top = stack.back();
-            int32_t v = top.first;
-            if (top.second < coff[v + 2]) {
-                int32_t c = child[top.second++];
-                int32_t vp = P->node_to_dfs[v];
-                visit(c, vp, P->depth[vp] + 1);
-            } else {
-                P->sub_end[P->node_to_dfs[v]] = (int32_t)pos;
-                stack.pop_back();
+    P->n_groups = 0; P->sum_group_prefix = 0;
+    if (monotone) {
+        // No stack walk: subtree sizes by one sweep from the last node to the first, then pre-order positions by one
+        // sweep forward -- a node's position is its parent's next free slot, siblings arriving in increasing id order.
+        std::vector<int32_t> size(n, 1), next_free(n);
+        for (int64_t i = n - 1; i >= 0; i--)
+            if (parent[i] >= 0) size[parent[i]] += size[i];
+        int64_t root_cursor = 0;
+        bool any_root = false;
+        for (int64_t i = 0; i < n; i++) {
+            const int32_t p = parent[i];
+            int32_t at;
+            if (p < 0) { at = (int32_t)root_cursor; root_cursor += size[i]; any_root = true; }
+            else { at = next_free[p]; next_free[p] += size[i]; }
+            next_free[i] = at + 1;
+            P->node_to_dfs[i] = at;
+            P->dfs_to_node[at] = (int32_t)i;
+            P->parent_dfs[at] = p < 0 ? -1 : P->node_to_dfs[p];
+            P->depth[at] = p < 0 ? 1 : P->depth[P->node_to_dfs[p]] + 1;
+            P->sub_end[at] = at + size[i];
+        }
+        P->n_groups = any_root ? 1 : 0;
+        for (int64_t i = 0; i < n; i++)
+            if (size[i] > 1) { P->n_groups++; P->sum_group_prefix += P->depth[P->node_to_dfs[i]]; }
+    } else {
+        // children lists (increasing id order) by counting sort on the parent
+        std::vector<int64_t> coff(n + 2, 0);
+        for (int64_t i = 0; i < n; i++) coff[parent[i] + 2]++;
+        for (int64_t i = 0; i <= n; i++) coff[i + 1] += coff[i];
+        std::vector<int32_t> child(n);
+        {
+            std::vector<int64_t> pos(coff.begin(), coff.end() - 1);
+            for (int64_t i = 0; i < n; i++) child[pos[parent[i] + 1]++] = (int32_t)i;
+        }
+        // iterative pre-order walk; slot -1 (index 0 of coff) is the key-less root
+        std::vector<std::pair<int32_t, int64_t>> stack;   // (node, next child cursor)
+        stack.reserve(256);
+        int64_t pos = 0;
+        for (int64_t rc = coff[0]; rc < coff[1]; rc++) {
+            stack.clear();
+            int32_t root = child[rc];
+            auto visit = [&](int32_t v, int32_t par_pos, int32_t dep) {
+                P->dfs_to_node[pos] = v; P->node_to_dfs[v] = (int32_t)pos; P->parent_dfs[pos] = par_pos; P->depth[pos] = dep;
+                pos++;
+                stack.emplace_back(v, coff[v + 1]);
+            };
+            visit(root, -1, 1);
+            while (!stack.empty()) {
+                auto &top = stack.back();
+                int32_t v = top.first;
+                if (top.second < coff[v + 2]) {
+                    int32_t c = child[top.second++];
+                    int32_t vp = P->node_to_dfs[v];
+                    visit(c, vp, P->depth[vp] + 1);
+                } else {
+                    P->sub_end[P->node_to_dfs[v]] = (int32_t)pos;
+                    stack.pop_back();
+                }
             }
         }
+        if (pos != n) { delete P; return agpt_set_error(AGPT_E_ARG, "plan_create: parent array has a cycle or unreachable nodes (%lld of %lld reached)", (long long)pos, (long long)n); }
+        // sibling groups (for the bytes model): one per node with children, plus the root's
+        P->n_groups = coff[1] > coff[0] ? 1 : 0;
+        for (int64_t v = 0; v < n; v++)
+            if (coff[v + 2] > coff[v + 1]) { P->n_groups++; P->sum_group_prefix += P->depth[P->node_to_dfs[v]]; }
     }
-    if (pos != n) { delete P; return agpt_set_error(AGPT_E_ARG, "plan_create: parent array has a cycle or unreachable nodes (%lld of %lld reached)", (long long)pos, (long long)n); }
     P->max_depth = 0; P->sum_depth = 0;
     for (int64_t i = 0; i < n; i++) { P->max_depth = std::max(P->max_depth, P->depth[i]); P->sum_depth += P->depth[i]; }
-    // sibling groups (for the bytes model): one per node with children, plus the root's
-    P->n_groups = coff[1] > coff[0] ? 1 : 0; P->sum_group_prefix = 0;
-    for (int64_t v = 0; v < n; v++)
-        if (coff[v + 2] > coff[v + 1]) { P->n_groups++; P->sum_group_prefix += P->depth[P->node_to_dfs[v]]; }
     // tiles: chain of the first query of each tile, root side first
     P->n_tiles = (n + tile_m - 1) / tile_m;
     P->chain_off.assign(P->n_tiles + 1, 0);
@@ -628,10 +656,14 @@ extern "C" int agpt_b200_plan_create(const int32_t *parent, int64_t n, int tile_
         }
         P->n_reduce_nodes++;
     }
-    {   // items ordered by their last tile, so that "every item whose tiles are all done" is a prefix of the list
-        std::vector<int64_t> ord(P->item_node.size());
-        std::iota(ord.begin(), ord.end(), 0);
-        std::stable_sort(ord.begin(), ord.end(), [&](int64_t x, int64_t y) { return P->item_t1[x] < P->item_t1[y]; });
+    {   // items ordered by their last tile (stable: a counting sort over the tiles), so that "every item whose tiles
+        // are all done" is a prefix of the list
+        const size_t ni = P->item_node.size();
+        std::vector<int64_t> start(P->n_tiles + 1, 0);
+        for (size_t i = 0; i < ni; i++) start[P->item_t1[i] + 1]++;
+        for (int64_t t = 0; t < P->n_tiles; t++) start[t + 1] += start[t];
+        std::vector<int64_t> ord(ni);
+        for (size_t i = 0; i < ni; i++) ord[start[P->item_t1[i]]++] = (int64_t)i;
         auto permute = [&](std::vector<int32_t> &v) { std::vector<int32_t> w(v.size()); for (size_t i = 0; i < ord.size(); i++) w[i] = v[ord[i]]; v.swap(w); };
         permute(P->item_node); permute(P->item_t0); permute(P->item_t1); permute(P->item_slot);
     }
