@@ -1436,10 +1436,24 @@ loss_batch_kernel(const float *__restrict__ logits, const int32_t *__restrict__ 
     if (lane < nrows) {
         float *row = tile + lane * V;
         // lane-skewed column order: with row stride V the banks of the 32 lanes differ iff the per-lane step V + skew
-        // is odd, so an even V starts lane l at column l (two plain segments: [first, V) then [0, first))
-        const int first = (V & 1) ? 0 : (lane % V);
+        // is odd, so an even V starts lane l at column l (two plain segments: [first, V) then [0, first)).  When V is a
+        // multiple of 4 the row is swept in 16-byte pieces instead (a quarter of the shared-memory instructions); there
+        // eight neighbouring lanes must fall into different 16-byte bank groups, which a V that is a multiple of 8
+        // needs a skew of one piece per lane for.
+        const bool vec = (V & 3) == 0;
+        const int V4 = V >> 2;
+        const int first = vec ? ((V & 7) ? 0 : (lane % V4)) : ((V & 1) ? 0 : (lane % V));
+        float4 *row4 = reinterpret_cast<float4 *>(row);
         float mx = -3.402823466e+38f;
-        {
+        if (vec) {
+            float m0 = mx, m1 = mx, m2 = mx, m3 = mx;
+            for (int jj = 0; jj < V4; jj++) {
+                int j = first + jj; if (j >= V4) j -= V4;
+                const float4 x = row4[j];
+                m0 = fmaxf(m0, x.x); m1 = fmaxf(m1, x.y); m2 = fmaxf(m2, x.z); m3 = fmaxf(m3, x.w);
+            }
+            mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+        } else {
             float m0 = mx, m1 = mx, m2 = mx, m3 = mx;
             int j = first;
             for (; j + 3 < V; j += 4) { m0 = fmaxf(m0, row[j]); m1 = fmaxf(m1, row[j + 1]); m2 = fmaxf(m2, row[j + 2]); m3 = fmaxf(m3, row[j + 3]); }
@@ -1449,7 +1463,18 @@ loss_batch_kernel(const float *__restrict__ logits, const int32_t *__restrict__ 
         }
         float sum = 0.f;
         const float mxl = mx * LOG2E;
-        {
+        if (vec) {
+            float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+            for (int jj = 0; jj < V4; jj++) {
+                int j = first + jj; if (j >= V4) j -= V4;
+                float4 x = row4[j];
+                x.x = fast_exp2(fmaf(x.x, LOG2E, -mxl)); x.y = fast_exp2(fmaf(x.y, LOG2E, -mxl));
+                x.z = fast_exp2(fmaf(x.z, LOG2E, -mxl)); x.w = fast_exp2(fmaf(x.w, LOG2E, -mxl));
+                row4[j] = x;
+                s0 += x.x; s1 += x.y; s2 += x.z; s3 += x.w;
+            }
+            sum = (s0 + s1) + (s2 + s3);
+        } else {
             float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
             int j = first;
             for (; j + 3 < V; j += 4) {
@@ -1505,7 +1530,14 @@ loss_batch_kernel(const float *__restrict__ logits, const int32_t *__restrict__ 
             loss = -logf(row[target] * inv + 1e-10f) * weight;
         }
         const float f = inv * weight;
-        {
+        if (vec) {
+            for (int jj = 0; jj < V4; jj++) {
+                int j = first + jj; if (j >= V4) j -= V4;
+                float4 x = row4[j];
+                x.x *= f; x.y *= f; x.z *= f; x.w *= f;
+                row4[j] = x;
+            }
+        } else {
             int j = first;
             for (; j + 3 < V; j += 4) { row[j] *= f; row[j + 1] *= f; row[j + 2] *= f; row[j + 3] *= f; }
             for (; j < V; j++) row[j] *= f;
