@@ -395,9 +395,10 @@ def run_gpu(args):
     ach_fwd = b_fwd / t_fwd / 1e9
     ach_all = (b_fwd + b_bwd) / (t_fwd + t_bwd) / 1e9
 
-    # end to end: the host-buffer C-ABI call on a bounded subset of this rank's units
+    # end to end: the host-buffer C-ABI call on a bounded subset of this rank's units; every rank runs its own sample
+    # at the same time (each GPU has its own host link), time = max over ranks, rows = sum over ranks
     e2e = None
-    if rank == 0 and not args.no_e2e:
+    if not args.no_e2e:
         budget = args.e2e_nodes
         chosen, tot = [], 0
         for u, p in zip(units, plans):
@@ -415,14 +416,23 @@ def run_gpu(args):
         for u, p, ins, outs, _, _ in host:                 # untimed: first call on a plan allocates its device arena
             A.attn_fwd_bwd_host(p, *ins, H, outs=outs)
         reps = 3
+        sync_all()
         t0 = time.perf_counter()
         for _ in range(reps):
             for u, p, ins, outs, _, _ in host:
                 A.attn_fwd_bwd_host(p, *ins, H, outs=outs)
         dt = (time.perf_counter() - t0) / reps
-        e2e = {"value": tot / dt, "unit": "nodes/s", "h2d_bytes_per_step": int(tot * D * 4 * 4),
-               "d2h_bytes_per_step": int(tot * (D * 4 * 4 + H * 4)),
-               "sample": f"{len(chosen)} launch groups, {tot} of {n_rank} rows of rank 0; attention fwd+bwd through agpt_b200_attn_fwd_bwd_host"}
+        tot_all = tot
+        if world > 1:
+            tmax = torch.tensor([dt], device=dev, dtype=torch.float64)
+            dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+            rows = torch.tensor([float(tot)], device=dev, dtype=torch.float64)
+            dist.all_reduce(rows)
+            dt, tot_all = float(tmax.item()), int(rows.item())
+        e2e = {"value": tot_all / dt, "unit": "nodes/s", "h2d_bytes_per_step": int(tot_all * D * 4 * 4),
+               "d2h_bytes_per_step": int(tot_all * (D * 4 * 4 + H * 4)),
+               "sample": f"{len(chosen)} launch group(s) per rank, {tot_all} rows over {world} rank(s) ({tot} of {n_rank} on rank 0); "
+                         "attention fwd+bwd through agpt_b200_attn_fwd_bwd_host, max time over ranks"}
         del host
 
     # whole-epoch time of the trie-walk trainer on the same trie (all layers, loss, backward, one gradient
