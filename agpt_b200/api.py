@@ -86,8 +86,11 @@ class RadixTrie:
     @classmethod
     def build_gpu(cls, corpus, max_depth: int, subtree_level: int = 1, prune_min_mass: int = 1, prune_min_depth: int = 4,
                   device: int = 0) -> "RadixTrie":
-        """The same trie as build(), with the suffix ordering done on the GPU."""
+        """The same trie as build(), with the suffix ordering done on the GPU.  A corpus shorter than max_depth + 2
+        tokens (nothing to order) goes to the level-by-level builder."""
         c = _np_i32(corpus)
+        if c.size < max_depth + 2:
+            return cls.build(c, max_depth, subtree_level, prune_min_mass, prune_min_depth)
         h = C.c_void_p()
         check(lib().agpt_b200_trie_build_gpu(_vp(c), c.size, max_depth, subtree_level, prune_min_mass, prune_min_depth, device,
                                              C.byref(h)), "trie_build_gpu")

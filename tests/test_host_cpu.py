@@ -271,3 +271,9 @@ def test_units_capped_partition_all_rows():
                 chain = all(plan.sub_end[j] == plan.sub_end[bb] for j in range(bb, ee))
                 assert whole or chain                       # a subtree, or the unary top of one
                 assert ee - bb <= cap or chain
+
+
+def test_build_gpu_on_a_tiny_corpus_uses_the_level_builder():
+    from tests.helpers import assert_same_trie
+    corpus = A.synth_markov_corpus(9, 3, 1, 2)
+    assert_same_trie(A.RadixTrie.build_gpu(corpus, 12), A.RadixTrie.build(corpus, 12))
