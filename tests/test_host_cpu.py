@@ -277,3 +277,47 @@ def test_build_gpu_on_a_tiny_corpus_uses_the_level_builder():
     from tests.helpers import assert_same_trie
     corpus = A.synth_markov_corpus(9, 3, 1, 2)
     assert_same_trie(A.RadixTrie.build_gpu(corpus, 12), A.RadixTrie.build(corpus, 12))
+
+
+@pytest.mark.parametrize("builder", ["level", "suffix_order"])
+def test_radix_trie_is_lossless_against_brute_force_counts(builder):
+    """The check of the reference's src/tools/radix_verify.cr:58-106 with the leveled trie replaced by brute force:
+    every radix node's root path is a prefix that occurs in the corpus, its counts are exactly the next-token
+    counts after the occurrences of that path, its edge mass is the number of occurrences of the path up to its
+    first edge character that continue, and every prefix with two or more continuations is some node's endpoint."""
+    from collections import Counter, defaultdict
+    from tests.helpers import suffix_order
+    depth = 6
+    corpus = A.synth_markov_corpus(1200, 6, 2, 4)
+    c = corpus.tolist()
+    n = len(c)
+    nxt = defaultdict(Counter)                 # prefix -> Counter(next token); starts 0 .. n-2 as the builders use
+    for s0 in range(n - 1):
+        for d in range(1, depth + 1):
+            if s0 + d - 1 > n - 1:
+                break
+            key = tuple(c[s0:s0 + d])
+            nxt[key]                           # the prefix exists even if nothing follows it
+            if s0 + d <= n - 1:
+                nxt[key][c[s0 + d]] += 1
+    if builder == "level":
+        t = A.RadixTrie.build(corpus, depth)
+    else:
+        t = A.RadixTrie.from_suffix_order(corpus, depth, *suffix_order(corpus, depth + 1))
+    endpoints = set()
+    for r in range(1, t.radix_count):
+        path, cur = [], r
+        while cur != 0:
+            path = t.edge_tok[t.edge_off[cur]:t.edge_off[cur + 1]].tolist() + path
+            cur = int(t.parent[cur])
+        key = tuple(path)
+        assert key in nxt and len(key) == t.endpoint_depth[r]
+        got = dict(zip(t.cnt_tok[t.cnt_off[r]:t.cnt_off[r + 1]].tolist(), t.cnt_val[t.cnt_off[r]:t.cnt_off[r + 1]].tolist()))
+        assert got == dict(nxt[key])
+        first = key[:t.first_char_depth[r]]
+        assert t.edge_mass[r] == sum(nxt[first].values())
+        endpoints.add(key)
+    for key, cnt in nxt.items():
+        if len(cnt) >= 2 or (len(key) == depth and len(cnt) >= 1):
+            assert key in endpoints
+    assert len(endpoints) == t.radix_count - 1
