@@ -155,3 +155,22 @@ def assert_same_trie(a, b):
         (b.radix_count, b.n_depth_files, b.total_edge_chars, b.leveled_nodes)
     for name in TRIE_ARRAYS:
         assert np.array_equal(getattr(a, name), getattr(b, name)), name
+
+
+def suffix_order_np(corpus, key_len):
+    """suffix_order() in numpy for corpora of millions of tokens: a lexicographic sort over key_len columns (a position
+    past the end is column value -1), then the common leading tokens of neighbours column by column."""
+    c = np.asarray(corpus, np.int64)
+    n = c.size
+    m = n - 1
+    pad = np.concatenate([c, np.full(key_len, -1, np.int64)])
+    starts = np.arange(m)
+    sa = np.lexsort(tuple(pad[starts + d] for d in range(key_len - 1, -1, -1)) )     # last key is the primary one
+    lcp = np.zeros(m, np.int64)
+    alive = np.ones(m - 1, bool)
+    a, b = sa[:-1], sa[1:]
+    for d in range(key_len):
+        same = alive & (pad[a + d] == pad[b + d]) & (pad[a + d] >= 0)
+        lcp[1:] += same
+        alive = same
+    return sa.astype(np.int32), lcp.astype(np.int32)

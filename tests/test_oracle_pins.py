@@ -243,6 +243,9 @@ def test_real_corpus_trie_shape(depth, endpoints, chars):
         tr = A.RadixTrie.build(tok, depth)
         assert tr.radix_count - 1 == endpoints and tr.total_edge_chars == chars
         assert np.array_equal(tr.edge_start, rx.edge_start) and np.array_equal(tr.cnt_val, rx.cnt_val)
+        # the suffix-order assembly on the real text: identical arrays
+        from tests.helpers import assert_same_trie, suffix_order_np
+        assert_same_trie(A.RadixTrie.from_suffix_order(tok, depth, *suffix_order_np(tok, depth + 1)), tr)
 
 
 def test_golden_vectors_reproduce():
