@@ -7,9 +7,10 @@ One step = one pass of the hot path over every position of the trie for one laye
 forward, backward with the deterministic dK/dV reduction, and the mass-weighted per-query loss, unit by
 unit (root-child subtrees at N=1, bigram subtrees balanced over ranks at N>1), followed at N>1 by one
 NCCL all-reduce of a gradient-sized buffer.  `value` is trie nodes (char positions) per second with
-inputs resident in HBM; `e2e` is the same through the host-buffer C-ABI call.
+inputs resident in HBM; `e2e` is the same through the host-buffer C-ABI call (every rank at once at N>1); `epoch` is
+one whole trainer epoch on the same trie.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload c2|c1|micro]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload c2|c1|micro|c4|c5] [--kv f32|bf16]
 """
 from __future__ import annotations
 
