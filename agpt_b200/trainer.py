@@ -364,11 +364,24 @@ class SampleSpace:
                            device, tile, None if trained.all() else trained)
 
 
+def lightning_lr_weights(masses, mode: str) -> np.ndarray:
+    """Per-sample learning-rate multipliers of the reference's --mass-lr (src/cuda/agpt_train.cu:4276-4300): the summed
+    edge mass of each sample compressed (log(1+m), sqrt(m) or m) and divided by the mean over the super-epoch's samples."""
+    m = np.asarray(masses, np.float64)
+    if mode == "off" or m.size == 0:
+        return np.ones(m.size, np.float64)
+    c = np.log(1.0 + m) if mode == "log" else (np.where(m > 0, np.sqrt(np.maximum(m, 0.0)), 0.0) if mode == "sqrt" else m.copy())
+    total = float(c.sum())
+    mean = total / m.size if total > 0.0 else 1.0
+    return c / mean
+
+
 def train_lightning_epoch(model: TrieWalkModel, space: SampleSpace, counts, opt, sampler: int, steps: int, rng_state: int,
-                          mass_mode="off", p_stop=0.3, max_mass=0, **loss_kw):
+                          mass_mode="off", p_stop=0.3, max_mass=0, mass_lr="off", **loss_kw):
     """One super-epoch of the reference's lightning mode: `steps` sampled units, each its own gradient and optimizer step
     (src/cuda/agpt_train.cu:152-157).  Returns (loss sum, queries, nodes trained, new generator state)."""
-    rs, na, off, _, nodes, rng_state = space.trie.lightning_sample(sampler, steps, rng_state, p_stop, max_mass)
+    rs, na, off, masses, nodes, rng_state = space.trie.lightning_sample(sampler, steps, rng_state, p_stop, max_mass)
+    lr_w = lightning_lr_weights(masses, mass_lr)
     model.bind_grads()
     loss_sum, n_q, n_nodes = 0.0, 0, 0
     for s in range(steps):
@@ -382,6 +395,8 @@ def train_lightning_epoch(model: TrieWalkModel, space: SampleSpace, counts, opt,
         g = space.group(ids, context, mass_mode, model.cfg.seq_len, model.device)
         opt.zero_grad(set_to_none=False)
         ls, nq = model.group_step(g, counts, **loss_kw)
+        if hasattr(opt, "lr_scale"):
+            opt.lr_scale = float(lr_w[s])
         opt.step()
         loss_sum += ls
         n_q += nq
@@ -398,6 +413,7 @@ class FlatOptimizer:
         self.base_lr = lr
         self.weight_decay, self.clip_norm, self.t = weight_decay, clip_norm, 0
         self.schedule = None             # (name, total steps, warm-up steps): lr of each step from A.compute_lr
+        self.lr_scale = 1.0              # per-step multiplier (the lightning mode's learning rate by sample mass)
         z = lambda: torch.zeros(model.n_flat, dtype=torch.float32, device=model.device)  # noqa: E731
         self.m = z() if kind in ("momentum", "adam") else None
         self.v = z() if kind in ("rmsprop", "adam") else None
@@ -408,7 +424,7 @@ class FlatOptimizer:
             self.lr = A.compute_lr(self.base_lr, self.t, total, warm, name)
         self.t += 1
         m = self.model
-        return A.optimizer_step(self.kind, m.flat, m.flat_grad[:m.n_flat], self.m, self.v, lr=self.lr, beta1=self.beta1,
+        return A.optimizer_step(self.kind, m.flat, m.flat_grad[:m.n_flat], self.m, self.v, lr=self.lr * self.lr_scale, beta1=self.beta1,
                                 beta2=self.beta2, eps=self.eps, t=self.t, weight_decay=self.weight_decay,
                                 clip_norm=self.clip_norm, zero_grads=True)
 
@@ -488,6 +504,7 @@ def main(argv=None):
     ap.add_argument("--lightning-p-stop", type=float, default=0.3)
     ap.add_argument("--lightning-seed", type=lambda v: int(v, 0), default=0x5c115e1)
     ap.add_argument("--lightning-max-mass", type=int, default=0)
+    ap.add_argument("--lightning-mass-lr", default="off", choices=["off", "log", "sqrt", "linear"])
     ap.add_argument("--partition-depth", type=int, default=0, choices=[0, 1, 2],
                     help="1 = root-child units, 2 = bigram units; 0 = 1 on one rank, 2 on several")
     args = ap.parse_args(argv)
@@ -532,7 +549,7 @@ def main(argv=None):
         if lightning:
             ls, nq, _, rng_state = train_lightning_epoch(model, space, counts, opt, int(args.lightning_sampler[1]), args.lightning_steps,
                                                          rng_state, args.mass_weight, args.lightning_p_stop, args.lightning_max_mass,
-                                                         **loss_kw)
+                                                         mass_lr=args.lightning_mass_lr, **loss_kw)
             units, chunks = args.lightning_steps, args.lightning_steps
         else:
             ls, nq = train_epoch(model, groups, counts, opt, accumulate=not args.no_accumulate or world > 1, world=world, **loss_kw)

@@ -556,3 +556,17 @@ def compute_lr(base_lr, step, total_steps, warmup_steps, schedule):
         return f(base_lr)
     progress = min(f(step - cos_start) / f(total_steps - cos_start), f(1.0))
     return f(f(0.5) * f(base_lr) * (f(1.0) + np.cos(f(f(3.14159265358979323846) * progress), dtype=np.float32)))
+
+
+def lightning_lr_weights(masses, mode):
+    """src/cuda/agpt_train.cu:4276-4300 as a plain loop; mode 0 off, 1 log, 2 sqrt, 3 linear."""
+    import math
+    comp = []
+    for m in masses:
+        m = float(m)
+        comp.append(math.log(1.0 + m) if mode == 1 else ((math.sqrt(m) if m > 0.0 else 0.0) if mode == 2 else (m if mode == 3 else 1.0)))
+    total = 0.0
+    for c in comp:
+        total += c
+    mean = total / len(comp) if (comp and total > 0.0) else 1.0
+    return [c / mean for c in comp]

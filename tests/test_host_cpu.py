@@ -321,3 +321,13 @@ def test_radix_trie_is_lossless_against_brute_force_counts(builder):
         if len(cnt) >= 2 or (len(key) == depth and len(cnt) >= 1):
             assert key in endpoints
     assert len(endpoints) == t.radix_count - 1
+
+
+def test_lightning_lr_weights_match_oracle():
+    from agpt_b200 import trainer as T
+    masses = [729.0, 1272.0, 3.0, 0.0, 88000.0]
+    for mode, code in (("off", 0), ("log", 1), ("sqrt", 2), ("linear", 3)):
+        got, want = T.lightning_lr_weights(masses, mode), O.lightning_lr_weights(masses, code)
+        assert np.allclose(got, want, rtol=1e-15, atol=0)
+        assert mode == "off" or abs(float(np.mean(got)) - 1.0) < 1e-12
+    assert T.lightning_lr_weights([], "log").size == 0 and np.array_equal(T.lightning_lr_weights([0.0, 0.0], "linear"), [0.0, 0.0])
