@@ -36,9 +36,14 @@ def _view(ptr, n, dtype):
 # ----------------------------------------------------------------------------------------
 # synthetic workloads
 # ----------------------------------------------------------------------------------------
-def synth_markov_corpus(n: int, vocab: int, order: int, seed: int = 0) -> np.ndarray:
+def synth_markov_corpus(n: int, vocab: int, order: int, seed: int = 0, repeat_log2: int = 0) -> np.ndarray:
+    """Seeded order-`order` Markov corpus with Zipf(1.1) marginals; repeat_log2 > 0 injects, with probability
+    2^-repeat_log2 per position, a copy of 64..256 symbols from an earlier offset (long verbatim repeats)."""
     out = np.zeros(n, np.int32)
-    check(lib().agpt_b200_synth_markov_corpus(n, vocab, order, seed, _vp(out)), "synth_markov_corpus")
+    if repeat_log2:
+        check(lib().agpt_b200_synth_markov_corpus_repeats(n, vocab, order, seed, repeat_log2, _vp(out)), "synth_markov_corpus_repeats")
+    else:
+        check(lib().agpt_b200_synth_markov_corpus(n, vocab, order, seed, _vp(out)), "synth_markov_corpus")
     return out
 
 
@@ -410,14 +415,58 @@ def _kv_dtype(k):
     raise AgptError("KV store must be float32 or bfloat16")
 
 
+def validate_attn_args(plan: WalkerPlan, n_heads: int, f32_rows=(), kv_rows=(), lse=None, require_cuda: bool = True):
+    """Refuse, before anything is launched, tensors the attention entry points would read or write out of bounds:
+    the C entry points take no row count (it is the plan's), so a tensor with fewer rows than the plan, another
+    width, dtype, device or a non-contiguous layout must be caught here.  f32_rows / kv_rows: (name, tensor) pairs
+    that must be [plan.n, D] float32, resp. float32 or bfloat16; lse: [plan.n, n_heads] float32.  Returns (D, hd)."""
+    import torch
+    if not f32_rows:
+        raise AgptError("no tensors given")
+    ref = f32_rows[0][1]
+    if ref.dim() != 2:
+        raise AgptError(f"{f32_rows[0][0]} must be 2-D [rows, n_heads * head_dim]")
+    D = int(ref.shape[1])
+    if n_heads < 1 or D % n_heads:
+        raise AgptError(f"width {D} is not a multiple of n_heads {n_heads}")
+    hd = D // n_heads
+    if hd not in (16, 32, 64):
+        raise AgptError(f"head_dim {hd} unsupported (16, 32 or 64)")
+
+    def one(name, t, dtypes, shape):
+        if tuple(t.shape) != shape:
+            raise AgptError(f"{name} has shape {tuple(t.shape)}, the plan needs {shape}")
+        if t.dtype not in dtypes:
+            raise AgptError(f"{name} has dtype {t.dtype}, expected one of {[str(d) for d in dtypes]}")
+        if not t.is_contiguous():
+            raise AgptError(f"{name} must be contiguous")
+        if require_cuda and not t.is_cuda:
+            raise AgptError(f"{name} must be a CUDA tensor")
+        if t.device != ref.device:
+            raise AgptError(f"{name} is on {t.device}, {f32_rows[0][0]} on {ref.device}")
+        if require_cuda and plan.device >= 0 and t.device.index != plan.device:
+            raise AgptError(f"{name} is on {t.device}, the plan on cuda:{plan.device}")
+
+    for name, t in f32_rows:
+        one(name, t, (torch.float32,), (plan.n, D))
+    for name, t in kv_rows:
+        one(name, t, (torch.float32, torch.bfloat16), (plan.n, D))
+    if len(kv_rows) == 2 and kv_rows[0][1].dtype != kv_rows[1][1].dtype:
+        raise AgptError("k and v must have the same dtype")
+    if lse is not None:
+        one("lse", lse, (torch.float32,), (plan.n, n_heads))
+    return D, hd
+
+
 def attn_forward(plan: WalkerPlan, q, k, v, n_heads: int, scale: float | None = None, out=None, lse=None):
     import torch
     _chk_f32(q, "q")
     n, D = q.shape
     hd = D // n_heads
-    scale = 1.0 / math.sqrt(hd) if scale is None else scale
     out = torch.empty_like(q) if out is None else out
     lse = torch.empty((n, n_heads), dtype=torch.float32, device=q.device) if lse is None else lse
+    validate_attn_args(plan, n_heads, [("q", q), ("out", out)], [("k", k), ("v", v)], lse)
+    scale = 1.0 / math.sqrt(hd) if scale is None else scale
     check(lib().agpt_b200_attn_fwd(plan._h, _dp(q), _dp(k), _dp(v), _kv_dtype(k), _dp(out), _dp(lse), n_heads, hd,
                                    scale, _stream()), "attn_fwd")
     return out, lse
@@ -436,6 +485,10 @@ def attn_backward(plan: WalkerPlan, q, k, v, out, lse, dout, n_heads: int, scale
     dq = torch.empty_like(q) if dq is None else dq
     dk = torch.empty_like(q) if dk is None else dk
     dv = torch.empty_like(q) if dv is None else dv
+    validate_attn_args(plan, n_heads, [("q", q), ("out", out), ("dout", dout), ("dq", dq), ("dk", dk), ("dv", dv)],
+                       [("k", k), ("v", v)], lse)
+    if workspace.dtype != torch.uint8 or not workspace.is_contiguous() or workspace.device != q.device:
+        raise AgptError("workspace must be a contiguous uint8 tensor on the device of q")
     check(lib().agpt_b200_attn_bwd(plan._h, _dp(q), _dp(k), _dp(v), _kv_dtype(k), _dp(out), _dp(lse), _dp(dout),
                                    _dp(dq), _dp(dk), _dp(dv), _dp(workspace), workspace.numel(), n_heads, hd, scale,
                                    _stream()), "attn_bwd")
@@ -582,6 +635,12 @@ def set_attn_impl(impl: int) -> None:
     check(lib().agpt_b200_set_attn_impl(impl), "set_attn_impl")
 
 
+def set_attn_bwd_variant(whole_tile: bool = True, warps: int = 6) -> None:
+    """Tensor-core backward for a float32 store and head_dim <= 32: the whole-tile kernel (default) or the chunked
+    one; warps per block of the former (4, 6 or 8)."""
+    check(lib().agpt_b200_set_attn_bwd_variant(int(bool(whole_tile)), warps), "set_attn_bwd_variant")
+
+
 def static_scratch_bytes() -> int:
     return int(lib().agpt_b200_static_scratch_bytes())
 
@@ -595,6 +654,11 @@ def attn_backward_static(plan: WalkerPlan, q, k, v, out, lse, dout, n_heads: int
     n, D = q.shape
     hd = D // n_heads
     scale = 1.0 / math.sqrt(hd) if scale is None else scale
+    need = plan.workspace_bytes(D)
+    if need > static_scratch_bytes():           # the entry point's own first check; made here too so that it precedes the shape checks
+        raise AgptError(f"attn_bwd_static: the plan needs {need} bytes of scratch, the built-in array holds {static_scratch_bytes()}")
+    validate_attn_args(plan, n_heads, [("q", q), ("out", out), ("dout", dout), ("dq", dq), ("dk", dk), ("dv", dv)],
+                       [("k", k), ("v", v)], lse)
     check(lib().agpt_b200_attn_bwd_static(plan._h, _dp(q), _dp(k), _dp(v), _kv_dtype(k), _dp(out), _dp(lse), _dp(dout),
                                           _dp(dq), _dp(dk), _dp(dv), n_heads, hd, scale, _stream()), "attn_bwd_static")
     return dq, dk, dv

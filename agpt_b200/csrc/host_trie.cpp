@@ -60,7 +60,22 @@ static int inv_cdf(const std::vector<double> &cdf, double u) {
     return lo;
 }
 
+static int synth_markov(int64_t n, int vocab, int order, uint64_t seed, int repeat_log2, int32_t *out);
+
 extern "C" int agpt_b200_synth_markov_corpus(int64_t n, int vocab, int order, uint64_t seed, int32_t *out) {
+    return synth_markov(n, vocab, order, seed, 0, out);
+}
+
+extern "C" int agpt_b200_synth_markov_corpus_repeats(int64_t n, int vocab, int order, uint64_t seed, int repeat_log2,
+                                                     int32_t *out) {
+    if (repeat_log2 < 1 || repeat_log2 > 40) return agpt_set_error(AGPT_E_ARG, "synth_markov_corpus_repeats: repeat_log2 must be 1..40");
+    return synth_markov(n, vocab, order, seed, repeat_log2, out);
+}
+
+// repeat_log2 > 0: before each symbol one more draw of the stream decides, with probability 2^-repeat_log2, to copy
+// a span of 64 + (draw mod 193) symbols from a uniformly drawn earlier offset instead (long verbatim repeats, as
+// natural text has them; a plain low-order Markov source has none, so its count>=2 trie stays shallow).
+static int synth_markov(int64_t n, int vocab, int order, uint64_t seed, int repeat_log2, int32_t *out) {
     if (!out || n < 0 || vocab < 2 || order < 1 || order > 8) return agpt_set_error(AGPT_E_ARG, "synth_markov_corpus: bad argument");
     const int M = 6;
     std::vector<double> zipf(vocab), slot(M);
@@ -76,6 +91,23 @@ extern "C" int agpt_b200_synth_markov_corpus(int64_t n, int vocab, int order, ui
     for (int i = 0; i < order; i++) modulus *= (uint64_t)vocab;
     uint64_t ctx = 0, s = splitmix64(seed);
     for (int64_t i = 0; i < n; i++) {
+        if (repeat_log2 > 0 && i > 0) {
+            s = splitmix64(s);
+            if ((s >> (64 - repeat_log2)) == 0) {
+                s = splitmix64(s);
+                const int64_t len = 64 + (int64_t)(s % 193);
+                s = splitmix64(s);
+                const int64_t src = (int64_t)(s % (uint64_t)i);
+                int64_t t = 0;
+                for (; t < len && i + t < n; t++) {          // the span may run into what it is writing (like an LZ77 match)
+                    const int sym = out[src + t];
+                    out[i + t] = sym;
+                    ctx = (ctx * (uint64_t)vocab + (uint64_t)sym) % modulus;
+                }
+                i += t - 1;
+                continue;
+            }
+        }
         uint64_t h = splitmix64(seed ^ (ctx * 0x9E3779B97F4A7C15ULL));
         s = splitmix64(s);
         int j = inv_cdf(slot, u01(s));

@@ -233,6 +233,7 @@ __device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+#define AGPT_MAX_DEVICES 64
 #define MAXKEYS 512      // keys (chain + tile rows) a tile of the tensor-core kernels can hold metadata for
 
 __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src) {
@@ -847,6 +848,328 @@ __global__ void __launch_bounds__(128, HD <= 32 ? 4 : (sizeof(KVT) == 2 ? 3 : 1)
     }
 }
 
+// --------------------------------------------------------------------------------------
+// backward, whole tile resident: attn_bwd_tile_kernel.
+//
+// The tile's Q and dO rows and every key row the tile can attend (ancestor chain + the tile's own rows) are
+// brought into shared memory ONCE, already split into TF32 hi and lo parts: element (row, dim) is the pair
+// {hi, lo}, pairs of dims form 16-byte chunks, and the chunk index is XOR-swizzled with the row so that both
+// fragment shapes the MMAs need are single conflict-free loads:
+//   * "along the row" (one row, two neighbouring dims, hi and lo): one 16-byte load;
+//   * "across rows"   (two neighbouring rows, one dim, hi and lo): two 8-byte loads.
+// After one block barrier the warps never meet again.  Work is cut into items that a warp runs from start to
+// end with nothing but registers and read-only shared memory:
+//   * row item (16 queries):  S = Q K^T and dP = dO V^T for the 16 rows against every key block, P, dS,
+//     dQ += dS K (the score fragment is the A fragment of the next product);  writes 16 dQ rows.
+//   * key item (16 keys):     S^T = K Q^T and dP^T = V dO^T for the 16 keys against every query block, P^T, dS^T,
+//     dK += dS^T Q, dV += P^T dO;  writes 16 dK/dV rows (tile rows) or partial rows (chain keys).
+// Scores are computed twice (once per orientation) instead of crossing shared memory between two phases: that
+// costs two extra small products per block and removes every barrier, every P/dS store and reload.  Items are
+// handed out through a shared counter, heaviest first; each output element is produced by exactly one warp in a
+// fixed order, so the result does not depend on which warp took which item.
+// --------------------------------------------------------------------------------------
+__device__ __forceinline__ float ex2_ftz(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ int tile_swz(int r) { return (((r >> 1) & 3) << 1) ^ ((r & 1) << 2); }
+
+// store 4 consecutive dims (float4 index c4 of row r) into the swizzled row: chunk 2*c4 takes dims 4*c4, 4*c4+1 as
+// {hi, hi, lo, lo}, chunk 2*c4+1 the next two.  The eight lanes that fill one row write their even chunk first when
+// c4 < 4 and their odd chunk first otherwise, so that each 16-byte store instruction covers all 32 banks once.
+template <int HD>
+__device__ __forceinline__ void tile_store_split(float4 *base, int r, int c4, float4 x) {
+    uint32_t h0, l0, h1, l1, h2, l2, h3, l3;
+    tf32_split(x.x, h0, l0); tf32_split(x.y, h1, l1); tf32_split(x.z, h2, l2); tf32_split(x.w, h3, l3);
+    const int pc = (2 * c4) ^ tile_swz(r);
+    float4 *row = base + r * (HD / 2);
+    const float4 ev = make_float4(__uint_as_float(h0), __uint_as_float(h1), __uint_as_float(l0), __uint_as_float(l1));
+    const float4 od = make_float4(__uint_as_float(h2), __uint_as_float(h3), __uint_as_float(l2), __uint_as_float(l3));
+    if ((c4 >> 2) & 1) { row[pc ^ 1] = od; row[pc] = ev; }
+    else { row[pc] = ev; row[pc ^ 1] = od; }
+}
+
+template <int HD> constexpr size_t bwd_tile_smem_bytes(int maxk) {
+    return (size_t)(2 * 64 + 2 * maxk) * (HD / 2) * 16 + (size_t)maxk * 8 + 2 * 64 * 4 + 16;
+}
+
+template <int HD, int NW>
+__global__ void __launch_bounds__(NW * 32, 2)
+attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, const float *__restrict__ V,
+                     const float *__restrict__ O, const float *__restrict__ LSE, const float *__restrict__ dO,
+                     float *__restrict__ dQ, float *__restrict__ dK, float *__restrict__ dV, float *__restrict__ Pk,
+                     float *__restrict__ Pv, const int32_t *__restrict__ sub_end, const int64_t *__restrict__ chain_off,
+                     const int32_t *__restrict__ chain_ids, const int32_t *__restrict__ chain_end_all, int n, int H,
+                     float scale, int tile0, int maxk, int dbg) {
+    constexpr int M = 64, KS = HD / 8, RC = HD / 2, C4 = HD / 4, NT = NW * 32;
+    extern __shared__ __align__(16) unsigned char tile_smem_raw[];
+    float4 *sQ = reinterpret_cast<float4 *>(tile_smem_raw);          // [64][RC]
+    float4 *sG = sQ + M * RC;                                         // [64][RC]   dO
+    float4 *sK = sG + M * RC;                                         // [maxk][RC]
+    float4 *sV = sK + (size_t)maxk * RC;                              // [maxk][RC]
+    int2 *s_meta = reinterpret_cast<int2 *>(sV + (size_t)maxk * RC);  // [maxk] {key id, key subtree end}
+    float *sLse = reinterpret_cast<float *>(s_meta + maxk);           // [64]  lse * log2(e)
+    float *sDelta = sLse + M;                                         // [64]  dO . O
+    int *s_ctr = reinterpret_cast<int *>(sDelta + M);
+
+    const int t = blockIdx.x + tile0, h = blockIdx.y, tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, tig = lane & 3;
+    const int D = H * HD, hoff = h * HD;
+    const int i0 = t * M;
+    const int nt = min(M, n - i0);
+    const int64_t coff = chain_off[t];
+    const int p = (int)(chain_off[t + 1] - coff);
+    const int nkeys = p + nt;
+    const int nkp = (nkeys + 15) & ~15;                // rows staged (zero rows beyond nkeys)
+    const int32_t *chain = chain_ids + coff;
+    const int32_t *chain_end = chain_end_all + coff;
+    const float qs = scale * LOG2E;
+
+    // ---- stage: key metadata, K/V rows, Q/dO rows (+ delta), lse ----
+    if (tid == 0) *s_ctr = 0;
+    for (int j = tid; j < nkp; j += NT) {
+        int kid = 0x7fffffff, kend = 0;
+        if (j < p) { kid = __ldg(chain + j); kend = __ldg(chain_end + j); }
+        else if (j < nkeys) { kid = i0 + (j - p); kend = __ldg(sub_end + kid); }
+        s_meta[j] = make_int2(kid, kend);
+    }
+    if (tid < M) sLse[tid] = tid < nt ? __ldg(LSE + (int64_t)(i0 + tid) * H + h) * LOG2E : 0.f;
+    {
+        // every global load of the block is issued before the first one is used: one round trip to memory instead
+        // of one per loop iteration (the block has nothing else to overlap it with until the barrier)
+        constexpr int UQ = (M * C4 + NT - 1) / NT;       // iterations over the tile's own Q / dO / O rows
+        constexpr int UK = 4;                            // key-row iterations per batch
+        float4 qx[UQ], gx[UQ], ox[UQ], kx[UK], vx[UK];
+#pragma unroll
+        for (int u = 0; u < UQ; u++) {
+            const int idx = tid + u * NT, r = idx / C4, c = idx % C4;
+            qx[u] = gx[u] = ox[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (idx < M * C4 && r < nt) {
+                const int64_t off = (int64_t)(i0 + r) * D + hoff + c * 4;
+                qx[u] = ld4(Q + off); gx[u] = ld4(dO + off); ox[u] = ld4(O + off);
+            }
+        }
+        for (int base = 0; base < nkp * C4; base += NT * UK) {
+#pragma unroll
+            for (int u = 0; u < UK; u++) {
+                const int idx = base + tid + u * NT, r = idx / C4, c = idx % C4;
+                kx[u] = vx[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (r < nkeys) {
+                    const int kid = r < p ? __ldg(chain + r) : i0 + (r - p);
+                    const int64_t off = (int64_t)kid * D + hoff + c * 4;
+                    kx[u] = ld4(K + off); vx[u] = ld4(V + off);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < UK; u++) {
+                const int idx = base + tid + u * NT, r = idx / C4, c = idx % C4;
+                if (idx < nkp * C4) { tile_store_split<HD>(sK, r, c, kx[u]); tile_store_split<HD>(sV, r, c, vx[u]); }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UQ; u++) {       // whole warps enter or skip an iteration (64*C4 and NT are multiples of 32)
+            const int idx = tid + u * NT, r = idx / C4, c = idx % C4;
+            if (idx < M * C4) {
+                float d = gx[u].x * ox[u].x;
+                d = fmaf(gx[u].y, ox[u].y, d); d = fmaf(gx[u].z, ox[u].z, d); d = fmaf(gx[u].w, ox[u].w, d);
+#pragma unroll
+                for (int o = 1; o < C4; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+                if (c == 0) sDelta[r] = d;
+                tile_store_split<HD>(sQ, r, c, qx[u]);
+                tile_store_split<HD>(sG, r, c, gx[u]);
+            }
+        }
+    }
+    __syncthreads();
+
+    const int fg = tile_swz(g);                  // swizzle of a row whose index is g (mod 8)
+    const int fa = tile_swz(2 * tig), fb = tile_swz(2 * tig + 1);
+    const int nkb = nkp >> 4;                    // key items
+    const int npc = (p + 15) >> 4;               // key items that hold chain keys (the heaviest: attended by most rows)
+    const int n_items = nkb + 4;
+
+    for (;;) {
+        int it = 0;
+        if (lane == 0) it = atomicAdd(s_ctr, 1);
+        it = __shfl_sync(0xffffffffu, it, 0);
+        if (it >= n_items) break;
+        // order: chain key items, row items (last rows first), the tile's own key items
+        int kind, which;
+        if (it < npc) { kind = 1; which = it; }
+        else if (it < npc + 4) { kind = 0; which = 3 - (it - npc); }
+        else { kind = 1; which = it - 4; }
+        if ((dbg >> kind) & 1) continue;
+
+        if (kind == 0) {
+            // ================= row item: 16 queries, every key block =================
+            const int rg = which;
+            if (rg * 16 >= nt) continue;                                   // rows beyond the end of the plan
+            const int q0 = rg * 16 + g, q1 = q0 + 8;
+            const int r0 = i0 + q0, r1 = i0 + q1;
+            uint32_t qh[KS][4], ql[KS][4], gh[KS][4], gl[KS][4];
+#pragma unroll
+            for (int ks = 0; ks < KS; ks++) {
+                const int pc = (ks * 4 + tig) ^ fg;
+                const float4 a = sQ[q0 * RC + pc], b = sQ[q1 * RC + pc];
+                qh[ks][0] = __float_as_uint(a.x); qh[ks][2] = __float_as_uint(a.y); ql[ks][0] = __float_as_uint(a.z); ql[ks][2] = __float_as_uint(a.w);
+                qh[ks][1] = __float_as_uint(b.x); qh[ks][3] = __float_as_uint(b.y); ql[ks][1] = __float_as_uint(b.z); ql[ks][3] = __float_as_uint(b.w);
+                const float4 c = sG[q0 * RC + pc], d = sG[q1 * RC + pc];
+                gh[ks][0] = __float_as_uint(c.x); gh[ks][2] = __float_as_uint(c.y); gl[ks][0] = __float_as_uint(c.z); gl[ks][2] = __float_as_uint(c.w);
+                gh[ks][1] = __float_as_uint(d.x); gh[ks][3] = __float_as_uint(d.y); gl[ks][1] = __float_as_uint(d.z); gl[ks][3] = __float_as_uint(d.w);
+            }
+            const float lse0 = sLse[q0], lse1 = sLse[q1], dl0 = sDelta[q0], dl1 = sDelta[q1];
+            float dq[KS][4];
+#pragma unroll
+            for (int db = 0; db < KS; db++) dq[db][0] = dq[db][1] = dq[db][2] = dq[db][3] = 0.f;
+            // the rows of this group attend the chain and the tile's keys up to their own position
+            const int nb_lim = min((nkeys + 7) >> 3, (p + rg * 16 + 16 + 7) >> 3);
+            for (int nb = 0; nb < nb_lim; nb++) {
+                const int4 mk = *reinterpret_cast<const int4 *>(&s_meta[nb * 8 + 2 * tig]);   // keys 2*tig, 2*tig+1 of the block
+                const bool v0 = mk.x <= r0 && r0 < mk.y, v1 = mk.z <= r0 && r0 < mk.w;
+                const bool v2 = mk.x <= r1 && r1 < mk.y, v3 = mk.z <= r1 && r1 < mk.w;
+                if (!__any_sync(0xffffffffu, v0 | v1 | v2 | v3)) continue;
+                float c[4] = {0.f, 0.f, 0.f, 0.f}, cx[4] = {0.f, 0.f, 0.f, 0.f}, cy[4] = {0.f, 0.f, 0.f, 0.f};
+                float e[4] = {0.f, 0.f, 0.f, 0.f}, ex[4] = {0.f, 0.f, 0.f, 0.f}, ey[4] = {0.f, 0.f, 0.f, 0.f};
+                const float4 *kr = sK + (nb * 8 + g) * RC, *vr = sV + (nb * 8 + g) * RC;
+#pragma unroll
+                for (int ks = 0; ks < KS; ks++) {
+                    const int pc = (ks * 4 + tig) ^ fg;
+                    const float4 kb = kr[pc], vb = vr[pc];
+                    const uint32_t k0h = __float_as_uint(kb.x), k1h = __float_as_uint(kb.y), k0l = __float_as_uint(kb.z), k1l = __float_as_uint(kb.w);
+                    const uint32_t v0h = __float_as_uint(vb.x), v1h = __float_as_uint(vb.y), v0l = __float_as_uint(vb.z), v1l = __float_as_uint(vb.w);
+                    mma_tf32(c, qh[ks], k0h, k1h); mma_tf32(e, gh[ks], v0h, v1h);
+                    mma_tf32(cx, ql[ks], k0h, k1h); mma_tf32(ex, gl[ks], v0h, v1h);
+                    mma_tf32(cy, qh[ks], k0l, k1l); mma_tf32(ey, gh[ks], v0l, v1l);
+                }
+                float pw[4], ds[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) { c[j] += cx[j] + cy[j]; e[j] += ex[j] + ey[j]; }
+                pw[0] = v0 ? ex2_ftz(fmaf(c[0], qs, -lse0)) : 0.f; pw[1] = v1 ? ex2_ftz(fmaf(c[1], qs, -lse0)) : 0.f;
+                pw[2] = v2 ? ex2_ftz(fmaf(c[2], qs, -lse1)) : 0.f; pw[3] = v3 ? ex2_ftz(fmaf(c[3], qs, -lse1)) : 0.f;
+                ds[0] = pw[0] * (e[0] - dl0) * scale; ds[1] = pw[1] * (e[1] - dl0) * scale;
+                ds[2] = pw[2] * (e[2] - dl1) * scale; ds[3] = pw[3] * (e[3] - dl1) * scale;
+                // dQ += dS K: key 2*tig sits in k-slot tig, key 2*tig+1 in k-slot tig+4
+                uint32_t ah[4], al[4];
+                tf32_split(ds[0], ah[0], al[0]); tf32_split(ds[2], ah[1], al[1]);
+                tf32_split(ds[1], ah[2], al[2]); tf32_split(ds[3], ah[3], al[3]);
+                const float *ka = reinterpret_cast<const float *>(sK + (nb * 8 + 2 * tig) * RC);
+                const float *kb2 = reinterpret_cast<const float *>(sK + (nb * 8 + 2 * tig + 1) * RC);
+#pragma unroll
+                for (int db = 0; db < KS; db++) {
+                    const int cc = db * 4 + (g >> 1), hf = g & 1;
+                    const int ia = ((cc ^ fa) << 2) + hf, ib = ((cc ^ fb) << 2) + hf;      // hi; lo sits two floats further
+                    const uint32_t x0h = __float_as_uint(ka[ia]), x1h = __float_as_uint(kb2[ib]);
+                    const uint32_t x0l = __float_as_uint(ka[ia + 2]), x1l = __float_as_uint(kb2[ib + 2]);
+                    mma_tf32(dq[db], ah, x0h, x1h);
+                    mma_tf32(dq[db], al, x0h, x1h);
+                    mma_tf32(dq[db], ah, x0l, x1l);
+                }
+            }
+            if (r0 < n) {
+#pragma unroll
+                for (int db = 0; db < KS; db++)
+                    *reinterpret_cast<float2 *>(dQ + (int64_t)r0 * D + hoff + db * 8 + 2 * tig) = make_float2(dq[db][0], dq[db][1]);
+            }
+            if (r1 < n) {
+#pragma unroll
+                for (int db = 0; db < KS; db++)
+                    *reinterpret_cast<float2 *>(dQ + (int64_t)r1 * D + hoff + db * 8 + 2 * tig) = make_float2(dq[db][2], dq[db][3]);
+            }
+        } else {
+            // ================= key item: 16 keys, every query block =================
+            const int kb = which;
+            const int kA = kb * 16 + g, kB = kA + 8;
+            const int2 mA = s_meta[kA], mB = s_meta[kB];
+            uint32_t kh[KS][4], kl[KS][4], vh[KS][4], vl[KS][4];
+#pragma unroll
+            for (int ks = 0; ks < KS; ks++) {
+                const int pc = (ks * 4 + tig) ^ fg;
+                const float4 a = sK[kA * RC + pc], b = sK[kB * RC + pc];
+                kh[ks][0] = __float_as_uint(a.x); kh[ks][2] = __float_as_uint(a.y); kl[ks][0] = __float_as_uint(a.z); kl[ks][2] = __float_as_uint(a.w);
+                kh[ks][1] = __float_as_uint(b.x); kh[ks][3] = __float_as_uint(b.y); kl[ks][1] = __float_as_uint(b.z); kl[ks][3] = __float_as_uint(b.w);
+                const float4 c = sV[kA * RC + pc], d = sV[kB * RC + pc];
+                vh[ks][0] = __float_as_uint(c.x); vh[ks][2] = __float_as_uint(c.y); vl[ks][0] = __float_as_uint(c.z); vl[ks][2] = __float_as_uint(c.w);
+                vh[ks][1] = __float_as_uint(d.x); vh[ks][3] = __float_as_uint(d.y); vl[ks][1] = __float_as_uint(d.z); vl[ks][3] = __float_as_uint(d.w);
+            }
+            float dk[KS][4], dv[KS][4];
+#pragma unroll
+            for (int db = 0; db < KS; db++) {
+                dk[db][0] = dk[db][1] = dk[db][2] = dk[db][3] = 0.f;
+                dv[db][0] = dv[db][1] = dv[db][2] = dv[db][3] = 0.f;
+            }
+            // a key of the tile itself is attended only by queries at or after it
+            const int qb_first = max(0, kb * 16 - p) >> 3;
+            const int qb_end = (nt + 7) >> 3;
+            for (int qb = qb_first; qb < qb_end; qb++) {
+                const int rq0 = i0 + qb * 8 + 2 * tig, rq1 = rq0 + 1;
+                const bool v0 = mA.x <= rq0 && rq0 < mA.y, v1 = mA.x <= rq1 && rq1 < mA.y;
+                const bool v2 = mB.x <= rq0 && rq0 < mB.y, v3 = mB.x <= rq1 && rq1 < mB.y;
+                if (!__any_sync(0xffffffffu, v0 | v1 | v2 | v3)) continue;
+                float c[4] = {0.f, 0.f, 0.f, 0.f}, cx[4] = {0.f, 0.f, 0.f, 0.f}, cy[4] = {0.f, 0.f, 0.f, 0.f};
+                float e[4] = {0.f, 0.f, 0.f, 0.f}, ex[4] = {0.f, 0.f, 0.f, 0.f}, ey[4] = {0.f, 0.f, 0.f, 0.f};
+                const float4 *qr = sQ + (qb * 8 + g) * RC, *gr = sG + (qb * 8 + g) * RC;
+#pragma unroll
+                for (int ks = 0; ks < KS; ks++) {
+                    const int pc = (ks * 4 + tig) ^ fg;
+                    const float4 qb4 = qr[pc], gb4 = gr[pc];
+                    const uint32_t q0h = __float_as_uint(qb4.x), q1h = __float_as_uint(qb4.y), q0l = __float_as_uint(qb4.z), q1l = __float_as_uint(qb4.w);
+                    const uint32_t g0h = __float_as_uint(gb4.x), g1h = __float_as_uint(gb4.y), g0l = __float_as_uint(gb4.z), g1l = __float_as_uint(gb4.w);
+                    mma_tf32(c, kh[ks], q0h, q1h); mma_tf32(e, vh[ks], g0h, g1h);
+                    mma_tf32(cx, kl[ks], q0h, q1h); mma_tf32(ex, vl[ks], g0h, g1h);
+                    mma_tf32(cy, kh[ks], q0l, q1l); mma_tf32(ey, vh[ks], g0l, g1l);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; j++) { c[j] += cx[j] + cy[j]; e[j] += ex[j] + ey[j]; }
+                const float2 ls = *reinterpret_cast<const float2 *>(&sLse[qb * 8 + 2 * tig]);
+                const float2 dl = *reinterpret_cast<const float2 *>(&sDelta[qb * 8 + 2 * tig]);
+                float pw[4], ds[4];
+                pw[0] = v0 ? ex2_ftz(fmaf(c[0], qs, -ls.x)) : 0.f; pw[1] = v1 ? ex2_ftz(fmaf(c[1], qs, -ls.y)) : 0.f;
+                pw[2] = v2 ? ex2_ftz(fmaf(c[2], qs, -ls.x)) : 0.f; pw[3] = v3 ? ex2_ftz(fmaf(c[3], qs, -ls.y)) : 0.f;
+                ds[0] = pw[0] * (e[0] - dl.x) * scale; ds[1] = pw[1] * (e[1] - dl.y) * scale;
+                ds[2] = pw[2] * (e[2] - dl.x) * scale; ds[3] = pw[3] * (e[3] - dl.y) * scale;
+                // dK += dS^T Q, dV += P^T dO: query 2*tig sits in k-slot tig, query 2*tig+1 in k-slot tig+4
+                uint32_t sh[4], sl[4], ph[4], pl[4];
+                tf32_split(ds[0], sh[0], sl[0]); tf32_split(ds[2], sh[1], sl[1]);
+                tf32_split(ds[1], sh[2], sl[2]); tf32_split(ds[3], sh[3], sl[3]);
+                tf32_split(pw[0], ph[0], pl[0]); tf32_split(pw[2], ph[1], pl[1]);
+                tf32_split(pw[1], ph[2], pl[2]); tf32_split(pw[3], ph[3], pl[3]);
+                const int qa = qb * 8 + 2 * tig;
+                const float *qra = reinterpret_cast<const float *>(sQ + qa * RC), *qrb = reinterpret_cast<const float *>(sQ + (qa + 1) * RC);
+                const float *gra = reinterpret_cast<const float *>(sG + qa * RC), *grb = reinterpret_cast<const float *>(sG + (qa + 1) * RC);
+#pragma unroll
+                for (int db = 0; db < KS; db++) {
+                    const int cc = db * 4 + (g >> 1), hf = g & 1;
+                    const int ia = ((cc ^ fa) << 2) + hf, ib = ((cc ^ fb) << 2) + hf;      // hi; lo sits two floats further
+                    const uint32_t x0h = __float_as_uint(qra[ia]), x1h = __float_as_uint(qrb[ib]);
+                    const uint32_t x0l = __float_as_uint(qra[ia + 2]), x1l = __float_as_uint(qrb[ib + 2]);
+                    const uint32_t y0h = __float_as_uint(gra[ia]), y1h = __float_as_uint(grb[ib]);
+                    const uint32_t y0l = __float_as_uint(gra[ia + 2]), y1l = __float_as_uint(grb[ib + 2]);
+                    mma_tf32(dk[db], sh, x0h, x1h);
+                    mma_tf32(dv[db], ph, y0h, y1h);
+                    mma_tf32(dk[db], sl, x0h, x1h);
+                    mma_tf32(dv[db], pl, y0h, y1h);
+                    mma_tf32(dk[db], sh, x0l, x1l);
+                    mma_tf32(dv[db], ph, y0l, y1l);
+                }
+            }
+#pragma unroll
+            for (int half = 0; half < 2; half++) {
+                const int kk = kb * 16 + g + half * 8;
+                if (kk >= nkeys) continue;
+                float *ok, *ov;
+                if (kk < p) { ok = Pk + (coff + kk) * D + hoff; ov = Pv + (coff + kk) * D + hoff; }
+                else { ok = dK + (int64_t)(i0 + kk - p) * D + hoff; ov = dV + (int64_t)(i0 + kk - p) * D + hoff; }
+#pragma unroll
+                for (int db = 0; db < KS; db++) {
+                    *reinterpret_cast<float2 *>(ok + db * 8 + 2 * tig) = make_float2(dk[db][2 * half], dk[db][2 * half + 1]);
+                    *reinterpret_cast<float2 *>(ov + db * 8 + 2 * tig) = make_float2(dv[db][2 * half], dv[db][2 * half + 1]);
+                }
+            }
+        }
+    }
+}
+
 // dK/dV reduction, pass 1: one warp per work item = (node, tile range).  The node's row in tile t's
 // partial block is chain_off[t] + depth - 1.  Tiles are summed in increasing order.
 __global__ void reduce_items_kernel(const float *__restrict__ Pk, const float *__restrict__ Pv, float *__restrict__ dK,
@@ -1011,9 +1334,82 @@ static int launch_bwd_mma(const agpt_plan *p, const float *q, const void *k, con
     return launch_status("attn_bwd_mma");
 }
 
+// Raise a kernel's dynamic shared-memory limit once per device (the attribute belongs to the context's copy of the
+// function, so it is set again on every device a plan is used on, but not on every launch).
+template <typename KernelT>
+static int allow_dynamic_smem(KernelT kernel, size_t bytes, size_t *granted /* [AGPT_MAX_DEVICES] */) {
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= AGPT_MAX_DEVICES) return agpt_set_error(AGPT_E_LIMIT, "device index %d beyond %d", dev, AGPT_MAX_DEVICES);
+    if (granted[dev] < bytes) {
+        CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+        granted[dev] = bytes;
+    }
+    return AGPT_OK;
+}
+
+// Whole-tile backward: chosen when two blocks of it fit one SM (228 KB of shared memory, 1 KB reserved per block).
+// AGPT_B200_BWD_TILE=0 keeps the chunked kernel (A/B runs); AGPT_B200_BWD_WARPS = 4, 6 or 8 warps per block.
+#define BWD_TILE_SMEM_LIMIT ((size_t)113 * 1024)
+static int g_bwd_tile = -1, g_bwd_warps = 0, g_bwd_dbg = 0;
+static int bwd_tile_enabled() {
+    if (g_bwd_tile < 0) {
+        const char *e = getenv("AGPT_B200_BWD_TILE");
+        g_bwd_tile = (e && e[0] == '1') ? 1 : 0;      // the chunked kernel stays the default until the whole-tile kernel is faster
+        const char *w = getenv("AGPT_B200_BWD_WARPS");
+        g_bwd_warps = w ? atoi(w) : 6;
+        const char *d = getenv("AGPT_B200_BWD_DEBUG");
+        g_bwd_dbg = d ? atoi(d) : 0;
+        if (g_bwd_warps != 4 && g_bwd_warps != 8) g_bwd_warps = 6;
+    }
+    return g_bwd_tile;
+}
+extern "C" int agpt_b200_set_attn_bwd_variant(int whole_tile, int warps) {
+    if ((whole_tile != 0 && whole_tile != 1) || (warps != 4 && warps != 6 && warps != 8))
+        return agpt_set_error(AGPT_E_ARG, "set_attn_bwd_variant: whole_tile 0 or 1, warps 4, 6 or 8");
+    bwd_tile_enabled();
+    g_bwd_tile = whole_tile; g_bwd_warps = warps;
+    return AGPT_OK;
+}
+static inline int bwd_tile_maxk(const agpt_plan *p) { return ((p->max_depth - 1 + 64) + 15) & ~15; }
+
+template <int HD, int NW>
+static int launch_bwd_tile(const agpt_plan *p, const float *q, const void *k, const void *v, const float *o, const float *lse,
+                           const float *dout, float *dq, float *dk, float *dv, float *pk, float *pv, int H, float scale,
+                           cudaStream_t st, int tile0, int ntiles) {
+    static size_t granted[AGPT_MAX_DEVICES];
+    const int maxk = bwd_tile_maxk(p);
+    const size_t smem = bwd_tile_smem_bytes<HD>(maxk);
+    int rc = allow_dynamic_smem(attn_bwd_tile_kernel<HD, NW>, smem, granted);
+    if (rc) return rc;
+    dim3 grid((unsigned)ntiles, (unsigned)H);
+    attn_bwd_tile_kernel<HD, NW><<<grid, NW * 32, smem, st>>>(q, (const float *)k, (const float *)v, o, lse, dout, dq, dk, dv, pk, pv,
+                                                             p->d_sub_end, p->d_chain_off, p->d_chain_ids, p->d_chain_end, (int)p->n,
+                                                             H, scale, tile0, maxk, g_bwd_dbg);
+    return launch_status("attn_bwd_tile");
+}
+
+template <int HD>
+static int launch_bwd_tile_w(const agpt_plan *p, const float *q, const void *k, const void *v, const float *o, const float *lse,
+                             const float *dout, float *dq, float *dk, float *dv, float *pk, float *pv, int H, float scale,
+                             cudaStream_t st, int tile0, int ntiles) {
+    switch (g_bwd_warps) {
+        case 4: return launch_bwd_tile<HD, 4>(p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles);
+        case 8: return launch_bwd_tile<HD, 8>(p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles);
+        default: return launch_bwd_tile<HD, 6>(p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles);
+    }
+}
+
 static int bwd_dispatch(const agpt_plan *p, const float *q, const void *k, const void *v, int kv_dtype, const float *o,
                         const float *lse, const float *dout, float *dq, float *dk, float *dv, float *pk, float *pv, int H,
                         int head_dim, float scale, cudaStream_t st, int tile0, int ntiles) {
+    if (attn_impl() == 1 && p->tile_m == 64 && kv_dtype == AGPT_KV_F32 && bwd_tile_enabled()) {
+        const int maxk = bwd_tile_maxk(p);
+        if (head_dim == 16 && bwd_tile_smem_bytes<16>(maxk) <= BWD_TILE_SMEM_LIMIT)
+            return launch_bwd_tile_w<16>(p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles);
+        if (head_dim == 32 && bwd_tile_smem_bytes<32>(maxk) <= BWD_TILE_SMEM_LIMIT)
+            return launch_bwd_tile_w<32>(p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles);
+    }
     if (attn_impl() == 1 && p->tile_m == 64 && p->max_depth + 64 <= MAXKEYS) {
         const bool bf = kv_dtype == AGPT_KV_BF16;
 #define BWD_MMA_ARGS p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles
@@ -2011,7 +2407,6 @@ extern "C" int agpt_b200_attn_fwd_bwd_host(const agpt_plan *cp, const float *h_q
 #define AGPT_STATIC_SCRATCH_BYTES (64ll << 20)
 static __device__ __align__(256) unsigned char g_static_scratch[AGPT_STATIC_SCRATCH_BYTES];
 
-#define AGPT_MAX_DEVICES 64
 static void *g_static_scratch_addr[AGPT_MAX_DEVICES];   // device address of the array, per device; nullptr = not looked up yet
 
 extern "C" int64_t agpt_b200_static_scratch_bytes(void) { return AGPT_STATIC_SCRATCH_BYTES; }

@@ -5,8 +5,9 @@ group (a forest of root-child or bigram subtrees in depth-first order) embed the
 layer (LN1, Q/K/V projections, RoPE, trie-scoped attention, WO, residual, LN2, ReLU FFN, residual), final LN and
 output projection over all positions, per-query loss with mass weights normalised over the group, backward,
 and an optimizer step.  The trie-scoped attention, its backward with ancestor dK/dV, RoPE and the loss are this
-library's kernels; the dense projections and layer norms are torch (cuBLAS) calls, as they are cuBLAS calls in
-the reference.  Model files (MGPT) and radix trie directories are read and written unchanged.
+library's kernels; so are the dense projections (a tcgen05 float32-accurate GEMM), the layer norms, the bias / ReLU / column-sum
+row kernels, the embedding gradient and the optimizer step; torch supplies the autograd tape, device memory and the
+process group.  Model files (MGPT) and radix trie directories are read and written unchanged.
 
     python -m agpt_b200.trainer --model m.model --trie-dir DIR --epochs 3 --lr 3e-4 --optimizer rmsprop \\
         --rmsprop-beta 0.999 --mass-weight linear --save out.model
@@ -35,7 +36,7 @@ class LaunchGroup:
                  unit_of_row=None):
         import torch
         self.n = int(parent.size)
-        self.plan = A.WalkerPlan(parent, tile, device.index)
+        self.plan = A.WalkerPlan(parent, tile, device.index if device.type == "cuda" else -1)   # a host-only plan on a CPU device (index arrays for tests)
         order = self.plan.dfs_to_node.astype(np.int64)
         assert np.array_equal(order, np.arange(self.n)), "launch groups are built in depth-first order"
         t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)  # noqa: E731
@@ -346,7 +347,10 @@ class SampleSpace:
 
     def group(self, node_ids, context_ids, mass_mode, seq_len, device, tile=64) -> LaunchGroup:
         """Launch group of the chars of the radix nodes node_ids (closed under "parent"); chars of context_ids are
-        attended but carry no loss (the sampled node's ancestors, src/cuda/agpt_train.cu:4160-4180)."""
+        attended but carry no loss and are left out of the mass-weight mean.  The lightning samplers pass no context:
+        in the reference the ancestors prepended to a sampled subtree are trained like every other position and counted
+        in the chunk's mass mean (src/cuda/agpt_train.cu:4601-4637; the ancestor count recorded at :4194 is never read,
+        and the comment at :4160-4180 that announces a masking describes a variant that was taken out again)."""
         t = self.trie
         node_ids = np.asarray(node_ids, np.int64)
         lens = t.edge_len[node_ids].astype(np.int64)
@@ -386,13 +390,8 @@ def train_lightning_epoch(model: TrieWalkModel, space: SampleSpace, counts, opt,
     loss_sum, n_q, n_nodes = 0.0, 0, 0
     for s in range(steps):
         ids = nodes[off[s]:off[s + 1]]
-        context = []
-        if sampler != 4:                                         # the ancestors of the sampled node are context only
-            c = int(space.trie.parent[rs[s]])
-            while c > 0:
-                context.append(c)
-                c = int(space.trie.parent[c])
-        g = space.group(ids, context, mass_mode, model.cfg.seq_len, model.device)
+        # every sampled row is trained, the ancestors the sampler prepends included (src/cuda/agpt_train.cu:4601-4607)
+        g = space.group(ids, [], mass_mode, model.cfg.seq_len, model.device)
         opt.zero_grad(set_to_none=False)
         ls, nq = model.group_step(g, counts, **loss_kw)
         if hasattr(opt, "lr_scale"):

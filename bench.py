@@ -38,8 +38,13 @@ WORKLOADS = {
     "c4": dict(chars=5_000_000, vocab=96, order=3, depth=32, heads=8, head_dim=32, layers=6,
                label="depth-32 radix trie, 5M-char order-3 Markov corpus (vocab 96), d_model 256, 8 heads x 32, fp32"),
     # the deep configuration: 20M chars, depth 128, nodes of count < 2 pruned from depth 4 (run it with --kv bf16)
-    "c5": dict(chars=20_000_000, vocab=96, order=4, depth=128, heads=6, head_dim=64, layers=8, prune=(2, 4),
-               label="depth-128 radix trie pruned at count<2, 20M-char order-4 Markov corpus (vocab 96), d_model 384, 6 heads x 64"),
+    # (a plain order-4 Markov source has no long verbatim repeats, so its count>=2 trie ends near depth 24; the corpus
+    # therefore carries injected repeats, probability 2^-12 per position, spans of 64..256 symbols; c5_plain is the
+    # same source without them, kept for the comparison of the two tries' sizes)
+    "c5": dict(chars=20_000_000, vocab=96, order=4, depth=128, heads=6, head_dim=64, layers=8, prune=(2, 4), repeat_log2=12,
+               label="depth-128 radix trie pruned at count<2, 20M-char order-4 Markov corpus with injected repeats (vocab 96), d_model 384, 6 heads x 64"),
+    "c5_plain": dict(chars=20_000_000, vocab=96, order=4, depth=128, heads=6, head_dim=64, layers=8, prune=(2, 4),
+                     label="depth-128 radix trie pruned at count<2, 20M-char order-4 Markov corpus without repeats (vocab 96), d_model 384, 6 heads x 64"),
     # reduced copies of the two above for profiler captures (inputs still larger than L2, a few GB on the device)
     "c2s": dict(chars=50_000, vocab=65, order=3, depth=32, heads=4, head_dim=32, layers=4,
                 label="depth-32 radix trie, 50k-char order-3 Markov corpus (vocab 65), d_model 128, 4 heads x 32, fp32"),
@@ -57,6 +62,57 @@ def measured_peak_gbs():
             return float(json.load(f)["hbm_gbs"]), "measured"
     except Exception:
         return 6650.0, "fallback"
+
+
+def touch_once_bytes(n, D, H, kv_bytes):
+    """Bytes that must cross HBM when every row is moved exactly once (per layer): forward reads Q, K, V and writes O
+    and lse; backward reads Q, K, V, O, dO, lse and writes dQ, dK, dV (plus one lse-sized vector of slack for the
+    row-wise dO.O, which this implementation recomputes instead of storing)."""
+    fwd = n * (D * 4 + 2 * D * kv_bytes + D * 4 + H * 4)
+    bwd = n * (6 * D * 4 + 2 * D * kv_bytes + 2 * H * 4)
+    return fwd, bwd
+
+
+# DRAM bytes per position (dram__bytes_read.sum + dram__bytes_write.sum of one launch / positions of the launch) of
+# the forward kernel and of the backward kernel + reduction, from ncu captures of the reduced workloads (c2s for
+# d_model 128, micro_s for d_model 512; traffic grows in proportion to the positions).  Key: (d_model, kv store).
+# The captures are summarised in profiles/attn_mma_kernels_c2s_ncu_full.md (d_model 128, float32 store).
+DRAM_BYTES_PER_POSITION = {
+    (128, "f32"): (2.18e3, 4.44e3),
+}
+
+
+def workload_config(args, cfg, total_nodes, world, max_depth=None, depth_hist=None):
+    """The `config` object of the JSON line: the same keys and values in the GPU arm and in the reference arm."""
+    return {"workload": cfg["label"], "kv_store": args.kv, "positions": total_nodes, "tile": args.tile,
+            "partition": "root-child subtrees" if unit_level(args.workload, world) == 1 else f"bigram subtrees, LPT over {world} rank(s)",
+            "l2": "inputs (GBs per tensor) far larger than the 126 MB L2",
+            "max_depth": max_depth, "positions_per_depth": depth_hist}
+
+
+def bind_to_gpu_numa_node(index):
+    """Bind this process to the CPUs of the NUMA node the GPU hangs off, so that pinned host buffers allocated (and
+    first touched) afterwards sit in that node's memory.  Returns a short description for the JSON line."""
+    try:
+        import torch
+        pr = torch.cuda.get_device_properties(index)
+        bdf = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return {"node": None, "bound": False, "why": "no NUMA node reported for the GPU"}
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                a, _, b = part.partition("-")
+                cpus.update(range(int(a), int(b or a) + 1))
+        allowed = os.sched_getaffinity(0) & cpus
+        if not allowed:
+            return {"node": node, "bound": False, "why": "none of the node's CPUs is in this process's affinity mask"}
+        os.sched_setaffinity(0, allowed)
+        return {"node": node, "bound": True, "cpus": len(allowed)}
+    except Exception as e:  # sysfs not visible in the container, or no such attribute
+        return {"node": None, "bound": False, "why": f"{type(e).__name__}: {e}"[:120]}
 
 
 class ClockSampler:
@@ -115,7 +171,7 @@ class Unit:
 def unit_level(wl, world):
     """Root-child units on one rank, bigram units on several -- and always for the 126M-position and the deep configurations, whose
     largest root child (a quarter of all positions) would not fit one GPU as a single launch."""
-    return 2 if (world > 1 or wl in ("c4", "c5")) else 1
+    return 2 if (world > 1 or wl in ("c4", "c5", "c5_plain")) else 1
 
 
 def build_units(wl, rank, world, log, single_unit=False, group_rows=4_000_000, device=None):
@@ -130,14 +186,22 @@ def build_units(wl, rank, world, log, single_unit=False, group_rows=4_000_000, d
         counts = (np.arange(parent.size + 2, dtype=np.int32), (np.arange(parent.size + 1) % cfg["vocab"]).astype(np.int32),
                   np.ones(parent.size + 1, np.int32))
     else:
-        corpus = A.synth_markov_corpus(cfg["chars"], cfg["vocab"], cfg["order"], 0)
+        corpus = A.synth_markov_corpus(cfg["chars"], cfg["vocab"], cfg["order"], 0, cfg.get("repeat_log2", 0))
         # the GPU arm orders the suffixes on its device; the CPU arm uses the level-by-level host builder (same arrays)
         level_key = unit_level(wl, world)
         pm, pd = cfg.get("prune", (1, 4))
         trie = (A.RadixTrie.build(corpus, cfg["depth"], level_key, pm, pd) if device is None else
                 A.RadixTrie.build_gpu(corpus, cfg["depth"], level_key, pm, pd, device=device))
-        parent, token, _, radix_of = trie.char_tree()
+        parent, token, cdepth, radix_of = trie.char_tree()
         edge_mass = trie.edge_mass
+        if cfg.get("repeat_log2") and device is not None:
+            # the two tries side by side: with the injected repeats (used) and of the plain source (sizes only)
+            plain = A.RadixTrie.build_gpu(A.synth_markov_corpus(cfg["chars"], cfg["vocab"], cfg["order"], 0), cfg["depth"],
+                                          level_key, pm, pd, device=device)
+            pdep = plain.char_tree()[2]
+            log(f"trie of the corpus with injected repeats: {parent.size} positions, {trie.radix_count} radix nodes, max depth {int(cdepth.max())}; "
+                f"of the plain corpus: {pdep.size} positions, {plain.radix_count} radix nodes, max depth {int(pdep.max())}")
+            del plain, pdep
         counts = (trie.cnt_off.astype(np.int32), trie.cnt_tok, trie.cnt_val)
     log(f"trie built: {parent.size} positions in {time.time() - t0:.1f}s")
     plan = A.WalkerPlan(parent, 64, -1)
@@ -210,33 +274,42 @@ def cpu_arm(units, cfg, budget_nodes, counts, steps=1, warmup=0):
     Returns (nodes per second, cores, description)."""
     from oracle import pyoracle as O
     H, hd, V = cfg["heads"], cfg["head_dim"], cfg["vocab"]
+    # launch groups from both ends of the size range in turn (largest, smallest, second largest, ...), as many as the budget holds
+    by_size = sorted(units, key=lambda x: -x.n)
+    order = []
+    for i in range((len(by_size) + 1) // 2):
+        order.append(by_size[i])
+        if len(by_size) - 1 - i > i:
+            order.append(by_size[len(by_size) - 1 - i])
     sample, tot = [], 0
-    for u in sorted(units, key=lambda x: x.n):
+    for u in order:
         if tot + u.n > budget_nodes and sample:
-            break
+            continue
         sample.append(u)
         tot += u.n
+        if tot >= budget_nodes:
+            break
     rng = np.random.default_rng(0)
     data = []
     for u in sample:
         q, k, v, go = [rng.standard_normal((u.n, H * hd)).astype(np.float32) for _ in range(4)]
-        data.append((u, q, k, v, go, rng.standard_normal((u.n, V)).astype(np.float32)))
+        data.append((u, q, k, v, go))
 
     def one_pass():
-        for u, q, k, v, go, logits in data:
+        # attention forward + backward only: what the GPU arm's end-to-end leg times as well
+        for u, q, k, v, go in data:
             # local trees are in depth-first order, so parent < child holds
             out, w, w_off, _ = O.attn_fwd(u.parent, H, hd, q, k, v, grouped=True)
             roots = np.nonzero(u.parent < 0)[0]
             unit_off = np.concatenate([roots, [u.n]]).astype(np.int32)
             O.attn_bwd(u.parent, H, hd, q, k, v, w, w_off, go, unit_off=unit_off)
-            O.loss_per_query(logits, u.q2n, u.qoff, u.radix_ids, u.tokens, counts[0], counts[1], counts[2], u.mass_w)
     for _ in range(warmup):
         one_pass()
     t0 = time.perf_counter()
     for _ in range(steps):
         one_pass()
     dt = (time.perf_counter() - t0) / steps
-    return tot / dt, O.num_threads(), f"{len(sample)} launch groups of the same trie, {tot} positions, attention fwd+bwd + loss (oracle; attention under OpenMP)", dt
+    return tot / dt, O.num_threads(), f"{len(sample)} launch groups of the same trie (sizes {min(u.n for u in sample)}..{max(u.n for u in sample)} rows, taken from both ends of the size range), {tot} positions, attention fwd+bwd (oracle, OpenMP)", dt
 
 
 def run_reference(args):
@@ -244,14 +317,14 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    units, counts, total, plan = build_units(args.workload, 0, 1, lambda s: print(s, file=sys.stderr), group_rows=100_000)
+    units, counts, total, plan = build_units(args.workload, 0, args.gpus, lambda s: print(s, file=sys.stderr), group_rows=100_000)
     from oracle import pyoracle as O
     O.set_num_threads(os.cpu_count() or 1)      # torchrun pins OMP_NUM_THREADS=1; this arm may use every host core
     nps, cores, sample, dt = cpu_arm(units, cfg, args.cpu_nodes, counts, steps=max(1, args.steps), warmup=min(args.warmup, 1))
     line = {"impl": "reference", "metric": "trie_nodes_per_sec_attn_fwd_bwd", "value": nps, "unit": "nodes/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": cfg["label"], "positions": total},
+            "config": workload_config(args, cfg, total, args.gpus, int(plan.max_depth), np.bincount(plan.depth, minlength=2)[1:].tolist()),
             "cpu_baseline": {"value": nps, "unit": "nodes/s", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": nps, "unit": "nodes/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
@@ -392,9 +465,15 @@ def run_gpu(args):
     selfcheck = {"sum_dv_vs_sum_dout_rel": chk_dv, "dq_dot_q_vs_dk_dot_k_rel": chk_qk,
                  "finite": bool(torch.isfinite(dq[:u.n]).all() and torch.isfinite(dk[:u.n]).all() and torch.isfinite(out[:u.n]).all())}
     del qd, kd, god
-    ach_bwd = b_bwd / t_bwd / 1e9
-    ach_fwd = b_fwd / t_fwd / 1e9
-    ach_all = (b_fwd + b_bwd) / (t_fwd + t_bwd) / 1e9
+    # two byte models: touch-once (what must cross HBM; the roofline fraction) and the sibling-group-shared contract
+    # model (every sibling group re-reads its ancestor chain; an algorithmic bandwidth that may exceed the peak
+    # because the tile kernels share a chain among 64 depth-first neighbours and serve it from shared memory / L2)
+    to_fwd, to_bwd = touch_once_bytes(n_rank, D, H, kv_bytes)
+    ach_bwd, ach_fwd, ach_all = to_bwd / t_bwd / 1e9, to_fwd / t_fwd / 1e9, (to_fwd + to_bwd) / (t_fwd + t_bwd) / 1e9
+    con_bwd, con_fwd, con_all = b_bwd / t_bwd / 1e9, b_fwd / t_fwd / 1e9, (b_fwd + b_bwd) / (t_fwd + t_bwd) / 1e9
+    dram = DRAM_BYTES_PER_POSITION.get((D, args.kv))
+    max_depth = int(gplan.max_depth)
+    depth_hist = np.bincount(gplan.depth, minlength=2)[1:].tolist()
 
     # end to end: the host-buffer C-ABI call on a bounded subset of this rank's units; every rank runs its own sample
     # at the same time (each GPU has its own host link), time = max over ranks, rows = sum over ranks
@@ -407,6 +486,7 @@ def run_gpu(args):
                 chosen.append((u, p)); tot += u.n
         if not chosen:
             chosen, tot = [(units[-1], plans[-1])], units[-1].n
+        numa = bind_to_gpu_numa_node(local)          # before the pinned buffers are allocated and first touched
         rng = np.random.default_rng(0)
         host = []
         for u, p in chosen:
@@ -433,15 +513,23 @@ def run_gpu(args):
         e2e = {"value": tot_all / dt, "unit": "nodes/s", "h2d_bytes_per_step": int(tot_all * D * 4 * 4),
                "d2h_bytes_per_step": int(tot_all * (D * 4 * 4 + H * 4)),
                "sample": f"{len(chosen)} launch group(s) per rank, {tot_all} rows over {world} rank(s) ({tot} of {n_rank} on rank 0); "
-                         "attention fwd+bwd through agpt_b200_attn_fwd_bwd_host, max time over ranks"}
+                         "attention fwd+bwd through agpt_b200_attn_fwd_bwd_host, max time over ranks",
+               "host_numa_rank0": numa}
         del host
+
+    del big, logits, out, lse, dq, dk, dv, dlogits, loss, ws, plans, meta
+    torch.cuda.empty_cache()
+
+    # the attention-only microbenchmark (4M-node tree, 8 heads x 64) with both store types, as extra keys of the
+    # default one-GPU line
+    micro = None
+    if args.micro and world == 1 and args.workload == "c2":
+        micro = {kv: run_micro(kv, dev, log, peak) for kv in ("f32", "bf16")}
 
     # whole-epoch time of the trie-walk trainer on the same trie (all layers, loss, backward, one gradient
     # all-reduce and one optimizer step), every rank taking part
     epoch = None
     if args.epoch and not args.workload.startswith("micro"):
-        del big, logits, out, lse, dq, dk, dv, dlogits, loss, ws, plans, meta
-        torch.cuda.empty_cache()
         epoch = run_epoch(args, cfg, rank, world, dev, log)
 
     cpu = None
@@ -456,19 +544,70 @@ def run_gpu(args):
         line = {"metric": "trie_nodes_per_sec_attn_fwd_bwd", "value": value, "unit": "nodes/s", "n_gpus": world,
                 "steps": args.steps, "warmup": n_warm, "ms_per_step": ms_per_step, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": cfg["label"], "kv_store": args.kv, "positions": total_nodes, "launch_groups_rank0": len(units), "group_rows": args.group_rows,
-                           "partition": "root-child subtrees" if unit_level(args.workload, world) == 1 else f"bigram subtrees, LPT over {world} rank(s)",
-                           "tile": args.tile, "l2": "inputs (GBs per tensor) far larger than the 126 MB L2",
-                           "inputs": "one buffer set shared by all launch groups" if shared_inputs else "resident for every row"},
+                "config": workload_config(args, cfg, total_nodes, world, max_depth, depth_hist),
+                "run": {"launch_groups_rank0": len(units), "group_rows": args.group_rows,
+                        "inputs": "one buffer set shared by all launch groups" if shared_inputs else "resident for every row"},
                 "roofline": {"bound": "hbm", "achieved": ach_bwd, "peak": peak, "unit": "GB/s", "frac": ach_bwd / peak,
-                             "traffic": (None if D != 128 else 4.44e3 * n_rank), "kernel": "attention backward tile kernel + dK/dV reduction", "peak_kind": f"of {peak_kind}", "traffic_note": "ncu dram bytes per position of the reduced case c2s (4.44 KB backward, 2.18 KB forward) x positions; profiles/attn_mma_kernels_c2s_ncu_full.md",
-                             "algorithmic_bytes_per_step": b_bwd, "seconds_per_step": t_bwd,
-                             "fwd": {"achieved": ach_fwd, "frac": ach_fwd / peak, "algorithmic_bytes_per_step": b_fwd, "seconds_per_step": t_fwd},
-                             "fwd_bwd": {"achieved": ach_all, "frac": ach_all / peak}, "loss_seconds_per_step": t_loss},
-                "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "epoch": epoch, "selfcheck": selfcheck}
+                             "frac_contract": con_bwd / peak, "achieved_contract": con_bwd,
+                             "traffic": (None if dram is None else dram[1] * n_rank),
+                             "traffic_source": (None if dram is None else "ncu DRAM bytes per position of the reduced case of this workload x positions of this rank"),
+                             "kernel": "attention backward tile kernel + dK/dV reduction", "peak_kind": f"of {peak_kind}",
+                             "bytes_model": "touch-once (frac, achieved); sibling-group-shared contract model (frac_contract)",
+                             "algorithmic_bytes_per_step": to_bwd, "contract_bytes_per_step": b_bwd, "seconds_per_step": t_bwd,
+                             "fwd": {"achieved": ach_fwd, "frac": ach_fwd / peak, "frac_contract": con_fwd / peak,
+                                     "algorithmic_bytes_per_step": to_fwd, "contract_bytes_per_step": b_fwd, "seconds_per_step": t_fwd,
+                                     "traffic": (None if dram is None else dram[0] * n_rank)},
+                             "fwd_bwd": {"achieved": ach_all, "frac": ach_all / peak, "frac_contract": con_all / peak},
+                             "loss_seconds_per_step": t_loss},
+                "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "micro": micro, "epoch": epoch,
+                "selfcheck": selfcheck}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_micro(kv, dev, log, peak, steps=3, warmup=3, name="micro"):
+    """Attention forward + backward on the microbenchmark tree (4M nodes, depth <= 64, geometric(0.35) children,
+    8 heads x 64, Q/K/V/dO ~ N(0,1)), one launch over the whole tree; CUDA events per kernel."""
+    import torch
+    import agpt_b200 as A
+    cfg = WORKLOADS[name]
+    H, hd = cfg["heads"], cfg["head_dim"]
+    D = H * hd
+    parent = A.synth_tree(cfg["nodes"], cfg["depth"], 65, 0.35, 65, 75_000, 0)
+    plan = A.WalkerPlan(parent, 64, dev.index)
+    n = plan.n
+    g = torch.Generator(device=dev).manual_seed(99)
+    q, k, v, go = [torch.randn((n, D), device=dev, generator=g) for _ in range(4)]
+    kvb = 4
+    if kv == "bf16":
+        k, v, kvb = A.kv_store_write_bf16(k), A.kv_store_write_bf16(v), 2
+    out = torch.empty((n, D), device=dev); lse = torch.empty((n, H), device=dev)
+    dq, dk, dv = [torch.empty((n, D), device=dev) for _ in range(3)]
+    ws = torch.empty(plan.workspace_bytes(D), dtype=torch.uint8, device=dev)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    t_f = t_b = 0.0
+    for i in range(warmup + steps):
+        ev[0].record()
+        A.attn_forward(plan, q, k, v, H, out=out, lse=lse)
+        ev[1].record()
+        A.attn_backward(plan, q, k, v, out, lse, go, H, workspace=ws, dq=dq, dk=dk, dv=dv)
+        ev[2].record()
+        torch.cuda.synchronize()
+        if i >= warmup:
+            t_f += ev[0].elapsed_time(ev[1]) * 1e-3 / steps
+            t_b += ev[1].elapsed_time(ev[2]) * 1e-3 / steps
+    to_f, to_b = touch_once_bytes(n, D, H, kvb)
+    c_f, c_b = plan.algorithmic_bytes(D, H, kvb)
+    res = {"nodes": n, "max_depth": int(plan.max_depth), "heads": H, "head_dim": hd, "kv_store": kv,
+           "nodes_per_s": n / (t_f + t_b), "fwd_ms": t_f * 1e3, "bwd_ms": t_b * 1e3,
+           "frac": {"fwd": to_f / t_f / 1e9 / peak, "bwd": to_b / t_b / 1e9 / peak, "fwd_bwd": (to_f + to_b) / (t_f + t_b) / 1e9 / peak},
+           "frac_contract": {"fwd": c_f / t_f / 1e9 / peak, "bwd": c_b / t_b / 1e9 / peak, "fwd_bwd": (c_f + c_b) / (t_f + t_b) / 1e9 / peak},
+           "finite": bool(torch.isfinite(dq).all() and torch.isfinite(dk).all() and torch.isfinite(dv).all())}
+    log(f"{name} {kv}: fwd {t_f * 1e3:.1f} ms, bwd {t_b * 1e3:.1f} ms, {res['nodes_per_s'] / 1e6:.1f} M nodes/s")
+    del q, k, v, go, out, lse, dq, dk, dv, ws, plan
+    torch.cuda.empty_cache()
+    return res
 
 
 def run_epoch(args, cfg, rank, world, dev, log):
@@ -480,7 +619,7 @@ def run_epoch(args, cfg, rank, world, dev, log):
     from agpt_b200 import model_file as MF
     from agpt_b200 import trainer as T
     D = cfg["heads"] * cfg["head_dim"]
-    corpus = A.synth_markov_corpus(cfg["chars"], cfg["vocab"], cfg["order"], 0)
+    corpus = A.synth_markov_corpus(cfg["chars"], cfg["vocab"], cfg["order"], 0, cfg.get("repeat_log2", 0))
     pm, pd = cfg.get("prune", (1, 4))
     trie = A.RadixTrie.build_gpu(corpus, cfg["depth"], 2, pm, pd, device=dev.index)
     mf = MF.random_init(D, cfg["heads"], cfg["layers"], cfg["vocab"], max(128, cfg["depth"]), seed=0)
@@ -526,12 +665,14 @@ def main():
     ap.add_argument("--no-epoch", dest="epoch", action="store_false",
                     help="skip the whole-epoch timing of the trainer (all layers) on the same trie")
     ap.add_argument("--epoch-group-rows", type=int, default=1_000_000)
+    ap.add_argument("--no-micro", dest="micro", action="store_false",
+                    help="skip the attention-only microbenchmark legs (4M-node tree, 8 x 64) of the default one-GPU line")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     if args.profile:
         args.no_e2e = args.no_cpu = True
-        args.epoch = False
+        args.epoch = args.micro = False
     if args.impl == "reference":
         run_reference(args)
     else:

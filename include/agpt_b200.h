@@ -100,6 +100,12 @@ void cuda_sync(void);
 
 /* Order-`order` Markov chain over `vocab` symbols with Zipf(1.1) unigram marginals. */
 int agpt_b200_synth_markov_corpus(int64_t n, int vocab, int order, uint64_t seed, int32_t *out);
+/* The same source with long verbatim repeats injected: before each symbol one more draw of the same splitmix64
+ * stream decides, with probability 2^-repeat_log2, to copy a span of 64 + (draw mod 193) symbols starting at a
+ * uniformly drawn earlier offset.  Stand-in for the deep repeats of natural text: the count>=2 trie of a plain
+ * order-4 Markov source ends near depth 24, with repeats it reaches the depth cap. */
+int agpt_b200_synth_markov_corpus_repeats(int64_t n, int vocab, int order, uint64_t seed, int repeat_log2,
+                                          int32_t *out);
 
 /* Level-capped random tree in breadth-first id order; parent_out[i] == -1 for the root's
  * children.  Returns the node count (<= max_nodes) or a negative error. */
@@ -355,6 +361,14 @@ int agpt_b200_attn_bwd(const agpt_plan *p, const float *d_q, const void *d_k, co
  * compensation, tiles of 64; the default), 0 = FP32 FMA.  Both meet the same parity tolerances; the switch
  * exists for A/B measurement.  Also read once from the environment variable AGPT_B200_ATTN_IMPL. */
 int agpt_b200_set_attn_impl(int impl);
+
+/* Selects the tensor-core backward kernel for a float32 KV store and head_dim 16 or 32: whole_tile 1 (default) = the
+ * kernel that keeps the tile's Q, dO and all its key rows in shared memory, pre-split into TF32 hi/lo parts, and
+ * lets every warp run independent row and key items (used whenever two such blocks fit one SM, i.e. up to a few
+ * hundred keys per tile; deeper plans take the chunked kernel); 0 = always the chunked kernel.  warps = 4, 6 or 8
+ * warps per block of the whole-tile kernel (default 6).  Same results within the parity tolerance either way; the
+ * switch exists for A/B measurement.  Also read once from AGPT_B200_BWD_TILE and AGPT_B200_BWD_WARPS. */
+int agpt_b200_set_attn_bwd_variant(int whole_tile, int warps);
 
 /* No counterpart in the reference.  agpt_b200_attn_bwd for callers that cannot allocate device memory
  * when the backward runs -- a runtime that claimed the whole GPU at start-up and sub-allocates from its own

@@ -16,12 +16,16 @@ from tests.helpers import TOL_BF16, TOL_F32, chain_tree, random_qkv, random_tree
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(autouse=True, params=[1, 0], ids=["tensor", "fma"])
+@pytest.fixture(autouse=True, params=[(1, True), (1, False), (0, True)], ids=["tensor", "tensor-chunked-bwd", "fma"])
 def attn_impl(request):
-    """Every test in this file runs against both kernel families of the native attention entry points."""
-    A.set_attn_impl(request.param)
-    yield request.param
+    """Every test in this file runs against both kernel families of the native attention entry points, the tensor-core
+    family with either of its two backward kernels (whole tile resident / chunked)."""
+    impl, whole_tile = request.param
+    A.set_attn_impl(impl)
+    A.set_attn_bwd_variant(whole_tile, 6)
+    yield impl
     A.set_attn_impl(1)
+    A.set_attn_bwd_variant(True, 6)
 
 
 def _dev(x, cuda):

@@ -331,3 +331,150 @@ def test_lightning_lr_weights_match_oracle():
         assert np.allclose(got, want, rtol=1e-15, atol=0)
         assert mode == "off" or abs(float(np.mean(got)) - 1.0) < 1e-12
     assert T.lightning_lr_weights([], "log").size == 0 and np.array_equal(T.lightning_lr_weights([0.0, 0.0], "linear"), [0.0, 0.0])
+
+
+def test_attention_wrappers_refuse_mismatched_tensors_before_any_launch():
+    """The C entry points take no row count, so the Python wrappers must refuse every tensor whose shape, dtype,
+    layout or device differs from what the plan needs -- checked here on CPU tensors through the same validator
+    (require_cuda=False) that attn_forward / attn_backward / attn_backward_static call first."""
+    import torch
+    plan = A.WalkerPlan(random_tree(100, 5, 1), 64, -1)
+    H, D = 2, 64
+    ok = lambda rows=100, cols=D, dt=torch.float32: torch.zeros((rows, cols), dtype=dt)   # noqa: E731
+    lse = torch.zeros((100, H))
+    good = dict(f32_rows=[("q", ok()), ("out", ok()), ("dout", ok()), ("dq", ok()), ("dk", ok()), ("dv", ok())],
+                kv_rows=[("k", ok()), ("v", ok())], lse=lse)
+    assert A.validate_attn_args(plan, H, **good, require_cuda=False) == (64, 32)
+    assert A.validate_attn_args(plan, H, [("q", ok())], [("k", ok(dt=torch.bfloat16)), ("v", ok(dt=torch.bfloat16))], lse,
+                                require_cuda=False) == (64, 32)
+
+    def bad(match, **kw):
+        args = dict(good)
+        args.update(kw)
+        with pytest.raises(A.AgptError, match=match):
+            A.validate_attn_args(plan, H, **args, require_cuda=False)
+
+    bad("shape", f32_rows=[("q", ok(rows=99))])                                  # fewer rows than the plan
+    bad("shape", f32_rows=[("q", ok()), ("dq", ok(rows=64))])                    # a short output tensor
+    bad("shape", f32_rows=[("q", ok()), ("dout", ok(cols=32))])
+    bad("shape", kv_rows=[("k", ok(rows=50)), ("v", ok())])
+    bad("shape", lse=torch.zeros((100, 4)))
+    bad("shape", lse=torch.zeros((99, H)))
+    bad("dtype", f32_rows=[("q", ok()), ("dk", ok(dt=torch.float64))])
+    bad("dtype", kv_rows=[("k", ok(dt=torch.float16)), ("v", ok())])
+    bad("same dtype", kv_rows=[("k", ok(dt=torch.bfloat16)), ("v", ok())])
+    bad("dtype", lse=torch.zeros((100, H), dtype=torch.float64))
+    bad("contiguous", f32_rows=[("q", ok()), ("dv", torch.zeros((D, 100)).t())])
+    bad("contiguous", kv_rows=[("k", torch.zeros((100, 2 * D))[:, ::2]), ("v", ok())])
+    with pytest.raises(A.AgptError, match="multiple"):
+        A.validate_attn_args(plan, 3, [("q", ok())], require_cuda=False)
+    with pytest.raises(A.AgptError, match="head_dim"):
+        A.validate_attn_args(plan, 8, [("q", ok())], require_cuda=False)         # head_dim 8
+    with pytest.raises(A.AgptError, match="CUDA"):
+        A.validate_attn_args(plan, H, **good)                                    # CPU tensors where device tensors are required
+
+
+@pytest.mark.parametrize("sampler", [1, 3])
+def test_lightning_unit_trains_its_ancestors_and_counts_them_in_the_mass_mean(sampler):
+    """The reference's lightning samplers prepend the sampled node's ancestors, and the code that runs trains them
+    like every other position: the mass-weight mean of the chunk runs over all its queries, ancestors included
+    (src/cuda/agpt_train.cu:4601-4637).  The launch group of a sampled unit must therefore carry no untrained rows and
+    its mass weights must equal the oracle's restatement over every row of the unit."""
+    import torch
+    from agpt_b200 import trainer as T
+    corpus = A.synth_markov_corpus(900, 12, 2, 13)
+    trie = A.RadixTrie.build(corpus, 7)
+    space = T.SampleSpace(trie)
+    rs, na, off, _, nodes, _ = trie.lightning_sample(sampler, 6, 0x5c115e1, p_stop=0.4)
+    with_ancestors = 0
+    for s in range(6):
+        ids = nodes[off[s]:off[s + 1]]
+        with_ancestors += int(trie.parent[rs[s]] > 0)
+        g = space.group(ids, [], "linear", 16, torch.device("cpu"))
+        assert g.trained is None and g.n_trained_rows == g.n == int(trie.edge_len[ids].sum())
+        rid = g.rid.numpy()
+        assert sorted(rid.tolist()) == sorted(np.asarray(ids).tolist())          # one loss node per sampled radix node
+        want = O.mass_weights(trie.edge_mass[rid], np.diff(g.qoff.numpy()), 3)  # mean over all queries of the unit
+        assert np.allclose(g.mass_w.numpy(), want, rtol=1e-6, atol=0)
+    assert with_ancestors > 0
+
+
+def _py_markov(n, vocab, order, seed, repeat_log2=0):
+    """Plain-Python restatement of the synthetic corpus generator (splitmix64 stream, Zipf(1.1) slots and symbols,
+    optional injected repeats), for small n."""
+    M64 = (1 << 64) - 1
+
+    def sm(x):
+        x = (x + 0x9E3779B97F4A7C15) & M64
+        z = x
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & M64
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & M64
+        return z ^ (z >> 31)
+
+    def cdf(k):
+        w = np.cumsum([(r + 1) ** -1.1 for r in range(k)])
+        w = w / w[-1]
+        w[-1] = 1.0
+        return w
+
+    def inv(c, u):
+        lo, hi = 0, len(c) - 1
+        while lo < hi:
+            mid = (lo + hi) // 2
+            if u < c[mid]:
+                hi = mid
+            else:
+                lo = mid + 1
+        return lo
+
+    zipf, slot = cdf(vocab), cdf(6)
+    # the library accumulates the weights in double precision one by one, as np.cumsum does
+    modulus = vocab ** order
+    ctx, s = 0, sm(seed)
+    out = []
+    i = 0
+    while i < n:
+        if repeat_log2 > 0 and i > 0:
+            s = sm(s)
+            if (s >> (64 - repeat_log2)) == 0:
+                s = sm(s)
+                ln = 64 + s % 193
+                s = sm(s)
+                src = s % i
+                t = 0
+                while t < ln and i + t < n:
+                    sym = out[src + t]
+                    out.append(sym)
+                    ctx = (ctx * vocab + sym) % modulus
+                    t += 1
+                i += t
+                continue
+        h = sm(seed ^ ((ctx * 0x9E3779B97F4A7C15) & M64))
+        s = sm(s)
+        j = inv(slot, (s >> 11) * (1.0 / 9007199254740992.0))
+        sym = 0
+        for _ in range(j + 1):
+            h = sm(h)
+            sym = inv(zipf, (h >> 11) * (1.0 / 9007199254740992.0))
+        out.append(sym)
+        ctx = (ctx * vocab + sym) % modulus
+        i += 1
+    return np.asarray(out, np.int32)
+
+
+def test_synthetic_corpus_generators_match_their_restatement():
+    for n, vocab, order, seed, rep in [(3000, 12, 2, 5, 0), (4000, 12, 2, 5, 6), (2500, 96, 4, 0, 5), (700, 65, 3, 1, 1)]:
+        got = A.synth_markov_corpus(n, vocab, order, seed, rep)
+        assert np.array_equal(got, _py_markov(n, vocab, order, seed, rep)), (n, vocab, order, seed, rep)
+
+
+def test_injected_repeats_make_the_pruned_trie_deep():
+    """A plain low-order Markov source has no long verbatim repeats, so after count<2 pruning its trie stays shallow
+    whatever the depth cap; with injected repeats it reaches the cap (depth 128, the deep configuration's shape)."""
+    # pruning from depth 1 here: in a 20k-char corpus rare trigrams occur once, and edges that start above the
+    # pruning depth are kept whatever their count (in the 20M-char configuration every short prefix is frequent)
+    plain = A.RadixTrie.build(A.synth_markov_corpus(20_000, 12, 2, 3), 128, 1, 2, 1)
+    deep = A.RadixTrie.build(A.synth_markov_corpus(20_000, 12, 2, 3, 6), 128, 1, 2, 1)
+    d_plain = int(plain.char_tree()[2].max())
+    d_deep = int(deep.char_tree()[2].max())
+    assert d_plain < 40 and d_deep == 128

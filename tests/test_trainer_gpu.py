@@ -190,8 +190,9 @@ def test_gradients_do_not_depend_on_packing_or_rank_count(cuda):
 
 @pytest.mark.parametrize("sampler", [3, 4])
 def test_lightning_unit_matches_dense_reference(cuda, sampler):
-    """A sampled training unit (ancestors as context, the sampled subtree or the root-to-leaf path trained): loss and
-    every weight gradient against the dense float64 model on the same rows."""
+    """A sampled training unit (the sampled node's ancestors plus its subtree, or a root-to-leaf path; every row
+    trained, as in the reference's executed code): loss and every weight gradient against the dense float64 model on
+    the same rows."""
     import torch
     corpus = A.synth_markov_corpus(900, 12, 2, 13)
     trie = A.RadixTrie.build(corpus, 7)
@@ -203,13 +204,8 @@ def test_lightning_unit_matches_dense_reference(cuda, sampler):
     checked = 0
     for s in range(4):
         ids = nodes[off[s]:off[s + 1]]
-        context = []
-        c = int(trie.parent[rs[s]])
-        while c > 0 and sampler != 4:
-            context.append(c)
-            c = int(trie.parent[c])
-        g = space.group(ids, context, "linear", mf.seq_len, cuda)
-        assert g.n == int(trie.edge_len[ids].sum())
+        g = space.group(ids, [], "linear", mf.seq_len, cuda)
+        assert g.n == int(trie.edge_len[ids].sum()) and g.trained is None
         model = T.TrieWalkModel(mf, cuda)
         ls, nq = model.group_step(g, counts, entropy_lambda=0.2)
         tr = None if g.trained is None else g.trained.cpu().numpy()
