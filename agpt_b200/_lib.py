@@ -46,8 +46,11 @@ SIGNATURES = {
     "agpt_b200_synth_markov_corpus": (C.c_int, [i64, C.c_int, C.c_int, u64, vp]),
     "agpt_b200_synth_markov_corpus_repeats": (C.c_int, [i64, C.c_int, C.c_int, u64, C.c_int, vp]),
     "agpt_b200_synth_tree": (i64, [i64, C.c_int, C.c_int, f64, C.c_int, i64, u64, vp]),
+    "agpt_b200_mass_weights": (C.c_int, [vp, vp, vp, vp, i64, i64, C.c_int, vp]),
     "agpt_b200_trie_build": (C.c_int, [vp, i64, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(vp)]),
     "agpt_b200_trie_load_dir": (C.c_int, [C.c_char_p, C.POINTER(vp)]),
+    "agpt_b200_trie_manifest": (i64, [C.c_char_p, i64, vp, vp, vp, vp]),
+    "agpt_b200_trie_load_subtree": (C.c_int, [C.c_char_p, i32, C.POINTER(vp)]),
     "agpt_b200_trie_save_dir": (C.c_int, [vp, C.c_char_p, C.c_int, i32, i32, u64, C.c_char_p]),
     "agpt_b200_trie_info": (C.c_int, [vp, C.POINTER(TrieInfo)]),
     "agpt_b200_trie_free": (None, [vp]),
@@ -104,8 +107,9 @@ SIGNATURES = {
     "agpt_b200_kv_store_write_bf16": (C.c_int, [vp, vp, i64, C.c_int, vp]),
     "agpt_b200_attn_fwd": (C.c_int, [vp, vp, vp, vp, C.c_int, vp, vp, C.c_int, C.c_int, f32, vp]),
     "agpt_b200_attn_bwd": (C.c_int, [vp, vp, vp, vp, C.c_int, vp, vp, vp, vp, vp, vp, vp, i64, C.c_int, C.c_int, f32, vp]),
+    "agpt_b200_attn_bwd_mode": (C.c_int, [vp, vp, vp, vp, C.c_int, vp, vp, vp, vp, vp, vp, vp, i64, C.c_int, C.c_int, f32, C.c_int, vp, vp]),
     "agpt_b200_set_attn_impl": (C.c_int, [C.c_int]),
-    "agpt_b200_set_attn_bwd_variant": (C.c_int, [C.c_int, C.c_int]),
+    "agpt_b200_set_attn_variant": (C.c_int, [C.c_int, C.c_int]),
     "agpt_b200_attn_bwd_static": (C.c_int, [vp, vp, vp, vp, C.c_int, vp, vp, vp, vp, vp, vp, C.c_int, C.c_int, f32, vp]),
     "agpt_b200_static_scratch_bytes": (i64, []),
     "agpt_b200_loss_per_query": (C.c_int, [vp] * 11 + [i64, C.c_int, f32, f32, C.c_int, vp]),

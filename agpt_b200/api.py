@@ -117,6 +117,22 @@ class RadixTrie:
         check(lib().agpt_b200_trie_load_dir(path.encode(), C.byref(h)), "trie_load_dir")
         return cls(h)
 
+    @classmethod
+    def load_subtree(cls, path: str, key: int) -> "RadixTrie":
+        """One per-subtree file of a radix directory as a trie of its own (local ids, 0 = root)."""
+        h = C.c_void_p()
+        check(lib().agpt_b200_trie_load_subtree(path.encode(), int(key), C.byref(h)), "trie_load_subtree")
+        return cls(h)
+
+    @staticmethod
+    def manifest(path: str):
+        """(keys, radix nodes, edge chars, deepest endpoint) of the per-subtree files listed in manifest.bin."""
+        n = check(lib().agpt_b200_trie_manifest(path.encode(), 0, None, None, None, None), "trie_manifest")
+        keys, nodes, ep = np.zeros(n, np.int32), np.zeros(n, np.int32), np.zeros(n, np.int32)
+        chars = np.zeros(n, np.int64)
+        check(lib().agpt_b200_trie_manifest(path.encode(), n, _vp(keys), _vp(nodes), _vp(chars), _vp(ep)), "trie_manifest")
+        return keys, nodes, chars, ep
+
     def save_dir(self, path: str, corpus_tokens: int, vocab: int, corpus_hash: int,
                  tag: str = "char.sorted_unique.v1", per_subtree: bool = False):
         os.makedirs(path, exist_ok=True)
@@ -472,8 +488,22 @@ def attn_forward(plan: WalkerPlan, q, k, v, n_heads: int, scale: float | None = 
     return out, lse
 
 
+GRAD_MODES = {"full": 0, "local_depth": 1, "own_edge": 2}
+
+
+def edge_first_positions(edge_id) -> np.ndarray:
+    """For rows in depth-first order with their radix node id: the row index of the first char of each row's edge
+    (the chars of one edge are consecutive rows)."""
+    e = np.asarray(edge_id)
+    starts = np.concatenate([[True], e[1:] != e[:-1]])
+    return np.maximum.accumulate(np.where(starts, np.arange(e.size), 0)).astype(np.int32)
+
+
 def attn_backward(plan: WalkerPlan, q, k, v, out, lse, dout, n_heads: int, scale: float | None = None,
-                  workspace=None, dq=None, dk=None, dv=None):
+                  workspace=None, dq=None, dk=None, dv=None, grad_mode: str = "full", edge_first=None):
+    """grad_mode: which attention pairs feed dK/dV -- "full" (a node and all its descendants), "local_depth" (the
+    node's own query only) or "own_edge" (the queries on the key's own radix edge; edge_first: int32 tensor [n], see
+    edge_first_positions).  dQ is the same in all three."""
     import torch
     _chk_f32(q, "q")
     _chk_f32(dout, "dout")
@@ -489,9 +519,16 @@ def attn_backward(plan: WalkerPlan, q, k, v, out, lse, dout, n_heads: int, scale
                        [("k", k), ("v", v)], lse)
     if workspace.dtype != torch.uint8 or not workspace.is_contiguous() or workspace.device != q.device:
         raise AgptError("workspace must be a contiguous uint8 tensor on the device of q")
-    check(lib().agpt_b200_attn_bwd(plan._h, _dp(q), _dp(k), _dp(v), _kv_dtype(k), _dp(out), _dp(lse), _dp(dout),
-                                   _dp(dq), _dp(dk), _dp(dv), _dp(workspace), workspace.numel(), n_heads, hd, scale,
-                                   _stream()), "attn_bwd")
+    if grad_mode not in GRAD_MODES:
+        raise AgptError(f"grad_mode {grad_mode!r}: one of {sorted(GRAD_MODES)}")
+    if grad_mode == "own_edge":
+        if edge_first is None or edge_first.dtype != torch.int32 or tuple(edge_first.shape) != (plan.n,) or \
+                not edge_first.is_contiguous() or edge_first.device != q.device:
+            raise AgptError("own_edge needs edge_first: a contiguous int32 tensor [plan.n] on the device of q")
+    check(lib().agpt_b200_attn_bwd_mode(plan._h, _dp(q), _dp(k), _dp(v), _kv_dtype(k), _dp(out), _dp(lse), _dp(dout),
+                                        _dp(dq), _dp(dk), _dp(dv), _dp(workspace), workspace.numel(), n_heads, hd, scale,
+                                        GRAD_MODES[grad_mode], _dp(edge_first) if grad_mode == "own_edge" else None,
+                                        _stream()), "attn_bwd")
     return dq, dk, dv
 
 
@@ -635,10 +672,10 @@ def set_attn_impl(impl: int) -> None:
     check(lib().agpt_b200_set_attn_impl(impl), "set_attn_impl")
 
 
-def set_attn_bwd_variant(whole_tile: bool = True, warps: int = 6) -> None:
-    """Tensor-core backward for a float32 store and head_dim <= 32: the whole-tile kernel (default) or the chunked
-    one; warps per block of the former (4, 6 or 8)."""
-    check(lib().agpt_b200_set_attn_bwd_variant(int(bool(whole_tile)), warps), "set_attn_bwd_variant")
+def set_attn_variant(whole_tile: bool = True, bwd_warps: int = 4) -> None:
+    """Tensor-core kernels for a float32 store and head_dim 32: the whole-tile pair (default) or the chunked pair;
+    warps per block of the whole-tile backward (4, 6 or 8)."""
+    check(lib().agpt_b200_set_attn_variant(int(bool(whole_tile)), bwd_warps), "set_attn_variant")
 
 
 def static_scratch_bytes() -> int:
@@ -705,48 +742,27 @@ def loss_per_node(logits, node_ids, counts_offset, counts_tok, counts_val):
     return loss, g
 
 
-def mass_weights(edge_mass, edge_len, mode: str = "linear") -> np.ndarray:
-    """Per-query mass weights of one chunk: f(edge_mass) / mean over the chunk's queries
-    (float32 arithmetic with a float64 running total, like the reference's host loop)."""
-    em = np.asarray(edge_mass, dtype=np.float32)
-    el = np.asarray(edge_len, dtype=np.int64)
-    if mode == "log":
-        w = np.log(np.float32(1.0) + em, dtype=np.float32)
-    elif mode == "sqrt":
-        w = np.sqrt(em, dtype=np.float32)
-    elif mode == "linear":
-        w = em
-    else:
-        w = np.ones_like(em)
-    tq = int(el.sum())
-    mean = np.float32((w.astype(np.float64) * el).sum() / tq) if tq > 0 else np.float32(1.0)
-    if mean <= 0:
-        mean = np.float32(1.0)
-    return np.repeat((w / mean).astype(np.float32), el)
+MASS_MODES = {"off": 0, "log": 1, "sqrt": 2, "linear": 3}
 
 
 def mass_weights_by_unit(edge_mass, edge_len, unit_of_node, counted, n_units: int, mode: str = "linear") -> np.ndarray:
     """Per-query mass weights where the mean is taken inside each unit (a root-child or bigram subtree) instead of over
     whatever rows share a launch: the weights then do not depend on how units are packed or spread over ranks.
     edge_mass, edge_len, unit_of_node, counted: one entry per loss node; nodes with counted == False (context rows)
-    get a weight but do not enter the mean."""
-    em = np.asarray(edge_mass, dtype=np.float32)
-    el = np.asarray(edge_len, dtype=np.int64)
-    un = np.asarray(unit_of_node, dtype=np.int64)
-    inc = np.asarray(counted, dtype=bool)
-    if mode == "log":
-        w = np.log(np.float32(1.0) + em, dtype=np.float32)
-    elif mode == "sqrt":
-        w = np.sqrt(em, dtype=np.float32)
-    elif mode == "linear":
-        w = em
-    else:
-        w = np.ones_like(em)
-    tot = np.bincount(un[inc], weights=(w.astype(np.float64) * el)[inc], minlength=n_units)
-    tq = np.bincount(un[inc], weights=el[inc].astype(np.float64), minlength=n_units)
-    mean = np.where(tq > 0, tot / np.maximum(tq, 1), 1.0).astype(np.float32)
-    mean[mean <= 0] = np.float32(1.0)
-    return np.repeat((w / mean[un]).astype(np.float32), el)
+    get a weight but do not enter the mean.  Computed by the library (agpt_b200_mass_weights)."""
+    em, el = _np_i32(edge_mass), _np_i32(edge_len)
+    un = None if unit_of_node is None else _np_i32(unit_of_node)
+    inc = None if counted is None else np.ascontiguousarray(counted, dtype=np.uint8)
+    out = np.empty(int(el.sum()), np.float32)
+    check(lib().agpt_b200_mass_weights(_vp(em), _vp(el), None if un is None else _vp(un), None if inc is None else _vp(inc),
+                                       em.size, max(int(n_units), 1), MASS_MODES[mode], _vp(out)), "mass_weights")
+    return out
+
+
+def mass_weights(edge_mass, edge_len, mode: str = "linear") -> np.ndarray:
+    """Per-query mass weights of one chunk: f(edge_mass) / mean over the chunk's queries
+    (float32 arithmetic with a float64 running total, like the reference's host loop)."""
+    return mass_weights_by_unit(edge_mass, edge_len, None, None, 1, mode)
 
 
 # legacy kernel boundary -------------------------------------------------------------------

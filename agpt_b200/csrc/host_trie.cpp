@@ -449,6 +449,85 @@ extern "C" int agpt_b200_trie_load_dir(const char *dir, agpt_trie **out) {
     return AGPT_OK;
 }
 
+// Per-subtree files (src/cuda/agpt_train.cu:431-493 manifest, :495-669 load_subtree).
+extern "C" int64_t agpt_b200_trie_manifest(const char *dir, int64_t cap, int32_t *keys, int32_t *n_nodes, int64_t *edge_chars,
+                                           int32_t *max_endpoint_depth) {
+    if (!dir) return agpt_set_error(AGPT_E_ARG, "trie_manifest: null");
+    std::string d(dir);
+    FILE *f = fopen((d + "/manifest.bin").c_str(), "rb");
+    if (!f) return agpt_set_error(AGPT_E_IO, "cannot open %s/manifest.bin", dir);
+    int32_t hd[3];
+    if (fread(hd, 4, 3, f) != 3 || (uint32_t)hd[0] != RADIX_MAGIC || hd[1] != 2 || hd[2] < 0) { fclose(f); return agpt_set_error(AGPT_E_IO, "%s/manifest.bin: bad header", dir); }
+    for (int32_t i = 0; i < hd[2]; i++) {
+        int32_t kn[2], me; int64_t ch;
+        if (fread(kn, 4, 2, f) != 2 || fread(&ch, 8, 1, f) != 1 || fread(&me, 4, 1, f) != 1) { fclose(f); return agpt_set_error(AGPT_E_IO, "%s/manifest.bin: truncated", dir); }
+        if (i < cap) {
+            if (keys) keys[i] = kn[0];
+            if (n_nodes) n_nodes[i] = kn[1];
+            if (edge_chars) edge_chars[i] = ch;
+            if (max_endpoint_depth) max_endpoint_depth[i] = me;
+        }
+    }
+    fclose(f);
+    return hd[2];
+}
+
+extern "C" int agpt_b200_trie_load_subtree(const char *dir, int32_t subtree_key, agpt_trie **out) {
+    if (!dir || !out) return agpt_set_error(AGPT_E_ARG, "trie_load_subtree: null");
+    char name[96];
+    snprintf(name, sizeof(name), "/subtrees/radix_subtree_%06d.bin", subtree_key);
+    std::string path = std::string(dir) + name;
+    FILE *f = fopen(path.c_str(), "rb");
+    if (!f) return agpt_set_error(AGPT_E_IO, "cannot open %s", path.c_str());
+    int32_t hd[4]; int64_t tec = 0; int32_t max_ep = 0;
+    if (fread(hd, 4, 4, f) != 4 || fread(&tec, 8, 1, f) != 1 || fread(&max_ep, 4, 1, f) != 1 || (uint32_t)hd[0] != RADIX_MAGIC || hd[1] != 2 ||
+        hd[2] != subtree_key || hd[3] < 0 || tec < 0) { fclose(f); return agpt_set_error(AGPT_E_IO, "%s: bad header", path.c_str()); }
+    const int32_t n = hd[3], rc = n + 1;                  // local id 0 = the (virtual) root, records 1..n in file order
+    agpt_trie *t = new agpt_trie();
+    t->radix_count = rc; t->n_depth_files = max_ep + 1; t->total_edge_chars = tec;
+    t->parent.assign(rc, -1); t->first_char_depth.assign(rc, 0); t->edge_len.assign(rc, 0); t->edge_mass.assign(rc, 0);
+    t->endpoint_depth.assign(rc, 0); t->subtree_key.assign(rc, subtree_key); t->edge_start.assign(rc, 0);
+    t->edge_off.assign(rc + 1, 0); t->cnt_off.assign(rc + 1, 0);
+    std::vector<int32_t> global_id(rc, 0), global_parent(rc, 0);
+    for (int32_t i = 1; i <= n; i++) {
+        int32_t r4[4], me[2];
+        if (fread(r4, 4, 4, f) != 4 || r4[3] < 0) { fclose(f); delete t; return agpt_set_error(AGPT_E_IO, "%s: bad record %d", path.c_str(), i); }
+        global_id[i] = r4[0]; global_parent[i] = r4[1];
+        t->first_char_depth[i] = r4[2]; t->edge_len[i] = r4[3]; t->endpoint_depth[i] = r4[2] + r4[3] - 1;
+        t->edge_start[i] = (int32_t)t->edge_tok.size();     // char positions in file order, as the reference numbers them
+        const size_t at = t->edge_tok.size();
+        t->edge_tok.resize(at + (size_t)r4[3]);
+        if (fread(t->edge_tok.data() + at, 4, (size_t)r4[3], f) != (size_t)r4[3] || fread(me, 4, 2, f) != 2 || me[1] < 0) { fclose(f); delete t; return agpt_set_error(AGPT_E_IO, "%s: truncated record %d", path.c_str(), i); }
+        t->edge_mass[i] = me[0];
+        for (int32_t e = 0; e < me[1]; e++) {
+            int32_t tv[2];
+            if (fread(tv, 4, 2, f) != 2) { fclose(f); delete t; return agpt_set_error(AGPT_E_IO, "%s: truncated counts", path.c_str()); }
+            t->cnt_tok.push_back(tv[0]); t->cnt_val.push_back(tv[1]);
+        }
+        t->edge_off[i + 1] = (int64_t)t->edge_tok.size();
+        t->cnt_off[i + 1] = (int64_t)t->cnt_tok.size();
+    }
+    fclose(f);
+    t->edge_off[1] = 0; t->cnt_off[1] = 0;
+    if ((int64_t)t->edge_tok.size() != tec) { delete t; return agpt_set_error(AGPT_E_IO, "%s: edge chars %lld != header %lld", path.c_str(), (long long)t->edge_tok.size(), (long long)tec); }
+    // global -> local ids; a parent that is the virtual root or lies outside the file (the depth-1 node of a bigram
+    // subtree) becomes the local root
+    std::vector<int32_t> order(n);
+    std::iota(order.begin(), order.end(), 1);
+    std::sort(order.begin(), order.end(), [&](int32_t a, int32_t b) { return global_id[a] < global_id[b]; });
+    for (int32_t i = 1; i <= n; i++) {
+        const int32_t gp = global_parent[i];
+        int32_t lp = 0;
+        if (gp != 0) {
+            auto it = std::lower_bound(order.begin(), order.end(), gp, [&](int32_t a, int32_t g) { return global_id[a] < g; });
+            if (it != order.end() && global_id[*it] == gp) lp = *it;
+        }
+        t->parent[i] = lp;
+    }
+    *out = t;
+    return AGPT_OK;
+}
+
 extern "C" int agpt_b200_trie_char_tree(const agpt_trie *t, int32_t *parent, int32_t *token, int32_t *depth, int32_t *radix_of_char) {
     if (!t) return agpt_set_error(AGPT_E_ARG, "trie_char_tree: null");
     for (int32_t r = 1; r < t->radix_count; r++) {
@@ -575,6 +654,34 @@ extern "C" float agpt_b200_compute_lr(float base_lr, int step, int total_steps, 
     float progress = (float)(step - cos_start) / (float)(total_steps - cos_start);
     if (progress > 1.0f) progress = 1.0f;
     return 0.5f * base_lr * (1.0f + cosf(3.14159265358979323846f * progress));
+}
+
+// --------------------------------------------------------------------------------------
+// per-query mass weights of a launch (host loop of src/cuda/agpt_train.cu:4608-4637, with the mean taken per unit)
+// --------------------------------------------------------------------------------------
+extern "C" int agpt_b200_mass_weights(const int32_t *edge_mass, const int32_t *edge_len, const int32_t *unit_of_node,
+                                      const uint8_t *counted, int64_t n_nodes, int64_t n_units, int mode, float *out_per_query) {
+    if (!edge_mass || !edge_len || !out_per_query || n_nodes < 0 || n_units < 1 || mode < 0 || mode > 3)
+        return agpt_set_error(AGPT_E_ARG, "mass_weights: bad argument");
+    std::vector<float> w((size_t)n_nodes);
+    std::vector<double> tot((size_t)n_units, 0.0), tq((size_t)n_units, 0.0);
+    for (int64_t i = 0; i < n_nodes; i++) {
+        const float c = (float)edge_mass[i];
+        w[i] = mode == 1 ? logf(1.0f + c) : mode == 2 ? sqrtf(c) : mode == 3 ? c : 1.0f;
+        const int64_t u = unit_of_node ? unit_of_node[i] : 0;
+        if (u < 0 || u >= n_units) return agpt_set_error(AGPT_E_ARG, "mass_weights: unit %lld of node %lld out of range", (long long)u, (long long)i);
+        if (edge_len[i] < 0) return agpt_set_error(AGPT_E_ARG, "mass_weights: negative edge length");
+        if (!counted || counted[i]) { tot[u] += (double)w[i] * edge_len[i]; tq[u] += (double)edge_len[i]; }
+    }
+    int64_t q = 0;
+    for (int64_t i = 0; i < n_nodes; i++) {
+        const int64_t u = unit_of_node ? unit_of_node[i] : 0;
+        float mean = tq[u] > 0 ? (float)(tot[u] / tq[u]) : 1.0f;
+        if (mean <= 0.0f) mean = 1.0f;
+        const float v = w[i] / mean;
+        for (int32_t j = 0; j < edge_len[i]; j++) out_per_query[q++] = v;
+    }
+    return AGPT_OK;
 }
 
 // --------------------------------------------------------------------------------------

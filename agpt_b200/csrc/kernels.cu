@@ -7,6 +7,7 @@
 // are exactly: the ancestor chain of the tile's first query (shared by the whole tile, listed in
 // chain_ids) plus the tile's own rows.  Key a is attended by query i iff a <= i < sub_end[a].
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <algorithm>
@@ -82,6 +83,19 @@ extern "C" void agpt_b200_plan_destroy(agpt_plan *p) { delete p; }
 // --------------------------------------------------------------------------------------
 // small helpers
 // --------------------------------------------------------------------------------------
+// Which (key, query) pairs feed dK/dV (dQ always takes every attended key).  A pair with key id a and query id i
+// (a <= i) is kept iff a >= first(i): first(i) = -inf keeps all (full: a node's dK/dV sum over the node itself and all
+// its descendants), first(i) = i keeps the query's own key only (local depth), first(i) = edge_first[i] keeps the keys
+// on the query's own radix edge.
+struct BwdMask {
+    int mode;                       // AGPT_GRAD_*
+    const int32_t *edge_first;      // [n] depth-first position of the first char of each position's radix edge (mode 2)
+};
+__device__ __forceinline__ int bwd_first_key(const BwdMask &mk, int i, int n) {
+    if (mk.mode == AGPT_GRAD_FULL || i >= n) return -0x7fffffff - 1;
+    return mk.mode == AGPT_GRAD_LOCAL_DEPTH ? i : __ldg(mk.edge_first + i);
+}
+
 #define KC 32            // keys staged per chunk
 #define LOG2E 1.4426950408889634f
 #define LN2 0.6931471805599453f
@@ -484,7 +498,8 @@ __global__ void __launch_bounds__(M) attn_bwd_kernel(const float *__restrict__ Q
                                                      float *__restrict__ dV, float *__restrict__ Pk,
                                                      float *__restrict__ Pv, const int32_t *__restrict__ sub_end,
                                                      const int64_t *__restrict__ chain_off,
-                                                     const int32_t *__restrict__ chain_ids, int n, int H, float scale, int tile0) {
+                                                     const int32_t *__restrict__ chain_ids, int n, int H, float scale, int tile0,
+                                                     BwdMask gmask) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     BwdSmem<HD, M> &S = *reinterpret_cast<BwdSmem<HD, M> *>(smem_raw);
     const int t = blockIdx.x + tile0, h = blockIdx.y, tid = threadIdx.x;
@@ -517,6 +532,7 @@ __global__ void __launch_bounds__(M) attn_bwd_kernel(const float *__restrict__ Q
     }
     const float qs = scale * LOG2E;
     const float lse2 = active ? LSE[(int64_t)i * H + h] * LOG2E : 0.f;
+    const int first_key = bwd_first_key(gmask, i, n);
 
     constexpr int NW = M / 32;          // warps = slices of head_dim in phase 2
     constexpr int SL = HD / NW;         // columns per slice
@@ -545,7 +561,8 @@ __global__ void __launch_bounds__(M) attn_bwd_kernel(const float *__restrict__ Q
             }
             float w = vld ? exp2f((d0 + d1) * qs - lse2) : 0.f;
             float ds = w * ((e0 + e1) - delta) * scale;
-            S.sW[tid][j] = w; S.sS[tid][j] = ds;
+            const bool keep = S.s_kid[j] >= first_key;             // dK/dV take this pair (dQ below always does)
+            S.sW[tid][j] = keep ? w : 0.f; S.sS[tid][j] = keep ? ds : 0.f;
 #pragma unroll
             for (int c = 0; c < HD / 4; c++) {
                 float4 kk = *reinterpret_cast<const float4 *>(&S.sK[j][c * 4]);
@@ -629,7 +646,7 @@ __global__ void __launch_bounds__(128, HD <= 32 ? 4 : (sizeof(KVT) == 2 ? 3 : 1)
                                                            const int64_t *__restrict__ chain_off,
                                                            const int32_t *__restrict__ chain_ids,
                                                            const int32_t *__restrict__ chain_end_all, int n, int H,
-                                                           float scale, int tile0) {
+                                                           float scale, int tile0, BwdMask gmask) {
     constexpr int M = 64, KS = HD / 8;
     constexpr bool SPLIT_KV = sizeof(KVT) == 4;
     constexpr int NB2 = (KS + 1) / 2;          // head_dim blocks of 8 per warp in phase 2
@@ -677,6 +694,7 @@ __global__ void __launch_bounds__(128, HD <= 32 ? 4 : (sizeof(KVT) == 2 ? 3 : 1)
     load_key_meta(sub_end, chain, chain_end_all + coff, p, i0, nkeys, S.s_kid, S.s_kend);
     const float lse0 = act0 ? LSE[(int64_t)r0 * H + h] * LOG2E : 0.f;
     const float lse1 = act1 ? LSE[(int64_t)r1 * H + h] * LOG2E : 0.f;
+    const int first0 = bwd_first_key(gmask, r0, n), first1 = bwd_first_key(gmask, r1, n);
     __syncthreads();                             // key metadata visible
     issue_chunk<HD, KVT>(K, V, S.s_kid, 0, min(KC, nkeys), D, hoff, S.sKb, S.sVb);
     asm volatile("cp.async.wait_group 1;" ::: "memory");      // the Q/dO/O group; chunk 0 may still be in flight
@@ -780,6 +798,13 @@ __global__ void __launch_bounds__(128, HD <= 32 ? 4 : (sizeof(KVT) == 2 ? 3 : 1)
                         }
                     }
                 }
+                if (gmask.mode != AGPT_GRAD_FULL && on[u]) {       // pairs that dK/dV do not take (dQ above took them all)
+                    const int kidA = kc + kA < nkeys ? S.s_kid[kc + kA] : 0, kidB = kc + kA + 1 < nkeys ? S.s_kid[kc + kA + 1] : 0;
+                    if (kidA < first0) { pw[0] = 0.f; ds[0] = 0.f; }
+                    if (kidB < first0) { pw[1] = 0.f; ds[1] = 0.f; }
+                    if (kidA < first1) { pw[2] = 0.f; ds[2] = 0.f; }
+                    if (kidB < first1) { pw[3] = 0.f; ds[3] = 0.f; }
+                }
                 *reinterpret_cast<float2 *>(&S.sP[q0][kA]) = make_float2(pw[0], pw[1]);
                 *reinterpret_cast<float2 *>(&S.sP[q1][kA]) = make_float2(pw[2], pw[3]);
                 *reinterpret_cast<float2 *>(&S.sS[q0][kA]) = make_float2(ds[0], ds[1]);
@@ -849,72 +874,142 @@ __global__ void __launch_bounds__(128, HD <= 32 ? 4 : (sizeof(KVT) == 2 ? 3 : 1)
 }
 
 // --------------------------------------------------------------------------------------
-// backward, whole tile resident: attn_bwd_tile_kernel.
+// backward, whole tile resident: attn_bwd_tile_kernel (head_dim 32, float32 store).
 //
-// The tile's Q and dO rows and every key row the tile can attend (ancestor chain + the tile's own rows) are
-// brought into shared memory ONCE, already split into TF32 hi and lo parts: element (row, dim) is the pair
-// {hi, lo}, pairs of dims form 16-byte chunks, and the chunk index is XOR-swizzled with the row so that both
-// fragment shapes the MMAs need are single conflict-free loads:
-//   * "along the row" (one row, two neighbouring dims, hi and lo): one 16-byte load;
-//   * "across rows"   (two neighbouring rows, one dim, hi and lo): two 8-byte loads.
-// After one block barrier the warps never meet again.  Work is cut into items that a warp runs from start to
-// end with nothing but registers and read-only shared memory:
-//   * row item (16 queries):  S = Q K^T and dP = dO V^T for the 16 rows against every key block, P, dS,
-//     dQ += dS K (the score fragment is the A fragment of the next product);  writes 16 dQ rows.
-//   * key item (16 keys):     S^T = K Q^T and dP^T = V dO^T for the 16 keys against every query block, P^T, dS^T,
-//     dK += dS^T Q, dV += P^T dO;  writes 16 dK/dV rows (tile rows) or partial rows (chain keys).
+// Operands.  The tile's Q and dO rows and every key row the tile can attend (ancestor chain + the tile's own
+// rows) are brought into shared memory ONCE (cp.async, raw float32) and converted in place to split half
+// precision: x * s = hi + lo with hi, lo in fp16 and s a power of two chosen per (tile, head, tensor) so that the
+// largest |x * s| lies in [1, 2).  hi carries 11 bits, lo the next 11 (its own rounding is 2^-24 absolute at this
+// scale), so hi*hi + lo*hi + hi*lo reproduces the float32 product to about 2^-22 -- the accuracy of three TF32
+// products -- while each mma.sync.m16n8k16 contracts twice as many elements as a TF32 m16n8k8, every fragment
+// register carries two elements, and the operands take 4 bytes per element instead of 8.  The scales are exact
+// (powers of two) and are divided out of the results.  A converted row is 128 bytes: 32 hi halves then 32 lo halves,
+// its eight 16-byte chunks XOR-swizzled with the row (chunk ^ row % 8), so that every fragment is one
+// conflict-free ldmatrix.x4: "along the row" fragments plain, "across rows" fragments with .trans.
+//
+// Work.  After the staging barriers the warps never meet again.  A warp takes items from a shared counter and runs
+// each from start to end with registers and read-only shared memory:
+//   * row item (16 queries):  S = Q K^T and dP = dO V^T for the 16 rows against every block of 16 keys, P, dS,
+//     dQ += dS K (the score fragments of two 8-key blocks are the A fragment of the next product); writes 16 dQ rows.
+//   * key item (16 keys):     S^T = K Q^T and dP^T = V dO^T for the 16 keys against every block of 16 queries, P^T,
+//     dS^T, dK += dS^T Q, dV += P^T dO;  writes 16 dK/dV rows (tile rows) or partial rows (chain keys).
 // Scores are computed twice (once per orientation) instead of crossing shared memory between two phases: that
-// costs two extra small products per block and removes every barrier, every P/dS store and reload.  Items are
-// handed out through a shared counter, heaviest first; each output element is produced by exactly one warp in a
-// fixed order, so the result does not depend on which warp took which item.
+// costs two extra small products per block and removes every barrier, every P/dS store and reload from the loops.
+// Each output element is produced by exactly one warp in a fixed order, so results do not depend on which warp
+// took which item.
 // --------------------------------------------------------------------------------------
 __device__ __forceinline__ float ex2_ftz(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-__device__ __forceinline__ int tile_swz(int r) { return (((r >> 1) & 3) << 1) ^ ((r & 1) << 2); }
-
-// store 4 consecutive dims (float4 index c4 of row r) into the swizzled row: chunk 2*c4 takes dims 4*c4, 4*c4+1 as
-// {hi, hi, lo, lo}, chunk 2*c4+1 the next two.  The eight lanes that fill one row write their even chunk first when
-// c4 < 4 and their odd chunk first otherwise, so that each 16-byte store instruction covers all 32 banks once.
-template <int HD>
-__device__ __forceinline__ void tile_store_split(float4 *base, int r, int c4, float4 x) {
-    uint32_t h0, l0, h1, l1, h2, l2, h3, l3;
-    tf32_split(x.x, h0, l0); tf32_split(x.y, h1, l1); tf32_split(x.z, h2, l2); tf32_split(x.w, h3, l3);
-    const int pc = (2 * c4) ^ tile_swz(r);
-    float4 *row = base + r * (HD / 2);
-    const float4 ev = make_float4(__uint_as_float(h0), __uint_as_float(h1), __uint_as_float(l0), __uint_as_float(l1));
-    const float4 od = make_float4(__uint_as_float(h2), __uint_as_float(h3), __uint_as_float(l2), __uint_as_float(l3));
-    if ((c4 >> 2) & 1) { row[pc ^ 1] = od; row[pc] = ev; }
-    else { row[pc] = ev; row[pc ^ 1] = od; }
+__device__ __forceinline__ uint32_t smem_u32_of(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t smem_addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr));
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// (x, y) -> packed fp16 pair hi (x in the low half) and the packed pair lo of the remainders.  LO_UP: the remainders
+// are stored times 2^11 (they are below 2^-11 |x|, so this keeps them in fp16's normal range and a small element keeps
+// its full 22 bits next to a large one); products with such a lo are accumulated apart and enter times 2^-11.
+#define LO_UP 2048.0f
+#define LO_DOWN 0.00048828125f
+template <bool UP>
+__device__ __forceinline__ void f16_split2(float x, float y, uint32_t &hi, uint32_t &lo) {
+    const __half2 h = __floats2half2_rn(x, y);
+    const float2 f = __half22float2(h);
+    const __half2 l = UP ? __floats2half2_rn((x - f.x) * LO_UP, (y - f.y) * LO_UP) : __floats2half2_rn(x - f.x, y - f.y);
+    hi = *reinterpret_cast<const uint32_t *>(&h);
+    lo = *reinterpret_cast<const uint32_t *>(&l);
+}
+__device__ __forceinline__ uint32_t f16_pack2(float x, float y) {
+    const __half2 h = __floats2half2_rn(x, y);
+    return *reinterpret_cast<const uint32_t *>(&h);
+}
+// A fragment of a product whose B operand is staged as (hi, lo * 2^11): P and dS enter times 2^11 (AUP), a = hi + lo
+// as halves, and the factor of the B operand's lo part is a_s = hi * 2^-11, one half-precision multiply (that term is
+// 2^-11 of the product, so the bits a_s loses below 2^-14 do not matter).  2^11 P <= 2048 and, with dO staged to a
+// maximum in [0.25, 0.5), 2^11 |dS'| < 2^11 * 2 * 32 * 0.5 * 2 * 0.18 < 65504.
+#define AUP 2048.0f
+#define ADOWN 0.00048828125f
+__device__ __forceinline__ uint32_t f16_down11(uint32_t h2) {
+    const __half2 r = __hmul2(*reinterpret_cast<const __half2 *>(&h2), __float2half2_rn(LO_DOWN));
+    return *reinterpret_cast<const uint32_t *>(&r);
+}
+// power of two s with max * s in [2^lift, 2^(lift+1)) (1 for max == 0), and its inverse
+__device__ __forceinline__ void pow2_scale(uint32_t max_bits, int lift, float &s, float &inv) {
+    int e = (int)(max_bits >> 23);
+    e = e < 1 ? 127 + lift : (e > 250 ? 250 : e);
+    s = __uint_as_float((uint32_t)(254 + lift - e) << 23);
+    inv = __uint_as_float((uint32_t)(e - lift) << 23);
 }
 
-template <int HD> constexpr size_t bwd_tile_smem_bytes(int maxk) {
-    return (size_t)(2 * 64 + 2 * maxk) * (HD / 2) * 16 + (size_t)maxk * 8 + 2 * 64 * 4 + 16;
+#define TILE_ROW_BYTES 128          // one staged row: 32 floats raw, then 32 hi + 32 lo halves
+
+// Staging geometry of one thread: it owns chunk c of rows r0, r0 + NT/8, r0 + 2 NT/8, ... of every plane.  NT/8 is a
+// multiple of 8, so the swizzle term (row % 8) and with it the three byte offsets below are the same for all its
+// rows up to a multiple of the row step: raw = where the raw float4 sits, hi / lo = where its four hi and four lo
+// halves go after the conversion.
+struct TileLane { int r0, c, raw, hi, lo; };
+__device__ __forceinline__ TileLane tile_lane(int tid) {
+    TileLane L;
+    L.r0 = tid >> 3; L.c = tid & 7;
+    const int x = L.r0 & 7, row = L.r0 * TILE_ROW_BYTES, half = (L.c & 1) << 3;
+    L.raw = row + ((L.c ^ x) << 4);
+    L.hi = row + (((L.c >> 1) ^ x) << 4) + half;
+    L.lo = row + (((4 + (L.c >> 1)) ^ x) << 4) + half;
+    return L;
+}
+__device__ __forceinline__ float abs_max4(float m, float4 a) {
+    return fmaxf(m, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))));
+}
+// In-place conversion of the thread's chunk (row offset o) of two planes: the eight lanes that own the chunks of one
+// row read them, the warp synchronises, and each lane writes its four hi and four lo halves into the row's hi and lo
+// part.  Called by whole warps.
+__device__ __forceinline__ void tile_convert2(unsigned char *pa, unsigned char *pb, const TileLane &L, int o, float sa, float sb) {
+    const float4 a = *reinterpret_cast<const float4 *>(pa + L.raw + o), b = *reinterpret_cast<const float4 *>(pb + L.raw + o);
+    uint2 ah, al, bh, bl;
+    f16_split2<true>(a.x * sa, a.y * sa, ah.x, al.x); f16_split2<true>(a.z * sa, a.w * sa, ah.y, al.y);
+    f16_split2<true>(b.x * sb, b.y * sb, bh.x, bl.x); f16_split2<true>(b.z * sb, b.w * sb, bh.y, bl.y);
+    __syncwarp();
+    *reinterpret_cast<uint2 *>(pa + L.hi + o) = ah; *reinterpret_cast<uint2 *>(pa + L.lo + o) = al;
+    *reinterpret_cast<uint2 *>(pb + L.hi + o) = bh; *reinterpret_cast<uint2 *>(pb + L.lo + o) = bl;
+    __syncwarp();
 }
 
-template <int HD, int NW>
-__global__ void __launch_bounds__(NW * 32, 2)
+constexpr size_t bwd_tile_smem_bytes(int maxk) {
+    return (size_t)(2 * 64 + 2 * maxk) * TILE_ROW_BYTES + (size_t)maxk * 8 + 3 * 64 * 4 + 32;
+}
+
+template <int NW, int MINB>
+__global__ void __launch_bounds__(NW * 32, MINB)
 attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, const float *__restrict__ V,
                      const float *__restrict__ O, const float *__restrict__ LSE, const float *__restrict__ dO,
                      float *__restrict__ dQ, float *__restrict__ dK, float *__restrict__ dV, float *__restrict__ Pk,
                      float *__restrict__ Pv, const int32_t *__restrict__ sub_end, const int64_t *__restrict__ chain_off,
                      const int32_t *__restrict__ chain_ids, const int32_t *__restrict__ chain_end_all, int n, int H,
-                     float scale, int tile0, int maxk, int dbg) {
-    constexpr int M = 64, KS = HD / 8, RC = HD / 2, C4 = HD / 4, NT = NW * 32;
-    extern __shared__ __align__(16) unsigned char tile_smem_raw[];
-    float4 *sQ = reinterpret_cast<float4 *>(tile_smem_raw);          // [64][RC]
-    float4 *sG = sQ + M * RC;                                         // [64][RC]   dO
-    float4 *sK = sG + M * RC;                                         // [maxk][RC]
-    float4 *sV = sK + (size_t)maxk * RC;                              // [maxk][RC]
-    int2 *s_meta = reinterpret_cast<int2 *>(sV + (size_t)maxk * RC);  // [maxk] {key id, key subtree end}
-    float *sLse = reinterpret_cast<float *>(s_meta + maxk);           // [64]  lse * log2(e)
-    float *sDelta = sLse + M;                                         // [64]  dO . O
-    int *s_ctr = reinterpret_cast<int *>(sDelta + M);
+                     float scale, int tile0, int maxk, int dbg, BwdMask gmask) {
+    constexpr int HD = 32, M = 64, NT = NW * 32;
+    extern __shared__ __align__(128) unsigned char tile_smem_raw[];
+    unsigned char *sQ = tile_smem_raw, *sG = sQ + M * TILE_ROW_BYTES, *sK = sG + M * TILE_ROW_BYTES;
+    unsigned char *sV = sK + (size_t)maxk * TILE_ROW_BYTES;
+    int2 *s_meta = reinterpret_cast<int2 *>(sV + (size_t)maxk * TILE_ROW_BYTES);   // [maxk] {key id, key subtree end}
+    float *sLse = reinterpret_cast<float *>(s_meta + maxk);                          // [64]  lse * log2(e)
+    float *sDelta = sLse + M;                                                        // [64]  dO . O
+    int *sFirst = reinterpret_cast<int *>(sDelta + M);                               // [64]  first key id each query feeds in dK/dV
+    uint32_t *s_max = reinterpret_cast<uint32_t *>(sFirst + M);                      // [4]   max |x| of Q, K, V, dO (float bits)
+    int *s_ctr = reinterpret_cast<int *>(s_max + 4);
 
     const int t = blockIdx.x + tile0, h = blockIdx.y, tid = threadIdx.x;
-    const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, tig = lane & 3;
+    const int lane = tid & 31, g = lane >> 2, tig = lane & 3;
     const int D = H * HD, hoff = h * HD;
     const int i0 = t * M;
     const int nt = min(M, n - i0);
@@ -924,67 +1019,111 @@ attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
     const int nkp = (nkeys + 15) & ~15;                // rows staged (zero rows beyond nkeys)
     const int32_t *chain = chain_ids + coff;
     const int32_t *chain_end = chain_end_all + coff;
-    const float qs = scale * LOG2E;
 
-    // ---- stage: key metadata, K/V rows, Q/dO rows (+ delta), lse ----
+    // ---- stage 1: raw rows by cp.async (chunk c of row r goes to chunk c ^ r % 8), O rows to registers ----
+    if (tid < 4) s_max[tid] = 0u;
     if (tid == 0) *s_ctr = 0;
+    constexpr int RSTEP = NT / 8, OSTEP = RSTEP * TILE_ROW_BYTES;
+    constexpr int UQ = (M + RSTEP - 1) / RSTEP;
+    const TileLane L = tile_lane(tid);
+    float4 ox[UQ];
+#pragma unroll
+    for (int u = 0; u < UQ; u++) {
+        const int r = L.r0 + u * RSTEP, o = L.raw + u * OSTEP;
+        ox[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < M) {
+            if (r < nt) {
+                const int64_t off = (int64_t)(i0 + r) * D + hoff + L.c * 4;
+                cp_async16(sQ + o, Q + off); cp_async16(sG + o, dO + off);
+                ox[u] = ld4(O + off);
+            } else {
+                *reinterpret_cast<float4 *>(sQ + o) = make_float4(0.f, 0.f, 0.f, 0.f);
+                *reinterpret_cast<float4 *>(sG + o) = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+    }
+    for (int r = L.r0, o = L.raw; r < nkp; r += RSTEP, o += OSTEP) {
+        if (r < nkeys) {
+            const int kid = r < p ? __ldg(chain + r) : i0 + (r - p);
+            const int64_t off = (int64_t)kid * D + hoff + L.c * 4;
+            cp_async16(sK + o, K + off); cp_async16(sV + o, V + off);
+        } else {
+            *reinterpret_cast<float4 *>(sK + o) = make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<float4 *>(sV + o) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    cp_async_commit();
     for (int j = tid; j < nkp; j += NT) {
         int kid = 0x7fffffff, kend = 0;
         if (j < p) { kid = __ldg(chain + j); kend = __ldg(chain_end + j); }
         else if (j < nkeys) { kid = i0 + (j - p); kend = __ldg(sub_end + kid); }
         s_meta[j] = make_int2(kid, kend);
     }
-    if (tid < M) sLse[tid] = tid < nt ? __ldg(LSE + (int64_t)(i0 + tid) * H + h) * LOG2E : 0.f;
+    if (tid < M) {
+        sLse[tid] = tid < nt ? __ldg(LSE + (int64_t)(i0 + tid) * H + h) * LOG2E : 0.f;
+        sFirst[tid] = bwd_first_key(gmask, i0 + tid, n);
+    }
+    cp_async_wait_all();                 // this thread's own chunks have landed (pass A reads only those)
+
+    // ---- stage 2 (pass A): maxima of |x| per tensor, delta = dO . O per row ----
     {
-        // every global load of the block is issued before the first one is used: one round trip to memory instead
-        // of one per loop iteration (the block has nothing else to overlap it with until the barrier)
-        constexpr int UQ = (M * C4 + NT - 1) / NT;       // iterations over the tile's own Q / dO / O rows
-        constexpr int UK = 4;                            // key-row iterations per batch
-        float4 qx[UQ], gx[UQ], ox[UQ], kx[UK], vx[UK];
+        float mq = 0.f, mg = 0.f, mk = 0.f, mv = 0.f;
 #pragma unroll
-        for (int u = 0; u < UQ; u++) {
-            const int idx = tid + u * NT, r = idx / C4, c = idx % C4;
-            qx[u] = gx[u] = ox[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (idx < M * C4 && r < nt) {
-                const int64_t off = (int64_t)(i0 + r) * D + hoff + c * 4;
-                qx[u] = ld4(Q + off); gx[u] = ld4(dO + off); ox[u] = ld4(O + off);
+        for (int u = 0; u < UQ; u++) {       // whole warps enter or skip an iteration (a warp holds four whole rows)
+            const int r = L.r0 + u * RSTEP, o = L.raw + u * OSTEP;
+            if (r < M) {
+                const float4 a = *reinterpret_cast<const float4 *>(sQ + o), b = *reinterpret_cast<const float4 *>(sG + o);
+                mq = abs_max4(mq, a); mg = abs_max4(mg, b);
+                float d = b.x * ox[u].x;
+                d = fmaf(b.y, ox[u].y, d); d = fmaf(b.z, ox[u].z, d); d = fmaf(b.w, ox[u].w, d);
+                d += __shfl_xor_sync(0xffffffffu, d, 1); d += __shfl_xor_sync(0xffffffffu, d, 2); d += __shfl_xor_sync(0xffffffffu, d, 4);
+                if (L.c == 0) sDelta[r] = d;
             }
         }
-        for (int base = 0; base < nkp * C4; base += NT * UK) {
-#pragma unroll
-            for (int u = 0; u < UK; u++) {
-                const int idx = base + tid + u * NT, r = idx / C4, c = idx % C4;
-                kx[u] = vx[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (r < nkeys) {
-                    const int kid = r < p ? __ldg(chain + r) : i0 + (r - p);
-                    const int64_t off = (int64_t)kid * D + hoff + c * 4;
-                    kx[u] = ld4(K + off); vx[u] = ld4(V + off);
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < UK; u++) {
-                const int idx = base + tid + u * NT, r = idx / C4, c = idx % C4;
-                if (idx < nkp * C4) { tile_store_split<HD>(sK, r, c, kx[u]); tile_store_split<HD>(sV, r, c, vx[u]); }
-            }
+        for (int r = L.r0, o = L.raw; r < nkp; r += RSTEP, o += OSTEP) {
+            mk = abs_max4(mk, *reinterpret_cast<const float4 *>(sK + o));
+            mv = abs_max4(mv, *reinterpret_cast<const float4 *>(sV + o));
         }
 #pragma unroll
-        for (int u = 0; u < UQ; u++) {       // whole warps enter or skip an iteration (64*C4 and NT are multiples of 32)
-            const int idx = tid + u * NT, r = idx / C4, c = idx % C4;
-            if (idx < M * C4) {
-                float d = gx[u].x * ox[u].x;
-                d = fmaf(gx[u].y, ox[u].y, d); d = fmaf(gx[u].z, ox[u].z, d); d = fmaf(gx[u].w, ox[u].w, d);
-#pragma unroll
-                for (int o = 1; o < C4; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-                if (c == 0) sDelta[r] = d;
-                tile_store_split<HD>(sQ, r, c, qx[u]);
-                tile_store_split<HD>(sG, r, c, gx[u]);
-            }
+        for (int o = 16; o > 0; o >>= 1) {
+            mq = fmaxf(mq, __shfl_xor_sync(0xffffffffu, mq, o)); mg = fmaxf(mg, __shfl_xor_sync(0xffffffffu, mg, o));
+            mk = fmaxf(mk, __shfl_xor_sync(0xffffffffu, mk, o)); mv = fmaxf(mv, __shfl_xor_sync(0xffffffffu, mv, o));
+        }
+        if (lane == 0) {                     // non-negative floats order like their bit patterns
+            atomicMax(&s_max[0], __float_as_uint(mq)); atomicMax(&s_max[1], __float_as_uint(mk));
+            atomicMax(&s_max[2], __float_as_uint(mv)); atomicMax(&s_max[3], __float_as_uint(mg));
         }
     }
     __syncthreads();
+    float sclQ, invQ, sclK, invK, sclV, invV, sclG, invG;
+    pow2_scale(s_max[0], 0, sclQ, invQ); pow2_scale(s_max[1], 0, sclK, invK);
+    pow2_scale(s_max[2], 0, sclV, invV); pow2_scale(s_max[3], -2, sclG, invG);
 
-    const int fg = tile_swz(g);                  // swizzle of a row whose index is g (mod 8)
-    const int fa = tile_swz(2 * tig), fb = tile_swz(2 * tig + 1);
+    // ---- stage 3 (pass B): convert in place ----
+#pragma unroll
+    for (int u = 0; u < UQ; u++)
+        if (L.r0 + u * RSTEP < M) tile_convert2(sQ, sG, L, u * OSTEP, sclQ, sclG);
+    for (int r = L.r0, o = 0; r < nkp; r += RSTEP, o += OSTEP) tile_convert2(sK, sV, L, o, sclK, sclV);
+    __syncthreads();
+
+    // units: S' = (Q sQ)(K sK)^T, dP' = (dO sG)(V sV)^T, P' = 2^11 P, dS' = P' (dP' - delta sG sV) scale = 2^11 dS sG sV
+    const float fS = scale * LOG2E * invQ * invK;       // log2-domain score = S' * fS
+    // dQ = (dS' K') / (2^11 sG sV sK), dK = (dS'^T Q') / (2^11 sG sV sQ), dV = (P'^T dO') / (2^11 sG); delta enters dS' as delta sG sV.
+    // The powers of two are applied one after the other, never as one product that could leave the float range.
+
+    // ldmatrix lane addressing: lane l names row l % 8 of matrix l / 8 (rows of 16 bytes).
+    const int l8 = lane & 7, mi = lane >> 3;
+    // B fragments of an 8-row block for k-step ks (16 dims): matrices {hi chunk 2ks, hi 2ks+1, lo 2ks, lo 2ks+1}
+    const uint32_t bRow = (uint32_t)(l8 * TILE_ROW_BYTES);
+    const int bC = (mi & 1) + ((mi >> 1) << 2);         // + 2 ks
+    // A fragments of a 16-row block for k-step ks: matrices {rows 0-7 chunk 2ks, rows 8-15 chunk 2ks, rows 0-7 chunk 2ks+1,
+    // rows 8-15 chunk 2ks+1} (+4 for the lo part); the .trans fragments of a 16-row block for dims 8 db..: {hi rows 0-7,
+    // hi rows 8-15, lo rows 0-7, lo rows 8-15} of chunk db (+4 for lo)
+    const uint32_t aRow = (uint32_t)((l8 + (mi & 1) * 8) * TILE_ROW_BYTES);
+    const int aC = mi >> 1;                             // + 2 ks (+ 4 for lo)
+    const int tC = (mi >> 1) << 2;                      // + db
+    const uint32_t uQ = smem_u32_of(sQ), uG = smem_u32_of(sG), uK = smem_u32_of(sK), uV = smem_u32_of(sV);
+
     const int nkb = nkp >> 4;                    // key items
     const int npc = (p + 15) >> 4;               // key items that hold chain keys (the heaviest: attended by most rows)
     const int n_items = nkb + 4;
@@ -1002,155 +1141,167 @@ attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
         if ((dbg >> kind) & 1) continue;
 
         if (kind == 0) {
-            // ================= row item: 16 queries, every key block =================
+            // ================= row item: 16 queries, every block of 16 keys =================
             const int rg = which;
             if (rg * 16 >= nt) continue;                                   // rows beyond the end of the plan
             const int q0 = rg * 16 + g, q1 = q0 + 8;
             const int r0 = i0 + q0, r1 = i0 + q1;
-            uint32_t qh[KS][4], ql[KS][4], gh[KS][4], gl[KS][4];
+            uint32_t qh[2][4], ql[2][4], gh[2][4], gl[2][4];
 #pragma unroll
-            for (int ks = 0; ks < KS; ks++) {
-                const int pc = (ks * 4 + tig) ^ fg;
-                const float4 a = sQ[q0 * RC + pc], b = sQ[q1 * RC + pc];
-                qh[ks][0] = __float_as_uint(a.x); qh[ks][2] = __float_as_uint(a.y); ql[ks][0] = __float_as_uint(a.z); ql[ks][2] = __float_as_uint(a.w);
-                qh[ks][1] = __float_as_uint(b.x); qh[ks][3] = __float_as_uint(b.y); ql[ks][1] = __float_as_uint(b.z); ql[ks][3] = __float_as_uint(b.w);
-                const float4 c = sG[q0 * RC + pc], d = sG[q1 * RC + pc];
-                gh[ks][0] = __float_as_uint(c.x); gh[ks][2] = __float_as_uint(c.y); gl[ks][0] = __float_as_uint(c.z); gl[ks][2] = __float_as_uint(c.w);
-                gh[ks][1] = __float_as_uint(d.x); gh[ks][3] = __float_as_uint(d.y); gl[ks][1] = __float_as_uint(d.z); gl[ks][3] = __float_as_uint(d.w);
+            for (int ks = 0; ks < 2; ks++) {
+                const uint32_t o = (uint32_t)(rg * 16 * TILE_ROW_BYTES) + aRow;
+                const uint32_t ch = (uint32_t)(((2 * ks + aC) ^ l8) << 4), cl = (uint32_t)(((2 * ks + aC + 4) ^ l8) << 4);
+                ldmatrix_x4(qh[ks], uQ + o + ch); ldmatrix_x4(ql[ks], uQ + o + cl);
+                ldmatrix_x4(gh[ks], uG + o + ch); ldmatrix_x4(gl[ks], uG + o + cl);
             }
-            const float lse0 = sLse[q0], lse1 = sLse[q1], dl0 = sDelta[q0], dl1 = sDelta[q1];
-            float dq[KS][4];
+            const float lse0 = sLse[q0], lse1 = sLse[q1], dl0 = sDelta[q0] * sclG * sclV, dl1 = sDelta[q1] * sclG * sclV;
+            float dq[4][4];
 #pragma unroll
-            for (int db = 0; db < KS; db++) dq[db][0] = dq[db][1] = dq[db][2] = dq[db][3] = 0.f;
+            for (int db = 0; db < 4; db++) dq[db][0] = dq[db][1] = dq[db][2] = dq[db][3] = 0.f;
             // the rows of this group attend the chain and the tile's keys up to their own position
-            const int nb_lim = min((nkeys + 7) >> 3, (p + rg * 16 + 16 + 7) >> 3);
-            for (int nb = 0; nb < nb_lim; nb++) {
-                const int4 mk = *reinterpret_cast<const int4 *>(&s_meta[nb * 8 + 2 * tig]);   // keys 2*tig, 2*tig+1 of the block
-                const bool v0 = mk.x <= r0 && r0 < mk.y, v1 = mk.z <= r0 && r0 < mk.w;
-                const bool v2 = mk.x <= r1 && r1 < mk.y, v3 = mk.z <= r1 && r1 < mk.w;
-                if (!__any_sync(0xffffffffu, v0 | v1 | v2 | v3)) continue;
-                float c[4] = {0.f, 0.f, 0.f, 0.f}, cx[4] = {0.f, 0.f, 0.f, 0.f}, cy[4] = {0.f, 0.f, 0.f, 0.f};
-                float e[4] = {0.f, 0.f, 0.f, 0.f}, ex[4] = {0.f, 0.f, 0.f, 0.f}, ey[4] = {0.f, 0.f, 0.f, 0.f};
-                const float4 *kr = sK + (nb * 8 + g) * RC, *vr = sV + (nb * 8 + g) * RC;
+            const int kp_lim = min((nkeys + 15) >> 4, (p + rg * 16 + 16 + 15) >> 4);
+            for (int kp = 0; kp < kp_lim; kp++) {
+                bool vld[2][4];
+                bool on[2];
 #pragma unroll
-                for (int ks = 0; ks < KS; ks++) {
-                    const int pc = (ks * 4 + tig) ^ fg;
-                    const float4 kb = kr[pc], vb = vr[pc];
-                    const uint32_t k0h = __float_as_uint(kb.x), k1h = __float_as_uint(kb.y), k0l = __float_as_uint(kb.z), k1l = __float_as_uint(kb.w);
-                    const uint32_t v0h = __float_as_uint(vb.x), v1h = __float_as_uint(vb.y), v0l = __float_as_uint(vb.z), v1l = __float_as_uint(vb.w);
-                    mma_tf32(c, qh[ks], k0h, k1h); mma_tf32(e, gh[ks], v0h, v1h);
-                    mma_tf32(cx, ql[ks], k0h, k1h); mma_tf32(ex, gl[ks], v0h, v1h);
-                    mma_tf32(cy, qh[ks], k0l, k1l); mma_tf32(ey, gh[ks], v0l, v1l);
+                for (int u = 0; u < 2; u++) {
+                    const int4 mk = *reinterpret_cast<const int4 *>(&s_meta[kp * 16 + u * 8 + 2 * tig]);   // keys 2*tig, 2*tig+1 of the block
+                    vld[u][0] = mk.x <= r0 && r0 < mk.y; vld[u][1] = mk.z <= r0 && r0 < mk.w;
+                    vld[u][2] = mk.x <= r1 && r1 < mk.y; vld[u][3] = mk.z <= r1 && r1 < mk.w;
+                    on[u] = __any_sync(0xffffffffu, vld[u][0] | vld[u][1] | vld[u][2] | vld[u][3]);
                 }
-                float pw[4], ds[4];
+                if (!(on[0] || on[1])) continue;
+                float ds[2][4];
 #pragma unroll
-                for (int j = 0; j < 4; j++) { c[j] += cx[j] + cy[j]; e[j] += ex[j] + ey[j]; }
-                pw[0] = v0 ? ex2_ftz(fmaf(c[0], qs, -lse0)) : 0.f; pw[1] = v1 ? ex2_ftz(fmaf(c[1], qs, -lse0)) : 0.f;
-                pw[2] = v2 ? ex2_ftz(fmaf(c[2], qs, -lse1)) : 0.f; pw[3] = v3 ? ex2_ftz(fmaf(c[3], qs, -lse1)) : 0.f;
-                ds[0] = pw[0] * (e[0] - dl0) * scale; ds[1] = pw[1] * (e[1] - dl0) * scale;
-                ds[2] = pw[2] * (e[2] - dl1) * scale; ds[3] = pw[3] * (e[3] - dl1) * scale;
-                // dQ += dS K: key 2*tig sits in k-slot tig, key 2*tig+1 in k-slot tig+4
-                uint32_t ah[4], al[4];
-                tf32_split(ds[0], ah[0], al[0]); tf32_split(ds[2], ah[1], al[1]);
-                tf32_split(ds[1], ah[2], al[2]); tf32_split(ds[3], ah[3], al[3]);
-                const float *ka = reinterpret_cast<const float *>(sK + (nb * 8 + 2 * tig) * RC);
-                const float *kb2 = reinterpret_cast<const float *>(sK + (nb * 8 + 2 * tig + 1) * RC);
+                for (int u = 0; u < 2; u++) {
+                    ds[u][0] = ds[u][1] = ds[u][2] = ds[u][3] = 0.f;
+                    if (!on[u]) continue;                                  // warp-uniform
+                    float c[4] = {0.f, 0.f, 0.f, 0.f}, cx[4] = {0.f, 0.f, 0.f, 0.f};
+                    float e[4] = {0.f, 0.f, 0.f, 0.f}, ex[4] = {0.f, 0.f, 0.f, 0.f};
+                    const uint32_t rowb = (uint32_t)((kp * 16 + u * 8) * TILE_ROW_BYTES) + bRow;
 #pragma unroll
-                for (int db = 0; db < KS; db++) {
-                    const int cc = db * 4 + (g >> 1), hf = g & 1;
-                    const int ia = ((cc ^ fa) << 2) + hf, ib = ((cc ^ fb) << 2) + hf;      // hi; lo sits two floats further
-                    const uint32_t x0h = __float_as_uint(ka[ia]), x1h = __float_as_uint(kb2[ib]);
-                    const uint32_t x0l = __float_as_uint(ka[ia + 2]), x1l = __float_as_uint(kb2[ib + 2]);
-                    mma_tf32(dq[db], ah, x0h, x1h);
-                    mma_tf32(dq[db], al, x0h, x1h);
-                    mma_tf32(dq[db], ah, x0l, x1l);
+                    for (int ks = 0; ks < 2; ks++) {
+                        const uint32_t o = rowb + (uint32_t)(((2 * ks + bC) ^ l8) << 4);
+                        uint32_t kf[4], vf[4];                 // {b0 hi, b1 hi, b0 lo, b1 lo}
+                        ldmatrix_x4(kf, uK + o); ldmatrix_x4(vf, uV + o);
+                        mma_f16(c, qh[ks], kf[0], kf[1]); mma_f16(e, gh[ks], vf[0], vf[1]);
+                        mma_f16(cx, ql[ks], kf[0], kf[1]); mma_f16(ex, gl[ks], vf[0], vf[1]);
+                        mma_f16(cx, qh[ks], kf[2], kf[3]); mma_f16(ex, gh[ks], vf[2], vf[3]);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const float sc = fmaf(cx[j], LO_DOWN, c[j]), dp = fmaf(ex[j], LO_DOWN, e[j]);
+                        const float pw = vld[u][j] ? ex2_ftz(fmaf(sc, fS, j < 2 ? -lse0 : -lse1)) : 0.f;
+                        ds[u][j] = pw * (dp - (j < 2 ? dl0 : dl1)) * (scale * AUP);
+                    }
+                }
+                // dQ += dS K over the 16 keys: the score fragments of the two 8-key blocks are the A fragment
+                uint32_t ah[4], al[4], as[4];
+                f16_split2<false>(ds[0][0], ds[0][1], ah[0], al[0]); f16_split2<false>(ds[0][2], ds[0][3], ah[1], al[1]);
+                f16_split2<false>(ds[1][0], ds[1][1], ah[2], al[2]); f16_split2<false>(ds[1][2], ds[1][3], ah[3], al[3]);
+#pragma unroll
+                for (int j = 0; j < 4; j++) as[j] = f16_down11(ah[j]);
+                const uint32_t rowt = uK + (uint32_t)(kp * 16 * TILE_ROW_BYTES) + aRow;
+#pragma unroll
+                for (int db = 0; db < 4; db++) {
+                    uint32_t kt[4];                            // {b0 hi, b1 hi, b0 lo, b1 lo}: keys 0-7 / 8-15 of the block, dims 8 db..
+                    ldmatrix_x4_trans(kt, rowt + (uint32_t)(((db + tC) ^ l8) << 4));
+                    mma_f16(dq[db], ah, kt[0], kt[1]);
+                    mma_f16(dq[db], al, kt[0], kt[1]);
+                    mma_f16(dq[db], as, kt[2], kt[3]);
                 }
             }
             if (r0 < n) {
 #pragma unroll
-                for (int db = 0; db < KS; db++)
-                    *reinterpret_cast<float2 *>(dQ + (int64_t)r0 * D + hoff + db * 8 + 2 * tig) = make_float2(dq[db][0], dq[db][1]);
+                for (int db = 0; db < 4; db++)
+                    *reinterpret_cast<float2 *>(dQ + (int64_t)r0 * D + hoff + db * 8 + 2 * tig) = make_float2(dq[db][0] * ADOWN * invG * invV * invK, dq[db][1] * ADOWN * invG * invV * invK);
             }
             if (r1 < n) {
 #pragma unroll
-                for (int db = 0; db < KS; db++)
-                    *reinterpret_cast<float2 *>(dQ + (int64_t)r1 * D + hoff + db * 8 + 2 * tig) = make_float2(dq[db][2], dq[db][3]);
+                for (int db = 0; db < 4; db++)
+                    *reinterpret_cast<float2 *>(dQ + (int64_t)r1 * D + hoff + db * 8 + 2 * tig) = make_float2(dq[db][2] * ADOWN * invG * invV * invK, dq[db][3] * ADOWN * invG * invV * invK);
             }
         } else {
-            // ================= key item: 16 keys, every query block =================
+            // ================= key item: 16 keys, every block of 16 queries =================
             const int kb = which;
             const int kA = kb * 16 + g, kB = kA + 8;
             const int2 mA = s_meta[kA], mB = s_meta[kB];
-            uint32_t kh[KS][4], kl[KS][4], vh[KS][4], vl[KS][4];
+            uint32_t kh[2][4], kl[2][4], vh[2][4], vl[2][4];
 #pragma unroll
-            for (int ks = 0; ks < KS; ks++) {
-                const int pc = (ks * 4 + tig) ^ fg;
-                const float4 a = sK[kA * RC + pc], b = sK[kB * RC + pc];
-                kh[ks][0] = __float_as_uint(a.x); kh[ks][2] = __float_as_uint(a.y); kl[ks][0] = __float_as_uint(a.z); kl[ks][2] = __float_as_uint(a.w);
-                kh[ks][1] = __float_as_uint(b.x); kh[ks][3] = __float_as_uint(b.y); kl[ks][1] = __float_as_uint(b.z); kl[ks][3] = __float_as_uint(b.w);
-                const float4 c = sV[kA * RC + pc], d = sV[kB * RC + pc];
-                vh[ks][0] = __float_as_uint(c.x); vh[ks][2] = __float_as_uint(c.y); vl[ks][0] = __float_as_uint(c.z); vl[ks][2] = __float_as_uint(c.w);
-                vh[ks][1] = __float_as_uint(d.x); vh[ks][3] = __float_as_uint(d.y); vl[ks][1] = __float_as_uint(d.z); vl[ks][3] = __float_as_uint(d.w);
+            for (int ks = 0; ks < 2; ks++) {
+                const uint32_t o = (uint32_t)(kb * 16 * TILE_ROW_BYTES) + aRow;
+                const uint32_t ch = (uint32_t)(((2 * ks + aC) ^ l8) << 4), cl = (uint32_t)(((2 * ks + aC + 4) ^ l8) << 4);
+                ldmatrix_x4(kh[ks], uK + o + ch); ldmatrix_x4(kl[ks], uK + o + cl);
+                ldmatrix_x4(vh[ks], uV + o + ch); ldmatrix_x4(vl[ks], uV + o + cl);
             }
-            float dk[KS][4], dv[KS][4];
+            float dk[4][4], dv[4][4];
 #pragma unroll
-            for (int db = 0; db < KS; db++) {
+            for (int db = 0; db < 4; db++) {
                 dk[db][0] = dk[db][1] = dk[db][2] = dk[db][3] = 0.f;
                 dv[db][0] = dv[db][1] = dv[db][2] = dv[db][3] = 0.f;
             }
             // a key of the tile itself is attended only by queries at or after it
-            const int qb_first = max(0, kb * 16 - p) >> 3;
-            const int qb_end = (nt + 7) >> 3;
-            for (int qb = qb_first; qb < qb_end; qb++) {
-                const int rq0 = i0 + qb * 8 + 2 * tig, rq1 = rq0 + 1;
-                const bool v0 = mA.x <= rq0 && rq0 < mA.y, v1 = mA.x <= rq1 && rq1 < mA.y;
-                const bool v2 = mB.x <= rq0 && rq0 < mB.y, v3 = mB.x <= rq1 && rq1 < mB.y;
-                if (!__any_sync(0xffffffffu, v0 | v1 | v2 | v3)) continue;
-                float c[4] = {0.f, 0.f, 0.f, 0.f}, cx[4] = {0.f, 0.f, 0.f, 0.f}, cy[4] = {0.f, 0.f, 0.f, 0.f};
-                float e[4] = {0.f, 0.f, 0.f, 0.f}, ex[4] = {0.f, 0.f, 0.f, 0.f}, ey[4] = {0.f, 0.f, 0.f, 0.f};
-                const float4 *qr = sQ + (qb * 8 + g) * RC, *gr = sG + (qb * 8 + g) * RC;
+            const int qp_first = max(0, kb * 16 - p) >> 4;
+            const int qp_end = (nt + 15) >> 4;
+            for (int qp = qp_first; qp < qp_end; qp++) {
+                bool vld[2][4];
+                bool on[2];
 #pragma unroll
-                for (int ks = 0; ks < KS; ks++) {
-                    const int pc = (ks * 4 + tig) ^ fg;
-                    const float4 qb4 = qr[pc], gb4 = gr[pc];
-                    const uint32_t q0h = __float_as_uint(qb4.x), q1h = __float_as_uint(qb4.y), q0l = __float_as_uint(qb4.z), q1l = __float_as_uint(qb4.w);
-                    const uint32_t g0h = __float_as_uint(gb4.x), g1h = __float_as_uint(gb4.y), g0l = __float_as_uint(gb4.z), g1l = __float_as_uint(gb4.w);
-                    mma_tf32(c, kh[ks], q0h, q1h); mma_tf32(e, vh[ks], g0h, g1h);
-                    mma_tf32(cx, kl[ks], q0h, q1h); mma_tf32(ex, vl[ks], g0h, g1h);
-                    mma_tf32(cy, kh[ks], q0l, q1l); mma_tf32(ey, vh[ks], g0l, g1l);
+                for (int u = 0; u < 2; u++) {
+                    const int rq0 = i0 + qp * 16 + u * 8 + 2 * tig, rq1 = rq0 + 1;
+                    const int2 fk = *reinterpret_cast<const int2 *>(&sFirst[qp * 16 + u * 8 + 2 * tig]);
+                    vld[u][0] = mA.x <= rq0 && rq0 < mA.y && mA.x >= fk.x; vld[u][1] = mA.x <= rq1 && rq1 < mA.y && mA.x >= fk.y;
+                    vld[u][2] = mB.x <= rq0 && rq0 < mB.y && mB.x >= fk.x; vld[u][3] = mB.x <= rq1 && rq1 < mB.y && mB.x >= fk.y;
+                    on[u] = __any_sync(0xffffffffu, vld[u][0] | vld[u][1] | vld[u][2] | vld[u][3]);
                 }
+                if (!(on[0] || on[1])) continue;
+                float ds[2][4], pw[2][4];
 #pragma unroll
-                for (int j = 0; j < 4; j++) { c[j] += cx[j] + cy[j]; e[j] += ex[j] + ey[j]; }
-                const float2 ls = *reinterpret_cast<const float2 *>(&sLse[qb * 8 + 2 * tig]);
-                const float2 dl = *reinterpret_cast<const float2 *>(&sDelta[qb * 8 + 2 * tig]);
-                float pw[4], ds[4];
-                pw[0] = v0 ? ex2_ftz(fmaf(c[0], qs, -ls.x)) : 0.f; pw[1] = v1 ? ex2_ftz(fmaf(c[1], qs, -ls.y)) : 0.f;
-                pw[2] = v2 ? ex2_ftz(fmaf(c[2], qs, -ls.x)) : 0.f; pw[3] = v3 ? ex2_ftz(fmaf(c[3], qs, -ls.y)) : 0.f;
-                ds[0] = pw[0] * (e[0] - dl.x) * scale; ds[1] = pw[1] * (e[1] - dl.y) * scale;
-                ds[2] = pw[2] * (e[2] - dl.x) * scale; ds[3] = pw[3] * (e[3] - dl.y) * scale;
-                // dK += dS^T Q, dV += P^T dO: query 2*tig sits in k-slot tig, query 2*tig+1 in k-slot tig+4
-                uint32_t sh[4], sl[4], ph[4], pl[4];
-                tf32_split(ds[0], sh[0], sl[0]); tf32_split(ds[2], sh[1], sl[1]);
-                tf32_split(ds[1], sh[2], sl[2]); tf32_split(ds[3], sh[3], sl[3]);
-                tf32_split(pw[0], ph[0], pl[0]); tf32_split(pw[2], ph[1], pl[1]);
-                tf32_split(pw[1], ph[2], pl[2]); tf32_split(pw[3], ph[3], pl[3]);
-                const int qa = qb * 8 + 2 * tig;
-                const float *qra = reinterpret_cast<const float *>(sQ + qa * RC), *qrb = reinterpret_cast<const float *>(sQ + (qa + 1) * RC);
-                const float *gra = reinterpret_cast<const float *>(sG + qa * RC), *grb = reinterpret_cast<const float *>(sG + (qa + 1) * RC);
+                for (int u = 0; u < 2; u++) {
+                    ds[u][0] = ds[u][1] = ds[u][2] = ds[u][3] = 0.f;
+                    pw[u][0] = pw[u][1] = pw[u][2] = pw[u][3] = 0.f;
+                    if (!on[u]) continue;                                  // warp-uniform
+                    float c[4] = {0.f, 0.f, 0.f, 0.f}, cx[4] = {0.f, 0.f, 0.f, 0.f};
+                    float e[4] = {0.f, 0.f, 0.f, 0.f}, ex[4] = {0.f, 0.f, 0.f, 0.f};
+                    const int qr = qp * 16 + u * 8;
+                    const uint32_t rowb = (uint32_t)(qr * TILE_ROW_BYTES) + bRow;
 #pragma unroll
-                for (int db = 0; db < KS; db++) {
-                    const int cc = db * 4 + (g >> 1), hf = g & 1;
-                    const int ia = ((cc ^ fa) << 2) + hf, ib = ((cc ^ fb) << 2) + hf;      // hi; lo sits two floats further
-                    const uint32_t x0h = __float_as_uint(qra[ia]), x1h = __float_as_uint(qrb[ib]);
-                    const uint32_t x0l = __float_as_uint(qra[ia + 2]), x1l = __float_as_uint(qrb[ib + 2]);
-                    const uint32_t y0h = __float_as_uint(gra[ia]), y1h = __float_as_uint(grb[ib]);
-                    const uint32_t y0l = __float_as_uint(gra[ia + 2]), y1l = __float_as_uint(grb[ib + 2]);
-                    mma_tf32(dk[db], sh, x0h, x1h);
-                    mma_tf32(dv[db], ph, y0h, y1h);
-                    mma_tf32(dk[db], sl, x0h, x1h);
-                    mma_tf32(dv[db], pl, y0h, y1h);
-                    mma_tf32(dk[db], sh, x0l, x1l);
-                    mma_tf32(dv[db], ph, y0l, y1l);
+                    for (int ks = 0; ks < 2; ks++) {
+                        const uint32_t o = rowb + (uint32_t)(((2 * ks + bC) ^ l8) << 4);
+                        uint32_t qf[4], gf[4];                 // {b0 hi, b1 hi, b0 lo, b1 lo}
+                        ldmatrix_x4(qf, uQ + o); ldmatrix_x4(gf, uG + o);
+                        mma_f16(c, kh[ks], qf[0], qf[1]); mma_f16(e, vh[ks], gf[0], gf[1]);
+                        mma_f16(cx, kl[ks], qf[0], qf[1]); mma_f16(ex, vl[ks], gf[0], gf[1]);
+                        mma_f16(cx, kh[ks], qf[2], qf[3]); mma_f16(ex, vh[ks], gf[2], gf[3]);
+                    }
+                    const float2 ls = *reinterpret_cast<const float2 *>(&sLse[qr + 2 * tig]);
+                    const float2 dl = *reinterpret_cast<const float2 *>(&sDelta[qr + 2 * tig]);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const float sc = fmaf(cx[j], LO_DOWN, c[j]), dp = fmaf(ex[j], LO_DOWN, e[j]);
+                        const float pr = vld[u][j] ? ex2_ftz(fmaf(sc, fS, (j & 1) ? -ls.y : -ls.x)) : 0.f;
+                        pw[u][j] = pr * AUP;
+                        ds[u][j] = pw[u][j] * (dp - ((j & 1) ? dl.y : dl.x) * sclG * sclV) * scale;
+                    }
+                }
+                // dK += dS^T Q, dV += P^T dO over the 16 queries
+                uint32_t sh[4], sl[4], ss[4], ph[4], pl[4], ps[4];
+#pragma unroll
+                for (int u = 0; u < 2; u++) {
+                    f16_split2<false>(ds[u][0], ds[u][1], sh[2 * u], sl[2 * u]); f16_split2<false>(ds[u][2], ds[u][3], sh[2 * u + 1], sl[2 * u + 1]);
+                    f16_split2<false>(pw[u][0], pw[u][1], ph[2 * u], pl[2 * u]); f16_split2<false>(pw[u][2], pw[u][3], ph[2 * u + 1], pl[2 * u + 1]);
+                    ss[2 * u] = f16_down11(sh[2 * u]); ss[2 * u + 1] = f16_down11(sh[2 * u + 1]);
+                    ps[2 * u] = f16_down11(ph[2 * u]); ps[2 * u + 1] = f16_down11(ph[2 * u + 1]);
+                }
+                const uint32_t ro = (uint32_t)(qp * 16 * TILE_ROW_BYTES) + aRow;
+#pragma unroll
+                for (int db = 0; db < 4; db++) {
+                    uint32_t qt[4], gt[4];                     // {b0 hi, b1 hi, b0 lo, b1 lo}: queries 0-7 / 8-15 of the block, dims 8 db..
+                    const uint32_t co = (uint32_t)(((db + tC) ^ l8) << 4);
+                    ldmatrix_x4_trans(qt, uQ + ro + co); ldmatrix_x4_trans(gt, uG + ro + co);
+                    mma_f16(dk[db], sh, qt[0], qt[1]); mma_f16(dv[db], ph, gt[0], gt[1]);
+                    mma_f16(dk[db], sl, qt[0], qt[1]); mma_f16(dv[db], pl, gt[0], gt[1]);
+                    mma_f16(dk[db], ss, qt[2], qt[3]); mma_f16(dv[db], ps, gt[2], gt[3]);
                 }
             }
 #pragma unroll
@@ -1161,12 +1312,210 @@ attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
                 if (kk < p) { ok = Pk + (coff + kk) * D + hoff; ov = Pv + (coff + kk) * D + hoff; }
                 else { ok = dK + (int64_t)(i0 + kk - p) * D + hoff; ov = dV + (int64_t)(i0 + kk - p) * D + hoff; }
 #pragma unroll
-                for (int db = 0; db < KS; db++) {
-                    *reinterpret_cast<float2 *>(ok + db * 8 + 2 * tig) = make_float2(dk[db][2 * half], dk[db][2 * half + 1]);
-                    *reinterpret_cast<float2 *>(ov + db * 8 + 2 * tig) = make_float2(dv[db][2 * half], dv[db][2 * half + 1]);
+                for (int db = 0; db < 4; db++) {
+                    *reinterpret_cast<float2 *>(ok + db * 8 + 2 * tig) = make_float2(dk[db][2 * half] * ADOWN * invG * invV * invQ, dk[db][2 * half + 1] * ADOWN * invG * invV * invQ);
+                    *reinterpret_cast<float2 *>(ov + db * 8 + 2 * tig) = make_float2(dv[db][2 * half] * ADOWN * invG, dv[db][2 * half + 1] * ADOWN * invG);
                 }
             }
         }
+    }
+}
+
+// --------------------------------------------------------------------------------------
+// forward, whole tile resident: attn_fwd_tile_kernel (head_dim 32, float32 store).  Same staging, operand format and
+// fragment addressing as attn_bwd_tile_kernel; one warp per 16 query rows (4 warps), online softmax over blocks of
+// 16 keys, O += P V with V read through ldmatrix.trans.
+// --------------------------------------------------------------------------------------
+constexpr size_t fwd_tile_smem_bytes(int maxk) {
+    return (size_t)(64 + 2 * maxk) * TILE_ROW_BYTES + (size_t)maxk * 8 + 32;
+}
+
+template <int MINB>
+__global__ void __launch_bounds__(128, MINB)
+attn_fwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, const float *__restrict__ V,
+                     float *__restrict__ O, float *__restrict__ LSE, const int32_t *__restrict__ sub_end,
+                     const int64_t *__restrict__ chain_off, const int32_t *__restrict__ chain_ids,
+                     const int32_t *__restrict__ chain_end_all, int n, int H, float scale, int tile0, int maxk) {
+    constexpr int HD = 32, M = 64, NT = 128;
+    extern __shared__ __align__(128) unsigned char tile_smem_raw[];
+    unsigned char *sQ = tile_smem_raw, *sK = sQ + M * TILE_ROW_BYTES, *sV = sK + (size_t)maxk * TILE_ROW_BYTES;
+    int2 *s_meta = reinterpret_cast<int2 *>(sV + (size_t)maxk * TILE_ROW_BYTES);   // [maxk] {key id, key subtree end}
+    uint32_t *s_max = reinterpret_cast<uint32_t *>(s_meta + maxk);                  // [3] max |x| of Q, K, V (float bits)
+
+    const int t = blockIdx.x + tile0, h = blockIdx.y, tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, tig = lane & 3;
+    const int D = H * HD, hoff = h * HD;
+    const int i0 = t * M;
+    const int nt = min(M, n - i0);
+    const int64_t coff = chain_off[t];
+    const int p = (int)(chain_off[t + 1] - coff);
+    const int nkeys = p + nt;
+    const int nkp = (nkeys + 15) & ~15;
+    const int32_t *chain = chain_ids + coff;
+    const int32_t *chain_end = chain_end_all + coff;
+
+    // ---- stage 1: raw rows by cp.async ----
+    if (tid < 3) s_max[tid] = 0u;
+    constexpr int RSTEP = NT / 8, OSTEP = RSTEP * TILE_ROW_BYTES;
+    const TileLane L = tile_lane(tid);
+#pragma unroll
+    for (int u = 0; u < M / RSTEP; u++) {
+        const int r = L.r0 + u * RSTEP, o = L.raw + u * OSTEP;
+        if (r < nt) cp_async16(sQ + o, Q + (int64_t)(i0 + r) * D + hoff + L.c * 4);
+        else *reinterpret_cast<float4 *>(sQ + o) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int r = L.r0, o = L.raw; r < nkp; r += RSTEP, o += OSTEP) {
+        if (r < nkeys) {
+            const int kid = r < p ? __ldg(chain + r) : i0 + (r - p);
+            const int64_t off = (int64_t)kid * D + hoff + L.c * 4;
+            cp_async16(sK + o, K + off); cp_async16(sV + o, V + off);
+        } else {
+            *reinterpret_cast<float4 *>(sK + o) = make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<float4 *>(sV + o) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    cp_async_commit();
+    for (int j = tid; j < nkp; j += NT) {
+        int kid = 0x7fffffff, kend = 0;
+        if (j < p) { kid = __ldg(chain + j); kend = __ldg(chain_end + j); }
+        else if (j < nkeys) { kid = i0 + (j - p); kend = __ldg(sub_end + kid); }
+        s_meta[j] = make_int2(kid, kend);
+    }
+    cp_async_wait_all();                 // this thread's own chunks have landed (pass A reads only those)
+
+    // ---- stage 2 (pass A): maxima of |x| per tensor ----
+    {
+        float mq = 0.f, mk = 0.f, mv = 0.f;
+#pragma unroll
+        for (int u = 0; u < M / RSTEP; u++) mq = abs_max4(mq, *reinterpret_cast<const float4 *>(sQ + L.raw + u * OSTEP));
+        for (int r = L.r0, o = L.raw; r < nkp; r += RSTEP, o += OSTEP) {
+            mk = abs_max4(mk, *reinterpret_cast<const float4 *>(sK + o));
+            mv = abs_max4(mv, *reinterpret_cast<const float4 *>(sV + o));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            mq = fmaxf(mq, __shfl_xor_sync(0xffffffffu, mq, o)); mk = fmaxf(mk, __shfl_xor_sync(0xffffffffu, mk, o));
+            mv = fmaxf(mv, __shfl_xor_sync(0xffffffffu, mv, o));
+        }
+        if (lane == 0) {
+            atomicMax(&s_max[0], __float_as_uint(mq)); atomicMax(&s_max[1], __float_as_uint(mk)); atomicMax(&s_max[2], __float_as_uint(mv));
+        }
+    }
+    __syncthreads();
+    float sclQ, invQ, sclK, invK, sclV, invV;
+    pow2_scale(s_max[0], 0, sclQ, invQ); pow2_scale(s_max[1], 0, sclK, invK); pow2_scale(s_max[2], 0, sclV, invV);
+
+    // ---- stage 3 (pass B): convert in place (Q rows two at a time through the two-plane helper) ----
+#pragma unroll
+    for (int u = 0; u < M / RSTEP; u += 2) tile_convert2(sQ, sQ + OSTEP, L, u * OSTEP, sclQ, sclQ);
+    for (int r = L.r0, o = 0; r < nkp; r += RSTEP, o += OSTEP) tile_convert2(sK, sV, L, o, sclK, sclV);
+    __syncthreads();
+
+    const int rg = warp;
+    if (rg * 16 >= nt) return;                                   // rows beyond the end of the plan (no barrier follows)
+    const float fS = scale * LOG2E * invQ * invK;               // log2-domain score = S' * fS
+    const int l8 = lane & 7, mi = lane >> 3;
+    const uint32_t bRow = (uint32_t)(l8 * TILE_ROW_BYTES);
+    const int bC = (mi & 1) + ((mi >> 1) << 2);
+    const uint32_t aRow = (uint32_t)((l8 + (mi & 1) * 8) * TILE_ROW_BYTES);
+    const int aC = mi >> 1, tC = (mi >> 1) << 2;
+    const uint32_t uQ = smem_u32_of(sQ), uK = smem_u32_of(sK), uV = smem_u32_of(sV);
+
+    const int q0 = rg * 16 + g, q1 = q0 + 8;
+    const int r0 = i0 + q0, r1 = i0 + q1;
+    uint32_t qh[2][4], ql[2][4];
+#pragma unroll
+    for (int ks = 0; ks < 2; ks++) {
+        const uint32_t o = (uint32_t)(rg * 16 * TILE_ROW_BYTES) + aRow;
+        ldmatrix_x4(qh[ks], uQ + o + (uint32_t)(((2 * ks + aC) ^ l8) << 4));
+        ldmatrix_x4(ql[ks], uQ + o + (uint32_t)(((2 * ks + aC + 4) ^ l8) << 4));
+    }
+    float o_[4][4];
+#pragma unroll
+    for (int db = 0; db < 4; db++) o_[db][0] = o_[db][1] = o_[db][2] = o_[db][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    const int kp_lim = min((nkeys + 15) >> 4, (p + rg * 16 + 16 + 15) >> 4);
+    for (int kp = 0; kp < kp_lim; kp++) {
+        bool vld[2][4];
+        bool on[2];
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            const int4 mk = *reinterpret_cast<const int4 *>(&s_meta[kp * 16 + u * 8 + 2 * tig]);
+            vld[u][0] = mk.x <= r0 && r0 < mk.y; vld[u][1] = mk.z <= r0 && r0 < mk.w;
+            vld[u][2] = mk.x <= r1 && r1 < mk.y; vld[u][3] = mk.z <= r1 && r1 < mk.w;
+            on[u] = __any_sync(0xffffffffu, vld[u][0] | vld[u][1] | vld[u][2] | vld[u][3]);
+        }
+        if (!(on[0] || on[1])) continue;
+        float s2[2][4];
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            s2[u][0] = s2[u][1] = s2[u][2] = s2[u][3] = -INFINITY;
+            if (!on[u]) continue;                                  // warp-uniform
+            float c[4] = {0.f, 0.f, 0.f, 0.f}, cx[4] = {0.f, 0.f, 0.f, 0.f};
+            const uint32_t rowb = (uint32_t)((kp * 16 + u * 8) * TILE_ROW_BYTES) + bRow;
+#pragma unroll
+            for (int ks = 0; ks < 2; ks++) {
+                uint32_t kf[4];
+                ldmatrix_x4(kf, uK + rowb + (uint32_t)(((2 * ks + bC) ^ l8) << 4));
+                mma_f16(c, qh[ks], kf[0], kf[1]);
+                mma_f16(cx, ql[ks], kf[0], kf[1]);
+                mma_f16(cx, qh[ks], kf[2], kf[3]);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                if (vld[u][j]) s2[u][j] = fmaf(cx[j], LO_DOWN, c[j]) * fS;
+        }
+        float mx0 = fmaxf(fmaxf(s2[0][0], s2[0][1]), fmaxf(s2[1][0], s2[1][1]));
+        float mx1 = fmaxf(fmaxf(s2[0][2], s2[0][3]), fmaxf(s2[1][2], s2[1][3]));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const float mu0 = mn0 == -INFINITY ? 0.f : mn0, mu1 = mn1 == -INFINITY ? 0.f : mn1;
+        const float corr0 = ex2_ftz(m0 - mu0), corr1 = ex2_ftz(m1 - mu1);
+        m0 = mn0; m1 = mn1;
+        l0 *= corr0; l1 *= corr1;
+#pragma unroll
+        for (int db = 0; db < 4; db++) { o_[db][0] *= corr0; o_[db][1] *= corr0; o_[db][2] *= corr1; o_[db][3] *= corr1; }
+        float pw[2][4];
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            pw[u][0] = ex2_ftz(s2[u][0] - mu0); pw[u][1] = ex2_ftz(s2[u][1] - mu0);
+            pw[u][2] = ex2_ftz(s2[u][2] - mu1); pw[u][3] = ex2_ftz(s2[u][3] - mu1);
+            l0 += pw[u][0] + pw[u][1]; l1 += pw[u][2] + pw[u][3];
+#pragma unroll
+            for (int j = 0; j < 4; j++) pw[u][j] *= AUP;
+        }
+        uint32_t ph[4], pl[4], ps[4];
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            f16_split2<false>(pw[u][0], pw[u][1], ph[2 * u], pl[2 * u]); f16_split2<false>(pw[u][2], pw[u][3], ph[2 * u + 1], pl[2 * u + 1]);
+            ps[2 * u] = f16_down11(ph[2 * u]); ps[2 * u + 1] = f16_down11(ph[2 * u + 1]);
+        }
+        const uint32_t rowt = uV + (uint32_t)(kp * 16 * TILE_ROW_BYTES) + aRow;
+#pragma unroll
+        for (int db = 0; db < 4; db++) {
+            uint32_t vt[4];                            // {b0 hi, b1 hi, b0 lo, b1 lo}: keys 0-7 / 8-15 of the block, dims 8 db..
+            ldmatrix_x4_trans(vt, rowt + (uint32_t)(((db + tC) ^ l8) << 4));
+            mma_f16(o_[db], ph, vt[0], vt[1]);
+            mma_f16(o_[db], pl, vt[0], vt[1]);
+            mma_f16(o_[db], ps, vt[2], vt[3]);
+        }
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    if (r0 < n) {
+        const float inv = ADOWN * invV / l0;
+#pragma unroll
+        for (int db = 0; db < 4; db++)
+            *reinterpret_cast<float2 *>(O + (int64_t)r0 * D + hoff + db * 8 + 2 * tig) = make_float2(o_[db][0] * inv, o_[db][1] * inv);
+        if (tig == 0) LSE[(int64_t)r0 * H + h] = (m0 + log2f(l0)) * LN2;
+    }
+    if (r1 < n) {
+        const float inv = ADOWN * invV / l1;
+#pragma unroll
+        for (int db = 0; db < 4; db++)
+            *reinterpret_cast<float2 *>(O + (int64_t)r1 * D + hoff + db * 8 + 2 * tig) = make_float2(o_[db][2] * inv, o_[db][3] * inv);
+        if (tig == 0) LSE[(int64_t)r1 * H + h] = (m1 + log2f(l1)) * LN2;
     }
 }
 
@@ -1256,12 +1605,12 @@ static int launch_fwd(const agpt_plan *p, const float *q, const void *k, const v
 template <int HD, int M, typename KVT>
 static int launch_bwd(const agpt_plan *p, const float *q, const void *k, const void *v, const float *o, const float *lse,
                       const float *dout, float *dq, float *dk, float *dv, float *pk, float *pv, int H, float scale,
-                      cudaStream_t st, int tile0, int ntiles) {
+                      cudaStream_t st, int tile0, int ntiles, BwdMask gmask) {
     dim3 grid((unsigned)ntiles, (unsigned)H);
     size_t smem = sizeof(BwdSmem<HD, M>);
     CUDA_TRY(cudaFuncSetAttribute(attn_bwd_kernel<HD, M, KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attn_bwd_kernel<HD, M, KVT><<<grid, M, smem, st>>>(q, (const KVT *)k, (const KVT *)v, o, lse, dout, dq, dk, dv, pk, pv,
-                                                       p->d_sub_end, p->d_chain_off, p->d_chain_ids, (int)p->n, H, scale, tile0);
+                                                       p->d_sub_end, p->d_chain_off, p->d_chain_ids, (int)p->n, H, scale, tile0, gmask);
     return launch_status("attn_bwd");
 }
 
@@ -1297,43 +1646,6 @@ extern "C" int agpt_b200_set_attn_impl(int impl) {
     return AGPT_OK;
 }
 
-template <int HD, typename KVT>
-static int launch_fwd_mma(const agpt_plan *p, const float *q, const void *k, const void *v, float *out, float *lse, int H,
-                          float scale, cudaStream_t st, int tile0, int ntiles) {
-    dim3 grid((unsigned)ntiles, (unsigned)H);
-    const size_t smem = fwd_mma_smem_bytes<HD>();
-    CUDA_TRY(cudaFuncSetAttribute(attn_fwd_mma_kernel<HD, KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attn_fwd_mma_kernel<HD, KVT><<<grid, 128, smem, st>>>(q, (const KVT *)k, (const KVT *)v, out, lse, p->d_sub_end,
-                                                       p->d_chain_off, p->d_chain_ids, p->d_chain_end, (int)p->n, H, scale, tile0);
-    return launch_status("attn_fwd_mma");
-}
-
-static int fwd_dispatch(const agpt_plan *p, const float *q, const void *k, const void *v, int kv_dtype, float *out,
-                        float *lse, int H, int head_dim, float scale, cudaStream_t st, int tile0, int ntiles) {
-    if (attn_impl() == 1 && p->tile_m == 64 && p->max_depth + 64 <= MAXKEYS) {
-        const bool bf = kv_dtype == AGPT_KV_BF16;
-        switch (head_dim) {
-            case 16: return bf ? launch_fwd_mma<16, __nv_bfloat16>(p, q, k, v, out, lse, H, scale, st, tile0, ntiles) : launch_fwd_mma<16, float>(p, q, k, v, out, lse, H, scale, st, tile0, ntiles);
-            case 32: return bf ? launch_fwd_mma<32, __nv_bfloat16>(p, q, k, v, out, lse, H, scale, st, tile0, ntiles) : launch_fwd_mma<32, float>(p, q, k, v, out, lse, H, scale, st, tile0, ntiles);
-            case 64: return bf ? launch_fwd_mma<64, __nv_bfloat16>(p, q, k, v, out, lse, H, scale, st, tile0, ntiles) : launch_fwd_mma<64, float>(p, q, k, v, out, lse, H, scale, st, tile0, ntiles);
-        }
-    }
-    DISPATCH_HD_M_KV(launch_fwd, p, q, k, v, out, lse, H, scale, st, tile0, ntiles);
-}
-
-template <int HD, typename KVT>
-static int launch_bwd_mma(const agpt_plan *p, const float *q, const void *k, const void *v, const float *o, const float *lse,
-                          const float *dout, float *dq, float *dk, float *dv, float *pk, float *pv, int H, float scale,
-                          cudaStream_t st, int tile0, int ntiles) {
-    dim3 grid((unsigned)ntiles, (unsigned)H);
-    size_t smem = sizeof(BwdMmaSmem<HD, KVT>);
-    CUDA_TRY(cudaFuncSetAttribute(attn_bwd_mma_kernel<HD, KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attn_bwd_mma_kernel<HD, KVT><<<grid, 128, smem, st>>>(q, (const KVT *)k, (const KVT *)v, o, lse, dout, dq, dk, dv, pk, pv,
-                                                          p->d_sub_end, p->d_chain_off, p->d_chain_ids, p->d_chain_end, (int)p->n, H,
-                                                          scale, tile0);
-    return launch_status("attn_bwd_mma");
-}
-
 // Raise a kernel's dynamic shared-memory limit once per device (the attribute belongs to the context's copy of the
 // function, so it is set again on every device a plan is used on, but not on every launch).
 template <typename KernelT>
@@ -1348,71 +1660,123 @@ static int allow_dynamic_smem(KernelT kernel, size_t bytes, size_t *granted /* [
     return AGPT_OK;
 }
 
-// Whole-tile backward: chosen when two blocks of it fit one SM (228 KB of shared memory, 1 KB reserved per block).
-// AGPT_B200_BWD_TILE=0 keeps the chunked kernel (A/B runs); AGPT_B200_BWD_WARPS = 4, 6 or 8 warps per block.
-#define BWD_TILE_SMEM_LIMIT ((size_t)113 * 1024)
+// Whole-tile kernels (forward and backward; float32 store, head_dim 32): chosen when four blocks of the backward
+// fit one SM (228 KB of shared memory, 1 KB reserved per block), i.e. up to about 150 keys per tile; deeper plans take
+// the chunked kernels.  AGPT_B200_ATTN_TILE=0 keeps the chunked kernels (A/B runs); AGPT_B200_BWD_WARPS = 4, 6 or 8
+// warps per block of the backward.
+#define BWD_TILE_SMEM_LIMIT ((size_t)56 * 1024)
 static int g_bwd_tile = -1, g_bwd_warps = 0, g_bwd_dbg = 0;
 static int bwd_tile_enabled() {
     if (g_bwd_tile < 0) {
-        const char *e = getenv("AGPT_B200_BWD_TILE");
-        g_bwd_tile = (e && e[0] == '1') ? 1 : 0;      // the chunked kernel stays the default until the whole-tile kernel is faster
+        const char *e = getenv("AGPT_B200_ATTN_TILE");
+        g_bwd_tile = (e && e[0] == '0') ? 0 : 1;
         const char *w = getenv("AGPT_B200_BWD_WARPS");
-        g_bwd_warps = w ? atoi(w) : 6;
+        g_bwd_warps = w ? atoi(w) : 4;
         const char *d = getenv("AGPT_B200_BWD_DEBUG");
         g_bwd_dbg = d ? atoi(d) : 0;
-        if (g_bwd_warps != 4 && g_bwd_warps != 8) g_bwd_warps = 6;
+        if (g_bwd_warps != 3 && g_bwd_warps != 6 && g_bwd_warps != 8) g_bwd_warps = 4;
     }
     return g_bwd_tile;
 }
-extern "C" int agpt_b200_set_attn_bwd_variant(int whole_tile, int warps) {
-    if ((whole_tile != 0 && whole_tile != 1) || (warps != 4 && warps != 6 && warps != 8))
-        return agpt_set_error(AGPT_E_ARG, "set_attn_bwd_variant: whole_tile 0 or 1, warps 4, 6 or 8");
+extern "C" int agpt_b200_set_attn_variant(int whole_tile, int warps) {
+    if ((whole_tile != 0 && whole_tile != 1) || (warps != 3 && warps != 4 && warps != 6 && warps != 8))
+        return agpt_set_error(AGPT_E_ARG, "set_attn_variant: whole_tile 0 or 1, bwd_warps 4, 6 or 8");
     bwd_tile_enabled();
     g_bwd_tile = whole_tile; g_bwd_warps = warps;
     return AGPT_OK;
 }
 static inline int bwd_tile_maxk(const agpt_plan *p) { return ((p->max_depth - 1 + 64) + 15) & ~15; }
 
-template <int HD, int NW>
-static int launch_bwd_tile(const agpt_plan *p, const float *q, const void *k, const void *v, const float *o, const float *lse,
-                           const float *dout, float *dq, float *dk, float *dv, float *pk, float *pv, int H, float scale,
-                           cudaStream_t st, int tile0, int ntiles) {
+static int launch_fwd_tile(const agpt_plan *p, const float *q, const void *k, const void *v, float *out, float *lse, int H,
+                           float scale, cudaStream_t st, int tile0, int ntiles) {
     static size_t granted[AGPT_MAX_DEVICES];
     const int maxk = bwd_tile_maxk(p);
-    const size_t smem = bwd_tile_smem_bytes<HD>(maxk);
-    int rc = allow_dynamic_smem(attn_bwd_tile_kernel<HD, NW>, smem, granted);
+    const size_t smem = fwd_tile_smem_bytes(maxk);
+    int rc = allow_dynamic_smem(attn_fwd_tile_kernel<5>, smem, granted);
     if (rc) return rc;
     dim3 grid((unsigned)ntiles, (unsigned)H);
-    attn_bwd_tile_kernel<HD, NW><<<grid, NW * 32, smem, st>>>(q, (const float *)k, (const float *)v, o, lse, dout, dq, dk, dv, pk, pv,
+    attn_fwd_tile_kernel<5><<<grid, 128, smem, st>>>(q, (const float *)k, (const float *)v, out, lse, p->d_sub_end, p->d_chain_off,
+                                                     p->d_chain_ids, p->d_chain_end, (int)p->n, H, scale, tile0, maxk);
+    return launch_status("attn_fwd_tile");
+}
+
+template <int HD, typename KVT>
+static int launch_fwd_mma(const agpt_plan *p, const float *q, const void *k, const void *v, float *out, float *lse, int H,
+                          float scale, cudaStream_t st, int tile0, int ntiles) {
+    dim3 grid((unsigned)ntiles, (unsigned)H);
+    const size_t smem = fwd_mma_smem_bytes<HD>();
+    CUDA_TRY(cudaFuncSetAttribute(attn_fwd_mma_kernel<HD, KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attn_fwd_mma_kernel<HD, KVT><<<grid, 128, smem, st>>>(q, (const KVT *)k, (const KVT *)v, out, lse, p->d_sub_end,
+                                                       p->d_chain_off, p->d_chain_ids, p->d_chain_end, (int)p->n, H, scale, tile0);
+    return launch_status("attn_fwd_mma");
+}
+
+static int fwd_dispatch(const agpt_plan *p, const float *q, const void *k, const void *v, int kv_dtype, float *out,
+                        float *lse, int H, int head_dim, float scale, cudaStream_t st, int tile0, int ntiles) {
+    if (attn_impl() == 1 && p->tile_m == 64 && kv_dtype == AGPT_KV_F32 && head_dim == 32 && bwd_tile_enabled() &&
+        bwd_tile_smem_bytes(bwd_tile_maxk(p)) <= BWD_TILE_SMEM_LIMIT)
+        return launch_fwd_tile(p, q, k, v, out, lse, H, scale, st, tile0, ntiles);
+    if (attn_impl() == 1 && p->tile_m == 64 && p->max_depth + 64 <= MAXKEYS) {
+        const bool bf = kv_dtype == AGPT_KV_BF16;
+        switch (head_dim) {
+            case 16: return bf ? launch_fwd_mma<16, __nv_bfloat16>(p, q, k, v, out, lse, H, scale, st, tile0, ntiles) : launch_fwd_mma<16, float>(p, q, k, v, out, lse, H, scale, st, tile0, ntiles);
+            case 32: return bf ? launch_fwd_mma<32, __nv_bfloat16>(p, q, k, v, out, lse, H, scale, st, tile0, ntiles) : launch_fwd_mma<32, float>(p, q, k, v, out, lse, H, scale, st, tile0, ntiles);
+            case 64: return bf ? launch_fwd_mma<64, __nv_bfloat16>(p, q, k, v, out, lse, H, scale, st, tile0, ntiles) : launch_fwd_mma<64, float>(p, q, k, v, out, lse, H, scale, st, tile0, ntiles);
+        }
+    }
+    DISPATCH_HD_M_KV(launch_fwd, p, q, k, v, out, lse, H, scale, st, tile0, ntiles);
+}
+
+template <int HD, typename KVT>
+static int launch_bwd_mma(const agpt_plan *p, const float *q, const void *k, const void *v, const float *o, const float *lse,
+                          const float *dout, float *dq, float *dk, float *dv, float *pk, float *pv, int H, float scale,
+                          cudaStream_t st, int tile0, int ntiles, BwdMask gmask) {
+    dim3 grid((unsigned)ntiles, (unsigned)H);
+    size_t smem = sizeof(BwdMmaSmem<HD, KVT>);
+    CUDA_TRY(cudaFuncSetAttribute(attn_bwd_mma_kernel<HD, KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attn_bwd_mma_kernel<HD, KVT><<<grid, 128, smem, st>>>(q, (const KVT *)k, (const KVT *)v, o, lse, dout, dq, dk, dv, pk, pv,
+                                                          p->d_sub_end, p->d_chain_off, p->d_chain_ids, p->d_chain_end, (int)p->n, H,
+                                                          scale, tile0, gmask);
+    return launch_status("attn_bwd_mma");
+}
+
+template <int NW, int MINB>
+static int launch_bwd_tile(const agpt_plan *p, const float *q, const void *k, const void *v, const float *o, const float *lse,
+                           const float *dout, float *dq, float *dk, float *dv, float *pk, float *pv, int H, float scale,
+                           cudaStream_t st, int tile0, int ntiles, BwdMask gmask) {
+    static size_t granted[AGPT_MAX_DEVICES];
+    const int maxk = bwd_tile_maxk(p);
+    const size_t smem = bwd_tile_smem_bytes(maxk);
+    int rc = allow_dynamic_smem(attn_bwd_tile_kernel<NW, MINB>, smem, granted);
+    if (rc) return rc;
+    dim3 grid((unsigned)ntiles, (unsigned)H);
+    attn_bwd_tile_kernel<NW, MINB><<<grid, NW * 32, smem, st>>>(q, (const float *)k, (const float *)v, o, lse, dout, dq, dk, dv, pk, pv,
                                                              p->d_sub_end, p->d_chain_off, p->d_chain_ids, p->d_chain_end, (int)p->n,
-                                                             H, scale, tile0, maxk, g_bwd_dbg);
+                                                             H, scale, tile0, maxk, g_bwd_dbg, gmask);
     return launch_status("attn_bwd_tile");
 }
 
-template <int HD>
 static int launch_bwd_tile_w(const agpt_plan *p, const float *q, const void *k, const void *v, const float *o, const float *lse,
                              const float *dout, float *dq, float *dk, float *dv, float *pk, float *pv, int H, float scale,
-                             cudaStream_t st, int tile0, int ntiles) {
+                             cudaStream_t st, int tile0, int ntiles, BwdMask gmask) {
     switch (g_bwd_warps) {
-        case 4: return launch_bwd_tile<HD, 4>(p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles);
-        case 8: return launch_bwd_tile<HD, 8>(p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles);
-        default: return launch_bwd_tile<HD, 6>(p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles);
+        case 3: return launch_bwd_tile<4, 3>(p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles, gmask);
+        case 6: return launch_bwd_tile<6, 3>(p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles, gmask);
+        case 8: return launch_bwd_tile<8, 2>(p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles, gmask);
+        default: return launch_bwd_tile<4, 4>(p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles, gmask);
     }
 }
 
 static int bwd_dispatch(const agpt_plan *p, const float *q, const void *k, const void *v, int kv_dtype, const float *o,
                         const float *lse, const float *dout, float *dq, float *dk, float *dv, float *pk, float *pv, int H,
-                        int head_dim, float scale, cudaStream_t st, int tile0, int ntiles) {
+                        int head_dim, float scale, cudaStream_t st, int tile0, int ntiles, BwdMask gmask = BwdMask{AGPT_GRAD_FULL, nullptr}) {
     if (attn_impl() == 1 && p->tile_m == 64 && kv_dtype == AGPT_KV_F32 && bwd_tile_enabled()) {
-        const int maxk = bwd_tile_maxk(p);
-        if (head_dim == 16 && bwd_tile_smem_bytes<16>(maxk) <= BWD_TILE_SMEM_LIMIT)
-            return launch_bwd_tile_w<16>(p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles);
-        if (head_dim == 32 && bwd_tile_smem_bytes<32>(maxk) <= BWD_TILE_SMEM_LIMIT)
-            return launch_bwd_tile_w<32>(p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles);
+        if (head_dim == 32 && bwd_tile_smem_bytes(bwd_tile_maxk(p)) <= BWD_TILE_SMEM_LIMIT)
+            return launch_bwd_tile_w(p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles, gmask);
     }
     if (attn_impl() == 1 && p->tile_m == 64 && p->max_depth + 64 <= MAXKEYS) {
         const bool bf = kv_dtype == AGPT_KV_BF16;
-#define BWD_MMA_ARGS p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles
+#define BWD_MMA_ARGS p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles, gmask
         switch (head_dim) {
             case 16: return bf ? launch_bwd_mma<16, __nv_bfloat16>(BWD_MMA_ARGS) : launch_bwd_mma<16, float>(BWD_MMA_ARGS);
             case 32: return bf ? launch_bwd_mma<32, __nv_bfloat16>(BWD_MMA_ARGS) : launch_bwd_mma<32, float>(BWD_MMA_ARGS);
@@ -1420,7 +1784,7 @@ static int bwd_dispatch(const agpt_plan *p, const float *q, const void *k, const
         }
 #undef BWD_MMA_ARGS
     }
-    DISPATCH_HD_M_KV(launch_bwd, p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles);
+    DISPATCH_HD_M_KV(launch_bwd, p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles, gmask);
 }
 
 extern "C" int agpt_b200_attn_fwd(const agpt_plan *p, const float *d_q, const void *d_k, const void *d_v, int kv_dtype,
@@ -1460,15 +1824,19 @@ static int run_reduce(const agpt_plan *p, float *pk, float *pv, float *segk, flo
     return run_reduce_range(p, pk, pv, segk, segv, dk, dv, D, st, 0, (int64_t)p->item_node.size(), true);
 }
 
-extern "C" int agpt_b200_attn_bwd(const agpt_plan *p, const float *d_q, const void *d_k, const void *d_v, int kv_dtype,
-                                  const float *d_out, const float *d_lse, const float *d_dout, float *d_dq, float *d_dk,
-                                  float *d_dv, void *d_workspace, int64_t workspace_bytes, int n_heads, int head_dim,
-                                  float scale, void *stream) {
+extern "C" int agpt_b200_attn_bwd_mode(const agpt_plan *p, const float *d_q, const void *d_k, const void *d_v, int kv_dtype,
+                                       const float *d_out, const float *d_lse, const float *d_dout, float *d_dq, float *d_dk,
+                                       float *d_dv, void *d_workspace, int64_t workspace_bytes, int n_heads, int head_dim,
+                                       float scale, int grad_mode, const int32_t *d_edge_first, void *stream) {
     int rc = check_common(p, n_heads, head_dim, "attn_bwd");
     if (rc) return rc;
     if (!d_q || !d_k || !d_v || !d_out || !d_lse || !d_dout || !d_dq || !d_dk || !d_dv || !d_workspace)
         return agpt_set_error(AGPT_E_ARG, "attn_bwd: null buffer");
     if (kv_dtype != AGPT_KV_F32 && kv_dtype != AGPT_KV_BF16) return agpt_set_error(AGPT_E_ARG, "attn_bwd: bad kv_dtype");
+    if (grad_mode != AGPT_GRAD_FULL && grad_mode != AGPT_GRAD_LOCAL_DEPTH && grad_mode != AGPT_GRAD_OWN_EDGE)
+        return agpt_set_error(AGPT_E_ARG, "attn_bwd: grad_mode %d unknown", grad_mode);
+    if (grad_mode == AGPT_GRAD_OWN_EDGE && !d_edge_first)
+        return agpt_set_error(AGPT_E_ARG, "attn_bwd: the own-edge mode needs the edge_first array");
     const int D = n_heads * head_dim;
     int64_t need = agpt_b200_attn_bwd_workspace_bytes(p, D);
     if (workspace_bytes < need)
@@ -1476,9 +1844,17 @@ extern "C" int agpt_b200_attn_bwd(const agpt_plan *p, const float *d_q, const vo
     const int64_t rows = (int64_t)p->chain_ids.size();
     float *pk = (float *)d_workspace, *pv = pk + rows * D, *segk = pv + rows * D, *segv = segk + p->n_multi_items * D;
     rc = bwd_dispatch(p, d_q, d_k, d_v, kv_dtype, d_out, d_lse, d_dout, d_dq, d_dk, d_dv, pk, pv, n_heads, head_dim, scale,
-                      (cudaStream_t)stream, 0, (int)p->n_tiles);
+                      (cudaStream_t)stream, 0, (int)p->n_tiles, BwdMask{grad_mode, d_edge_first});
     if (rc) return rc;
     return run_reduce(p, pk, pv, segk, segv, d_dk, d_dv, D, (cudaStream_t)stream);
+}
+
+extern "C" int agpt_b200_attn_bwd(const agpt_plan *p, const float *d_q, const void *d_k, const void *d_v, int kv_dtype,
+                                  const float *d_out, const float *d_lse, const float *d_dout, float *d_dq, float *d_dk,
+                                  float *d_dv, void *d_workspace, int64_t workspace_bytes, int n_heads, int head_dim,
+                                  float scale, void *stream) {
+    return agpt_b200_attn_bwd_mode(p, d_q, d_k, d_v, kv_dtype, d_out, d_lse, d_dout, d_dq, d_dk, d_dv, d_workspace, workspace_bytes,
+                                   n_heads, head_dim, scale, AGPT_GRAD_FULL, nullptr, stream);
 }
 
 // --------------------------------------------------------------------------------------

@@ -58,6 +58,7 @@ class LaunchGroup:
         counted = np.ones(rid.size, bool) if trained is None else trained[starts]
         mw = (A.mass_weights_by_unit(edge_mass[rid], np.diff(qoff), unit_of_row[starts], counted, self.n_units, mass_mode)
               if mass_mode != "off" else None)
+        self.edge_first = t(A.edge_first_positions(radix_of))    # for the own-edge gradient mode
         self.trained = None if trained is None else t(trained.astype(np.float32))
         self.mass_w = None if mw is None else t(mw)
         self.n_trained_rows = self.n if trained is None else int(trained.sum())
@@ -206,7 +207,7 @@ def _attention_function():
         """RoPE + trie-scoped attention; backward returns gradients w.r.t. the pre-RoPE q and k."""
 
         @staticmethod
-        def forward(ctx, q, k, v, group, cos, sin, n_heads, bf16_store):
+        def forward(ctx, q, k, v, group, cos, sin, n_heads, bf16_store, grad_mode="full"):
             # q and k are rotated in place: they are fresh projection outputs that nothing else reads or saves
             q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
             A.rope_(q, group.pos, cos, sin, n_heads)
@@ -214,16 +215,17 @@ def _attention_function():
             ks, vs = (A.kv_store_write_bf16(k), A.kv_store_write_bf16(v)) if bf16_store else (k, v)
             out, lse = A.attn_forward(group.plan, q, ks, vs, n_heads)
             ctx.save_for_backward(q, ks, vs, out, lse)
-            ctx.group, ctx.cos, ctx.sin, ctx.n_heads = group, cos, sin, n_heads
+            ctx.group, ctx.cos, ctx.sin, ctx.n_heads, ctx.grad_mode = group, cos, sin, n_heads, grad_mode
             return out
 
         @staticmethod
         def backward(ctx, dout):
             q, ks, vs, out, lse = ctx.saved_tensors
-            dq, dk, dv = A.attn_backward(ctx.group.plan, q, ks, vs, out, lse, dout.contiguous(), ctx.n_heads)
+            dq, dk, dv = A.attn_backward(ctx.group.plan, q, ks, vs, out, lse, dout.contiguous(), ctx.n_heads,
+                                         grad_mode=ctx.grad_mode, edge_first=ctx.group.edge_first)
             A.rope_(dq, ctx.group.pos, ctx.cos, ctx.sin, ctx.n_heads, inverse=True)
             A.rope_(dk, ctx.group.pos, ctx.cos, ctx.sin, ctx.n_heads, inverse=True)
-            return dq, dk, dv, None, None, None, None, None
+            return dq, dk, dv, None, None, None, None, None, None
 
     return TrieAttention
 
@@ -261,6 +263,9 @@ class TrieWalkModel:
         self.linear = _linear_function()
         self.dense_impl = "tensor"       # "tensor": the library's 3xTF32 GEMM; "torch": torch.addmm (cuBLAS float32)
         self.ffn_recompute = False       # True: recompute the d_ff-wide activations in the backward instead of keeping them
+        # which attention pairs feed dK/dV: "full" (persistent accumulators, src/agpt/incremental_backward.cr), "local_depth"
+        # (the Crystal walker, src/agpt/trie_walk_trainer.cr:189) or "own_edge" (the CUDA trainer, src/cuda/agpt_train.cu:5016-5020)
+        self.grad_mode = "full"
 
     def parameters(self):
         return list(self.params.values())
@@ -302,12 +307,22 @@ class TrieWalkModel:
             q = lin(x1, g("wq.w"), g("wq.b")[0])
             k = lin(x1, g("wk.w"), g("wk.b")[0])
             v = lin(x1, g("wv.w"), g("wv.b")[0])
-            a = self.attn.apply(q, k, v, group, self.cos, self.sin, m.n_heads, bf16_store)
+            a = self.attn.apply(q, k, v, group, self.cos, self.sin, m.n_heads, bf16_store, self.grad_mode)
             x = lin(a, g("wo.w"), g("wo.b")[0], residual=x)
             args = (x, g("ln2.gamma")[0], g("ln2.beta")[0], g("l1.w"), g("l1.b")[0], g("l2.w"), g("l2.b")[0])
             x = checkpoint(ffn, *args, use_reentrant=False) if self.ffn_recompute else ffn(*args)
         xf = ln(x, P["final.gamma"][0], P["final.beta"][0])
-        return lin(xf, P["out.w"], P["out.b"][0])
+        w, b = P["out.w"], P["out.b"][0]
+        pad = (-m.vocab) % 4
+        if pad and self.dense_impl == "tensor":
+            # A vocabulary that is not a multiple of 4 (65 symbols) would leave rows off a 16-byte boundary, which the
+            # library GEMM does not take.  The projection is padded to the next multiple of 4: zero weight columns and a
+            # bias of -1e30 there, so the extra logits have probability exactly 0, contribute nothing to any loss and
+            # receive a zero gradient; the padding is differentiable (its backward is a slice), so out.w and out.b get
+            # their gradients as before.
+            w = torch.nn.functional.pad(w, (0, pad))
+            b = torch.cat([b, torch.full((pad,), -1e30, dtype=b.dtype, device=b.device)])
+        return lin(xf, w, b)
 
     def group_step(self, group: LaunchGroup, counts, entropy_lambda=0.0, intermediate_weight=1.0, ce_only=False,
                    bf16_store=False, sync=True):
@@ -318,6 +333,10 @@ class TrieWalkModel:
         import torch
         logits = self.logits(group, bf16_store).contiguous()
         c_off, c_tok, c_val = counts
+        if logits.shape[1] != self.cfg.vocab:
+            # padded vocabulary: the entropy weight 1 + lambda H / ln V (src/cuda/agpt_train.cu:2147-2160) is taken with the
+            # true V, so lambda is rescaled by ln(padded V) / ln(V) for the kernel, which divides by ln of the row width
+            entropy_lambda = entropy_lambda * float(np.log(logits.shape[1]) / np.log(self.cfg.vocab))
         loss, dlogits = A.loss_per_query(logits.detach(), group.q2n, group.qoff, group.rid, group.tokens32, c_off, c_tok,
                                          c_val, group.mass_w, entropy_lambda, intermediate_weight, ce_only)
         if group.trained is not None:               # context rows carry no loss
@@ -495,6 +514,8 @@ def main(argv=None):
     ap.add_argument("--ce-only", action="store_true")
     ap.add_argument("--no-accumulate", action="store_true")
     ap.add_argument("--bf16-kv", action="store_true")
+    ap.add_argument("--grad-mode", default="full", choices=["full", "local_depth", "own_edge"],
+                    help="attention pairs that feed dK/dV: every descendant (default), the node's own query, or the queries on the key's radix edge")
     ap.add_argument("--group-rows", type=int, default=1_000_000)
     ap.add_argument("--ffn-recompute", action="store_true", help="recompute the FFN activations in the backward (less memory)")
     ap.add_argument("--lightning-sampler", default=None, choices=["l1", "l2", "l3", "l4"],
@@ -532,6 +553,7 @@ def main(argv=None):
     counts = [torch.from_numpy(np.ascontiguousarray(c)).to(dev) for c in (trie.cnt_off.astype(np.int32), trie.cnt_tok, trie.cnt_val)]
     model = TrieWalkModel(mf, dev)
     model.ffn_recompute = args.ffn_recompute
+    model.grad_mode = args.grad_mode
     opt = make_optimizer(args.optimizer, model, args.lr, args.rmsprop_beta, weight_decay=args.weight_decay,
                          clip_norm=args.grad_clip_norm)
     n_sub = int((trie.parent[1:] == 0).sum())

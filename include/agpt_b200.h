@@ -112,6 +112,14 @@ int agpt_b200_synth_markov_corpus_repeats(int64_t n, int vocab, int order, uint6
 int64_t agpt_b200_synth_tree(int64_t max_nodes, int max_depth, int root_children, double p_stop,
                              int max_children, int64_t level_cap, uint64_t seed, int32_t *parent_out);
 
+/* Per-query mass weights of one launch: w = f(edge_mass) / mean over the counted queries, f = 1, log(1 + m), sqrt(m)
+ * or m for mode 0..3 (off, log, sqrt, linear) -- the host loop of src/cuda/agpt_train.cu:4608-4637 with the mean taken
+ * inside each unit (unit_of_node, NULL = one unit), so that weights do not depend on how units are packed into
+ * launches.  One entry per loss node; a node with counted[i] == 0 (a context row) gets a weight but does not enter
+ * the mean (counted NULL = all counted).  out_per_query holds sum(edge_len) floats, node by node. */
+int agpt_b200_mass_weights(const int32_t *edge_mass, const int32_t *edge_len, const int32_t *unit_of_node,
+                           const uint8_t *counted, int64_t n_nodes, int64_t n_units, int mode, float *out_per_query);
+
 /* ---- radix trie: build, on-disk directory format, char-position tree ---- */
 
 typedef struct agpt_trie agpt_trie;
@@ -141,6 +149,14 @@ int agpt_b200_trie_load_dir(const char *dir, agpt_trie **out);
  * + manifest.bin, byte-identical to src/agpt/streaming_radix_builder.cr:245-343, :388-451. */
 int agpt_b200_trie_save_dir(const agpt_trie *t, const char *dir, int per_subtree, int32_t corpus_tokens,
                             int32_t vocab, uint64_t corpus_hash, const char *tokenizer_tag);
+/* Replaces load_manifest and load_subtree (src/cuda/agpt_train.cu:431-493, :495-669): manifest.bin lists the
+ * per-subtree files (key, radix nodes, edge chars, deepest endpoint; returns their number, fills at most cap entries);
+ * a subtree file becomes a trie of its own with local ids (0 = root, records 1..n in file order, char positions in
+ * file order); a parent that is the virtual root or is not in the file (the depth-1 node above a bigram subtree)
+ * becomes the local root. */
+int64_t agpt_b200_trie_manifest(const char *dir, int64_t cap, int32_t *keys, int32_t *n_nodes, int64_t *edge_chars,
+                                int32_t *max_endpoint_depth);
+int agpt_b200_trie_load_subtree(const char *dir, int32_t subtree_key, agpt_trie **out);
 int agpt_b200_trie_info(const agpt_trie *t, agpt_trie_info *out);
 /* The same trie (identical arrays, node for node) built from a suffix order: sa[0 .. n-2] are the start positions
  * 0 .. n-2 ordered by their first max_depth + 1 tokens (a position past the end of the corpus orders before every
@@ -357,18 +373,38 @@ int agpt_b200_attn_bwd(const agpt_plan *p, const float *d_q, const void *d_k, co
                        float *d_dv, void *d_workspace, int64_t workspace_bytes, int n_heads, int head_dim,
                        float scale, void *stream);
 
+/* agpt_b200_attn_bwd with a choice of which attention pairs feed dK/dV; dQ always takes every attended key.  The
+ * reference has three behaviours and this entry point reproduces each:
+ *   AGPT_GRAD_FULL         a node's dK/dV sum over the node itself and all its descendants (persistent
+ *                          accumulators: src/agpt/incremental_backward.cr:101-147 + src/agpt/node_state.cr:58-74);
+ *   AGPT_GRAD_LOCAL_DEPTH  only the node's own query (the accumulators are dropped after each depth and subtrie:
+ *                          src/agpt/trie_walk_trainer.cr:189);
+ *   AGPT_GRAD_OWN_EDGE     the queries on the key's own radix edge (the ancestor part of the packed dK/dV is dropped:
+ *                          src/cuda/agpt_train.cu:5016-5020).  d_edge_first [n] int32: for every position, the
+ *                          depth-first position of the first char of its radix edge (ignored by the other modes). */
+#define AGPT_GRAD_FULL 0
+#define AGPT_GRAD_LOCAL_DEPTH 1
+#define AGPT_GRAD_OWN_EDGE 2
+int agpt_b200_attn_bwd_mode(const agpt_plan *p, const float *d_q, const void *d_k, const void *d_v, int kv_dtype,
+                            const float *d_out, const float *d_lse, const float *d_dout, float *d_dq, float *d_dk,
+                            float *d_dv, void *d_workspace, int64_t workspace_bytes, int n_heads, int head_dim,
+                            float scale, int grad_mode, const int32_t *d_edge_first, void *stream);
+
 /* Selects the kernel family behind agpt_b200_attn_fwd/_bwd: 1 = tensor cores (mma.sync TF32 with error
  * compensation, tiles of 64; the default), 0 = FP32 FMA.  Both meet the same parity tolerances; the switch
  * exists for A/B measurement.  Also read once from the environment variable AGPT_B200_ATTN_IMPL. */
 int agpt_b200_set_attn_impl(int impl);
 
-/* Selects the tensor-core backward kernel for a float32 KV store and head_dim 16 or 32: whole_tile 1 (default) = the
- * kernel that keeps the tile's Q, dO and all its key rows in shared memory, pre-split into TF32 hi/lo parts, and
- * lets every warp run independent row and key items (used whenever two such blocks fit one SM, i.e. up to a few
- * hundred keys per tile; deeper plans take the chunked kernel); 0 = always the chunked kernel.  warps = 4, 6 or 8
- * warps per block of the whole-tile kernel (default 6).  Same results within the parity tolerance either way; the
- * switch exists for A/B measurement.  Also read once from AGPT_B200_BWD_TILE and AGPT_B200_BWD_WARPS. */
-int agpt_b200_set_attn_bwd_variant(int whole_tile, int warps);
+/* Selects between the two tensor-core kernel pairs for a float32 KV store and head_dim 32.  whole_tile 1 (default):
+ * forward and backward keep the tile's Q (and dO) rows and all its key rows in shared memory, converted once to
+ * split half precision (x * 2^e = hi + lo, fp16 each, e per tile, head and tensor; three m16n8k16 products give the
+ * accuracy of three TF32 products), every fragment one ldmatrix, and the backward's warps run independent row and
+ * key items with no barrier in their loops.  Used whenever four blocks of the backward fit one SM (about 150 keys
+ * per tile, i.e. depth <= ~90); deeper plans, other head sizes and a bf16 store take the chunked TF32 kernels.
+ * whole_tile 0: always the chunked kernels.  bwd_warps = 4 (default), 6 or 8 warps per block of the whole-tile
+ * backward.  Same results within the parity tolerance either way; the switch exists for A/B measurement.  Also read
+ * once from AGPT_B200_ATTN_TILE and AGPT_B200_BWD_WARPS. */
+int agpt_b200_set_attn_variant(int whole_tile, int bwd_warps);
 
 /* No counterpart in the reference.  agpt_b200_attn_bwd for callers that cannot allocate device memory
  * when the backward runs -- a runtime that claimed the whole GPU at start-up and sub-allocates from its own

@@ -528,12 +528,16 @@ ORC_API int orc_attn_fwd_grouped(int32_t n, const int32_t *parent, int32_t n_gro
 /* node is reached: dk_cur = ds_last*q + accum, dv_cur = w_last*dO + accum.    */
 /* Gradients are in post-RoPE space; the caller applies the inverse rotation. */
 /* With accumulate_ancestors == 0 the ancestor rows are dropped (the          */
-/* local-depth behaviour of src/agpt/trie_walk_trainer.cr:189).               */
+/* local-depth behaviour of src/agpt/trie_walk_trainer.cr:189); with 2 only   */
+/* the ancestors on the node's own radix edge are kept, edge_id[a] ==         */
+/* edge_id[i] (the CUDA trainer extracts the own-edge part of the packed      */
+/* dK/dV and drops the ancestor part, src/cuda/agpt_train.cu:5016-5020).      */
 /* ------------------------------------------------------------------------- */
 static int attn_bwd_range(int32_t lo, int32_t hi, int h0, int h1, const int32_t *parent, int H, int hd,
                           const float *q, const float *k, const float *v,
                           const float *weights, const int64_t *w_off, const float *d_out,
-                          float *dq, float *dk, float *dv, int max_depth, int accumulate_ancestors) {
+                          float *dq, float *dk, float *dv, int max_depth, int accumulate_ancestors,
+                          const int32_t *edge_id) {
     int D = H * hd;
     float scale = (float)(1.0 / sqrt((double)hd));
     int32_t *chain = (int32_t *)malloc((size_t)(max_depth + 1) * 4);
@@ -569,7 +573,7 @@ static int attn_bwd_range(int32_t lo, int32_t hi, int h0, int h1, const int32_t 
                         dkc[j] = ds[p] * qh[j] + dkc[j];
                         dvc[j] = w[p] * go[j] + dvc[j];
                     }
-                } else if (accumulate_ancestors) {
+                } else if (accumulate_ancestors == 1 || (accumulate_ancestors == 2 && edge_id[chain[p]] == edge_id[i])) {
                     float *dka = dk + (int64_t)chain[p] * D + h * hd, *dva = dv + (int64_t)chain[p] * D + h * hd;
                     for (int j = 0; j < hd; j++) { dka[j] += ds[p] * qh[j]; dva[j] += w[p] * go[j]; }
                 }
@@ -588,19 +592,20 @@ ORC_API int orc_attn_bwd(int32_t n, const int32_t *parent, int H, int hd,
                          const float *q, const float *k, const float *v,
                          const float *weights, const int64_t *w_off, const float *d_out,
                          float *dq, float *dk, float *dv, int max_depth, int accumulate_ancestors,
-                         int32_t n_units, const int32_t *unit_off) {
+                         int32_t n_units, const int32_t *unit_off, const int32_t *edge_id) {
     int D = H * hd;
     memset(dk, 0, (size_t)n * D * 4);      /* dk/dv double as the per-node accumulators */
     memset(dv, 0, (size_t)n * D * 4);
     int32_t one[2] = {0, n};
     if (!unit_off) { unit_off = one; n_units = 1; }
+    if (accumulate_ancestors == 2 && !edge_id) return -1;
     int bad = 0;
     int64_t n_tasks = (int64_t)n_units * H;
 #pragma omp parallel for schedule(dynamic, 1)
     for (int64_t t = 0; t < n_tasks; t++) {
         int32_t u = (int32_t)(t / H); int h = (int)(t % H);
         if (attn_bwd_range(unit_off[u], unit_off[u + 1], h, h + 1, parent, H, hd, q, k, v, weights, w_off,
-                           d_out, dq, dk, dv, max_depth, accumulate_ancestors) != 0) bad = 1;
+                           d_out, dq, dk, dv, max_depth, accumulate_ancestors, edge_id) != 0) bad = 1;
     }
     return bad ? -1 : 0;
 }

@@ -152,6 +152,41 @@ class Radix:
         if rc != 0:
             raise OSError("orc_radix_write_dir failed")
 
+    def write_subtree_files(self, path):
+        """subtrees/radix_subtree_KKKKKK.bin and manifest.bin as the reference's builder streams them
+        (src/agpt/streaming_radix_builder.cr:257-276 header and records in emission order, :315-330 header patch and
+        manifest order, :396-408 record, :413-426 manifest): header u32 magic, i32 version 2, i32 key, i32 records,
+        i64 edge chars, i32 deepest endpoint; records with GLOBAL radix ids."""
+        import struct
+        os.makedirs(os.path.join(path, "subtrees"), exist_ok=True)
+        magic = 0x52445841
+        keys = {}
+        for r in range(1, self.radix_count):
+            keys.setdefault(int(self.subtree_key[r]), []).append(r)
+        manifest = []
+        for key, ids in keys.items():
+            body = bytearray()
+            chars, max_ep = 0, 0
+            for r in ids:
+                el = int(self.edge_len[r])
+                body += struct.pack("<4i", r, int(self.parent[r]), int(self.first_char_depth[r]), el)
+                body += np.asarray(self.edge_tok[self.edge_off[r]:self.edge_off[r] + el], "<i4").tobytes()
+                c0, c1 = int(self.cnt_off[r]), int(self.cnt_off[r + 1])
+                body += struct.pack("<2i", int(self.edge_mass[r]), c1 - c0)
+                for e in range(c0, c1):
+                    body += struct.pack("<2i", int(self.cnt_tok[e]), int(self.cnt_val[e]))
+                chars += el
+                max_ep = max(max_ep, int(self.endpoint_depth[r]))
+            with open(os.path.join(path, "subtrees", "radix_subtree_%06d.bin" % key), "wb") as f:
+                f.write(struct.pack("<I3iqi", magic, 2, key, len(ids), chars, max_ep))
+                f.write(bytes(body))
+            manifest.append((key, len(ids), chars, max_ep))
+        manifest.sort()
+        with open(os.path.join(path, "manifest.bin"), "wb") as f:
+            f.write(struct.pack("<I2i", magic, 2, len(manifest)))
+            for key, cnt, chars, max_ep in manifest:
+                f.write(struct.pack("<2iqi", key, cnt, chars, max_ep))
+
     def char_tree(self):
         """Char-position tree: parent char position of every edge char (-1 under the root),
         in the trainer's char numbering (``agpt_train.cu:832``); plus token and depth."""
@@ -250,7 +285,9 @@ def attn_fwd(parent, H, hd, q, k, v, grouped=False, save_weights=True):
     return out, w, w_off, depth
 
 
-def attn_bwd(parent, H, hd, q, k, v, w, w_off, d_out, accumulate_ancestors=True, unit_off=None):
+def attn_bwd(parent, H, hd, q, k, v, w, w_off, d_out, accumulate_ancestors=True, unit_off=None, edge_id=None):
+    """accumulate_ancestors: True / 1 = every ancestor row receives its dK/dV (persistent accumulators), False / 0 =
+    none does (local depth), 2 = only the ancestors on the node's own radix edge (edge_id[a] == edge_id[i])."""
     parent = i32(parent)
     n = parent.size
     q, k, v, d_out = f32(q), f32(k), f32(v), f32(d_out)
@@ -262,8 +299,9 @@ def attn_bwd(parent, H, hd, q, k, v, w, w_off, d_out, accumulate_ancestors=True,
     uo = i32(unit_off) if unit_off is not None else None
     rc = lib().orc_attn_bwd(C.c_int32(n), _p(parent), C.c_int(H), C.c_int(hd), _p(q), _p(k), _p(v),
                             _p(f32(w)), _p(np.ascontiguousarray(w_off, np.int64)), _p(d_out), _p(dq), _p(dk),
-                            _p(dv), C.c_int(md), C.c_int(1 if accumulate_ancestors else 0),
-                            C.c_int32(0 if uo is None else uo.size - 1), _p(uo))
+                            _p(dv), C.c_int(md), C.c_int(int(accumulate_ancestors)),
+                            C.c_int32(0 if uo is None else uo.size - 1), _p(uo),
+                            _p(i32(edge_id)) if edge_id is not None else None)
     if rc != 0:
         raise RuntimeError("oracle attention backward failed")
     return dq, dk, dv

@@ -7,6 +7,10 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+# Where the reference project is mounted, for the tests that pin counts and file bytes on its own data files; they
+# are skipped where it is absent.  AGPT_REFERENCE_ROOT overrides the default mount point.
+REFERENCE_ROOT = os.environ.get("AGPT_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
+
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")

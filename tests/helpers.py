@@ -174,3 +174,25 @@ def suffix_order_np(corpus, key_len):
         lcp[1:] += same
         alive = same
     return sa.astype(np.int32), lcp.astype(np.int32)
+
+
+def model_oracle_step(mf, parent, tokens, depth, q2n, qoff, rid, counts, mass_w, lam, iw, trained, unit_of_row, keep="all",
+                      edge_id=None):
+    """One launch group through the whole-model CPU oracle (oracle/model_oracle.py: the reference's per-node forward and
+    backward) with the oracle's loss in between and the per-unit 1 / trained-queries scaling of the gradient rows.
+    Returns (loss sum, trained queries, weight gradients, logits)."""
+    from oracle import pyoracle as O
+    from oracle.model_oracle import ModelOracle
+    hd = mf.d_model // mf.n_heads
+    cos, sin = O.rope_table(mf.seq_len, hd)
+    mo = ModelOracle(dict(mf.mats), mf.d_model, mf.n_heads, mf.n_layers, cos, sin)
+    pos = np.minimum(np.maximum(depth - 1, 0), mf.seq_len - 1)
+    logits = mo.forward(np.asarray(parent), np.asarray(tokens), pos)
+    loss, dlog = O.loss_per_query(logits, q2n, qoff, rid, tokens, *counts, mass_w, lam, iw)
+    if trained is not None:
+        loss = loss * trained
+        dlog = dlog * trained[:, None]
+    per_unit = np.bincount(unit_of_row, weights=(loss > 0).astype(np.float64), minlength=int(unit_of_row.max()) + 1)
+    scale = np.where(per_unit > 0, 1.0 / np.maximum(per_unit, 1), 0.0)[unit_of_row]
+    grads = mo.backward((dlog.astype(np.float64) * scale[:, None]).astype(np.float32), keep, edge_id)
+    return float(loss[loss > 0].sum()), int((loss > 0).sum()), grads, logits

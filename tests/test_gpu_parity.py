@@ -16,16 +16,16 @@ from tests.helpers import TOL_BF16, TOL_F32, chain_tree, random_qkv, random_tree
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(autouse=True, params=[(1, True), (1, False), (0, True)], ids=["tensor", "tensor-chunked-bwd", "fma"])
+@pytest.fixture(autouse=True, params=[(1, True), (1, False), (0, True)], ids=["tensor", "tensor-chunked", "fma"])
 def attn_impl(request):
     """Every test in this file runs against both kernel families of the native attention entry points, the tensor-core
-    family with either of its two backward kernels (whole tile resident / chunked)."""
+    family with either of its two kernel pairs (whole tile resident / chunked)."""
     impl, whole_tile = request.param
     A.set_attn_impl(impl)
-    A.set_attn_bwd_variant(whole_tile, 6)
+    A.set_attn_variant(whole_tile, 4)
     yield impl
     A.set_attn_impl(1)
-    A.set_attn_bwd_variant(True, 6)
+    A.set_attn_variant(True, 4)
 
 
 def _dev(x, cuda):
@@ -551,3 +551,35 @@ def test_trie_build_gpu_equals_host_builder(cuda, n, vocab, order, depth):
         want = A.RadixTrie.build(corpus, depth, subtree_level=level, prune_min_mass=mass, prune_min_depth=mdepth)
         got = A.RadixTrie.build_gpu(corpus, depth, subtree_level=level, prune_min_mass=mass, prune_min_depth=mdepth)
         assert_same_trie(got, want)
+
+
+@pytest.mark.parametrize("mode,acc", [("local_depth", 0), ("own_edge", 2), ("full", 1)])
+@pytest.mark.parametrize("hd,tile", [(32, 64), (16, 64), (64, 128)])
+def test_gradient_modes_match_oracle(cuda, mode, acc, hd, tile):
+    """The reference's three dK/dV behaviours (persistent accumulators; accumulators dropped per depth,
+    src/agpt/trie_walk_trainer.cr:189; own radix edge only, src/cuda/agpt_train.cu:5016-5020) on a radix trie whose
+    edges span tile boundaries; dQ is the same in all of them."""
+    import torch
+    corpus = A.synth_markov_corpus(4000, 12, 2, 4)
+    trie = A.RadixTrie.build(corpus, 24)
+    parent, token, depth, radix_of = trie.char_tree()
+    n, H = parent.size, 2
+    q, k, v, go = random_qkv(n, H * hd, 91)
+    out, w, w_off, _ = O.attn_fwd(parent, H, hd, q, k, v, grouped=True)
+    ref_dq, ref_dk, ref_dv = O.attn_bwd(parent, H, hd, q, k, v, w, w_off, go, accumulate_ancestors=acc, edge_id=radix_of)
+    full_dq = O.attn_bwd(parent, H, hd, q, k, v, w, w_off, go)[0]
+    assert np.array_equal(ref_dq, full_dq)
+    plan = A.WalkerPlan(parent, tile, 0)
+    order, inv = plan.dfs_to_node.astype(np.int64), plan.node_to_dfs.astype(np.int64)
+    tq, tk, tv, tg = [_dev(x[order], cuda) for x in (q, k, v, go)]
+    ef = torch.from_numpy(A.edge_first_positions(radix_of[order])).to(cuda)
+    o, lse = A.attn_forward(plan, tq, tk, tv, H)
+    dq, dk, dv = A.attn_backward(plan, tq, tk, tv, o, lse, tg, H, grad_mode=mode, edge_first=ef)
+    torch.cuda.synchronize()
+    for got, want in zip((dq, dk, dv), (ref_dq, ref_dk, ref_dv)):
+        assert rel_err(got.cpu().numpy()[inv], want) < TOL_F32
+    if mode != "full":
+        with pytest.raises(A.AgptError):
+            A.attn_backward(plan, tq, tk, tv, o, lse, tg, H, grad_mode="own_edge")          # edge_first missing
+        with pytest.raises(A.AgptError):
+            A.attn_backward(plan, tq, tk, tv, o, lse, tg, H, grad_mode="ancestors")

@@ -91,6 +91,45 @@ def test_radix_dir_bytes_and_reload(tmp_path):
         A.RadixTrie.load_dir(str(tmp_path / "missing"))
 
 
+@pytest.mark.parametrize("level", [1, 2])
+def test_subtree_files_bytes_and_reload(tmp_path, level):
+    """subtrees/*.bin and manifest.bin byte for byte against the oracle's writer (unigram and bigram keys), and
+    each file read back as a trie of its own: local ids in file order, parents remapped (a parent outside the file
+    becomes the local root), edges, counts and char positions as the reference's load_subtree lays them out
+    (src/cuda/agpt_train.cu:495-669)."""
+    corpus = A.synth_markov_corpus(5_000, 30, 2, 7)
+    tr = A.RadixTrie.build(corpus, 9, subtree_level=level)
+    rx = O.Radix(O.Leveled(corpus, 9), level)
+    a, b = str(tmp_path / "product"), str(tmp_path / "oracle")
+    tr.save_dir(a, corpus.size, 30, A.token_hash(corpus), per_subtree=True)
+    os.makedirs(b)
+    rx.write_subtree_files(b)
+    assert filecmp.cmp(os.path.join(a, "manifest.bin"), os.path.join(b, "manifest.bin"), shallow=False)
+    names = sorted(os.listdir(os.path.join(b, "subtrees")))
+    assert names == sorted(os.listdir(os.path.join(a, "subtrees"))) and len(names) > 10
+    for f in names:
+        assert filecmp.cmp(os.path.join(a, "subtrees", f), os.path.join(b, "subtrees", f), shallow=False), f
+    keys, nodes, chars, ep = A.RadixTrie.manifest(a)
+    assert np.array_equal(keys, np.unique(tr.subtree_key[1:])) and nodes.sum() == tr.radix_count - 1
+    assert chars.sum() == tr.total_edge_chars
+    for key, nn, ch, me in zip(keys, nodes, chars, ep):
+        sub = A.RadixTrie.load_subtree(a, int(key))
+        ids = np.nonzero(tr.subtree_key == key)[0]
+        ids = ids[ids > 0]                                   # global ids in emission (= file) order
+        assert sub.radix_count == nn + 1 == ids.size + 1 and sub.total_edge_chars == ch
+        assert int(tr.endpoint_depth[ids].max()) == me
+        local = {int(g): i + 1 for i, g in enumerate(ids)}
+        assert np.array_equal(sub.parent[1:], [local.get(int(tr.parent[g]), 0) for g in ids])
+        for name in ("first_char_depth", "edge_len", "edge_mass", "endpoint_depth"):
+            assert np.array_equal(getattr(sub, name)[1:], getattr(tr, name)[ids]), name
+        assert np.array_equal(sub.edge_start[1:], np.concatenate([[0], np.cumsum(tr.edge_len[ids])[:-1]]))
+        assert np.array_equal(sub.edge_tok, np.concatenate([tr.edge_tok[tr.edge_off[g]:tr.edge_off[g + 1]] for g in ids]))
+        assert np.array_equal(sub.cnt_val, np.concatenate([tr.cnt_val[tr.cnt_off[g]:tr.cnt_off[g + 1]] for g in ids]))
+        assert np.array_equal(np.diff(sub.cnt_off)[1:], np.diff(tr.cnt_off)[ids])
+    with pytest.raises(A.AgptError):
+        A.RadixTrie.load_subtree(a, 999_999)
+
+
 def _brute_plan_check(parent, tile_m):
     plan = A.WalkerPlan(parent, tile_m, -1)
     n = parent.size

@@ -6,8 +6,9 @@ import numpy as np
 import pytest
 
 from agpt_b200 import model_file as MF
+from tests.conftest import REFERENCE_ROOT
 
-REF_MODEL = "/root/reference/data/input.model"
+REF_MODEL = os.path.join(REFERENCE_ROOT, "data", "input.model")
 
 
 def test_round_trip(tmp_path):

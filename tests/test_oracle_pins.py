@@ -13,9 +13,11 @@ import numpy as np
 import pytest
 
 from oracle import pyoracle as O
+from tests.conftest import REFERENCE_ROOT
 from tests.helpers import MemTrie, SpecModel, random_qkv, random_tree, rel_err
 
 SPEC_TOL = 1e-5   # absolute, as in the reference spec
+REF_CORPUS = os.path.join(REFERENCE_ROOT, "data", "input.txt")
 
 
 def _spec_forward(model, trie, node_ids):
@@ -226,14 +228,18 @@ def test_loss_variants_agree():
     assert np.abs(g_node[has].sum(axis=1)).max() < 1e-5
 
 
-@pytest.mark.skipif(not os.path.exists("/root/reference/data/input.txt"), reason="reference corpus not mounted")
+def _real_corpus_tokens():
+    text = open(REF_CORPUS, "rb").read().decode("utf-8")
+    vocab = {c: i for i, c in enumerate(sorted(set(text)))}
+    return np.fromiter((vocab[c] for c in text), dtype=np.int32, count=len(text))
+
+
+@pytest.mark.skipif(not os.path.exists(REF_CORPUS), reason="reference corpus not mounted")
 @pytest.mark.parametrize("depth,endpoints,chars", [(8, 845_539, 1_545_081), (16, 1_607_927, 9_313_896)])
 def test_real_corpus_trie_shape(depth, endpoints, chars):
     """Counts published for the reference's own corpus (rnd/sparsity-profile/README.md:97-101); the
     tokenizer is the sorted set of characters (src/agpt.cr:28)."""
-    text = open("/root/reference/data/input.txt", "rb").read().decode("utf-8")
-    vocab = {c: i for i, c in enumerate(sorted(set(text)))}
-    tok = np.fromiter((vocab[c] for c in text), dtype=np.int32, count=len(text))
+    tok = _real_corpus_tokens()
     lv = O.Leveled(tok, depth)
     rx = O.Radix(lv)
     assert rx.radix_count - 1 == endpoints
@@ -248,6 +254,30 @@ def test_real_corpus_trie_shape(depth, endpoints, chars):
         assert_same_trie(A.RadixTrie.from_suffix_order(tok, depth, *suffix_order_np(tok, depth + 1)), tr)
 
 
+@pytest.mark.skipif(not os.path.exists(REF_CORPUS), reason="reference corpus not mounted")
+def test_real_corpus_depth_32_anchors():
+    """What the reference's own trainer log prints for its depth-32 radix trie of the same corpus
+    (rnd/hotspot-curriculum/logs/d32-base-3SE_r1.log:5-6, :12-13, :17; rnd/sparsity-profile/README.md:97-101):
+    radix nodes and edge chars, endpoint depths, count entries, the longest edge, chars on mass-1 edges, nodes of
+    mass > 1, and the 65 root-child subtrees with their smallest and largest size.  Built with the product's level
+    builder (bit-identical to the oracle's builders at depths 8 and 16 on the same text, and on synthetic corpora)."""
+    import agpt_b200 as A
+    tr = A.RadixTrie.build(_real_corpus_tokens(), 32)
+    assert tr.radix_count - 1 == 1_666_214 and tr.total_edge_chars == 27_046_236
+    assert tr.n_depth_files == 33 and tr.cnt_val.size == 2_780_616
+    assert int(tr.edge_len[1:].max()) == 32
+    mass1 = tr.edge_mass[1:] == 1
+    assert int(tr.edge_len[1:][mass1].sum()) == 25_933_966
+    assert int((~mass1).sum()) == 552_869
+    assert int(tr.edge_len[1:][~mass1].sum()) == 1_112_270           # positions the reference's compact KV cache holds
+    root_child = np.zeros(tr.radix_count, np.int64)
+    for r in range(1, tr.radix_count):                               # ids are in breadth-first order: parents come first
+        root_child[r] = r if tr.parent[r] == 0 else root_child[tr.parent[r]]
+    sizes = np.bincount(root_child[1:])
+    sizes = sizes[sizes > 0]
+    assert sizes.size == 65 and sizes.min() == 1 and sizes.max() == 254_737 and sizes.sum() == 1_666_214
+
+
 def test_golden_vectors_reproduce():
     path = os.path.join(os.path.dirname(__file__), "golden", "attention_small.npz")
     g = np.load(path)
@@ -260,3 +290,34 @@ def test_golden_vectors_reproduce():
     loss, grad = O.loss_per_query(gl["logits"], gl["q2n"], gl["qoff"], gl["radix_ids"], gl["token_ids"], gl["cnt_off"],
                                   gl["cnt_tok"], gl["cnt_val"], gl["mass_w"], float(gl["lam"]), float(gl["iw"]), False)
     assert rel_err(loss, gl["loss"]) < 1e-6 and rel_err(grad, gl["grad"]) < 1e-6
+
+
+def test_model_oracle_agrees_with_an_independent_dense_model():
+    """The whole-model restatement (per-node forward / backward of src/agpt/incremental_forward.cr and
+    incremental_backward.cr with the ancestor accumulators) against a dense float64 autograd model that knows nothing
+    of nodes, caches or accumulators -- only an ancestor mask: logits, loss and every weight gradient."""
+    import agpt_b200 as A
+    from agpt_b200 import model_file as MF
+    from tests.helpers import model_oracle_step
+    from tests.test_trainer_gpu import _reference
+    corpus = A.synth_markov_corpus(260, 12, 2, 3)
+    trie = A.RadixTrie.build(corpus, 6)
+    parent, tokens, depth, radix_of = trie.char_tree()
+    plan = A.WalkerPlan(parent, 64, -1)
+    order = plan.dfs_to_node.astype(np.int64)
+    p_dfs, tok, dep, rof = plan.parent_dfs.copy(), tokens[order], depth[order], radix_of[order]
+    starts = np.concatenate([[True], rof[1:] != rof[:-1]])
+    q2n = (np.cumsum(starts) - 1).astype(np.int32)
+    qoff = np.concatenate([np.nonzero(starts)[0], [rof.size]]).astype(np.int32)
+    rid = rof[starts].astype(np.int32)
+    counts = (trie.cnt_off.astype(np.int32), trie.cnt_tok, trie.cnt_val)
+    mw = A.mass_weights(trie.edge_mass[rid], np.diff(qoff), "linear")
+    mf = MF.random_init(32, 2, 2, 12, 16, seed=1, std=0.2)
+    unit = np.zeros(rof.size, np.int64)
+    args = (mf, p_dfs, tok.astype(np.int32), dep, q2n, qoff, rid, counts, mw, 0.5, 0.7, None, unit)
+    rl, rq, rg, rlog = _reference(*args)
+    ol, oq, og, olog = model_oracle_step(*args)
+    assert oq == rq and abs(ol - rl) / rl < 1e-5
+    assert rel_err(olog, rlog) < 1e-5
+    for k in rg:
+        assert rel_err(og[k], rg[k], floor=1e-6) < 2e-5, k

@@ -64,12 +64,14 @@ def _reference(mf, parent, tokens, depth, q2n, qoff, rid, counts, mass_w, lam, i
     return float(loss[loss > 0].sum()), n_tr, {k: v.grad.numpy() for k, v in P.items()}, logits.detach().numpy()
 
 
-@pytest.mark.parametrize("world,bf16,unit_cap", [(1, False, None), (2, False, None), (1, True, None), (2, False, 40)])
-def test_group_step_matches_dense_reference(cuda, world, bf16, unit_cap):
+@pytest.mark.parametrize("world,bf16,unit_cap,vocab", [(1, False, None, 12), (2, False, None, 12), (1, True, None, 12), (2, False, 40, 12),
+                                                       (1, False, None, 13)])
+def test_group_step_matches_dense_reference(cuda, world, bf16, unit_cap, vocab):
+    """vocab 13: a vocabulary that is not a multiple of 4 (like the reference's 65) takes the padded logits projection."""
     import torch
-    corpus = A.synth_markov_corpus(700, 12, 2, 3)
+    corpus = A.synth_markov_corpus(700, vocab, 2, 3)
     trie = A.RadixTrie.build(corpus, 7, subtree_level=1 if world == 1 else 2)
-    mf = MF.random_init(32, 2, 2, 12, 16, seed=1, std=0.2)
+    mf = MF.random_init(32, 2, 2, vocab, 16, seed=1, std=0.2)
     counts_np = (trie.cnt_off.astype(np.int32), trie.cnt_tok, trie.cnt_val)
     counts = [torch.from_numpy(np.ascontiguousarray(c)).to(cuda) for c in counts_np]
     lam, iw = 0.5, 0.7
@@ -235,3 +237,41 @@ def test_lightning_training_runs_from_the_command_line(cuda, tmp_path):
     new = MF.load(out)
     assert all(np.isfinite(a).all() for _, a in new.mats)
     assert any(not np.array_equal(a, b) for (_, a), (_, b) in zip(mf.mats, new.mats))
+
+
+@pytest.mark.parametrize("mode,keep", [("full", "all"), ("local_depth", "none"), ("own_edge", "own_edge")])
+def test_trainer_step_matches_the_reference_model_restatement(cuda, mode, keep):
+    """One step of the trainer against the CPU restatement of the reference's own per-node model step
+    (oracle/model_oracle.py: src/agpt/incremental_forward.cr:14-217 + incremental_backward.cr:33-187 with the ancestor
+    accumulators), for each of the reference's three dK/dV behaviours: persistent accumulators, accumulators dropped
+    (src/agpt/trie_walk_trainer.cr:189) and own radix edge only (src/cuda/agpt_train.cu:5016-5020).  Loss and every
+    weight gradient within the float32 parity tolerance."""
+    import torch
+    from tests.helpers import model_oracle_step
+    corpus = A.synth_markov_corpus(420, 12, 2, 9)
+    trie = A.RadixTrie.build(corpus, 7)
+    mf = MF.random_init(32, 2, 2, 12, 16, seed=8, std=0.2)
+    counts_np = (trie.cnt_off.astype(np.int32), trie.cnt_tok, trie.cnt_val)
+    counts = [torch.from_numpy(np.ascontiguousarray(c)).to(cuda) for c in counts_np]
+    groups, total = T.build_groups(trie, 0, 1, 10_000, "linear", mf.seq_len, cuda)
+    assert len(groups) == 1
+    g = groups[0]
+    model = T.TrieWalkModel(mf, cuda)
+    model.grad_mode = mode
+    for p in model.parameters():
+        p.grad = torch.zeros_like(p)
+    ls, nq = model.group_step(g, counts, entropy_lambda=0.4, intermediate_weight=0.8)
+    # the group's rows in its own depth-first order; the radix node of each row is its edge id
+    rid = g.rid.cpu().numpy()
+    edge_id = rid[g.q2n.cpu().numpy()]
+    ol, oq, og, _ = model_oracle_step(mf, g.plan.parent_dfs.copy(), g.tokens32.cpu().numpy(), g.plan.depth.copy(), g.q2n.cpu().numpy(),
+                                      g.qoff.cpu().numpy(), rid, counts_np, g.mass_w.cpu().numpy(), 0.4, 0.8, None,
+                                      g.unit_of_row.cpu().numpy(), keep, edge_id)
+    assert nq == oq and abs(ls - ol) <= TOL_F32 * ol
+    for k, v in model.params.items():
+        assert rel_err(v.grad.cpu().numpy().astype(np.float64), og[k], floor=1e-6) < TOL_F32, k
+    if mode != "full":        # the truncated modes really differ from the full one in the K/V projections
+        full = model_oracle_step(mf, g.plan.parent_dfs.copy(), g.tokens32.cpu().numpy(), g.plan.depth.copy(), g.q2n.cpu().numpy(),
+                                 g.qoff.cpu().numpy(), rid, counts_np, g.mass_w.cpu().numpy(), 0.4, 0.8, None,
+                                 g.unit_of_row.cpu().numpy())[2]
+        assert rel_err(og["layer0.wk.w"], full["layer0.wk.w"], floor=1e-6) > 1e-2
