@@ -25,6 +25,10 @@ class TrieInfo(C.Structure):
                 ("edge_start", P32)]
 
 
+class GroupInfo(C.Structure):
+    _fields_ = [("n", i64), ("n_units", i32), ("parent", P32), ("row", P64), ("trained", C.POINTER(C.c_uint8)), ("unit_of_row", P32)]
+
+
 class PlanInfo(C.Structure):
     _fields_ = [("n", i64), ("tile_m", i32), ("n_tiles", i64), ("chain_rows", i64), ("max_depth", i32),
                 ("sum_depth", i64), ("sum_group_prefix", i64), ("n_groups", i64), ("n_reduce_items", i64),
@@ -46,6 +50,10 @@ SIGNATURES = {
     "agpt_b200_synth_markov_corpus": (C.c_int, [i64, C.c_int, C.c_int, u64, vp]),
     "agpt_b200_synth_markov_corpus_repeats": (C.c_int, [i64, C.c_int, C.c_int, u64, C.c_int, vp]),
     "agpt_b200_synth_tree": (i64, [i64, C.c_int, C.c_int, f64, C.c_int, i64, u64, vp]),
+    "agpt_b200_groups_create": (C.c_int, [vp, vp, vp, vp, i64, C.c_int, i64, C.POINTER(vp)]),
+    "agpt_b200_groups_count": (i64, [vp]),
+    "agpt_b200_groups_get": (C.c_int, [vp, i64, C.POINTER(GroupInfo)]),
+    "agpt_b200_groups_free": (None, [vp]),
     "agpt_b200_mass_weights": (C.c_int, [vp, vp, vp, vp, i64, i64, C.c_int, vp]),
     "agpt_b200_trie_build": (C.c_int, [vp, i64, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(vp)]),
     "agpt_b200_trie_load_dir": (C.c_int, [C.c_char_p, C.POINTER(vp)]),

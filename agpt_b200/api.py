@@ -13,7 +13,7 @@ import os
 
 import numpy as np
 
-from ._lib import AgptError, PlanInfo, TrieInfo, check, lib
+from ._lib import AgptError, GroupInfo, PlanInfo, TrieInfo, check, lib
 
 KV_F32, KV_BF16 = 0, 1
 
@@ -270,6 +270,28 @@ class WalkerPlan:
             self.close()
         except Exception:
             pass
+
+
+def launch_groups(plan: WalkerPlan, unit_begin, unit_end, unit_rank, rank: int, group_rows: int):
+    """This rank's units packed into launch groups (agpt_b200_groups_create).  Returns a list of
+    (local parent int32, plan position of each row int64, trained bool, unit_of_row int32)."""
+    ub = np.ascontiguousarray(unit_begin, dtype=np.int64)
+    ue = np.ascontiguousarray(unit_end, dtype=np.int64)
+    ur = None if unit_rank is None else _np_i32(unit_rank)
+    h = C.c_void_p()
+    check(lib().agpt_b200_groups_create(plan._h, _vp(ub), _vp(ue), None if ur is None else _vp(ur), ub.size, rank, int(group_rows),
+                                        C.byref(h)), "groups_create")
+    out = []
+    try:
+        for i in range(int(lib().agpt_b200_groups_count(h))):
+            info = GroupInfo()
+            check(lib().agpt_b200_groups_get(h, i, C.byref(info)), "groups_get")
+            n = int(info.n)
+            out.append((_view(info.parent, n, np.int32).copy(), _view(info.row, n, np.int64).copy(),
+                        _view(info.trained, n, np.uint8).astype(bool), _view(info.unit_of_row, n, np.int32).copy()))
+    finally:
+        lib().agpt_b200_groups_free(h)
+    return out
 
 
 def partition_lpt(unit_weight, n_ranks: int) -> np.ndarray:

@@ -825,6 +825,67 @@ extern "C" int agpt_b200_plan_info(const agpt_plan *p, agpt_plan_info *o) {
     return AGPT_OK;
 }
 
+// --------------------------------------------------------------------------------------
+// launch groups: this rank's units packed, in depth-first order, into forests of at most group_rows rows
+// (the chunker of src/cuda/agpt_train.cu:4424-4443, on units instead of radix-node counts)
+// --------------------------------------------------------------------------------------
+struct agpt_groups {
+    struct Group { std::vector<int32_t> parent, unit_of_row; std::vector<int64_t> row; std::vector<uint8_t> trained; int32_t n_units = 0; };
+    std::vector<Group> groups;
+};
+
+extern "C" int agpt_b200_groups_create(const agpt_plan *p, const int64_t *unit_begin, const int64_t *unit_end, const int32_t *unit_rank,
+                                       int64_t n_units, int rank, int64_t group_rows, agpt_groups **out) {
+    if (!p || !unit_begin || !unit_end || !out || n_units < 0 || group_rows < 1) return agpt_set_error(AGPT_E_ARG, "groups_create: bad argument");
+    agpt_groups *G = new agpt_groups();
+    agpt_groups::Group cur;
+    auto flush = [&]() {
+        if (!cur.row.empty()) { G->groups.push_back(std::move(cur)); cur = agpt_groups::Group(); }
+    };
+    std::vector<int64_t> chain;
+    for (int64_t u = 0; u < n_units; u++) {
+        if (unit_rank && unit_rank[u] != rank) continue;
+        const int64_t b = unit_begin[u], e = unit_end[u];
+        if (b < 0 || e > p->n || b >= e) { delete G; return agpt_set_error(AGPT_E_ARG, "groups_create: unit %lld has a bad range", (long long)u); }
+        // a unit that does not start at depth 1 carries its ancestors as context rows (attended, not trained), so every
+        // chain is complete and results do not depend on the partition
+        chain.clear();
+        for (int64_t a = p->parent_dfs[b]; a >= 0; a = p->parent_dfs[a]) chain.push_back(a);
+        std::reverse(chain.begin(), chain.end());
+        const int64_t k = (int64_t)chain.size(), rows = k + (e - b);
+        if (!cur.row.empty() && (int64_t)cur.row.size() + rows > group_rows) flush();
+        const int64_t off = (int64_t)cur.row.size();
+        if (off + rows >= (1LL << 31) - 256) { delete G; return agpt_set_error(AGPT_E_LIMIT, "groups_create: more than 2^31 rows in one group"); }
+        const int32_t unit_local = cur.n_units++;
+        for (int64_t j = 0; j < k; j++) {
+            cur.parent.push_back((int32_t)(j == 0 ? -1 : off + j - 1));
+            cur.row.push_back(chain[j]); cur.trained.push_back(0); cur.unit_of_row.push_back(unit_local);
+        }
+        for (int64_t i = b; i < e; i++) {
+            const int64_t pp = p->parent_dfs[i];
+            // the unit's first row hangs under its context chain (a root without one); rows inside keep their parent
+            const int64_t lp = i == b ? (k ? off + k - 1 : -1) : (pp < b ? -1 : off + k + (pp - b));
+            cur.parent.push_back((int32_t)lp);
+            cur.row.push_back(i); cur.trained.push_back(1); cur.unit_of_row.push_back(unit_local);
+        }
+    }
+    flush();
+    *out = G;
+    return AGPT_OK;
+}
+
+extern "C" int64_t agpt_b200_groups_count(const agpt_groups *g) { return g ? (int64_t)g->groups.size() : 0; }
+
+extern "C" int agpt_b200_groups_get(const agpt_groups *g, int64_t i, agpt_group_info *o) {
+    if (!g || !o || i < 0 || i >= (int64_t)g->groups.size()) return agpt_set_error(AGPT_E_ARG, "groups_get: bad argument");
+    const agpt_groups::Group &x = g->groups[i];
+    o->n = (int64_t)x.row.size(); o->n_units = x.n_units;
+    o->parent = x.parent.data(); o->row = x.row.data(); o->trained = x.trained.data(); o->unit_of_row = x.unit_of_row.data();
+    return AGPT_OK;
+}
+
+extern "C" void agpt_b200_groups_free(agpt_groups *g) { delete g; }
+
 extern "C" int64_t agpt_b200_attn_bwd_workspace_bytes(const agpt_plan *p, int d_model) {
     if (!p || d_model <= 0) return agpt_set_error(AGPT_E_ARG, "attn_bwd_workspace_bytes: bad argument");
     // partial dK and dV rows of every tile's chain, then the per-segment sums of long reductions

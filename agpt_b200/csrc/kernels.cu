@@ -32,6 +32,21 @@ static inline int launch_status(const char *what) {
     return AGPT_OK;
 }
 
+#define AGPT_MAX_DEVICES 64
+// Raise a kernel's dynamic shared-memory limit once per device (the attribute belongs to the context's copy of the
+// function, so it is set again on every device a plan is used on, but not on every launch).
+template <typename KernelT>
+static int allow_dynamic_smem(KernelT kernel, size_t bytes, size_t *granted /* [AGPT_MAX_DEVICES] */) {
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= AGPT_MAX_DEVICES) return agpt_set_error(AGPT_E_LIMIT, "device index %d beyond %d", dev, AGPT_MAX_DEVICES);
+    if (granted[dev] < bytes) {
+        CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+        granted[dev] = bytes;
+    }
+    return AGPT_OK;
+}
+
 // --------------------------------------------------------------------------------------
 // plan: device copies
 // --------------------------------------------------------------------------------------
@@ -247,7 +262,6 @@ __device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-#define AGPT_MAX_DEVICES 64
 #define MAXKEYS 512      // keys (chain + tile rows) a tile of the tensor-core kernels can hold metadata for
 
 __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src) {
@@ -874,7 +888,7 @@ __global__ void __launch_bounds__(128, HD <= 32 ? 4 : (sizeof(KVT) == 2 ? 3 : 1)
 }
 
 // --------------------------------------------------------------------------------------
-// backward, whole tile resident: attn_bwd_tile_kernel (head_dim 32, float32 store).
+// backward, whole tile resident: attn_bwd_tile_kernel (head_dim 32 or 64, float32 store).
 //
 // Operands.  The tile's Q and dO rows and every key row the tile can attend (ancestor chain + the tile's own
 // rows) are brought into shared memory ONCE (cp.async, raw float32) and converted in place to split half
@@ -883,8 +897,8 @@ __global__ void __launch_bounds__(128, HD <= 32 ? 4 : (sizeof(KVT) == 2 ? 3 : 1)
 // scale), so hi*hi + lo*hi + hi*lo reproduces the float32 product to about 2^-22 -- the accuracy of three TF32
 // products -- while each mma.sync.m16n8k16 contracts twice as many elements as a TF32 m16n8k8, every fragment
 // register carries two elements, and the operands take 4 bytes per element instead of 8.  The scales are exact
-// (powers of two) and are divided out of the results.  A converted row is 128 bytes: 32 hi halves then 32 lo halves,
-// its eight 16-byte chunks XOR-swizzled with the row (chunk ^ row % 8), so that every fragment is one
+// (powers of two) and are divided out of the results.  A converted row is 4 * head_dim bytes: the hi halves then the lo
+// halves, its 16-byte chunks XOR-swizzled with the row (chunk ^ row % 8), so that every fragment is one
 // conflict-free ldmatrix.x4: "along the row" fragments plain, "across rows" fragments with .trans.
 //
 // Work.  After the staging barriers the warps never meet again.  A warp takes items from a shared counter and runs
@@ -952,20 +966,23 @@ __device__ __forceinline__ void pow2_scale(uint32_t max_bits, int lift, float &s
     inv = __uint_as_float((uint32_t)(e - lift) << 23);
 }
 
-#define TILE_ROW_BYTES 128          // one staged row: 32 floats raw, then 32 hi + 32 lo halves
+// One staged row holds head_dim floats raw, then head_dim hi halves followed by head_dim lo halves: 4 * head_dim bytes,
+// head_dim / 4 chunks of 16 bytes, the low three bits of the chunk index XOR-ed with row % 8.
 
-// Staging geometry of one thread: it owns chunk c of rows r0, r0 + NT/8, r0 + 2 NT/8, ... of every plane.  NT/8 is a
-// multiple of 8, so the swizzle term (row % 8) and with it the three byte offsets below are the same for all its
-// rows up to a multiple of the row step: raw = where the raw float4 sits, hi / lo = where its four hi and four lo
-// halves go after the conversion.
+// Staging geometry of one thread: it owns chunk c of rows r0, r0 + s, r0 + 2 s, ... of every plane, s = threads /
+// chunks per row.  s is a multiple of 8, so the swizzle term (row % 8) and with it the three byte offsets below are
+// the same for all its rows up to a multiple of the row step: raw = where the raw float4 sits, hi / lo = where its
+// four hi and four lo halves go after the conversion.
 struct TileLane { int r0, c, raw, hi, lo; };
+template <int HD>
 __device__ __forceinline__ TileLane tile_lane(int tid) {
+    constexpr int NCH = HD / 4;
     TileLane L;
-    L.r0 = tid >> 3; L.c = tid & 7;
-    const int x = L.r0 & 7, row = L.r0 * TILE_ROW_BYTES, half = (L.c & 1) << 3;
+    L.r0 = tid / NCH; L.c = tid % NCH;
+    const int x = L.r0 & 7, row = L.r0 * (HD * 4), half = (L.c & 1) << 3;
     L.raw = row + ((L.c ^ x) << 4);
     L.hi = row + (((L.c >> 1) ^ x) << 4) + half;
-    L.lo = row + (((4 + (L.c >> 1)) ^ x) << 4) + half;
+    L.lo = row + (((HD / 8 + (L.c >> 1)) ^ x) << 4) + half;
     return L;
 }
 __device__ __forceinline__ float abs_max4(float m, float4 a) {
@@ -985,11 +1002,11 @@ __device__ __forceinline__ void tile_convert2(unsigned char *pa, unsigned char *
     __syncwarp();
 }
 
-constexpr size_t bwd_tile_smem_bytes(int maxk) {
-    return (size_t)(2 * 64 + 2 * maxk) * TILE_ROW_BYTES + (size_t)maxk * 8 + 3 * 64 * 4 + 32;
+constexpr size_t bwd_tile_smem_bytes(int hd, int maxk) {
+    return (size_t)(2 * 64 + 2 * maxk) * (size_t)(hd * 4) + (size_t)maxk * 8 + 3 * 64 * 4 + 32;
 }
 
-template <int NW, int MINB>
+template <int HD, int NW, int MINB>
 __global__ void __launch_bounds__(NW * 32, MINB)
 attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, const float *__restrict__ V,
                      const float *__restrict__ O, const float *__restrict__ LSE, const float *__restrict__ dO,
@@ -997,7 +1014,7 @@ attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
                      float *__restrict__ Pv, const int32_t *__restrict__ sub_end, const int64_t *__restrict__ chain_off,
                      const int32_t *__restrict__ chain_ids, const int32_t *__restrict__ chain_end_all, int n, int H,
                      float scale, int tile0, int maxk, int dbg, BwdMask gmask) {
-    constexpr int HD = 32, M = 64, NT = NW * 32;
+    constexpr int M = 64, NT = NW * 32, TILE_ROW_BYTES = HD * 4, KS = HD / 16, NDB = HD / 8, NCH = HD / 4;
     extern __shared__ __align__(128) unsigned char tile_smem_raw[];
     unsigned char *sQ = tile_smem_raw, *sG = sQ + M * TILE_ROW_BYTES, *sK = sG + M * TILE_ROW_BYTES;
     unsigned char *sV = sK + (size_t)maxk * TILE_ROW_BYTES;
@@ -1023,9 +1040,10 @@ attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
     // ---- stage 1: raw rows by cp.async (chunk c of row r goes to chunk c ^ r % 8), O rows to registers ----
     if (tid < 4) s_max[tid] = 0u;
     if (tid == 0) *s_ctr = 0;
-    constexpr int RSTEP = NT / 8, OSTEP = RSTEP * TILE_ROW_BYTES;
+    constexpr int RSTEP = NT / NCH, OSTEP = RSTEP * TILE_ROW_BYTES;
+    static_assert(NT % NCH == 0 && RSTEP % 8 == 0, "a thread's rows must share their swizzle term");
     constexpr int UQ = (M + RSTEP - 1) / RSTEP;
-    const TileLane L = tile_lane(tid);
+    const TileLane L = tile_lane<HD>(tid);
     float4 ox[UQ];
 #pragma unroll
     for (int u = 0; u < UQ; u++) {
@@ -1076,7 +1094,8 @@ attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
                 mq = abs_max4(mq, a); mg = abs_max4(mg, b);
                 float d = b.x * ox[u].x;
                 d = fmaf(b.y, ox[u].y, d); d = fmaf(b.z, ox[u].z, d); d = fmaf(b.w, ox[u].w, d);
-                d += __shfl_xor_sync(0xffffffffu, d, 1); d += __shfl_xor_sync(0xffffffffu, d, 2); d += __shfl_xor_sync(0xffffffffu, d, 4);
+#pragma unroll
+                for (int o = 1; o < NCH; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
                 if (L.c == 0) sDelta[r] = d;
             }
         }
@@ -1115,13 +1134,13 @@ attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
     const int l8 = lane & 7, mi = lane >> 3;
     // B fragments of an 8-row block for k-step ks (16 dims): matrices {hi chunk 2ks, hi 2ks+1, lo 2ks, lo 2ks+1}
     const uint32_t bRow = (uint32_t)(l8 * TILE_ROW_BYTES);
-    const int bC = (mi & 1) + ((mi >> 1) << 2);         // + 2 ks
+    const int bC = (mi & 1) + (mi >> 1) * NDB;          // + 2 ks
     // A fragments of a 16-row block for k-step ks: matrices {rows 0-7 chunk 2ks, rows 8-15 chunk 2ks, rows 0-7 chunk 2ks+1,
     // rows 8-15 chunk 2ks+1} (+4 for the lo part); the .trans fragments of a 16-row block for dims 8 db..: {hi rows 0-7,
     // hi rows 8-15, lo rows 0-7, lo rows 8-15} of chunk db (+4 for lo)
     const uint32_t aRow = (uint32_t)((l8 + (mi & 1) * 8) * TILE_ROW_BYTES);
     const int aC = mi >> 1;                             // + 2 ks (+ 4 for lo)
-    const int tC = (mi >> 1) << 2;                      // + db
+    const int tC = (mi >> 1) * NDB;                     // + db
     const uint32_t uQ = smem_u32_of(sQ), uG = smem_u32_of(sG), uK = smem_u32_of(sK), uV = smem_u32_of(sV);
 
     const int nkb = nkp >> 4;                    // key items
@@ -1146,18 +1165,18 @@ attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
             if (rg * 16 >= nt) continue;                                   // rows beyond the end of the plan
             const int q0 = rg * 16 + g, q1 = q0 + 8;
             const int r0 = i0 + q0, r1 = i0 + q1;
-            uint32_t qh[2][4], ql[2][4], gh[2][4], gl[2][4];
+            uint32_t qh[KS][4], ql[KS][4], gh[KS][4], gl[KS][4];
 #pragma unroll
-            for (int ks = 0; ks < 2; ks++) {
+            for (int ks = 0; ks < KS; ks++) {
                 const uint32_t o = (uint32_t)(rg * 16 * TILE_ROW_BYTES) + aRow;
-                const uint32_t ch = (uint32_t)(((2 * ks + aC) ^ l8) << 4), cl = (uint32_t)(((2 * ks + aC + 4) ^ l8) << 4);
+                const uint32_t ch = (uint32_t)(((2 * ks + aC) ^ l8) << 4), cl = (uint32_t)(((2 * ks + aC + NDB) ^ l8) << 4);
                 ldmatrix_x4(qh[ks], uQ + o + ch); ldmatrix_x4(ql[ks], uQ + o + cl);
                 ldmatrix_x4(gh[ks], uG + o + ch); ldmatrix_x4(gl[ks], uG + o + cl);
             }
             const float lse0 = sLse[q0], lse1 = sLse[q1], dl0 = sDelta[q0] * sclG * sclV, dl1 = sDelta[q1] * sclG * sclV;
-            float dq[4][4];
+            float dq[NDB][4];
 #pragma unroll
-            for (int db = 0; db < 4; db++) dq[db][0] = dq[db][1] = dq[db][2] = dq[db][3] = 0.f;
+            for (int db = 0; db < NDB; db++) dq[db][0] = dq[db][1] = dq[db][2] = dq[db][3] = 0.f;
             // the rows of this group attend the chain and the tile's keys up to their own position
             const int kp_lim = min((nkeys + 15) >> 4, (p + rg * 16 + 16 + 15) >> 4);
             for (int kp = 0; kp < kp_lim; kp++) {
@@ -1180,7 +1199,7 @@ attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
                     float e[4] = {0.f, 0.f, 0.f, 0.f}, ex[4] = {0.f, 0.f, 0.f, 0.f};
                     const uint32_t rowb = (uint32_t)((kp * 16 + u * 8) * TILE_ROW_BYTES) + bRow;
 #pragma unroll
-                    for (int ks = 0; ks < 2; ks++) {
+                    for (int ks = 0; ks < KS; ks++) {
                         const uint32_t o = rowb + (uint32_t)(((2 * ks + bC) ^ l8) << 4);
                         uint32_t kf[4], vf[4];                 // {b0 hi, b1 hi, b0 lo, b1 lo}
                         ldmatrix_x4(kf, uK + o); ldmatrix_x4(vf, uV + o);
@@ -1203,7 +1222,7 @@ attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
                 for (int j = 0; j < 4; j++) as[j] = f16_down11(ah[j]);
                 const uint32_t rowt = uK + (uint32_t)(kp * 16 * TILE_ROW_BYTES) + aRow;
 #pragma unroll
-                for (int db = 0; db < 4; db++) {
+                for (int db = 0; db < NDB; db++) {
                     uint32_t kt[4];                            // {b0 hi, b1 hi, b0 lo, b1 lo}: keys 0-7 / 8-15 of the block, dims 8 db..
                     ldmatrix_x4_trans(kt, rowt + (uint32_t)(((db + tC) ^ l8) << 4));
                     mma_f16(dq[db], ah, kt[0], kt[1]);
@@ -1213,12 +1232,12 @@ attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
             }
             if (r0 < n) {
 #pragma unroll
-                for (int db = 0; db < 4; db++)
+                for (int db = 0; db < NDB; db++)
                     *reinterpret_cast<float2 *>(dQ + (int64_t)r0 * D + hoff + db * 8 + 2 * tig) = make_float2(dq[db][0] * ADOWN * invG * invV * invK, dq[db][1] * ADOWN * invG * invV * invK);
             }
             if (r1 < n) {
 #pragma unroll
-                for (int db = 0; db < 4; db++)
+                for (int db = 0; db < NDB; db++)
                     *reinterpret_cast<float2 *>(dQ + (int64_t)r1 * D + hoff + db * 8 + 2 * tig) = make_float2(dq[db][2] * ADOWN * invG * invV * invK, dq[db][3] * ADOWN * invG * invV * invK);
             }
         } else {
@@ -1226,17 +1245,17 @@ attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
             const int kb = which;
             const int kA = kb * 16 + g, kB = kA + 8;
             const int2 mA = s_meta[kA], mB = s_meta[kB];
-            uint32_t kh[2][4], kl[2][4], vh[2][4], vl[2][4];
+            uint32_t kh[KS][4], kl[KS][4], vh[KS][4], vl[KS][4];
 #pragma unroll
-            for (int ks = 0; ks < 2; ks++) {
+            for (int ks = 0; ks < KS; ks++) {
                 const uint32_t o = (uint32_t)(kb * 16 * TILE_ROW_BYTES) + aRow;
-                const uint32_t ch = (uint32_t)(((2 * ks + aC) ^ l8) << 4), cl = (uint32_t)(((2 * ks + aC + 4) ^ l8) << 4);
+                const uint32_t ch = (uint32_t)(((2 * ks + aC) ^ l8) << 4), cl = (uint32_t)(((2 * ks + aC + NDB) ^ l8) << 4);
                 ldmatrix_x4(kh[ks], uK + o + ch); ldmatrix_x4(kl[ks], uK + o + cl);
                 ldmatrix_x4(vh[ks], uV + o + ch); ldmatrix_x4(vl[ks], uV + o + cl);
             }
-            float dk[4][4], dv[4][4];
+            float dk[NDB][4], dv[NDB][4];
 #pragma unroll
-            for (int db = 0; db < 4; db++) {
+            for (int db = 0; db < NDB; db++) {
                 dk[db][0] = dk[db][1] = dk[db][2] = dk[db][3] = 0.f;
                 dv[db][0] = dv[db][1] = dv[db][2] = dv[db][3] = 0.f;
             }
@@ -1266,7 +1285,7 @@ attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
                     const int qr = qp * 16 + u * 8;
                     const uint32_t rowb = (uint32_t)(qr * TILE_ROW_BYTES) + bRow;
 #pragma unroll
-                    for (int ks = 0; ks < 2; ks++) {
+                    for (int ks = 0; ks < KS; ks++) {
                         const uint32_t o = rowb + (uint32_t)(((2 * ks + bC) ^ l8) << 4);
                         uint32_t qf[4], gf[4];                 // {b0 hi, b1 hi, b0 lo, b1 lo}
                         ldmatrix_x4(qf, uQ + o); ldmatrix_x4(gf, uG + o);
@@ -1295,7 +1314,7 @@ attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
                 }
                 const uint32_t ro = (uint32_t)(qp * 16 * TILE_ROW_BYTES) + aRow;
 #pragma unroll
-                for (int db = 0; db < 4; db++) {
+                for (int db = 0; db < NDB; db++) {
                     uint32_t qt[4], gt[4];                     // {b0 hi, b1 hi, b0 lo, b1 lo}: queries 0-7 / 8-15 of the block, dims 8 db..
                     const uint32_t co = (uint32_t)(((db + tC) ^ l8) << 4);
                     ldmatrix_x4_trans(qt, uQ + ro + co); ldmatrix_x4_trans(gt, uG + ro + co);
@@ -1312,7 +1331,7 @@ attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
                 if (kk < p) { ok = Pk + (coff + kk) * D + hoff; ov = Pv + (coff + kk) * D + hoff; }
                 else { ok = dK + (int64_t)(i0 + kk - p) * D + hoff; ov = dV + (int64_t)(i0 + kk - p) * D + hoff; }
 #pragma unroll
-                for (int db = 0; db < 4; db++) {
+                for (int db = 0; db < NDB; db++) {
                     *reinterpret_cast<float2 *>(ok + db * 8 + 2 * tig) = make_float2(dk[db][2 * half] * ADOWN * invG * invV * invQ, dk[db][2 * half + 1] * ADOWN * invG * invV * invQ);
                     *reinterpret_cast<float2 *>(ov + db * 8 + 2 * tig) = make_float2(dv[db][2 * half] * ADOWN * invG, dv[db][2 * half + 1] * ADOWN * invG);
                 }
@@ -1322,21 +1341,21 @@ attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
 }
 
 // --------------------------------------------------------------------------------------
-// forward, whole tile resident: attn_fwd_tile_kernel (head_dim 32, float32 store).  Same staging, operand format and
+// forward, whole tile resident: attn_fwd_tile_kernel (head_dim 32 or 64, float32 store).  Same staging, operand format and
 // fragment addressing as attn_bwd_tile_kernel; one warp per 16 query rows (4 warps), online softmax over blocks of
 // 16 keys, O += P V with V read through ldmatrix.trans.
 // --------------------------------------------------------------------------------------
-constexpr size_t fwd_tile_smem_bytes(int maxk) {
-    return (size_t)(64 + 2 * maxk) * TILE_ROW_BYTES + (size_t)maxk * 8 + 32;
+constexpr size_t fwd_tile_smem_bytes(int hd, int maxk) {
+    return (size_t)(64 + 2 * maxk) * (size_t)(hd * 4) + (size_t)maxk * 8 + 32;
 }
 
-template <int MINB>
+template <int HD, int MINB>
 __global__ void __launch_bounds__(128, MINB)
 attn_fwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, const float *__restrict__ V,
                      float *__restrict__ O, float *__restrict__ LSE, const int32_t *__restrict__ sub_end,
                      const int64_t *__restrict__ chain_off, const int32_t *__restrict__ chain_ids,
                      const int32_t *__restrict__ chain_end_all, int n, int H, float scale, int tile0, int maxk) {
-    constexpr int HD = 32, M = 64, NT = 128;
+    constexpr int M = 64, NT = 128, TILE_ROW_BYTES = HD * 4, KS = HD / 16, NDB = HD / 8, NCH = HD / 4;
     extern __shared__ __align__(128) unsigned char tile_smem_raw[];
     unsigned char *sQ = tile_smem_raw, *sK = sQ + M * TILE_ROW_BYTES, *sV = sK + (size_t)maxk * TILE_ROW_BYTES;
     int2 *s_meta = reinterpret_cast<int2 *>(sV + (size_t)maxk * TILE_ROW_BYTES);   // [maxk] {key id, key subtree end}
@@ -1356,8 +1375,8 @@ attn_fwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
 
     // ---- stage 1: raw rows by cp.async ----
     if (tid < 3) s_max[tid] = 0u;
-    constexpr int RSTEP = NT / 8, OSTEP = RSTEP * TILE_ROW_BYTES;
-    const TileLane L = tile_lane(tid);
+    constexpr int RSTEP = NT / NCH, OSTEP = RSTEP * TILE_ROW_BYTES;
+    const TileLane L = tile_lane<HD>(tid);
 #pragma unroll
     for (int u = 0; u < M / RSTEP; u++) {
         const int r = L.r0 + u * RSTEP, o = L.raw + u * OSTEP;
@@ -1416,23 +1435,23 @@ attn_fwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
     const float fS = scale * LOG2E * invQ * invK;               // log2-domain score = S' * fS
     const int l8 = lane & 7, mi = lane >> 3;
     const uint32_t bRow = (uint32_t)(l8 * TILE_ROW_BYTES);
-    const int bC = (mi & 1) + ((mi >> 1) << 2);
+    const int bC = (mi & 1) + (mi >> 1) * NDB;
     const uint32_t aRow = (uint32_t)((l8 + (mi & 1) * 8) * TILE_ROW_BYTES);
-    const int aC = mi >> 1, tC = (mi >> 1) << 2;
+    const int aC = mi >> 1, tC = (mi >> 1) * NDB;
     const uint32_t uQ = smem_u32_of(sQ), uK = smem_u32_of(sK), uV = smem_u32_of(sV);
 
     const int q0 = rg * 16 + g, q1 = q0 + 8;
     const int r0 = i0 + q0, r1 = i0 + q1;
-    uint32_t qh[2][4], ql[2][4];
+    uint32_t qh[KS][4], ql[KS][4];
 #pragma unroll
-    for (int ks = 0; ks < 2; ks++) {
+    for (int ks = 0; ks < KS; ks++) {
         const uint32_t o = (uint32_t)(rg * 16 * TILE_ROW_BYTES) + aRow;
         ldmatrix_x4(qh[ks], uQ + o + (uint32_t)(((2 * ks + aC) ^ l8) << 4));
-        ldmatrix_x4(ql[ks], uQ + o + (uint32_t)(((2 * ks + aC + 4) ^ l8) << 4));
+        ldmatrix_x4(ql[ks], uQ + o + (uint32_t)(((2 * ks + aC + NDB) ^ l8) << 4));
     }
-    float o_[4][4];
+    float o_[NDB][4];
 #pragma unroll
-    for (int db = 0; db < 4; db++) o_[db][0] = o_[db][1] = o_[db][2] = o_[db][3] = 0.f;
+    for (int db = 0; db < NDB; db++) o_[db][0] = o_[db][1] = o_[db][2] = o_[db][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
     const int kp_lim = min((nkeys + 15) >> 4, (p + rg * 16 + 16 + 15) >> 4);
     for (int kp = 0; kp < kp_lim; kp++) {
@@ -1454,7 +1473,7 @@ attn_fwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
             float c[4] = {0.f, 0.f, 0.f, 0.f}, cx[4] = {0.f, 0.f, 0.f, 0.f};
             const uint32_t rowb = (uint32_t)((kp * 16 + u * 8) * TILE_ROW_BYTES) + bRow;
 #pragma unroll
-            for (int ks = 0; ks < 2; ks++) {
+            for (int ks = 0; ks < KS; ks++) {
                 uint32_t kf[4];
                 ldmatrix_x4(kf, uK + rowb + (uint32_t)(((2 * ks + bC) ^ l8) << 4));
                 mma_f16(c, qh[ks], kf[0], kf[1]);
@@ -1475,7 +1494,7 @@ attn_fwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
         m0 = mn0; m1 = mn1;
         l0 *= corr0; l1 *= corr1;
 #pragma unroll
-        for (int db = 0; db < 4; db++) { o_[db][0] *= corr0; o_[db][1] *= corr0; o_[db][2] *= corr1; o_[db][3] *= corr1; }
+        for (int db = 0; db < NDB; db++) { o_[db][0] *= corr0; o_[db][1] *= corr0; o_[db][2] *= corr1; o_[db][3] *= corr1; }
         float pw[2][4];
 #pragma unroll
         for (int u = 0; u < 2; u++) {
@@ -1493,7 +1512,7 @@ attn_fwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
         }
         const uint32_t rowt = uV + (uint32_t)(kp * 16 * TILE_ROW_BYTES) + aRow;
 #pragma unroll
-        for (int db = 0; db < 4; db++) {
+        for (int db = 0; db < NDB; db++) {
             uint32_t vt[4];                            // {b0 hi, b1 hi, b0 lo, b1 lo}: keys 0-7 / 8-15 of the block, dims 8 db..
             ldmatrix_x4_trans(vt, rowt + (uint32_t)(((db + tC) ^ l8) << 4));
             mma_f16(o_[db], ph, vt[0], vt[1]);
@@ -1506,14 +1525,14 @@ attn_fwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
     if (r0 < n) {
         const float inv = ADOWN * invV / l0;
 #pragma unroll
-        for (int db = 0; db < 4; db++)
+        for (int db = 0; db < NDB; db++)
             *reinterpret_cast<float2 *>(O + (int64_t)r0 * D + hoff + db * 8 + 2 * tig) = make_float2(o_[db][0] * inv, o_[db][1] * inv);
         if (tig == 0) LSE[(int64_t)r0 * H + h] = (m0 + log2f(l0)) * LN2;
     }
     if (r1 < n) {
         const float inv = ADOWN * invV / l1;
 #pragma unroll
-        for (int db = 0; db < 4; db++)
+        for (int db = 0; db < NDB; db++)
             *reinterpret_cast<float2 *>(O + (int64_t)r1 * D + hoff + db * 8 + 2 * tig) = make_float2(o_[db][2] * inv, o_[db][3] * inv);
         if (tig == 0) LSE[(int64_t)r1 * H + h] = (m1 + log2f(l1)) * LN2;
     }
@@ -1608,7 +1627,8 @@ static int launch_bwd(const agpt_plan *p, const float *q, const void *k, const v
                       cudaStream_t st, int tile0, int ntiles, BwdMask gmask) {
     dim3 grid((unsigned)ntiles, (unsigned)H);
     size_t smem = sizeof(BwdSmem<HD, M>);
-    CUDA_TRY(cudaFuncSetAttribute(attn_bwd_kernel<HD, M, KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    static size_t granted[AGPT_MAX_DEVICES];
+    if (int rc = allow_dynamic_smem(attn_bwd_kernel<HD, M, KVT>, smem, granted)) return rc;
     attn_bwd_kernel<HD, M, KVT><<<grid, M, smem, st>>>(q, (const KVT *)k, (const KVT *)v, o, lse, dout, dq, dk, dv, pk, pv,
                                                        p->d_sub_end, p->d_chain_off, p->d_chain_ids, (int)p->n, H, scale, tile0, gmask);
     return launch_status("attn_bwd");
@@ -1646,25 +1666,12 @@ extern "C" int agpt_b200_set_attn_impl(int impl) {
     return AGPT_OK;
 }
 
-// Raise a kernel's dynamic shared-memory limit once per device (the attribute belongs to the context's copy of the
-// function, so it is set again on every device a plan is used on, but not on every launch).
-template <typename KernelT>
-static int allow_dynamic_smem(KernelT kernel, size_t bytes, size_t *granted /* [AGPT_MAX_DEVICES] */) {
-    int dev = 0;
-    CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= AGPT_MAX_DEVICES) return agpt_set_error(AGPT_E_LIMIT, "device index %d beyond %d", dev, AGPT_MAX_DEVICES);
-    if (granted[dev] < bytes) {
-        CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
-        granted[dev] = bytes;
-    }
-    return AGPT_OK;
-}
-
 // Whole-tile kernels (forward and backward; float32 store, head_dim 32): chosen when four blocks of the backward
 // fit one SM (228 KB of shared memory, 1 KB reserved per block), i.e. up to about 150 keys per tile; deeper plans take
 // the chunked kernels.  AGPT_B200_ATTN_TILE=0 keeps the chunked kernels (A/B runs); AGPT_B200_BWD_WARPS = 4, 6 or 8
 // warps per block of the backward.
-#define BWD_TILE_SMEM_LIMIT ((size_t)56 * 1024)
+// head_dim 32: four blocks of the backward per SM; head_dim 64 (rows twice as long, twice the registers): two
+static inline bool tile_kernels_fit(const agpt_plan *p, int head_dim);
 static int g_bwd_tile = -1, g_bwd_warps = 0, g_bwd_dbg = 0;
 static int bwd_tile_enabled() {
     if (g_bwd_tile < 0) {
@@ -1686,17 +1693,22 @@ extern "C" int agpt_b200_set_attn_variant(int whole_tile, int warps) {
     return AGPT_OK;
 }
 static inline int bwd_tile_maxk(const agpt_plan *p) { return ((p->max_depth - 1 + 64) + 15) & ~15; }
+static inline bool tile_kernels_fit(const agpt_plan *p, int head_dim) {
+    if (head_dim != 32 && head_dim != 64) return false;
+    return bwd_tile_smem_bytes(head_dim, bwd_tile_maxk(p)) <= (head_dim == 32 ? (size_t)56 * 1024 : (size_t)113 * 1024);
+}
 
+template <int HD, int MINB>
 static int launch_fwd_tile(const agpt_plan *p, const float *q, const void *k, const void *v, float *out, float *lse, int H,
                            float scale, cudaStream_t st, int tile0, int ntiles) {
     static size_t granted[AGPT_MAX_DEVICES];
     const int maxk = bwd_tile_maxk(p);
-    const size_t smem = fwd_tile_smem_bytes(maxk);
-    int rc = allow_dynamic_smem(attn_fwd_tile_kernel<5>, smem, granted);
+    const size_t smem = fwd_tile_smem_bytes(HD, maxk);
+    int rc = allow_dynamic_smem(attn_fwd_tile_kernel<HD, MINB>, smem, granted);
     if (rc) return rc;
     dim3 grid((unsigned)ntiles, (unsigned)H);
-    attn_fwd_tile_kernel<5><<<grid, 128, smem, st>>>(q, (const float *)k, (const float *)v, out, lse, p->d_sub_end, p->d_chain_off,
-                                                     p->d_chain_ids, p->d_chain_end, (int)p->n, H, scale, tile0, maxk);
+    attn_fwd_tile_kernel<HD, MINB><<<grid, 128, smem, st>>>(q, (const float *)k, (const float *)v, out, lse, p->d_sub_end,
+                                                            p->d_chain_off, p->d_chain_ids, p->d_chain_end, (int)p->n, H, scale, tile0, maxk);
     return launch_status("attn_fwd_tile");
 }
 
@@ -1705,7 +1717,8 @@ static int launch_fwd_mma(const agpt_plan *p, const float *q, const void *k, con
                           float scale, cudaStream_t st, int tile0, int ntiles) {
     dim3 grid((unsigned)ntiles, (unsigned)H);
     const size_t smem = fwd_mma_smem_bytes<HD>();
-    CUDA_TRY(cudaFuncSetAttribute(attn_fwd_mma_kernel<HD, KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    static size_t granted[AGPT_MAX_DEVICES];
+    if (int rc = allow_dynamic_smem(attn_fwd_mma_kernel<HD, KVT>, smem, granted)) return rc;
     attn_fwd_mma_kernel<HD, KVT><<<grid, 128, smem, st>>>(q, (const KVT *)k, (const KVT *)v, out, lse, p->d_sub_end,
                                                        p->d_chain_off, p->d_chain_ids, p->d_chain_end, (int)p->n, H, scale, tile0);
     return launch_status("attn_fwd_mma");
@@ -1713,9 +1726,9 @@ static int launch_fwd_mma(const agpt_plan *p, const float *q, const void *k, con
 
 static int fwd_dispatch(const agpt_plan *p, const float *q, const void *k, const void *v, int kv_dtype, float *out,
                         float *lse, int H, int head_dim, float scale, cudaStream_t st, int tile0, int ntiles) {
-    if (attn_impl() == 1 && p->tile_m == 64 && kv_dtype == AGPT_KV_F32 && head_dim == 32 && bwd_tile_enabled() &&
-        bwd_tile_smem_bytes(bwd_tile_maxk(p)) <= BWD_TILE_SMEM_LIMIT)
-        return launch_fwd_tile(p, q, k, v, out, lse, H, scale, st, tile0, ntiles);
+    if (attn_impl() == 1 && p->tile_m == 64 && kv_dtype == AGPT_KV_F32 && bwd_tile_enabled() && tile_kernels_fit(p, head_dim))
+        return head_dim == 32 ? launch_fwd_tile<32, 5>(p, q, k, v, out, lse, H, scale, st, tile0, ntiles)
+                              : launch_fwd_tile<64, 2>(p, q, k, v, out, lse, H, scale, st, tile0, ntiles);
     if (attn_impl() == 1 && p->tile_m == 64 && p->max_depth + 64 <= MAXKEYS) {
         const bool bf = kv_dtype == AGPT_KV_BF16;
         switch (head_dim) {
@@ -1733,46 +1746,55 @@ static int launch_bwd_mma(const agpt_plan *p, const float *q, const void *k, con
                           cudaStream_t st, int tile0, int ntiles, BwdMask gmask) {
     dim3 grid((unsigned)ntiles, (unsigned)H);
     size_t smem = sizeof(BwdMmaSmem<HD, KVT>);
-    CUDA_TRY(cudaFuncSetAttribute(attn_bwd_mma_kernel<HD, KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    static size_t granted[AGPT_MAX_DEVICES];
+    if (int rc = allow_dynamic_smem(attn_bwd_mma_kernel<HD, KVT>, smem, granted)) return rc;
     attn_bwd_mma_kernel<HD, KVT><<<grid, 128, smem, st>>>(q, (const KVT *)k, (const KVT *)v, o, lse, dout, dq, dk, dv, pk, pv,
                                                           p->d_sub_end, p->d_chain_off, p->d_chain_ids, p->d_chain_end, (int)p->n, H,
                                                           scale, tile0, gmask);
     return launch_status("attn_bwd_mma");
 }
 
-template <int NW, int MINB>
+template <int HD, int NW, int MINB>
 static int launch_bwd_tile(const agpt_plan *p, const float *q, const void *k, const void *v, const float *o, const float *lse,
                            const float *dout, float *dq, float *dk, float *dv, float *pk, float *pv, int H, float scale,
                            cudaStream_t st, int tile0, int ntiles, BwdMask gmask) {
     static size_t granted[AGPT_MAX_DEVICES];
     const int maxk = bwd_tile_maxk(p);
-    const size_t smem = bwd_tile_smem_bytes(maxk);
-    int rc = allow_dynamic_smem(attn_bwd_tile_kernel<NW, MINB>, smem, granted);
+    const size_t smem = bwd_tile_smem_bytes(HD, maxk);
+    int rc = allow_dynamic_smem(attn_bwd_tile_kernel<HD, NW, MINB>, smem, granted);
     if (rc) return rc;
     dim3 grid((unsigned)ntiles, (unsigned)H);
-    attn_bwd_tile_kernel<NW, MINB><<<grid, NW * 32, smem, st>>>(q, (const float *)k, (const float *)v, o, lse, dout, dq, dk, dv, pk, pv,
-                                                             p->d_sub_end, p->d_chain_off, p->d_chain_ids, p->d_chain_end, (int)p->n,
-                                                             H, scale, tile0, maxk, g_bwd_dbg, gmask);
+    attn_bwd_tile_kernel<HD, NW, MINB><<<grid, NW * 32, smem, st>>>(q, (const float *)k, (const float *)v, o, lse, dout, dq, dk, dv, pk, pv,
+                                                                    p->d_sub_end, p->d_chain_off, p->d_chain_ids, p->d_chain_end,
+                                                                    (int)p->n, H, scale, tile0, maxk, g_bwd_dbg, gmask);
     return launch_status("attn_bwd_tile");
 }
 
 static int launch_bwd_tile_w(const agpt_plan *p, const float *q, const void *k, const void *v, const float *o, const float *lse,
-                             const float *dout, float *dq, float *dk, float *dv, float *pk, float *pv, int H, float scale,
-                             cudaStream_t st, int tile0, int ntiles, BwdMask gmask) {
-    switch (g_bwd_warps) {
-        case 3: return launch_bwd_tile<4, 3>(p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles, gmask);
-        case 6: return launch_bwd_tile<6, 3>(p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles, gmask);
-        case 8: return launch_bwd_tile<8, 2>(p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles, gmask);
-        default: return launch_bwd_tile<4, 4>(p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles, gmask);
+                             const float *dout, float *dq, float *dk, float *dv, float *pk, float *pv, int H, int head_dim,
+                             float scale, cudaStream_t st, int tile0, int ntiles, BwdMask gmask) {
+#define TILE_ARGS p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles, gmask
+    if (head_dim == 64) {        // twice the fragment and accumulator registers: two blocks per SM
+        switch (g_bwd_warps) {
+            case 6: case 8: return launch_bwd_tile<64, 8, 1>(TILE_ARGS);
+            default: return launch_bwd_tile<64, 4, 2>(TILE_ARGS);
+        }
     }
+    switch (g_bwd_warps) {
+        case 3: return launch_bwd_tile<32, 4, 3>(TILE_ARGS);
+        case 6: return launch_bwd_tile<32, 6, 3>(TILE_ARGS);
+        case 8: return launch_bwd_tile<32, 8, 2>(TILE_ARGS);
+        default: return launch_bwd_tile<32, 4, 4>(TILE_ARGS);
+    }
+#undef TILE_ARGS
 }
 
 static int bwd_dispatch(const agpt_plan *p, const float *q, const void *k, const void *v, int kv_dtype, const float *o,
                         const float *lse, const float *dout, float *dq, float *dk, float *dv, float *pk, float *pv, int H,
                         int head_dim, float scale, cudaStream_t st, int tile0, int ntiles, BwdMask gmask = BwdMask{AGPT_GRAD_FULL, nullptr}) {
     if (attn_impl() == 1 && p->tile_m == 64 && kv_dtype == AGPT_KV_F32 && bwd_tile_enabled()) {
-        if (head_dim == 32 && bwd_tile_smem_bytes(bwd_tile_maxk(p)) <= BWD_TILE_SMEM_LIMIT)
-            return launch_bwd_tile_w(p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles, gmask);
+        if (tile_kernels_fit(p, head_dim))
+            return launch_bwd_tile_w(p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, head_dim, scale, st, tile0, ntiles, gmask);
     }
     if (attn_impl() == 1 && p->tile_m == 64 && p->max_depth + 64 <= MAXKEYS) {
         const bool bf = kv_dtype == AGPT_KV_BF16;
@@ -2648,9 +2670,26 @@ extern "C" void cuda_sync(void) {
 // can run forward and backward: chunk c+1 uploads while chunk c computes and chunk c-1's out/lse/dq download.
 // Only dK/dV (complete after the last tile and the reduction) download at the end.
 // --------------------------------------------------------------------------------------
+static int attn_fwd_bwd_host_impl(const agpt_plan *cp, const float *h_q, const float *h_k, const float *h_v,
+                                  const float *h_dout, float *h_out, float *h_lse, float *h_dq, float *h_dk, float *h_dv,
+                                  int kv_dtype, int n_heads, int head_dim, float scale);
+
 extern "C" int agpt_b200_attn_fwd_bwd_host(const agpt_plan *cp, const float *h_q, const float *h_k, const float *h_v,
                                            const float *h_dout, float *h_out, float *h_lse, float *h_dq, float *h_dk, float *h_dv,
                                            int kv_dtype, int n_heads, int head_dim, float scale) {
+    const int rc = attn_fwd_bwd_host_impl(cp, h_q, h_k, h_v, h_dout, h_out, h_lse, h_dq, h_dk, h_dv, kv_dtype, n_heads, head_dim, scale);
+    if (rc != AGPT_OK && cp && cp->device >= 0) {
+        // copies queued before the failure still read and write the caller's buffers (and the cached arena): wait for
+        // them before the buffers go back to the caller
+        for (void *st : cp->host_streams)
+            if (st) cudaStreamSynchronize((cudaStream_t)st);
+    }
+    return rc;
+}
+
+static int attn_fwd_bwd_host_impl(const agpt_plan *cp, const float *h_q, const float *h_k, const float *h_v,
+                                  const float *h_dout, float *h_out, float *h_lse, float *h_dq, float *h_dk, float *h_dv,
+                                  int kv_dtype, int n_heads, int head_dim, float scale) {
     int rc = check_common(cp, n_heads, head_dim, "attn_fwd_bwd_host");
     if (rc) return rc;
     if (!h_q || !h_k || !h_v || !h_dout || !h_out || !h_lse || !h_dq || !h_dk || !h_dv)

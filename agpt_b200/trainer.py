@@ -78,49 +78,11 @@ def build_groups(trie: A.RadixTrie, rank: int, world: int, group_rows: int, mass
     ub, ue = gplan.units(level) if unit_cap is None else gplan.units_capped(level, unit_cap)
     owner = A.partition_lpt(ue - ub, world)
     d2n = gplan.dfs_to_node
-    groups, pieces, rows = [], [], 0
-
-    def flush():
-        nonlocal pieces, rows
-        if not pieces:
-            return
-        off, pars, ids, trained, units = 0, [], [], [], []
-        for u, (pp, idv, tr) in enumerate(pieces):
-            pars.append(np.where(pp < 0, -1, pp + off))
-            ids.append(idv)
-            trained.append(tr)
-            units.append(np.full(idv.size, u, np.int64))
-            off += idv.size
-        idv = np.concatenate(ids)
-        tr = np.concatenate(trained)
-        groups.append(LaunchGroup(np.concatenate(pars).astype(np.int32), token[idv], depth[idv], radix_of[idv],
-                                  trie.edge_mass, mass_mode, seq_len, device, tile, None if tr.all() else tr,
-                                  np.concatenate(units)))
-        pieces, rows = [], 0
-
-    for b, e, o in zip(ub, ue, owner):
-        if o != rank:
-            continue
-        b, e = int(b), int(e)
-        chain, a = [], int(gplan.parent_dfs[b])
-        while a >= 0:
-            chain.append(a)
-            a = int(gplan.parent_dfs[a])
-        chain.reverse()
-        k = len(chain)
-        pp = gplan.parent_dfs[b:e].astype(np.int64) - b + k
-        pp[0] = k - 1                                        # the unit's first row hangs under its context chain (-1: a root)
-        idv = d2n[b:e]
-        tr = np.ones(e - b, bool)
-        if k:
-            pp = np.concatenate([np.arange(-1, k - 1), pp])
-            idv = np.concatenate([d2n[np.asarray(chain)], idv])
-            tr = np.concatenate([np.zeros(k, bool), tr])
-        if rows and rows + idv.size > group_rows:
-            flush()
-        pieces.append((pp, idv, tr))
-        rows += idv.size
-    flush()
+    groups = []
+    for par, row, tr, unit in A.launch_groups(gplan, ub, ue, owner, rank, group_rows):
+        idv = d2n[row]
+        groups.append(LaunchGroup(par, token[idv], depth[idv], radix_of[idv], trie.edge_mass, mass_mode, seq_len, device, tile,
+                                  None if tr.all() else tr, unit))
     return groups, int(gplan.n)
 
 

@@ -199,8 +199,10 @@ def build_units(wl, rank, world, log, single_unit=False, group_rows=4_000_000, d
             plain = A.RadixTrie.build_gpu(A.synth_markov_corpus(cfg["chars"], cfg["vocab"], cfg["order"], 0), cfg["depth"],
                                           level_key, pm, pd, device=device)
             pdep = plain.char_tree()[2]
-            log(f"trie of the corpus with injected repeats: {parent.size} positions, {trie.radix_count} radix nodes, max depth {int(cdepth.max())}; "
-                f"of the plain corpus: {pdep.size} positions, {plain.radix_count} radix nodes, max depth {int(pdep.max())}")
+            deep = lambda d: f"{int((d > 24).sum())} deeper than 24, {int((d > 64).sum())} deeper than 64"  # noqa: E731
+            log(f"trie of the corpus with injected repeats: {parent.size} positions ({deep(cdepth)}), {trie.radix_count} radix nodes, "
+                f"max depth {int(cdepth.max())}; of the plain corpus: {pdep.size} positions ({deep(pdep)}), {plain.radix_count} radix nodes, "
+                f"max depth {int(pdep.max())}")
             del plain, pdep
         counts = (trie.cnt_off.astype(np.int32), trie.cnt_tok, trie.cnt_val)
     log(f"trie built: {parent.size} positions in {time.time() - t0:.1f}s")

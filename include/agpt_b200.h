@@ -239,6 +239,29 @@ int64_t agpt_b200_plan_units(const agpt_plan *p, int level, int64_t cap, int64_t
 int agpt_b200_partition_lpt(const int64_t *unit_weight, int64_t n_units, int n_ranks,
                             int32_t *rank_of_unit);
 
+/* Launch groups of one rank: its units (depth-first [begin, end) ranges of a plan, e.g. from agpt_b200_plan_units; the
+ * units with unit_rank[u] == rank, all of them if unit_rank is NULL) packed in order into forests of at most
+ * group_rows rows -- the chunker of src/cuda/agpt_train.cu:4424-4443 on whole units.  A unit that does not start at
+ * depth 1 is preceded by its ancestor chain as context rows (trained == 0: attended and differentiated through, but
+ * they carry no loss), so every query finds its whole chain inside the group.  Per group: parent (local row index, -1
+ * for roots; rows are in depth-first order, so it can go straight to agpt_b200_plan_create), row (the plan's
+ * depth-first position of each row), trained, unit_of_row (index of the row's unit inside the group). */
+typedef struct agpt_groups agpt_groups;
+typedef struct {
+    int64_t n;
+    int32_t n_units;
+    const int32_t *parent;
+    const int64_t *row;
+    const uint8_t *trained;
+    const int32_t *unit_of_row;
+} agpt_group_info;
+int agpt_b200_groups_create(const agpt_plan *p, const int64_t *unit_begin, const int64_t *unit_end,
+                            const int32_t *unit_rank, int64_t n_units, int rank, int64_t group_rows, agpt_groups **out);
+int64_t agpt_b200_groups_count(const agpt_groups *g);
+int agpt_b200_groups_get(const agpt_groups *g, int64_t i, agpt_group_info *out);
+void agpt_b200_groups_free(agpt_groups *g);
+
+
 /* ---- device kernels (all asynchronous on `stream`, a cudaStream_t passed as void*) ---- */
 
 /* Row gather: dst[i, :] = src[index[i], :] (float32 rows of `cols`).  Used to bring
@@ -395,15 +418,16 @@ int agpt_b200_attn_bwd_mode(const agpt_plan *p, const float *d_q, const void *d_
  * exists for A/B measurement.  Also read once from the environment variable AGPT_B200_ATTN_IMPL. */
 int agpt_b200_set_attn_impl(int impl);
 
-/* Selects between the two tensor-core kernel pairs for a float32 KV store and head_dim 32.  whole_tile 1 (default):
- * forward and backward keep the tile's Q (and dO) rows and all its key rows in shared memory, converted once to
- * split half precision (x * 2^e = hi + lo, fp16 each, e per tile, head and tensor; three m16n8k16 products give the
- * accuracy of three TF32 products), every fragment one ldmatrix, and the backward's warps run independent row and
- * key items with no barrier in their loops.  Used whenever four blocks of the backward fit one SM (about 150 keys
- * per tile, i.e. depth <= ~90); deeper plans, other head sizes and a bf16 store take the chunked TF32 kernels.
- * whole_tile 0: always the chunked kernels.  bwd_warps = 4 (default), 6 or 8 warps per block of the whole-tile
- * backward.  Same results within the parity tolerance either way; the switch exists for A/B measurement.  Also read
- * once from AGPT_B200_ATTN_TILE and AGPT_B200_BWD_WARPS. */
+/* Selects between the two tensor-core kernel pairs for a float32 KV store and head_dim 32 or 64.  whole_tile 1
+ * (default): forward and backward keep the tile's Q (and dO) rows and all its key rows in shared memory, converted
+ * once to split half precision (x * 2^e = hi + lo, fp16 each, e per tile, head and tensor; three m16n8k16 products
+ * give the accuracy of three TF32 products), every fragment one ldmatrix, and the backward's warps run independent
+ * row and key items with no barrier in their loops.  Used whenever four (head_dim 32) or two (head_dim 64) blocks
+ * of the backward fit one SM, i.e. up to about 150 / 128 keys per tile (depth <= ~90 / 65); deeper plans, head_dim 16
+ * and a bf16 store take the chunked TF32 kernels.  whole_tile 0: always the chunked kernels.  bwd_warps = 4
+ * (default), 6 or 8 warps per block of the whole-tile backward, 3 = four warps with three blocks per SM.  Same
+ * results within the parity tolerance either way; the switch exists for A/B measurement.  Also read once from
+ * AGPT_B200_ATTN_TILE and AGPT_B200_BWD_WARPS. */
 int agpt_b200_set_attn_variant(int whole_tile, int bwd_warps);
 
 /* No counterpart in the reference.  agpt_b200_attn_bwd for callers that cannot allocate device memory
@@ -446,9 +470,12 @@ int agpt_b200_loss_per_node(const float *d_logits, const int32_t *d_node_ids, co
  * gpu_attention_backward_depth do around the kernels, src/agpt/batched_depth_forward.cr:745-823,
  * src/agpt/batched_depth_backward.cr:453-500): uploads q, k, v, d_out from host memory, runs forward
  * and backward, downloads out, lse, dq, dk, dv.  Upload, compute and download run as a pipeline over row chunks
- * on three internal streams (pinned host memory lets them overlap); the call returns when everything is on the
- * host.  The device arena is allocated at the first call on a plan and kept until agpt_b200_plan_destroy, so one
- * plan must not be used by two host threads at once. */
+ * on three internal streams; the call returns when everything is on the host.  The overlap needs page-locked host
+ * buffers (cudaHostAlloc / cudaHostRegister): with pageable memory every copy is staged by the driver and blocks the
+ * host thread, so the three stages run one after the other (results are the same).  If a step fails midway the
+ * call waits for the copies already queued before it returns the error, so the host buffers are never touched
+ * after the call has returned.  The device arena is allocated at the first call on a plan and kept until
+ * agpt_b200_plan_destroy, so one plan must not be used by two host threads at once. */
 int agpt_b200_attn_fwd_bwd_host(const agpt_plan *p, const float *h_q, const float *h_k, const float *h_v,
                                 const float *h_dout, float *h_out, float *h_lse, float *h_dq, float *h_dk,
                                 float *h_dv, int kv_dtype, int n_heads, int head_dim, float scale);

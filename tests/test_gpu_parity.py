@@ -583,3 +583,23 @@ def test_gradient_modes_match_oracle(cuda, mode, acc, hd, tile):
             A.attn_backward(plan, tq, tk, tv, o, lse, tg, H, grad_mode="own_edge")          # edge_first missing
         with pytest.raises(A.AgptError):
             A.attn_backward(plan, tq, tk, tv, o, lse, tg, H, grad_mode="ancestors")
+
+
+def test_injected_repeats_deep_trie_bf16_store(cuda, attn_impl):
+    """Miniature of the deep configuration: a corpus with injected verbatim repeats, depth-128 radix trie pruned at
+    count < 2, bf16 KV store, 64-wide heads.  Chains reach depth 128, so a tile holds up to 191 keys (the chunked
+    tensor-core kernels; the whole-tile kernels take neither a bf16 store nor 64-wide heads)."""
+    corpus = A.synth_markov_corpus(6_000, 12, 2, 3, 6)
+    trie = A.RadixTrie.build(corpus, 128, 1, 2, 1)
+    parent, token, depth, _ = trie.char_tree()
+    assert int(depth.max()) == 128 and parent.size > 50_000 and int((depth >= 100).sum()) > 5_000
+    n, H, hd = parent.size, 2, 64
+    q, k, v, go = random_qkv(n, H * hd, 41)
+    plan, (out, lse, dq, dk, dv) = _run_native(parent, H, hd, q, k, v, go, cuda, 64, bf16=True)
+    assert plan.max_depth == 128
+    ref = _oracle(parent, H, hd, q, _bf16_round(k), _bf16_round(v), go)        # the oracle on the rounded store
+    for got, want in zip((out, dq, dk, dv), ref[:4]):
+        assert rel_err(got, want) < 2e-3
+    ref32 = _oracle(parent, H, hd, q, k, v, go)                                # and within the bf16 tolerance of the float32 oracle
+    for got, want in zip((out, dq, dk, dv), ref32[:4]):
+        assert rel_err(got, want) < TOL_BF16
