@@ -1726,9 +1726,10 @@ static int launch_fwd_mma(const agpt_plan *p, const float *q, const void *k, con
 
 static int fwd_dispatch(const agpt_plan *p, const float *q, const void *k, const void *v, int kv_dtype, float *out,
                         float *lse, int H, int head_dim, float scale, cudaStream_t st, int tile0, int ntiles) {
-    if (attn_impl() == 1 && p->tile_m == 64 && kv_dtype == AGPT_KV_F32 && bwd_tile_enabled() && tile_kernels_fit(p, head_dim))
-        return head_dim == 32 ? launch_fwd_tile<32, 5>(p, q, k, v, out, lse, H, scale, st, tile0, ntiles)
-                              : launch_fwd_tile<64, 2>(p, q, k, v, out, lse, H, scale, st, tile0, ntiles);
+    // head_dim 64: the whole-tile forward (two blocks per SM) measured slower than the chunked one (17.5 vs 15.0 ms on the
+    // 4M-node microbenchmark), the whole-tile backward faster (37.7 vs 50.3 ms): the forward stays chunked there
+    if (attn_impl() == 1 && p->tile_m == 64 && kv_dtype == AGPT_KV_F32 && head_dim == 32 && bwd_tile_enabled() && tile_kernels_fit(p, head_dim))
+        return launch_fwd_tile<32, 5>(p, q, k, v, out, lse, H, scale, st, tile0, ntiles);
     if (attn_impl() == 1 && p->tile_m == 64 && p->max_depth + 64 <= MAXKEYS) {
         const bool bf = kv_dtype == AGPT_KV_BF16;
         switch (head_dim) {

@@ -76,9 +76,11 @@ def touch_once_bytes(n, D, H, kv_bytes):
 # DRAM bytes per position (dram__bytes_read.sum + dram__bytes_write.sum of one launch / positions of the launch) of
 # the forward kernel and of the backward kernel + reduction, from ncu captures of the reduced workloads (c2s for
 # d_model 128, micro_s for d_model 512; traffic grows in proportion to the positions).  Key: (d_model, kv store).
-# The captures are summarised in profiles/attn_mma_kernels_c2s_ncu_full.md (d_model 128, float32 store).
+# The captures are summarised in profiles/attn_tile_kernels_c2s_ncu_full.md (d_model 128, float32 store; the dK/dV
+# reduction adds 0.70 KB per position) and profiles/attn_kernels_micro_s_ncu_full.md (d_model 512, float32 store).
 DRAM_BYTES_PER_POSITION = {
     (128, "f32"): (2.18e3, 4.44e3),
+    (512, "f32"): (8.71e3, 17.5e3),
 }
 
 
