@@ -101,13 +101,26 @@ def bind_to_gpu_numa_node(index):
         bdf = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
         with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
             node = int(f.read().strip())
-        if node < 0:
-            return {"node": None, "bound": False, "why": "no NUMA node reported for the GPU"}
-        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
-            cpus = set()
-            for part in f.read().strip().split(","):
+        def cpu_set(text):
+            out = set()
+            for part in text.strip().split(","):
                 a, _, b = part.partition("-")
-                cpus.update(range(int(a), int(b or a) + 1))
+                out.update(range(int(a), int(b or a) + 1))
+            return out
+
+        if node < 0:
+            # sysfs has no node for the device (usual inside a container): ask the driver's topology table for the
+            # GPU's CPU affinity instead (read-only query)
+            topo = subprocess.run(["nvidia-smi", "topo", "-m"], capture_output=True, text=True, timeout=20).stdout.splitlines()
+            head = next(ln for ln in topo if "CPU Affinity" in ln)
+            cols = [c.strip() for c in head.split("\t")]
+            row = next(ln for ln in topo if ln.startswith(f"GPU{index}\t") or ln.startswith(f"GPU{index} "))
+            cells = [c.strip() for c in row.split("\t")]
+            cpus = cpu_set(cells[cols.index("CPU Affinity")])
+            node = cells[cols.index("NUMA Affinity")] if "NUMA Affinity" in cols else None
+        else:
+            with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+                cpus = cpu_set(f.read())
         allowed = os.sched_getaffinity(0) & cpus
         if not allowed:
             return {"node": node, "bound": False, "why": "none of the node's CPUs is in this process's affinity mask"}
@@ -279,7 +292,7 @@ def cpu_arm(units, cfg, budget_nodes, counts, steps=1, warmup=0):
     from oracle import pyoracle as O
     H, hd, V = cfg["heads"], cfg["head_dim"], cfg["vocab"]
     # launch groups from both ends of the size range in turn (largest, smallest, second largest, ...), as many as the budget holds
-    by_size = sorted(units, key=lambda x: -x.n)
+    by_size = sorted((u for u in units if u.n <= budget_nodes), key=lambda x: -x.n) or [min(units, key=lambda x: x.n)]
     order = []
     for i in range((len(by_size) + 1) // 2):
         order.append(by_size[i])
