@@ -75,6 +75,7 @@ SIGNATURES = {
     "cuda_layer_norm_backward": (None, [vp] * 7 + [C.c_int, C.c_int]),
     "agpt_b200_layer_norm_fwd": (C.c_int, [vp] * 6 + [i64, C.c_int, vp]),
     "agpt_b200_layer_norm_bwd": (C.c_int, [vp] * 7 + [i64, C.c_int, vp, i64, vp]),
+    "agpt_b200_layer_norm_bwd_add": (C.c_int, [vp] * 8 + [i64, C.c_int, vp, i64, vp]),
     "agpt_b200_layer_norm_bwd_workspace_bytes": (i64, [i64, C.c_int]),
     "cuda_bias_add": (None, [vp, vp, C.c_int, C.c_int]),
     "cuda_fused_bias_relu": (None, [vp] * 4 + [C.c_int, C.c_int]),

@@ -422,16 +422,21 @@ def layer_norm_forward(x, gamma, beta):
     return y, norm, sinv
 
 
-def layer_norm_backward(grad, norm, sinv, gamma, dgamma, dbeta):
-    """dx (returned); dgamma and dbeta are accumulated into."""
+def layer_norm_backward(grad, norm, sinv, gamma, dgamma, dbeta, add=None):
+    """dx (returned); dgamma and dbeta are accumulated into.  add [rows, cols]: a gradient added to dx in the same
+    pass (what reaches the same rows by the residual path)."""
     import torch
     _chk_f32(grad, "grad")
     rows, cols = grad.shape
+    if add is not None:
+        _chk_f32(add, "add")
+        if tuple(add.shape) != (rows, cols):
+            raise AgptError("layer_norm_backward: add has another shape than grad")
     dx = torch.empty_like(grad)
     wsb = check(lib().agpt_b200_layer_norm_bwd_workspace_bytes(rows, cols), "layer_norm_bwd_workspace_bytes")
     ws = torch.empty(wsb, dtype=torch.uint8, device=grad.device)
-    check(lib().agpt_b200_layer_norm_bwd(_dp(grad), _dp(norm), _dp(sinv), _dp(gamma), _dp(dx), _dp(dgamma), _dp(dbeta), rows,
-                                         cols, _dp(ws), wsb, _stream()), "layer_norm_bwd")
+    check(lib().agpt_b200_layer_norm_bwd_add(_dp(grad), _dp(norm), _dp(sinv), _dp(gamma), _dp(add), _dp(dx), _dp(dgamma), _dp(dbeta),
+                                             rows, cols, _dp(ws), wsb, _stream()), "layer_norm_bwd")
     return dx
 
 

@@ -66,7 +66,8 @@ layer_norm_fwd_kernel(const float *__restrict__ x, float *__restrict__ y, float 
 template <int NV>
 __global__ void __launch_bounds__(LN_WARPS * 32)
 layer_norm_bwd_kernel(const float *grad, const float *__restrict__ norm, const float *__restrict__ std_inv,
-                      const float *__restrict__ gamma, float *dx, float *__restrict__ partial, int64_t rows, int cols) {
+                      const float *__restrict__ gamma, const float *add, float *dx, float *__restrict__ partial, int64_t rows,
+                      int cols) {
     extern __shared__ float s_part[];      // [LN_WARPS][2][cols]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, c4n = cols >> 2;
     float4 gam[NV], ag[NV], ab[NV];
@@ -99,9 +100,11 @@ layer_norm_bwd_kernel(const float *grad, const float *__restrict__ norm, const f
         for (int k = 0; k < NV; k++) {
             const int c4 = lane + 32 * k;
             if (c4 >= c4n) continue;
+            // the gradient that reaches the same rows by the residual path (may be dx itself: read before written)
+            const float4 a = add ? __ldcs(reinterpret_cast<const float4 *>(add + r * cols) + c4) : make_float4(0.f, 0.f, 0.f, 0.f);
             reinterpret_cast<float4 *>(dx + r * cols)[c4] =
-                make_float4((g[k].x - m1 - nm[k].x * m2) * sinv, (g[k].y - m1 - nm[k].y * m2) * sinv,
-                            (g[k].z - m1 - nm[k].z * m2) * sinv, (g[k].w - m1 - nm[k].w * m2) * sinv);
+                make_float4((g[k].x - m1 - nm[k].x * m2) * sinv + a.x, (g[k].y - m1 - nm[k].y * m2) * sinv + a.y,
+                            (g[k].z - m1 - nm[k].z * m2) * sinv + a.z, (g[k].w - m1 - nm[k].w * m2) * sinv + a.w);
         }
     }
     // warps -> block, in warp order
@@ -178,6 +181,13 @@ extern "C" int agpt_b200_layer_norm_fwd(const float *d_x, float *d_y, float *d_n
 extern "C" int agpt_b200_layer_norm_bwd(const float *d_grad, const float *d_norm, const float *d_std_inv, const float *d_gamma,
                                         float *d_dx, float *d_dgamma, float *d_dbeta, int64_t rows, int cols, void *d_workspace,
                                         int64_t workspace_bytes, void *stream) {
+    return agpt_b200_layer_norm_bwd_add(d_grad, d_norm, d_std_inv, d_gamma, nullptr, d_dx, d_dgamma, d_dbeta, rows, cols, d_workspace,
+                                        workspace_bytes, stream);
+}
+
+extern "C" int agpt_b200_layer_norm_bwd_add(const float *d_grad, const float *d_norm, const float *d_std_inv, const float *d_gamma,
+                                            const float *d_add, float *d_dx, float *d_dgamma, float *d_dbeta, int64_t rows, int cols,
+                                            void *d_workspace, int64_t workspace_bytes, void *stream) {
     int rc = ln_check(rows, cols, "layer_norm_bwd");
     if (rc) return rc;
     if (!d_grad || !d_norm || !d_std_inv || !d_gamma || !d_dx || !d_dgamma || !d_dbeta || !d_workspace)
@@ -194,7 +204,7 @@ extern "C" int agpt_b200_layer_norm_bwd(const float *d_grad, const float *d_norm
     do {                                                                                                               \
         cudaError_t e_ = cudaFuncSetAttribute(layer_norm_bwd_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         if (e_ != cudaSuccess) return agpt_set_error(AGPT_E_CUDA, "layer_norm_bwd: %s", cudaGetErrorString(e_));       \
-        layer_norm_bwd_kernel<NV><<<(unsigned)n_blocks, LN_WARPS * 32, smem, st>>>(d_grad, d_norm, d_std_inv, d_gamma, d_dx, partial, rows, cols); \
+        layer_norm_bwd_kernel<NV><<<(unsigned)n_blocks, LN_WARPS * 32, smem, st>>>(d_grad, d_norm, d_std_inv, d_gamma, d_add, d_dx, partial, rows, cols); \
     } while (0)
     if (nv <= 1) LN_BWD(1); else if (nv <= 2) LN_BWD(2); else if (nv <= 4) LN_BWD(4); else LN_BWD(8);
 #undef LN_BWD

@@ -5,8 +5,11 @@
 // accuracy of the reference's cublasSgemm calls (src/cuda/agpt_train.cu:4675-4683, :4752, :4766-4771, :4803,
 // :4840-5061) at several times their speed.  The kernel is CUTLASS's SM100 warp-specialised "fast FP32" mainloop
 // (TMA load warp -> transform warps -> MMA warp -> epilogue warps), instantiated here for one CTA per tile
-// (no cluster multicast), a 128x128x16 tile, and three epilogues: bias row; bias row + ReLU (the first
+// (no cluster multicast), a 128x128x32 tile, and three epilogues: bias row; bias row + ReLU (the first
 // feed-forward projection); bias row + a source matrix (the residual stream added in the same pass).
+// Measured on a B200, [1M, 128] x [128, 128]: the builder's defaults (k extent 16, all nine partial products, the
+// accumulator read out of tensor memory after every k block of 16) 0.332 ms; six products 0.316 ms; six products,
+// k extent 32 and a read-out every second k block 0.263 ms (3.9 TB/s of compulsory traffic).
 #include <cuda_runtime.h>
 
 #include "../../include/agpt_b200.h"
@@ -30,9 +33,38 @@ using Col = cutlass::layout::ColumnMajor;
 
 enum { EPI_BIAS = 0, EPI_BIAS_RELU = 1, EPI_BIAS_SOURCE = 2 };
 
+// The builder fixes the mainloop at all five significance bands of the 3 x 3 bf16 partial products (nine MMAs per
+// k block).  The two lowest bands (a1 b2, a2 b1, a2 b2) are below 2^-24 of the product, the rounding of the float32
+// accumulation itself, so the mainloop is re-instantiated with the same stage counts, layouts and copies,
+// BANDS = 3 (six MMAs per k block) and a longer promotion interval: the accumulator warps read the whole
+// 128 x 128 tile out of tensor memory and add it in registers once per interval, which bounds the loop when the
+// interval is one k block.
+#ifndef AGPT_GEMM_BANDS
+#define AGPT_GEMM_BANDS 3      // 3, 4 or 5 bands of partial products (6, 8 or 9 MMAs per k block)
+#endif
+#ifndef AGPT_GEMM_TILE_K
+#define AGPT_GEMM_TILE_K 32    // k extent of one pipeline stage (64 leaves fewer than two stages of shared memory)
+#endif
+#ifndef AGPT_GEMM_PROMOTE
+#define AGPT_GEMM_PROMOTE 2    // k blocks (of 16) summed in tensor memory before the accumulator warps add them in registers
+#endif
+
+template <typename Built, int BANDS, int PROMOTE>
+struct WithBands {
+    using P0 = typename Built::DispatchPolicy;
+    using Policy = cutlass::gemm::MainloopSm100TmaUmmaWarpSpecializedFastF32<
+        P0::Load2TransformPipelineStageCount, P0::Transform2MmaPipelineStageCount, P0::Schedule::SchedulerPipelineStageCount,
+        P0::Schedule::AccumulatorPipelineStageCount, BANDS, P0::ScalingFactor, PROMOTE, typename P0::ClusterShape,
+        typename P0::AccumulatorCopyAtom, typename P0::ArchTag>;
+    using type = cutlass::gemm::collective::CollectiveMma<
+        Policy, typename Built::TileShape, float, typename Built::StrideA, float, typename Built::StrideB, typename Built::TiledMma,
+        typename Built::GmemTiledCopyA, typename Built::SmemLayoutAtomsA, typename Built::CopyAtomsA, typename Built::TransformA,
+        typename Built::GmemTiledCopyB, typename Built::SmemLayoutAtomsB, typename Built::CopyAtomsB, typename Built::TransformB>;
+};
+
 template <typename LayoutA, typename LayoutB, int EPI = EPI_BIAS>
 struct Sm100Gemm {
-    using TileShape = Shape<_128, _128, _16>;
+    using TileShape = Shape<_128, _128, Int<AGPT_GEMM_TILE_K>>;
     using ClusterShape = Shape<_1, _1, _1>;
     // D = act(alpha * acc + beta * C + bias[column]); without a source matrix none is read (ElementC = void)
     using Fusion = cute::conditional_t<EPI == EPI_BIAS_RELU,
@@ -42,10 +74,11 @@ struct Sm100Gemm {
     using Epilogue = typename cutlass::epilogue::collective::CollectiveBuilder<
         cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, TileShape, ClusterShape, cutlass::epilogue::collective::EpilogueTileAuto,
         float, float, ElementC, Row, 4, float, Row, 4, cutlass::epilogue::TmaWarpSpecialized1Sm, Fusion>::CollectiveOp;
-    using Mainloop = typename cutlass::gemm::collective::CollectiveBuilder<
+    using Built = typename cutlass::gemm::collective::CollectiveBuilder<
         cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, float, LayoutA, 4, float, LayoutB, 4, float, TileShape, ClusterShape,
         cutlass::gemm::collective::StageCountAutoCarveout<static_cast<int>(sizeof(typename Epilogue::SharedStorage))>,
         cutlass::gemm::KernelTmaWarpSpecialized1SmFastFP32Sm100>::CollectiveOp;
+    using Mainloop = typename WithBands<Built, AGPT_GEMM_BANDS, AGPT_GEMM_PROMOTE>::type;
     using Kernel = cutlass::gemm::kernel::GemmUniversal<Shape<int, int, int, int>, Mainloop, Epilogue, void>;
     using Gemm = cutlass::gemm::device::GemmUniversalAdapter<Kernel>;
 };
@@ -103,12 +136,14 @@ int run(int M, int N, int K, int L, float alpha, const float *A, int64_t lda, in
 
 }  // namespace
 
-// which (layout, epilogue) pairs are instantiated: every layout with the bias epilogue; the ReLU and source epilogues
-// only for the forward projection layout (A and B as stored)
+// which (layout, epilogue) pairs are instantiated: every layout with the bias epilogue; the ReLU epilogue for the
+// forward projection layout (A and B as stored); the source epilogue for that layout and for A * B^T (the input
+// gradient of a projection accumulated onto the gradient of another one that read the same rows)
 bool agpt_gemm_sm100_takes(int trans_a, int trans_b, int relu, int has_source) {
     if (trans_a && trans_b) return false;
     if (relu && has_source) return false;
-    return (!relu && !has_source) || (!trans_a && !trans_b);
+    if (has_source) return !trans_a;
+    return !relu || (!trans_a && !trans_b);
 }
 
 // D[l] = act(alpha * op(A[l]) * op(B[l]) + beta * C + bias), l < L; row-major storage, op as in agpt_b200_gemm_f32
@@ -123,7 +158,10 @@ int agpt_gemm_sm100(int trans_a, int trans_b, int M, int N, int K, int L, float 
         if (C) return run<Sm100Gemm<Row, Row, EPI_BIAS_SOURCE>>(M, N, K, L, alpha, A, lda, batch_a, B, ldb, batch_b, bias, beta, C, ldc, D, ldd, batch_d, st);
         return run<Sm100Gemm<Row, Row>>(M, N, K, L, alpha, A, lda, batch_a, B, ldb, batch_b, bias, 0.f, nullptr, ldd, D, ldd, batch_d, st);
     }
-    if (!trans_a && trans_b) return run<Sm100Gemm<Row, Col>>(M, N, K, L, alpha, A, lda, batch_a, B, ldb, batch_b, bias, 0.f, nullptr, ldd, D, ldd, batch_d, st);
+    if (!trans_a && trans_b) {
+        if (C) return run<Sm100Gemm<Row, Col, EPI_BIAS_SOURCE>>(M, N, K, L, alpha, A, lda, batch_a, B, ldb, batch_b, bias, beta, C, ldc, D, ldd, batch_d, st);
+        return run<Sm100Gemm<Row, Col>>(M, N, K, L, alpha, A, lda, batch_a, B, ldb, batch_b, bias, 0.f, nullptr, ldd, D, ldd, batch_d, st);
+    }
     return run<Sm100Gemm<Col, Row>>(M, N, K, L, alpha, A, lda, batch_a, B, ldb, batch_b, bias, 0.f, nullptr, ldd, D, ldd, batch_d, st);
 }
 #endif  // AGPT_NO_CUTLASS

@@ -50,6 +50,11 @@ class LaunchGroup:
         starts |= np.concatenate([[True], unit_of_row[1:] != unit_of_row[:-1]])
         self.n_units = int(unit_of_row.max()) + 1 if self.n else 0
         self.unit_of_row = t(unit_of_row)
+        # rows of a unit are consecutive in every group build_groups makes: per-unit sums are then differences of a
+        # running sum at these offsets (no scattered adds)
+        self.unit_off = None
+        if self.n and np.all(unit_of_row[1:] >= unit_of_row[:-1]):
+            self.unit_off = t(np.searchsorted(unit_of_row, np.arange(self.n_units + 1)).astype(np.int64))
         qoff = np.concatenate([np.nonzero(starts)[0], [self.n]]).astype(np.int32)
         rid = radix_of[starts].astype(np.int32)
         self.q2n = t((np.cumsum(starts) - 1).astype(np.int32))
@@ -129,6 +134,70 @@ def _layer_norm_function():
     return RowLayerNorm
 
 
+def _norm_skip_function():
+    import torch
+
+    class NormWithSkip(torch.autograd.Function):
+        """Layer norm of the residual stream x, returned together with x for the skip connection.  The two gradients
+        that come back -- through the normalised rows and through the skip -- are added inside the layer-norm
+        backward kernel instead of in a pass of their own (the reference's launch_elem_add after each
+        cuda_layer_norm_backward, src/cuda/agpt_train.cu:4907-4909, :5066-5068)."""
+
+        @staticmethod
+        def forward(ctx, x, gamma, beta):
+            x = x.contiguous()
+            y, norm, sinv = A.layer_norm_forward(x, gamma.contiguous(), beta.contiguous())
+            ctx.save_for_backward(norm, sinv, gamma)
+            return y, x.view_as(x)
+
+        @staticmethod
+        def backward(ctx, grad, grad_skip):
+            norm, sinv, gamma = ctx.saved_tensors
+            dgamma, dbeta = torch.zeros_like(gamma), torch.zeros_like(gamma)
+            add = None if grad_skip is None else grad_skip.contiguous()
+            if grad is None:
+                return add, dgamma, dbeta
+            dx = A.layer_norm_backward(grad.contiguous(), norm, sinv, gamma.contiguous(), dgamma, dbeta, add=add)
+            return dx, dgamma, dbeta
+
+    return NormWithSkip
+
+
+def _weight_grad(x, grad, w):
+    """x^T grad with the row dimension cut into slices that are summed in a fixed order."""
+    tiles = -(-w.shape[0] // 128) * -(-w.shape[1] // 128)
+    split_k = max(1, min(x.shape[0] // 2048, -(-296 // tiles)))
+    return A.gemm_f32(x, grad, trans_a=True, split_k=split_k)
+
+
+def _qkv_function():
+    import torch
+
+    class QKVProjection(torch.autograd.Function):
+        """q, k, v = x W + b for the three projections that read the same normalised rows
+        (src/cuda/agpt_train.cu:4675-4683).  Backward (:5026-5061): the three input gradients are accumulated by the GEMMs
+        themselves (the second and third take the running sum as their source matrix and write it back in place)."""
+
+        @staticmethod
+        def forward(ctx, x, wq, bq, wk, bk, wv, bv):
+            x = x.contiguous()
+            ctx.save_for_backward(x, wq, wk, wv)
+            return A.gemm_f32(x, wq, bias=bq), A.gemm_f32(x, wk, bias=bk), A.gemm_f32(x, wv, bias=bv)
+
+        @staticmethod
+        def backward(ctx, dq, dk, dv):
+            x, wq, wk, wv = ctx.saved_tensors
+            dx, out = None, []
+            for g, w in ((dq, wq), (dk, wk), (dv, wv)):
+                g = g.contiguous()
+                db, _ = A.col_sum(g)
+                dx = A.gemm_f32(g, w, trans_b=True, residual=dx, out=dx)
+                out += [_weight_grad(x, g, w), db]
+            return (dx, *out)
+
+    return QKVProjection
+
+
 def _linear_function():
     import torch
 
@@ -154,10 +223,7 @@ def _linear_function():
             else:
                 db, _ = A.col_sum(grad)
             dx = A.gemm_f32(grad, w, trans_b=True)
-            tiles = -(-w.shape[0] // 128) * -(-w.shape[1] // 128)
-            split_k = max(1, min(x.shape[0] // 2048, -(-296 // tiles)))
-            dw = A.gemm_f32(x, grad, trans_a=True, split_k=split_k)
-            return dx, dw, db, None, (grad if ctx.has_residual else None)
+            return dx, _weight_grad(x, grad, w), db, None, (grad if ctx.has_residual else None)
 
     return TensorLinear
 
@@ -223,6 +289,8 @@ class TrieWalkModel:
         self.embed = _embedding_function()
         self.ln = _layer_norm_function()
         self.linear = _linear_function()
+        self.norm_skip = _norm_skip_function()
+        self.qkv = _qkv_function()
         self.dense_impl = "tensor"       # "tensor": the library's 3xTF32 GEMM; "torch": torch.addmm (cuBLAS float32)
         self.ffn_recompute = False       # True: recompute the d_ff-wide activations in the backward instead of keeping them
         # which attention pairs feed dK/dV: "full" (persistent accumulators, src/agpt/incremental_backward.cr), "local_depth"
@@ -262,17 +330,28 @@ class TrieWalkModel:
         def ffn(x, g2, b2, w1, b1, w2, bo):
             return lin(lin(ln(x, g2, b2), w1, b1, relu=True), w2, bo, residual=x)
 
+        fused = self.dense_impl == "tensor" and m.d_model % 4 == 0 and m.d_ff % 4 == 0
         x = self.embed.apply(P["token_emb"], group.tokens32)
         for l in range(m.n_layers):
             g = lambda n: P[f"layer{l}.{n}"]  # noqa: E731
-            x1 = ln(x, g("ln1.gamma")[0], g("ln1.beta")[0])
-            q = lin(x1, g("wq.w"), g("wq.b")[0])
-            k = lin(x1, g("wk.w"), g("wk.b")[0])
-            v = lin(x1, g("wv.w"), g("wv.b")[0])
+            if fused:
+                x1, skip = self.norm_skip.apply(x, g("ln1.gamma")[0], g("ln1.beta")[0])
+                q, k, v = self.qkv.apply(x1, g("wq.w"), g("wq.b")[0], g("wk.w"), g("wk.b")[0], g("wv.w"), g("wv.b")[0])
+            else:
+                x1, skip = ln(x, g("ln1.gamma")[0], g("ln1.beta")[0]), x
+                q = lin(x1, g("wq.w"), g("wq.b")[0])
+                k = lin(x1, g("wk.w"), g("wk.b")[0])
+                v = lin(x1, g("wv.w"), g("wv.b")[0])
             a = self.attn.apply(q, k, v, group, self.cos, self.sin, m.n_heads, bf16_store, self.grad_mode)
-            x = lin(a, g("wo.w"), g("wo.b")[0], residual=x)
+            x = lin(a, g("wo.w"), g("wo.b")[0], residual=skip)
             args = (x, g("ln2.gamma")[0], g("ln2.beta")[0], g("l1.w"), g("l1.b")[0], g("l2.w"), g("l2.b")[0])
-            x = checkpoint(ffn, *args, use_reentrant=False) if self.ffn_recompute else ffn(*args)
+            if self.ffn_recompute:
+                x = checkpoint(ffn, *args, use_reentrant=False)
+            elif fused:
+                x2, skip = self.norm_skip.apply(x, args[1], args[2])
+                x = lin(lin(x2, args[3], args[4], relu=True), args[5], args[6], residual=skip)
+            else:
+                x = ffn(*args)
         xf = ln(x, P["final.gamma"][0], P["final.beta"][0])
         w, b = P["out.w"], P["out.b"][0]
         pad = (-m.vocab) % 4
@@ -309,7 +388,11 @@ class TrieWalkModel:
         loss_sum = torch.where(pos, loss, torch.zeros_like(loss)).sum(dtype=torch.float64)
         # every gradient row is scaled by 1 / (trained queries of its unit): the reference's per-chunk scaling
         # (src/cuda/agpt_train.cu:4834) with the unit as the chunk
-        per_unit = torch.zeros(group.n_units, dtype=torch.float32, device=loss.device).index_add_(0, group.unit_of_row, pos.to(torch.float32))
+        if group.unit_off is not None:
+            run = torch.nn.functional.pad(torch.cumsum(pos, 0, dtype=torch.int32), (1, 0))
+            per_unit = (run[group.unit_off[1:]] - run[group.unit_off[:-1]]).to(torch.float32)
+        else:
+            per_unit = torch.zeros(group.n_units, dtype=torch.float32, device=loss.device).index_add_(0, group.unit_of_row, pos.to(torch.float32))
         scale = torch.where(per_unit > 0, 1.0 / per_unit.clamp(min=1.0), torch.zeros_like(per_unit))
         logits.backward(dlogits * scale[group.unit_of_row][:, None])
         if sync:

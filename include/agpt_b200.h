@@ -293,6 +293,12 @@ int agpt_b200_layer_norm_fwd(const float *d_x, float *d_y, float *d_norm, float 
 int agpt_b200_layer_norm_bwd(const float *d_grad, const float *d_norm, const float *d_std_inv, const float *d_gamma,
                              float *d_dx, float *d_dgamma, float *d_dbeta, int64_t rows, int cols, void *d_workspace,
                              int64_t workspace_bytes, void *stream);
+/* The same with d_add[rows, cols] (NULL: none) added to dx: the gradient that reaches the normalised rows' input by
+ * the residual path (the reference adds the two in its own pass, src/cuda/agpt_train.cu:4907-4909, :5066-5068).
+ * d_add may be d_dx. */
+int agpt_b200_layer_norm_bwd_add(const float *d_grad, const float *d_norm, const float *d_std_inv, const float *d_gamma,
+                                 const float *d_add, float *d_dx, float *d_dgamma, float *d_dbeta, int64_t rows, int cols,
+                                 void *d_workspace, int64_t workspace_bytes, void *stream);
 int64_t agpt_b200_layer_norm_bwd_workspace_bytes(int64_t rows, int cols);
 
 /* Replace the row-wise kernels of the reference's kernel dependency (declared src/cuda/agpt_train.cu:48-49,
