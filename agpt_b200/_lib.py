@@ -113,6 +113,7 @@ SIGNATURES = {
     "agpt_b200_set_gemm_impl": (C.c_int, [C.c_int]),
     "agpt_b200_rope_table": (C.c_int, [vp, vp, C.c_int, C.c_int, f32]),
     "agpt_b200_rope": (C.c_int, [vp, vp, vp, vp, i64, C.c_int, C.c_int, C.c_int, vp]),
+    "agpt_b200_rope_pair": (C.c_int, [vp, vp, vp, vp, vp, i64, C.c_int, C.c_int, C.c_int, vp]),
     "agpt_b200_kv_store_write_bf16": (C.c_int, [vp, vp, i64, C.c_int, vp]),
     "agpt_b200_attn_fwd": (C.c_int, [vp, vp, vp, vp, C.c_int, vp, vp, C.c_int, C.c_int, f32, vp]),
     "agpt_b200_attn_bwd": (C.c_int, [vp, vp, vp, vp, C.c_int, vp, vp, vp, vp, vp, vp, vp, i64, C.c_int, C.c_int, f32, vp]),

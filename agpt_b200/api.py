@@ -380,6 +380,18 @@ def rope_(x, pos, cos, sin, n_heads: int, inverse: bool = False):
     return x
 
 
+def rope_pair_(a, b, pos, cos, sin, n_heads: int, inverse: bool = False):
+    """rope_ of two matrices of one shape (q and k, or their gradients) in one launch."""
+    _chk_f32(a, "a")
+    _chk_f32(b, "b")
+    if a.shape != b.shape:
+        raise AgptError("rope_pair_: the two matrices differ in shape")
+    hd = a.shape[1] // n_heads
+    check(lib().agpt_b200_rope_pair(_dp(a), _dp(b), _dp(pos), _dp(cos), _dp(sin), a.shape[0], n_heads, hd, int(inverse), _stream()),
+          "rope_pair")
+    return a, b
+
+
 _gemm_ws = {}
 
 

@@ -1916,14 +1916,63 @@ __global__ void rope_kernel(float *__restrict__ x, const int32_t *__restrict__ p
     else *px = make_float2(v.x * c + v.y * s, -v.x * s + v.y * c);
 }
 
-extern "C" int agpt_b200_rope(float *d_x, const int32_t *d_pos, const float *d_cos, const float *d_sin, int64_t n, int n_heads,
-                              int head_dim, int inverse, void *stream) {
-    if (!d_x || !d_pos || !d_cos || !d_sin || n < 0 || n_heads < 1 || head_dim < 2 || head_dim % 2)
+// Four columns (two rotation pairs) per thread and step, ROPE_ROWS rows per block, one or two matrices that share
+// the row positions (q and k, or dq and dk): every thread has several independent 16-byte loads in flight and the
+// position and table reads are shared between the two matrices.
+#define ROPE_ROWS 32
+template <bool TWO>
+__global__ void __launch_bounds__(256)
+rope4_kernel(float *a, float *b, const int32_t *__restrict__ pos, const float *__restrict__ cosv, const float *__restrict__ sinv,
+             int64_t n, int D, int hd, int inverse) {
+    const int q4n = D >> 2;
+    const int64_t row0 = (int64_t)blockIdx.x * ROPE_ROWS;
+    const int rows = (int)(n - row0 < ROPE_ROWS ? n - row0 : ROPE_ROWS);
+    const float sign = inverse ? -1.f : 1.f;
+    for (int t = threadIdx.x; t < rows * q4n; t += 256) {
+        const int r = t / q4n, c = (t - r * q4n) << 2;
+        const int64_t off = (row0 + r) * D + c;
+        const int tab = __ldg(pos + row0 + r) * hd + (c % hd);
+        const float4 cs = __ldg(reinterpret_cast<const float4 *>(cosv + tab));
+        float4 sn = __ldg(reinterpret_cast<const float4 *>(sinv + tab));
+        sn.x *= sign; sn.z *= sign;
+        float4 v = __ldcs(reinterpret_cast<const float4 *>(a + off));
+        __stcs(reinterpret_cast<float4 *>(a + off),
+               make_float4(v.x * cs.x - v.y * sn.x, v.x * sn.x + v.y * cs.x, v.z * cs.z - v.w * sn.z, v.z * sn.z + v.w * cs.z));
+        if (TWO) {
+            v = __ldcs(reinterpret_cast<const float4 *>(b + off));
+            __stcs(reinterpret_cast<float4 *>(b + off),
+                   make_float4(v.x * cs.x - v.y * sn.x, v.x * sn.x + v.y * cs.x, v.z * cs.z - v.w * sn.z, v.z * sn.z + v.w * cs.z));
+        }
+    }
+}
+
+static int rope_launch(float *d_a, float *d_b, const int32_t *d_pos, const float *d_cos, const float *d_sin, int64_t n, int n_heads,
+                       int head_dim, int inverse, cudaStream_t st) {
+    if (!d_a || !d_pos || !d_cos || !d_sin || n < 0 || n_heads < 1 || head_dim < 2 || head_dim % 2)
         return agpt_set_error(AGPT_E_ARG, "rope: bad argument");
     if (n == 0) return AGPT_OK;
+    const bool vec = head_dim % 4 == 0 && (((uintptr_t)d_a | (uintptr_t)d_b | (uintptr_t)d_cos | (uintptr_t)d_sin) & 15) == 0;
+    if (vec) {
+        const unsigned blocks = (unsigned)((n + ROPE_ROWS - 1) / ROPE_ROWS);
+        if (d_b) rope4_kernel<true><<<blocks, 256, 0, st>>>(d_a, d_b, d_pos, d_cos, d_sin, n, n_heads * head_dim, head_dim, inverse);
+        else rope4_kernel<false><<<blocks, 256, 0, st>>>(d_a, nullptr, d_pos, d_cos, d_sin, n, n_heads * head_dim, head_dim, inverse);
+        return launch_status("rope");
+    }
     int64_t total = n * n_heads * (head_dim / 2);
-    rope_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(d_x, d_pos, d_cos, d_sin, n, n_heads, head_dim, inverse);
+    rope_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(d_a, d_pos, d_cos, d_sin, n, n_heads, head_dim, inverse);
+    if (d_b) rope_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(d_b, d_pos, d_cos, d_sin, n, n_heads, head_dim, inverse);
     return launch_status("rope");
+}
+
+extern "C" int agpt_b200_rope(float *d_x, const int32_t *d_pos, const float *d_cos, const float *d_sin, int64_t n, int n_heads,
+                              int head_dim, int inverse, void *stream) {
+    return rope_launch(d_x, nullptr, d_pos, d_cos, d_sin, n, n_heads, head_dim, inverse, (cudaStream_t)stream);
+}
+
+extern "C" int agpt_b200_rope_pair(float *d_a, float *d_b, const int32_t *d_pos, const float *d_cos, const float *d_sin, int64_t n,
+                                   int n_heads, int head_dim, int inverse, void *stream) {
+    if (!d_b) return agpt_set_error(AGPT_E_ARG, "rope_pair: bad argument");
+    return rope_launch(d_a, d_b, d_pos, d_cos, d_sin, n, n_heads, head_dim, inverse, (cudaStream_t)stream);
 }
 
 __global__ void store_bf16_kernel(const float *__restrict__ src, __nv_bfloat16 *__restrict__ dst, int64_t total4) {

@@ -238,8 +238,7 @@ def _attention_function():
         def forward(ctx, q, k, v, group, cos, sin, n_heads, bf16_store, grad_mode="full"):
             # q and k are rotated in place: they are fresh projection outputs that nothing else reads or saves
             q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-            A.rope_(q, group.pos, cos, sin, n_heads)
-            A.rope_(k, group.pos, cos, sin, n_heads)
+            A.rope_pair_(q, k, group.pos, cos, sin, n_heads)
             ks, vs = (A.kv_store_write_bf16(k), A.kv_store_write_bf16(v)) if bf16_store else (k, v)
             out, lse = A.attn_forward(group.plan, q, ks, vs, n_heads)
             ctx.save_for_backward(q, ks, vs, out, lse)
@@ -251,8 +250,7 @@ def _attention_function():
             q, ks, vs, out, lse = ctx.saved_tensors
             dq, dk, dv = A.attn_backward(ctx.group.plan, q, ks, vs, out, lse, dout.contiguous(), ctx.n_heads,
                                          grad_mode=ctx.grad_mode, edge_first=ctx.group.edge_first)
-            A.rope_(dq, ctx.group.pos, ctx.cos, ctx.sin, ctx.n_heads, inverse=True)
-            A.rope_(dk, ctx.group.pos, ctx.cos, ctx.sin, ctx.n_heads, inverse=True)
+            A.rope_pair_(dq, dk, ctx.group.pos, ctx.cos, ctx.sin, ctx.n_heads, inverse=True)
             return dq, dk, dv, None, None, None, None, None, None
 
     return TrieAttention

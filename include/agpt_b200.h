@@ -277,6 +277,9 @@ int agpt_b200_rope_table(float *cos_out, float *sin_out, int max_seq, int head_d
  * x [n, n_heads*head_dim] rotated in place, pair (2i, 2i+1) of each head by pos[row]. */
 int agpt_b200_rope(float *d_x, const int32_t *d_pos, const float *d_cos, const float *d_sin, int64_t n,
                    int n_heads, int head_dim, int inverse, void *stream);
+/* The same for two matrices of one shape that share the row positions (q and k, or their gradients), in one launch. */
+int agpt_b200_rope_pair(float *d_a, float *d_b, const int32_t *d_pos, const float *d_cos, const float *d_sin, int64_t n,
+                        int n_heads, int head_dim, int inverse, void *stream);
 
 /* Replace cuda_layer_norm_forward / cuda_layer_norm_backward of the reference's kernel dependency (declared
  * src/cuda/agpt_train.cu:50-55; called :4671, :4762, :4801, :4850, :4907, :5066), with the arithmetic the reference

@@ -205,19 +205,28 @@ def test_size_independent_properties_at_scale(cuda):
     del gh
 
 
-def test_rope_and_row_gather(cuda):
+@pytest.mark.parametrize("n,H,hd", [(3000, 4, 32), (3001, 8, 64), (77, 4, 6)])     # the last takes the two-column kernel
+def test_rope_and_row_gather(cuda, n, H, hd):
     import torch
-    n, H, hd = 3000, 4, 32
     rng = np.random.default_rng(9)
     x = rng.standard_normal((n, H * hd)).astype(np.float32)
+    y = rng.standard_normal((n, H * hd)).astype(np.float32)
     pos = rng.integers(0, 128, size=n).astype(np.int32)
     cos, sin = A.rope_table(128, hd)
-    want = O.rope_apply(x.reshape(n * H, hd), np.repeat(pos, H), cos, sin).reshape(n, -1)
+    rot = lambda m, inv=False: O.rope_apply(m.reshape(n * H, hd), np.repeat(pos, H), cos, sin, inverse=inv).reshape(n, -1)  # noqa: E731
+    want = rot(x)
     tx = _dev(x, cuda)
     A.rope_(tx, _dev(pos, cuda), _dev(cos, cuda), _dev(sin, cuda), H)
     assert rel_err(tx.cpu().numpy(), want) < 1e-6
     A.rope_(tx, _dev(pos, cuda), _dev(cos, cuda), _dev(sin, cuda), H, inverse=True)
     assert rel_err(tx.cpu().numpy(), x) < 1e-5
+    # two matrices in one launch: the same values as one at a time, both directions
+    for inv in (False, True):
+        ta, tb, t1 = _dev(x, cuda), _dev(y, cuda), _dev(y, cuda)
+        A.rope_pair_(ta, tb, _dev(pos, cuda), _dev(cos, cuda), _dev(sin, cuda), H, inverse=inv)
+        A.rope_(t1, _dev(pos, cuda), _dev(cos, cuda), _dev(sin, cuda), H, inverse=inv)
+        assert torch.equal(tb, t1)
+        assert rel_err(ta.cpu().numpy(), rot(x, inv)) < 1e-6 and rel_err(tb.cpu().numpy(), rot(y, inv)) < 1e-6
     idx = rng.permutation(n).astype(np.int32)
     got = A.gather_rows(_dev(x, cuda), _dev(idx, cuda))
     assert torch.equal(got.cpu(), torch.from_numpy(x[idx]))
