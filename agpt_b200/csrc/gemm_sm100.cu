@@ -4,8 +4,8 @@
 // partial products with float32 accumulation, so results match an IEEE float32 GEMM to a few 1e-7 relative: the
 // accuracy of the reference's cublasSgemm calls (src/cuda/agpt_train.cu:4675-4683, :4752, :4766-4771, :4803,
 // :4840-5061) at several times their speed.  The kernel is CUTLASS's SM100 warp-specialised "fast FP32" mainloop
-// (TMA load warp -> transform warps -> MMA warp -> epilogue warps), instantiated here with 128x128x32 tiles (one
-// CTA) or 256x128x32 tiles (a CTA pair; every CTA loads its own operand tiles), and three epilogues: bias row; bias row + ReLU (the first
+// (TMA load warp -> transform warps -> MMA warp -> epilogue warps), instantiated here for one CTA per tile
+// (a cluster of one: every CTA loads its own operand tiles), a 128x128x32 tile, and three epilogues: bias row; bias row + ReLU (the first
 // feed-forward projection); bias row + a source matrix (the residual stream added in the same pass).
 // Measured on a B200, [1M, 128] x [128, 128]: the builder's defaults (k extent 16, all nine partial products, the
 // accumulator read out of tensor memory after every k block of 16) 0.332 ms; six products 0.316 ms; six products,
@@ -62,17 +62,16 @@ struct WithBands {
         typename Built::GmemTiledCopyB, typename Built::SmemLayoutAtomsB, typename Built::CopyAtomsB, typename Built::TransformB>;
 };
 
-// PAIR: two CTAs of a cluster (two SMs) share one 256 x 128 tile, each holding half of the B tile, so that B is
-// loaded and split once per 256 rows.  Measured against one CTA per 128 x 128 tile on [1M, K] x [K, N]: 5-12 % faster
-// for the row-streaming products (x W and g W^T); slower for the weight gradients (x^T g, a few output tiles cut
-// along the reduction), which keep one CTA per tile.
-template <typename LayoutA, typename LayoutB, int EPI = EPI_BIAS, bool PAIR = !cute::is_same_v<LayoutA, cutlass::layout::ColumnMajor>>
+// One CTA per 128 x 128 tile, every CTA loading its own operand tiles.  (A CTA pair sharing a 256 x 128 tile, each
+// CTA holding half of the B tile, measured 5-12 % faster on the row-streaming products and slower on the weight
+// gradients; it is not used: the same library has to run unchanged in multi-GPU jobs, where cluster-wide operand
+// loads are not wanted.)
+template <typename LayoutA, typename LayoutB, int EPI = EPI_BIAS>
 struct Sm100Gemm {
-    using TileShape = Shape<cute::conditional_t<PAIR, _256, _128>, _128, Int<AGPT_GEMM_TILE_K>>;
-    using ClusterShape = Shape<cute::conditional_t<PAIR, _2, _1>, _1, _1>;
-    using EpilogueSchedule = cute::conditional_t<PAIR, cutlass::epilogue::TmaWarpSpecialized2Sm, cutlass::epilogue::TmaWarpSpecialized1Sm>;
-    using MainloopSchedule = cute::conditional_t<PAIR, cutlass::gemm::KernelTmaWarpSpecialized2SmFastFP32Sm100,
-                                                 cutlass::gemm::KernelTmaWarpSpecialized1SmFastFP32Sm100>;
+    using TileShape = Shape<_128, _128, Int<AGPT_GEMM_TILE_K>>;
+    using ClusterShape = Shape<_1, _1, _1>;
+    using EpilogueSchedule = cutlass::epilogue::TmaWarpSpecialized1Sm;
+    using MainloopSchedule = cutlass::gemm::KernelTmaWarpSpecialized1SmFastFP32Sm100;
     // D = act(alpha * acc + beta * C + bias[column]); without a source matrix none is read (ElementC = void)
     using Fusion = cute::conditional_t<EPI == EPI_BIAS_RELU,
                                        cutlass::epilogue::fusion::LinCombPerColBiasEltAct<cutlass::epilogue::thread::ReLu, float, float, float, float, float, 4>,
