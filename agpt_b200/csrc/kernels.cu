@@ -1002,19 +1002,52 @@ __device__ __forceinline__ void tile_convert2(unsigned char *pa, unsigned char *
     __syncwarp();
 }
 
+// bfloat16 store: a key row arrives as head_dim bf16 (head_dim / 8 chunks of 16 bytes).  The raw chunk c is parked in the
+// row's lo part (chunk head_dim / 8 + c, swizzled like every chunk) and converted to the hi chunk c of the same row: a
+// bf16 value has 8 significant bits, so its scaled fp16 image is exact and the row has no lo part.  With such a store
+// every product is a single fp16 product (Q, dO, P and dS are rounded to their 11-bit hi halves): about 1e-3 relative,
+// below the store's own rounding (2^-9).  The thread that copied a chunk is the one that converts it.
+struct KvLane { int r0, raw, hi; };
+template <int HD>
+__device__ __forceinline__ KvLane kv_lane(int tid) {
+    constexpr int NCHK = HD / 8;
+    KvLane L;
+    L.r0 = tid / NCHK;
+    const int c = tid % NCHK, x = L.r0 & 7, row = L.r0 * (HD * 4);
+    L.raw = row + (((NCHK + c) ^ x) << 4);
+    L.hi = row + ((c ^ x) << 4);
+    return L;
+}
+__device__ __forceinline__ float abs_max_bf16x8(float m, uint4 a) {
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+        m = fmaxf(m, fmaxf(fabsf(__uint_as_float(w[j] << 16)), fabsf(__uint_as_float(w[j] & 0xffff0000u))));
+    return m;
+}
+__device__ __forceinline__ void kv_convert_bf16(unsigned char *pa, const KvLane &L, int o, float sa) {
+    const uint4 a = *reinterpret_cast<const uint4 *>(pa + L.raw + o);
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+    uint32_t h[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) h[j] = f16_pack2(__uint_as_float(w[j] << 16) * sa, __uint_as_float(w[j] & 0xffff0000u) * sa);
+    *reinterpret_cast<uint4 *>(pa + L.hi + o) = make_uint4(h[0], h[1], h[2], h[3]);
+}
+
 constexpr size_t bwd_tile_smem_bytes(int hd, int maxk) {
     return (size_t)(2 * 64 + 2 * maxk) * (size_t)(hd * 4) + (size_t)maxk * 8 + 3 * 64 * 4 + 32;
 }
 
-template <int HD, int NW, int MINB>
+template <int HD, int NW, int MINB, typename KVT>
 __global__ void __launch_bounds__(NW * 32, MINB)
-attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, const float *__restrict__ V,
+attn_bwd_tile_kernel(const float *__restrict__ Q, const KVT *__restrict__ K, const KVT *__restrict__ V,
                      const float *__restrict__ O, const float *__restrict__ LSE, const float *__restrict__ dO,
                      float *__restrict__ dQ, float *__restrict__ dK, float *__restrict__ dV, float *__restrict__ Pk,
                      float *__restrict__ Pv, const int32_t *__restrict__ sub_end, const int64_t *__restrict__ chain_off,
                      const int32_t *__restrict__ chain_ids, const int32_t *__restrict__ chain_end_all, int n, int H,
                      float scale, int tile0, int maxk, int dbg, BwdMask gmask) {
     constexpr int M = 64, NT = NW * 32, TILE_ROW_BYTES = HD * 4, KS = HD / 16, NDB = HD / 8, NCH = HD / 4;
+    constexpr bool LP = sizeof(KVT) == 2;              // bfloat16 store: single fp16 products, no lo parts
     extern __shared__ __align__(128) unsigned char tile_smem_raw[];
     unsigned char *sQ = tile_smem_raw, *sG = sQ + M * TILE_ROW_BYTES, *sK = sG + M * TILE_ROW_BYTES;
     unsigned char *sV = sK + (size_t)maxk * TILE_ROW_BYTES;
@@ -1060,14 +1093,30 @@ attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
             }
         }
     }
-    for (int r = L.r0, o = L.raw; r < nkp; r += RSTEP, o += OSTEP) {
-        if (r < nkeys) {
-            const int kid = r < p ? __ldg(chain + r) : i0 + (r - p);
-            const int64_t off = (int64_t)kid * D + hoff + L.c * 4;
-            cp_async16(sK + o, K + off); cp_async16(sV + o, V + off);
-        } else {
-            *reinterpret_cast<float4 *>(sK + o) = make_float4(0.f, 0.f, 0.f, 0.f);
-            *reinterpret_cast<float4 *>(sV + o) = make_float4(0.f, 0.f, 0.f, 0.f);
+    constexpr int RSTEPK = NT / (HD / 8), OSTEPK = RSTEPK * TILE_ROW_BYTES;
+    static_assert(NT % (HD / 8) == 0 && RSTEPK % 8 == 0, "a thread's key rows must share their swizzle term");
+    const KvLane LK = kv_lane<HD>(tid);
+    if constexpr (LP) {
+        for (int r = LK.r0, o = LK.raw; r < nkp; r += RSTEPK, o += OSTEPK) {
+            if (r < nkeys) {
+                const int kid = r < p ? __ldg(chain + r) : i0 + (r - p);
+                const int64_t off = (int64_t)kid * D + hoff + (tid % (HD / 8)) * 8;
+                cp_async16(sK + o, K + off); cp_async16(sV + o, V + off);
+            } else {
+                *reinterpret_cast<uint4 *>(sK + o) = make_uint4(0u, 0u, 0u, 0u);
+                *reinterpret_cast<uint4 *>(sV + o) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+    } else {
+        for (int r = L.r0, o = L.raw; r < nkp; r += RSTEP, o += OSTEP) {
+            if (r < nkeys) {
+                const int kid = r < p ? __ldg(chain + r) : i0 + (r - p);
+                const int64_t off = (int64_t)kid * D + hoff + L.c * 4;
+                cp_async16(sK + o, K + off); cp_async16(sV + o, V + off);
+            } else {
+                *reinterpret_cast<float4 *>(sK + o) = make_float4(0.f, 0.f, 0.f, 0.f);
+                *reinterpret_cast<float4 *>(sV + o) = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
         }
     }
     cp_async_commit();
@@ -1099,9 +1148,16 @@ attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
                 if (L.c == 0) sDelta[r] = d;
             }
         }
-        for (int r = L.r0, o = L.raw; r < nkp; r += RSTEP, o += OSTEP) {
-            mk = abs_max4(mk, *reinterpret_cast<const float4 *>(sK + o));
-            mv = abs_max4(mv, *reinterpret_cast<const float4 *>(sV + o));
+        if constexpr (LP) {
+            for (int r = LK.r0, o = LK.raw; r < nkp; r += RSTEPK, o += OSTEPK) {
+                mk = abs_max_bf16x8(mk, *reinterpret_cast<const uint4 *>(sK + o));
+                mv = abs_max_bf16x8(mv, *reinterpret_cast<const uint4 *>(sV + o));
+            }
+        } else {
+            for (int r = L.r0, o = L.raw; r < nkp; r += RSTEP, o += OSTEP) {
+                mk = abs_max4(mk, *reinterpret_cast<const float4 *>(sK + o));
+                mv = abs_max4(mv, *reinterpret_cast<const float4 *>(sV + o));
+            }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
@@ -1122,7 +1178,11 @@ attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
 #pragma unroll
     for (int u = 0; u < UQ; u++)
         if (L.r0 + u * RSTEP < M) tile_convert2(sQ, sG, L, u * OSTEP, sclQ, sclG);
-    for (int r = L.r0, o = 0; r < nkp; r += RSTEP, o += OSTEP) tile_convert2(sK, sV, L, o, sclK, sclV);
+    if constexpr (LP) {
+        for (int r = LK.r0, o = 0; r < nkp; r += RSTEPK, o += OSTEPK) { kv_convert_bf16(sK, LK, o, sclK); kv_convert_bf16(sV, LK, o, sclV); }
+    } else {
+        for (int r = L.r0, o = 0; r < nkp; r += RSTEP, o += OSTEP) tile_convert2(sK, sV, L, o, sclK, sclV);
+    }
     __syncthreads();
 
     // units: S' = (Q sQ)(K sK)^T, dP' = (dO sG)(V sV)^T, P' = 2^11 P, dS' = P' (dP' - delta sG sV) scale = 2^11 dS sG sV
@@ -1170,8 +1230,8 @@ attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
             for (int ks = 0; ks < KS; ks++) {
                 const uint32_t o = (uint32_t)(rg * 16 * TILE_ROW_BYTES) + aRow;
                 const uint32_t ch = (uint32_t)(((2 * ks + aC) ^ l8) << 4), cl = (uint32_t)(((2 * ks + aC + NDB) ^ l8) << 4);
-                ldmatrix_x4(qh[ks], uQ + o + ch); ldmatrix_x4(ql[ks], uQ + o + cl);
-                ldmatrix_x4(gh[ks], uG + o + ch); ldmatrix_x4(gl[ks], uG + o + cl);
+                ldmatrix_x4(qh[ks], uQ + o + ch); ldmatrix_x4(gh[ks], uG + o + ch);
+                if constexpr (!LP) { ldmatrix_x4(ql[ks], uQ + o + cl); ldmatrix_x4(gl[ks], uG + o + cl); }
             }
             const float lse0 = sLse[q0], lse1 = sLse[q1], dl0 = sDelta[q0] * sclG * sclV, dl1 = sDelta[q1] * sclG * sclV;
             float dq[NDB][4];
@@ -1204,8 +1264,10 @@ attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
                         uint32_t kf[4], vf[4];                 // {b0 hi, b1 hi, b0 lo, b1 lo}
                         ldmatrix_x4(kf, uK + o); ldmatrix_x4(vf, uV + o);
                         mma_f16(c, qh[ks], kf[0], kf[1]); mma_f16(e, gh[ks], vf[0], vf[1]);
-                        mma_f16(cx, ql[ks], kf[0], kf[1]); mma_f16(ex, gl[ks], vf[0], vf[1]);
-                        mma_f16(cx, qh[ks], kf[2], kf[3]); mma_f16(ex, gh[ks], vf[2], vf[3]);
+                        if constexpr (!LP) {
+                            mma_f16(cx, ql[ks], kf[0], kf[1]); mma_f16(ex, gl[ks], vf[0], vf[1]);
+                            mma_f16(cx, qh[ks], kf[2], kf[3]); mma_f16(ex, gh[ks], vf[2], vf[3]);
+                        }
                     }
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
@@ -1226,8 +1288,7 @@ attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
                     uint32_t kt[4];                            // {b0 hi, b1 hi, b0 lo, b1 lo}: keys 0-7 / 8-15 of the block, dims 8 db..
                     ldmatrix_x4_trans(kt, rowt + (uint32_t)(((db + tC) ^ l8) << 4));
                     mma_f16(dq[db], ah, kt[0], kt[1]);
-                    mma_f16(dq[db], al, kt[0], kt[1]);
-                    mma_f16(dq[db], as, kt[2], kt[3]);
+                    if constexpr (!LP) { mma_f16(dq[db], al, kt[0], kt[1]); mma_f16(dq[db], as, kt[2], kt[3]); }
                 }
             }
             if (r0 < n) {
@@ -1250,8 +1311,8 @@ attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
             for (int ks = 0; ks < KS; ks++) {
                 const uint32_t o = (uint32_t)(kb * 16 * TILE_ROW_BYTES) + aRow;
                 const uint32_t ch = (uint32_t)(((2 * ks + aC) ^ l8) << 4), cl = (uint32_t)(((2 * ks + aC + NDB) ^ l8) << 4);
-                ldmatrix_x4(kh[ks], uK + o + ch); ldmatrix_x4(kl[ks], uK + o + cl);
-                ldmatrix_x4(vh[ks], uV + o + ch); ldmatrix_x4(vl[ks], uV + o + cl);
+                ldmatrix_x4(kh[ks], uK + o + ch); ldmatrix_x4(vh[ks], uV + o + ch);
+                if constexpr (!LP) { ldmatrix_x4(kl[ks], uK + o + cl); ldmatrix_x4(vl[ks], uV + o + cl); }
             }
             float dk[NDB][4], dv[NDB][4];
 #pragma unroll
@@ -1290,8 +1351,10 @@ attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
                         uint32_t qf[4], gf[4];                 // {b0 hi, b1 hi, b0 lo, b1 lo}
                         ldmatrix_x4(qf, uQ + o); ldmatrix_x4(gf, uG + o);
                         mma_f16(c, kh[ks], qf[0], qf[1]); mma_f16(e, vh[ks], gf[0], gf[1]);
-                        mma_f16(cx, kl[ks], qf[0], qf[1]); mma_f16(ex, vl[ks], gf[0], gf[1]);
-                        mma_f16(cx, kh[ks], qf[2], qf[3]); mma_f16(ex, vh[ks], gf[2], gf[3]);
+                        if constexpr (!LP) {
+                            mma_f16(cx, kl[ks], qf[0], qf[1]); mma_f16(ex, vl[ks], gf[0], gf[1]);
+                            mma_f16(cx, kh[ks], qf[2], qf[3]); mma_f16(ex, vh[ks], gf[2], gf[3]);
+                        }
                     }
                     const float2 ls = *reinterpret_cast<const float2 *>(&sLse[qr + 2 * tig]);
                     const float2 dl = *reinterpret_cast<const float2 *>(&sDelta[qr + 2 * tig]);
@@ -1319,8 +1382,10 @@ attn_bwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
                     const uint32_t co = (uint32_t)(((db + tC) ^ l8) << 4);
                     ldmatrix_x4_trans(qt, uQ + ro + co); ldmatrix_x4_trans(gt, uG + ro + co);
                     mma_f16(dk[db], sh, qt[0], qt[1]); mma_f16(dv[db], ph, gt[0], gt[1]);
-                    mma_f16(dk[db], sl, qt[0], qt[1]); mma_f16(dv[db], pl, gt[0], gt[1]);
-                    mma_f16(dk[db], ss, qt[2], qt[3]); mma_f16(dv[db], ps, gt[2], gt[3]);
+                    if constexpr (!LP) {
+                        mma_f16(dk[db], sl, qt[0], qt[1]); mma_f16(dv[db], pl, gt[0], gt[1]);
+                        mma_f16(dk[db], ss, qt[2], qt[3]); mma_f16(dv[db], ps, gt[2], gt[3]);
+                    }
                 }
             }
 #pragma unroll
@@ -1349,13 +1414,14 @@ constexpr size_t fwd_tile_smem_bytes(int hd, int maxk) {
     return (size_t)(64 + 2 * maxk) * (size_t)(hd * 4) + (size_t)maxk * 8 + 32;
 }
 
-template <int HD, int MINB>
+template <int HD, int MINB, typename KVT>
 __global__ void __launch_bounds__(128, MINB)
-attn_fwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, const float *__restrict__ V,
+attn_fwd_tile_kernel(const float *__restrict__ Q, const KVT *__restrict__ K, const KVT *__restrict__ V,
                      float *__restrict__ O, float *__restrict__ LSE, const int32_t *__restrict__ sub_end,
                      const int64_t *__restrict__ chain_off, const int32_t *__restrict__ chain_ids,
                      const int32_t *__restrict__ chain_end_all, int n, int H, float scale, int tile0, int maxk) {
     constexpr int M = 64, NT = 128, TILE_ROW_BYTES = HD * 4, KS = HD / 16, NDB = HD / 8, NCH = HD / 4;
+    constexpr bool LP = sizeof(KVT) == 2;              // bfloat16 store: single fp16 products, no lo parts
     extern __shared__ __align__(128) unsigned char tile_smem_raw[];
     unsigned char *sQ = tile_smem_raw, *sK = sQ + M * TILE_ROW_BYTES, *sV = sK + (size_t)maxk * TILE_ROW_BYTES;
     int2 *s_meta = reinterpret_cast<int2 *>(sV + (size_t)maxk * TILE_ROW_BYTES);   // [maxk] {key id, key subtree end}
@@ -1383,14 +1449,30 @@ attn_fwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
         if (r < nt) cp_async16(sQ + o, Q + (int64_t)(i0 + r) * D + hoff + L.c * 4);
         else *reinterpret_cast<float4 *>(sQ + o) = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    for (int r = L.r0, o = L.raw; r < nkp; r += RSTEP, o += OSTEP) {
-        if (r < nkeys) {
-            const int kid = r < p ? __ldg(chain + r) : i0 + (r - p);
-            const int64_t off = (int64_t)kid * D + hoff + L.c * 4;
-            cp_async16(sK + o, K + off); cp_async16(sV + o, V + off);
-        } else {
-            *reinterpret_cast<float4 *>(sK + o) = make_float4(0.f, 0.f, 0.f, 0.f);
-            *reinterpret_cast<float4 *>(sV + o) = make_float4(0.f, 0.f, 0.f, 0.f);
+    constexpr int RSTEPK = NT / (HD / 8), OSTEPK = RSTEPK * TILE_ROW_BYTES;
+    static_assert(NT % (HD / 8) == 0 && RSTEPK % 8 == 0, "a thread's key rows must share their swizzle term");
+    const KvLane LK = kv_lane<HD>(tid);
+    if constexpr (LP) {
+        for (int r = LK.r0, o = LK.raw; r < nkp; r += RSTEPK, o += OSTEPK) {
+            if (r < nkeys) {
+                const int kid = r < p ? __ldg(chain + r) : i0 + (r - p);
+                const int64_t off = (int64_t)kid * D + hoff + (tid % (HD / 8)) * 8;
+                cp_async16(sK + o, K + off); cp_async16(sV + o, V + off);
+            } else {
+                *reinterpret_cast<uint4 *>(sK + o) = make_uint4(0u, 0u, 0u, 0u);
+                *reinterpret_cast<uint4 *>(sV + o) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+    } else {
+        for (int r = L.r0, o = L.raw; r < nkp; r += RSTEP, o += OSTEP) {
+            if (r < nkeys) {
+                const int kid = r < p ? __ldg(chain + r) : i0 + (r - p);
+                const int64_t off = (int64_t)kid * D + hoff + L.c * 4;
+                cp_async16(sK + o, K + off); cp_async16(sV + o, V + off);
+            } else {
+                *reinterpret_cast<float4 *>(sK + o) = make_float4(0.f, 0.f, 0.f, 0.f);
+                *reinterpret_cast<float4 *>(sV + o) = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
         }
     }
     cp_async_commit();
@@ -1407,9 +1489,16 @@ attn_fwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
         float mq = 0.f, mk = 0.f, mv = 0.f;
 #pragma unroll
         for (int u = 0; u < M / RSTEP; u++) mq = abs_max4(mq, *reinterpret_cast<const float4 *>(sQ + L.raw + u * OSTEP));
-        for (int r = L.r0, o = L.raw; r < nkp; r += RSTEP, o += OSTEP) {
-            mk = abs_max4(mk, *reinterpret_cast<const float4 *>(sK + o));
-            mv = abs_max4(mv, *reinterpret_cast<const float4 *>(sV + o));
+        if constexpr (LP) {
+            for (int r = LK.r0, o = LK.raw; r < nkp; r += RSTEPK, o += OSTEPK) {
+                mk = abs_max_bf16x8(mk, *reinterpret_cast<const uint4 *>(sK + o));
+                mv = abs_max_bf16x8(mv, *reinterpret_cast<const uint4 *>(sV + o));
+            }
+        } else {
+            for (int r = L.r0, o = L.raw; r < nkp; r += RSTEP, o += OSTEP) {
+                mk = abs_max4(mk, *reinterpret_cast<const float4 *>(sK + o));
+                mv = abs_max4(mv, *reinterpret_cast<const float4 *>(sV + o));
+            }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
@@ -1427,7 +1516,11 @@ attn_fwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
     // ---- stage 3 (pass B): convert in place (Q rows two at a time through the two-plane helper) ----
 #pragma unroll
     for (int u = 0; u < M / RSTEP; u += 2) tile_convert2(sQ, sQ + OSTEP, L, u * OSTEP, sclQ, sclQ);
-    for (int r = L.r0, o = 0; r < nkp; r += RSTEP, o += OSTEP) tile_convert2(sK, sV, L, o, sclK, sclV);
+    if constexpr (LP) {
+        for (int r = LK.r0, o = 0; r < nkp; r += RSTEPK, o += OSTEPK) { kv_convert_bf16(sK, LK, o, sclK); kv_convert_bf16(sV, LK, o, sclV); }
+    } else {
+        for (int r = L.r0, o = 0; r < nkp; r += RSTEP, o += OSTEP) tile_convert2(sK, sV, L, o, sclK, sclV);
+    }
     __syncthreads();
 
     const int rg = warp;
@@ -1447,7 +1540,7 @@ attn_fwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
     for (int ks = 0; ks < KS; ks++) {
         const uint32_t o = (uint32_t)(rg * 16 * TILE_ROW_BYTES) + aRow;
         ldmatrix_x4(qh[ks], uQ + o + (uint32_t)(((2 * ks + aC) ^ l8) << 4));
-        ldmatrix_x4(ql[ks], uQ + o + (uint32_t)(((2 * ks + aC + NDB) ^ l8) << 4));
+        if constexpr (!LP) ldmatrix_x4(ql[ks], uQ + o + (uint32_t)(((2 * ks + aC + NDB) ^ l8) << 4));
     }
     float o_[NDB][4];
 #pragma unroll
@@ -1477,8 +1570,7 @@ attn_fwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
                 uint32_t kf[4];
                 ldmatrix_x4(kf, uK + rowb + (uint32_t)(((2 * ks + bC) ^ l8) << 4));
                 mma_f16(c, qh[ks], kf[0], kf[1]);
-                mma_f16(cx, ql[ks], kf[0], kf[1]);
-                mma_f16(cx, qh[ks], kf[2], kf[3]);
+                if constexpr (!LP) { mma_f16(cx, ql[ks], kf[0], kf[1]); mma_f16(cx, qh[ks], kf[2], kf[3]); }
             }
 #pragma unroll
             for (int j = 0; j < 4; j++)
@@ -1516,8 +1608,7 @@ attn_fwd_tile_kernel(const float *__restrict__ Q, const float *__restrict__ K, c
             uint32_t vt[4];                            // {b0 hi, b1 hi, b0 lo, b1 lo}: keys 0-7 / 8-15 of the block, dims 8 db..
             ldmatrix_x4_trans(vt, rowt + (uint32_t)(((db + tC) ^ l8) << 4));
             mma_f16(o_[db], ph, vt[0], vt[1]);
-            mma_f16(o_[db], pl, vt[0], vt[1]);
-            mma_f16(o_[db], ps, vt[2], vt[3]);
+            if constexpr (!LP) { mma_f16(o_[db], pl, vt[0], vt[1]); mma_f16(o_[db], ps, vt[2], vt[3]); }
         }
     }
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
@@ -1697,18 +1788,29 @@ static inline bool tile_kernels_fit(const agpt_plan *p, int head_dim) {
     if (head_dim != 32 && head_dim != 64) return false;
     return bwd_tile_smem_bytes(head_dim, bwd_tile_maxk(p)) <= (head_dim == 32 ? (size_t)56 * 1024 : (size_t)113 * 1024);
 }
+// Whole-tile backward for a bfloat16 store (AGPT_B200_ATTN_TILE_BF16=0: the chunked kernel, which keeps float32-level
+// products).  Measured: head_dim 32 (depth-32 trie, 28.3M positions) 42.3 ms against 45.5 ms chunked; head_dim 64 (4M-node
+// tree) 29.4 ms against 26.8 ms, so head_dim 64 stays chunked; the forward is no faster either way (15.1 ms) and stays chunked.
+static int tile_bf16_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char *e = getenv("AGPT_B200_ATTN_TILE_BF16");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on;
+}
 
-template <int HD, int MINB>
+template <int HD, int MINB, typename KVT>
 static int launch_fwd_tile(const agpt_plan *p, const float *q, const void *k, const void *v, float *out, float *lse, int H,
                            float scale, cudaStream_t st, int tile0, int ntiles) {
     static size_t granted[AGPT_MAX_DEVICES];
     const int maxk = bwd_tile_maxk(p);
     const size_t smem = fwd_tile_smem_bytes(HD, maxk);
-    int rc = allow_dynamic_smem(attn_fwd_tile_kernel<HD, MINB>, smem, granted);
+    int rc = allow_dynamic_smem(attn_fwd_tile_kernel<HD, MINB, KVT>, smem, granted);
     if (rc) return rc;
     dim3 grid((unsigned)ntiles, (unsigned)H);
-    attn_fwd_tile_kernel<HD, MINB><<<grid, 128, smem, st>>>(q, (const float *)k, (const float *)v, out, lse, p->d_sub_end,
-                                                            p->d_chain_off, p->d_chain_ids, p->d_chain_end, (int)p->n, H, scale, tile0, maxk);
+    attn_fwd_tile_kernel<HD, MINB, KVT><<<grid, 128, smem, st>>>(q, (const KVT *)k, (const KVT *)v, out, lse, p->d_sub_end,
+                                                                 p->d_chain_off, p->d_chain_ids, p->d_chain_end, (int)p->n, H, scale, tile0, maxk);
     return launch_status("attn_fwd_tile");
 }
 
@@ -1729,7 +1831,7 @@ static int fwd_dispatch(const agpt_plan *p, const float *q, const void *k, const
     // head_dim 64: the whole-tile forward (two blocks per SM) measured slower than the chunked one (17.5 vs 15.0 ms on the
     // 4M-node microbenchmark), the whole-tile backward faster (37.7 vs 50.3 ms): the forward stays chunked there
     if (attn_impl() == 1 && p->tile_m == 64 && kv_dtype == AGPT_KV_F32 && head_dim == 32 && bwd_tile_enabled() && tile_kernels_fit(p, head_dim))
-        return launch_fwd_tile<32, 5>(p, q, k, v, out, lse, H, scale, st, tile0, ntiles);
+        return launch_fwd_tile<32, 5, float>(p, q, k, v, out, lse, H, scale, st, tile0, ntiles);
     if (attn_impl() == 1 && p->tile_m == 64 && p->max_depth + 64 <= MAXKEYS) {
         const bool bf = kv_dtype == AGPT_KV_BF16;
         switch (head_dim) {
@@ -1755,26 +1857,27 @@ static int launch_bwd_mma(const agpt_plan *p, const float *q, const void *k, con
     return launch_status("attn_bwd_mma");
 }
 
-template <int HD, int NW, int MINB>
+template <int HD, int NW, int MINB, typename KVT = float>
 static int launch_bwd_tile(const agpt_plan *p, const float *q, const void *k, const void *v, const float *o, const float *lse,
                            const float *dout, float *dq, float *dk, float *dv, float *pk, float *pv, int H, float scale,
                            cudaStream_t st, int tile0, int ntiles, BwdMask gmask) {
     static size_t granted[AGPT_MAX_DEVICES];
     const int maxk = bwd_tile_maxk(p);
     const size_t smem = bwd_tile_smem_bytes(HD, maxk);
-    int rc = allow_dynamic_smem(attn_bwd_tile_kernel<HD, NW, MINB>, smem, granted);
+    int rc = allow_dynamic_smem(attn_bwd_tile_kernel<HD, NW, MINB, KVT>, smem, granted);
     if (rc) return rc;
     dim3 grid((unsigned)ntiles, (unsigned)H);
-    attn_bwd_tile_kernel<HD, NW, MINB><<<grid, NW * 32, smem, st>>>(q, (const float *)k, (const float *)v, o, lse, dout, dq, dk, dv, pk, pv,
-                                                                    p->d_sub_end, p->d_chain_off, p->d_chain_ids, p->d_chain_end,
-                                                                    (int)p->n, H, scale, tile0, maxk, g_bwd_dbg, gmask);
+    attn_bwd_tile_kernel<HD, NW, MINB, KVT><<<grid, NW * 32, smem, st>>>(q, (const KVT *)k, (const KVT *)v, o, lse, dout, dq, dk, dv, pk, pv,
+                                                                         p->d_sub_end, p->d_chain_off, p->d_chain_ids, p->d_chain_end,
+                                                                         (int)p->n, H, scale, tile0, maxk, g_bwd_dbg, gmask);
     return launch_status("attn_bwd_tile");
 }
 
-static int launch_bwd_tile_w(const agpt_plan *p, const float *q, const void *k, const void *v, const float *o, const float *lse,
-                             const float *dout, float *dq, float *dk, float *dv, float *pk, float *pv, int H, int head_dim,
-                             float scale, cudaStream_t st, int tile0, int ntiles, BwdMask gmask) {
+static int launch_bwd_tile_w(const agpt_plan *p, const float *q, const void *k, const void *v, int kv_dtype, const float *o,
+                             const float *lse, const float *dout, float *dq, float *dk, float *dv, float *pk, float *pv, int H,
+                             int head_dim, float scale, cudaStream_t st, int tile0, int ntiles, BwdMask gmask) {
 #define TILE_ARGS p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, scale, st, tile0, ntiles, gmask
+    if (kv_dtype == AGPT_KV_BF16) return launch_bwd_tile<32, 4, 4, __nv_bfloat16>(TILE_ARGS);    // head_dim 32 only (bwd_dispatch)
     if (head_dim == 64) {        // twice the fragment and accumulator registers: two blocks per SM
         switch (g_bwd_warps) {
             case 6: case 8: return launch_bwd_tile<64, 8, 1>(TILE_ARGS);
@@ -1793,9 +1896,10 @@ static int launch_bwd_tile_w(const agpt_plan *p, const float *q, const void *k, 
 static int bwd_dispatch(const agpt_plan *p, const float *q, const void *k, const void *v, int kv_dtype, const float *o,
                         const float *lse, const float *dout, float *dq, float *dk, float *dv, float *pk, float *pv, int H,
                         int head_dim, float scale, cudaStream_t st, int tile0, int ntiles, BwdMask gmask = BwdMask{AGPT_GRAD_FULL, nullptr}) {
-    if (attn_impl() == 1 && p->tile_m == 64 && kv_dtype == AGPT_KV_F32 && bwd_tile_enabled()) {
+    if (attn_impl() == 1 && p->tile_m == 64 && bwd_tile_enabled() &&
+        (kv_dtype == AGPT_KV_F32 || (head_dim == 32 && tile_bf16_enabled()))) {
         if (tile_kernels_fit(p, head_dim))
-            return launch_bwd_tile_w(p, q, k, v, o, lse, dout, dq, dk, dv, pk, pv, H, head_dim, scale, st, tile0, ntiles, gmask);
+            return launch_bwd_tile_w(p, q, k, v, kv_dtype, o, lse, dout, dq, dk, dv, pk, pv, H, head_dim, scale, st, tile0, ntiles, gmask);
     }
     if (attn_impl() == 1 && p->tile_m == 64 && p->max_depth + 64 <= MAXKEYS) {
         const bool bf = kv_dtype == AGPT_KV_BF16;
