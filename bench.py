@@ -640,8 +640,10 @@ def run_epoch(args, cfg, rank, world, dev, log):
     pm, pd = cfg.get("prune", (1, 4))
     trie = A.RadixTrie.build_gpu(corpus, cfg["depth"], 2, pm, pd, device=dev.index)
     mf = MF.random_init(D, cfg["heads"], cfg["layers"], cfg["vocab"], max(128, cfg["depth"]), seed=0)
-    groups, total = T.build_groups(trie, rank, world, args.epoch_group_rows, "linear", mf.seq_len, dev, level=2,
-                                   unit_cap=args.epoch_group_rows)
+    # a launch group keeps about 14 rows of d_model floats per position and layer for the backward pass: bound the
+    # group so that this stays near 80 GB of the 180 GB
+    group_rows = int(min(args.epoch_group_rows, 80e9 / (cfg["layers"] * D * 4 * 14)))
+    groups, total = T.build_groups(trie, rank, world, group_rows, "linear", mf.seq_len, dev, level=2, unit_cap=group_rows)
     counts = [torch.from_numpy(np.ascontiguousarray(c)).to(dev) for c in (trie.cnt_off.astype(np.int32), trie.cnt_tok, trie.cnt_val)]
     model = T.TrieWalkModel(mf, dev)
     opt = T.make_optimizer("rmsprop", model, 3e-4, 0.999)
@@ -662,7 +664,7 @@ def run_epoch(args, cfg, rank, world, dev, log):
     return {"seconds": times[-1], "positions_per_s": total / times[-1], "loss_first": losses[0], "loss_second": losses[-1],
             "model": f"d_model {D}, {cfg['layers']} layers, {cfg['heads']} heads x {cfg['head_dim']}, d_ff {4 * D}, vocab {cfg['vocab']}, fp32",
             "recipe": "rmsprop beta 0.999, lr 3e-4, linear mass weighting, one step per epoch (accumulate)", "kv_store": args.kv,
-            "group_rows": args.epoch_group_rows, "partition": "bigram subtrees", "chunks_rank0": len(groups)}
+            "group_rows": group_rows, "partition": "bigram subtrees", "chunks_rank0": len(groups)}
 
 
 def main():
@@ -681,7 +683,11 @@ def main():
     ap.add_argument("--profile", action="store_true", help="profiler capture mode: warm-up as given, no e2e, no CPU arm")
     ap.add_argument("--no-epoch", dest="epoch", action="store_false",
                     help="skip the whole-epoch timing of the trainer (all layers) on the same trie")
-    ap.add_argument("--epoch-group-rows", type=int, default=1_000_000)
+    ap.add_argument("--epoch-group-rows", type=int, default=4_000_000,
+                    help="upper bound on the rows per launch group of the trainer epoch; also bounded by memory "
+                         "(measured on c2: 1M rows 1.99 s, 2M 1.95 s, 4M 1.93 s)")
+    ap.add_argument("--profile-epoch", action="store_true",
+                    help="with --profile: keep the trainer epoch (to capture its dense-step kernels)")
     ap.add_argument("--no-micro", dest="micro", action="store_false",
                     help="skip the attention-only microbenchmark legs (4M-node tree, 8 x 64) of the default one-GPU line")
     ap.add_argument("--no-e2e", action="store_true")
@@ -689,7 +695,7 @@ def main():
     args = ap.parse_args()
     if args.profile:
         args.no_e2e = args.no_cpu = True
-        args.epoch = args.micro = False
+        args.epoch, args.micro = args.profile_epoch, False
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -488,6 +488,13 @@ def test_layer_norm_kernels(cuda, rows, cols):
     dx = A.layer_norm_backward(_dev(grad, cuda), norm, sinv, _dev(gamma, cuda), dg, db)
     assert rel_err(dx.cpu().numpy(), wdx) < TOL_F32
     assert rel_err(dg.cpu().numpy() - 1.0, wdg) < TOL_F32 and rel_err(db.cpu().numpy() - 2.0, wdb) < TOL_F32
+    # the gradient of the residual path added in the same pass (also in place: add is the output buffer of a first call)
+    skip = rng.standard_normal((rows, cols)).astype(np.float32)
+    dg3, db3 = torch.zeros(cols, device=cuda), torch.zeros(cols, device=cuda)
+    dx3 = A.layer_norm_backward(_dev(grad, cuda), norm, sinv, _dev(gamma, cuda), dg3, db3, add=_dev(skip, cuda))
+    assert rel_err(dx3.cpu().numpy(), wdx + skip) < TOL_F32 and rel_err(dg3.cpu().numpy(), wdg) < TOL_F32
+    with pytest.raises(A.AgptError):
+        A.layer_norm_backward(_dev(grad, cuda), norm, sinv, _dev(gamma, cuda), dg3, db3, add=_dev(skip[:, :cols // 2 or 1], cuda))
     # legacy symbols, in place, default stream
     g2, n2 = _dev(grad, cuda), norm.clone()
     dg2, db2 = torch.zeros(cols, device=cuda), torch.zeros(cols, device=cuda)
@@ -524,6 +531,12 @@ def test_gemm_f32_tensor_core(shape, gemm_impl):
     close(A.gemm_f32(dy, w, trans_b=True, bias=torch.ones(din, device="cuda"), relu=True),
           torch.relu(dy.double() @ w.double().t() + 1.0))
     close(A.gemm_f32(dy, w, trans_b=True), dy.double() @ w.double().t())
+    # input gradients of several projections of the same rows: the running sum is the source matrix and the output
+    acc = A.gemm_f32(dy, w, trans_b=True)
+    w2 = torch.randn(din, dout, device="cuda", generator=g)
+    same = A.gemm_f32(dy, w2, trans_b=True, residual=acc, out=acc)
+    assert same.data_ptr() == acc.data_ptr()
+    close(acc, dy.double() @ w.double().t() + dy.double() @ w2.double().t())
     want = x.double().t() @ dy.double()
     for split_k in (1, 2, 7, 64):
         got = A.gemm_f32(x, dy, trans_a=True, split_k=split_k)
