@@ -371,7 +371,8 @@ int64_t agpt_b200_optimizer_scratch_bytes(void);
  * :4803, :4840-5061) with a tensor-core GEMM of float32-level accuracy (three TF32 MMAs per product).  Row-major:
  *     out[M, N] = act(alpha * op(A)[M, K] * op(B)[K, N] + beta * C + bias)
  * trans_a / trans_b select A^T / B^T (not both).  d_c (with beta != 0) is a source matrix such as the residual
- * stream, d_bias a row added to every row, relu != 0 applies max(., 0); each may be absent (NULL / 0).  split_k > 1
+ * stream, or the running sum of the input gradients of several projections of the same rows (:5026-5061); it may be
+ * d_out itself.  d_bias is a row added to every row, relu != 0 applies max(., 0); each may be absent (NULL / 0).  split_k > 1
  * cuts K into slices (for weight gradients, whose K is the number of trie positions; no bias or activation then): the
  * slices run as one batched GEMM into partial matrices in d_workspace (agpt_b200_gemm_f32_workspace_bytes, 0 when
  * split_k == 1) and are added in slice order, so the result is repeatable bit for bit.  Pointers and leading
