@@ -363,6 +363,9 @@ def run_gpu(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        # stdout carries the one JSON line only: where the environment asks NCCL for its version banner or debug lines,
+        # they go to stderr like this program's own log
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
     log = (lambda s: print(f"[bench r{rank}] {s}", file=sys.stderr, flush=True))
     cfg = WORKLOADS[args.workload]

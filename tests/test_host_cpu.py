@@ -438,6 +438,27 @@ def test_lightning_unit_trains_its_ancestors_and_counts_them_in_the_mass_mean(sa
     assert with_ancestors > 0
 
 
+def test_launch_groups_keep_units_consecutive_and_count_them_by_offsets():
+    """Rows of a unit are consecutive in a launch group, so the trainer counts a unit's trained queries as the difference of
+    a running sum at the unit offsets; that must equal the scattered count over unit_of_row, whatever the packing."""
+    import torch
+    from agpt_b200 import trainer as T
+    corpus = A.synth_markov_corpus(6000, 20, 2, 5)
+    trie = A.RadixTrie.build(corpus, 9)
+    for group_rows, cap in ((700, None), (2500, 900), (10**9, None)):
+        groups, total = T.build_groups(trie, 0, 1, group_rows, "linear", 16, torch.device("cpu"), level=2, unit_cap=cap)
+        assert sum(g.n for g in groups) >= total
+        for g in groups:
+            assert g.unit_off is not None and g.unit_off.numel() == g.n_units + 1
+            u = g.unit_of_row.numpy()
+            assert np.all(np.diff(u) >= 0) and int(g.unit_off[-1]) == g.n
+            pos = torch.from_numpy(np.random.default_rng(g.n).random(g.n) < 0.6)
+            run = torch.nn.functional.pad(torch.cumsum(pos, 0, dtype=torch.int32), (1, 0))
+            got = (run[g.unit_off[1:]] - run[g.unit_off[:-1]]).to(torch.float32)
+            want = torch.zeros(g.n_units).index_add_(0, g.unit_of_row, pos.to(torch.float32))
+            assert torch.equal(got, want)
+
+
 def _py_markov(n, vocab, order, seed, repeat_log2=0):
     """Plain-Python restatement of the synthetic corpus generator (splitmix64 stream, Zipf(1.1) slots and symbols,
     optional injected repeats), for small n."""
