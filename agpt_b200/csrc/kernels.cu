@@ -1582,11 +1582,14 @@ attn_fwd_tile_kernel(const float *__restrict__ Q, const KVT *__restrict__ K, con
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
         const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
         const float mu0 = mn0 == -INFINITY ? 0.f : mn0, mu1 = mn1 == -INFINITY ? 0.f : mn1;
-        const float corr0 = ex2_ftz(m0 - mu0), corr1 = ex2_ftz(m1 - mu1);
-        m0 = mn0; m1 = mn1;
-        l0 *= corr0; l1 *= corr1;
+        // the running maxima of most rows stop moving after the first blocks: the rescaling (by exactly 1) is skipped then
+        if (__any_sync(0xffffffffu, mn0 != m0 || mn1 != m1)) {
+            const float corr0 = ex2_ftz(m0 - mu0), corr1 = ex2_ftz(m1 - mu1);
+            l0 *= corr0; l1 *= corr1;
 #pragma unroll
-        for (int db = 0; db < NDB; db++) { o_[db][0] *= corr0; o_[db][1] *= corr0; o_[db][2] *= corr1; o_[db][3] *= corr1; }
+            for (int db = 0; db < NDB; db++) { o_[db][0] *= corr0; o_[db][1] *= corr0; o_[db][2] *= corr1; o_[db][3] *= corr1; }
+        }
+        m0 = mn0; m1 = mn1;
         float pw[2][4];
 #pragma unroll
         for (int u = 0; u < 2; u++) {
@@ -1831,7 +1834,15 @@ static int fwd_dispatch(const agpt_plan *p, const float *q, const void *k, const
     // head_dim 64: the whole-tile forward (two blocks per SM) measured slower than the chunked one (17.5 vs 15.0 ms on the
     // 4M-node microbenchmark), the whole-tile backward faster (37.7 vs 50.3 ms): the forward stays chunked there
     if (attn_impl() == 1 && p->tile_m == 64 && kv_dtype == AGPT_KV_F32 && head_dim == 32 && bwd_tile_enabled() && tile_kernels_fit(p, head_dim))
+    {
+        // six blocks of four warps per SM (80 registers, no spills; the 33.6 KB of a depth-32 tile fit six times): 19.0 ms on
+        // the depth-32 trie against 20.1 ms with five (95 registers; AGPT_B200_FWD_BLOCKS=5).  The backward does not gain
+        // from a fifth block (96 registers with spills: 52.5 against 49.9 ms).
+        static int blocks = 0;
+        if (!blocks) { const char *e = getenv("AGPT_B200_FWD_BLOCKS"); blocks = (e && atoi(e) == 5) ? 5 : 6; }
+        if (blocks == 6) return launch_fwd_tile<32, 6, float>(p, q, k, v, out, lse, H, scale, st, tile0, ntiles);
         return launch_fwd_tile<32, 5, float>(p, q, k, v, out, lse, H, scale, st, tile0, ntiles);
+    }
     if (attn_impl() == 1 && p->tile_m == 64 && p->max_depth + 64 <= MAXKEYS) {
         const bool bf = kv_dtype == AGPT_KV_BF16;
         switch (head_dim) {
