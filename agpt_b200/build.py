@@ -14,17 +14,44 @@ SOURCES = [os.path.join(HERE, "csrc", "kernels.cu"), os.path.join(HERE, "csrc", 
            os.path.join(HERE, "csrc", "trie_gpu.cu")]
 
 
+# The two GEMM translation units instantiate CUTLASS templates, and gemm_sm100.cu re-instantiates the SM100 fast-FP32
+# mainloop through type aliases of that collective, so the header tree is pinned to the release it was written and
+# measured against.  AGPT_CUTLASS_INCLUDE names a tree explicitly (a checkout of that release); otherwise the copies
+# shipped inside installed Python packages are tried, and one of another release is passed over.
+CUTLASS_PINNED = (4, 5)
+
+
+def cutlass_version(include_dir):
+    """(major, minor, patch) from cutlass/version.h of a header tree, or None."""
+    import re
+    try:
+        text = open(os.path.join(include_dir, "cutlass", "version.h")).read()
+    except OSError:
+        return None
+    got = [re.search(r"#define\s+CUTLASS_%s\s+(\d+)" % k, text) for k in ("MAJOR", "MINOR", "PATCH")]
+    return tuple(int(m.group(1)) for m in got) if all(got) else None
+
+
 def cutlass_include():
-    """CUTLASS header tree vendored inside an installed Python package (header-only; templates are instantiated in
-    gemm3x.cu).  None if no tree is found: the library is then built with AGPT_NO_CUTLASS."""
+    """CUTLASS header tree of the pinned release (header-only).  None if there is none: the library is then built with
+    AGPT_NO_CUTLASS (the GEMM entry points report that; everything else works)."""
     import importlib.util
+    explicit = os.environ.get("AGPT_CUTLASS_INCLUDE")
+    if explicit:
+        v = cutlass_version(explicit)
+        if v is None or v[:2] != CUTLASS_PINNED:
+            raise RuntimeError(f"AGPT_CUTLASS_INCLUDE={explicit}: CUTLASS {v} found, {CUTLASS_PINNED[0]}.{CUTLASS_PINNED[1]}.x needed")
+        return explicit
     for pkg, rel in (("flashinfer", ("data", "cutlass", "include")), ("tilelang", ("3rdparty", "cutlass", "include"))):
         spec = importlib.util.find_spec(pkg)
         if spec and spec.submodule_search_locations:
             path = os.path.join(list(spec.submodule_search_locations)[0], *rel)
-            if os.path.exists(os.path.join(path, "cutlass", "gemm", "device", "gemm_universal.h")):
+            v = cutlass_version(path)
+            if v is not None and v[:2] == CUTLASS_PINNED and os.path.exists(os.path.join(path, "cutlass", "gemm", "device", "gemm_universal.h")):
                 return path
     return None
+
+
 HEADERS = [os.path.join(HERE, "csrc", "internal.h"), os.path.join(HERE, "..", "include", "agpt_b200.h")]
 
 

@@ -438,6 +438,26 @@ def test_lightning_unit_trains_its_ancestors_and_counts_them_in_the_mass_mean(sa
     assert with_ancestors > 0
 
 
+def test_build_pins_the_cutlass_release(tmp_path, monkeypatch):
+    """The GEMM sources re-instantiate a CUTLASS collective through its type aliases, so the build takes header trees of
+    the pinned release only: another release inside a package is passed over, one named explicitly is refused."""
+    from agpt_b200 import build as B
+    inc = tmp_path / "include" / "cutlass"
+    (inc / "gemm" / "device").mkdir(parents=True)
+    (inc / "gemm" / "device" / "gemm_universal.h").write_text("")
+    (inc / "version.h").write_text("#define CUTLASS_MAJOR 3\n#define CUTLASS_MINOR 9\n#define CUTLASS_PATCH 2\n")
+    assert B.cutlass_version(str(tmp_path / "include")) == (3, 9, 2)
+    assert B.cutlass_version(str(tmp_path)) is None
+    monkeypatch.setenv("AGPT_CUTLASS_INCLUDE", str(tmp_path / "include"))
+    with pytest.raises(RuntimeError, match="needed"):
+        B.cutlass_include()
+    (inc / "version.h").write_text("#define CUTLASS_MAJOR %d\n#define CUTLASS_MINOR %d\n#define CUTLASS_PATCH 7\n" % B.CUTLASS_PINNED)
+    assert B.cutlass_include() == str(tmp_path / "include")
+    monkeypatch.delenv("AGPT_CUTLASS_INCLUDE")
+    found = B.cutlass_include()
+    assert found is None or B.cutlass_version(found)[:2] == B.CUTLASS_PINNED
+
+
 def test_launch_groups_keep_units_consecutive_and_count_them_by_offsets():
     """Rows of a unit are consecutive in a launch group, so the trainer counts a unit's trained queries as the difference of
     a running sum at the unit offsets; that must equal the scattered count over unit_of_row, whatever the packing."""
