@@ -344,7 +344,7 @@ def run_reference(args):
             "config": workload_config(args, cfg, total, args.gpus, int(plan.max_depth), np.bincount(plan.depth, minlength=2)[1:].tolist()),
             "cpu_baseline": {"value": nps, "unit": "nodes/s", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": nps, "unit": "nodes/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line))
+    print(json.dumps(line), file=RESULT_OUT, flush=True)
 
 
 # ----------------------------------------------------------------------------------------------------------
@@ -363,9 +363,6 @@ def run_gpu(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        # stdout carries the one JSON line only: where the environment asks NCCL for its version banner or debug lines,
-        # they go to stderr like this program's own log
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
     log = (lambda s: print(f"[bench r{rank}] {s}", file=sys.stderr, flush=True))
     cfg = WORKLOADS[args.workload]
@@ -581,7 +578,7 @@ def run_gpu(args):
                              "loss_seconds_per_step": t_loss},
                 "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "micro": micro, "epoch": epoch,
                 "selfcheck": selfcheck}
-        print(json.dumps(line))
+        print(json.dumps(line), file=RESULT_OUT, flush=True)
     if world > 1:
         dist.destroy_process_group()
 
@@ -670,7 +667,16 @@ def run_epoch(args, cfg, rank, world, dev, log):
             "group_rows": group_rows, "partition": "bigram subtrees", "chunks_rank0": len(groups)}
 
 
+# stdout carries the one JSON line and nothing else: what libraries print to file descriptor 1 (NCCL's version banner
+# when the environment asks for it) goes to stderr with this program's own log
+RESULT_OUT = sys.stdout
+
+
 def main():
+    global RESULT_OUT
+    sys.stdout.flush()
+    RESULT_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
