@@ -936,7 +936,10 @@ __device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], u
 // in one basic block and interleave; otherwise each half is skipped on its own.  Measured: head_dim 64 backward 35.9 ms
 // against 37.6 ms on the 4M-node tree (eight warps per SM: the interleaving pays); head_dim 32 backward 51.7 against 49.6
 // and forward 19.3 against 19.0 on the depth-32 trie (more spills, more warps to hide latency already).
-template <int HD> struct TileBothHalves { static constexpr bool bwd = HD >= 64, fwd = false; };
+#ifndef AGPT_TILE_BOTH_MIN_HD
+#define AGPT_TILE_BOTH_MIN_HD 64
+#endif
+template <int HD> struct TileBothHalves { static constexpr bool bwd = HD >= AGPT_TILE_BOTH_MIN_HD, fwd = false; };
 // (x, y) -> packed fp16 pair hi (x in the low half) and the packed pair lo of the remainders.  LO_UP: the remainders
 // are stored times 2^11 (they are below 2^-11 |x|, so this keeps them in fp16's normal range and a small element keeps
 // its full 22 bits next to a large one); products with such a lo are accumulated apart and enter times 2^-11.
