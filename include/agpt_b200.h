@@ -433,11 +433,14 @@ int agpt_b200_set_attn_impl(int impl);
  * once to split half precision (x * 2^e = hi + lo, fp16 each, e per tile, head and tensor; three m16n8k16 products
  * give the accuracy of three TF32 products), every fragment one ldmatrix, and the backward's warps run independent
  * row and key items with no barrier in their loops.  Used whenever four (head_dim 32) or two (head_dim 64) blocks
- * of the backward fit one SM, i.e. up to about 150 / 128 keys per tile (depth <= ~90 / 65); deeper plans, head_dim 16
- * and a bf16 store take the chunked TF32 kernels.  whole_tile 0: always the chunked kernels.  bwd_warps = 4
- * (default), 6 or 8 warps per block of the whole-tile backward, 3 = four warps with three blocks per SM.  Same
- * results within the parity tolerance either way; the switch exists for A/B measurement.  Also read once from
- * AGPT_B200_ATTN_TILE and AGPT_B200_BWD_WARPS. */
+ * of the backward fit one SM, i.e. up to about 150 / 128 keys per tile (depth <= ~90 / 65); deeper plans and head_dim 16
+ * take the chunked TF32 kernels, and so does the head_dim-64 forward (the chunked one measured faster there).  With a
+ * bf16 store the whole-tile backward runs at head_dim 32 (single fp16 products: the store's own rounding is coarser;
+ * AGPT_B200_ATTN_TILE_BF16=0 in the environment keeps the chunked kernel), everything else chunked.  whole_tile 0:
+ * always the chunked kernels.  bwd_warps = 4 (default), 6 or 8 warps per block of the whole-tile backward, 3 = four
+ * warps with three blocks per SM.  Same results within the parity tolerance either way; the switch exists for A/B
+ * measurement.  Also read once from AGPT_B200_ATTN_TILE and AGPT_B200_BWD_WARPS; AGPT_B200_FWD_BLOCKS=5 runs the
+ * head_dim-32 forward with five blocks per SM instead of six. */
 int agpt_b200_set_attn_variant(int whole_tile, int bwd_warps);
 
 /* No counterpart in the reference.  agpt_b200_attn_bwd for callers that cannot allocate device memory
